@@ -1,0 +1,90 @@
+// Shared device helpers for every kernel of the library (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define YALIS_API extern "C" __attribute__((visibility("default")))
+
+// dtype codes used across the C boundary
+enum : int { YALIS_F32 = 0, YALIS_BF16 = 1 };
+
+// Error codes returned by launchers (0 = launched).
+enum : int {
+  YALIS_OK = 0,
+  YALIS_ERR_DTYPE = -1,      // dtype code not handled by this kernel
+  YALIS_ERR_SHAPE = -2,      // a size this kernel refuses
+  YALIS_ERR_LAUNCH = -3,     // cudaGetLastError() after the launch was not cudaSuccess
+  YALIS_ERR_ALIGN = -4,      // a pointer or stride not aligned as the kernel needs
+};
+
+inline int yalis_launch_status() {
+  return cudaGetLastError() == cudaSuccess ? YALIS_OK : YALIS_ERR_LAUNCH;
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` is 32 floats of shared memory; safe to call repeatedly.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? scratch[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? scratch[lane] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+// Dispatch on a dtype code to a templated callable.
+#define YALIS_DISPATCH_DTYPE(code, T, ...)                 \
+  do {                                                     \
+    if ((code) == YALIS_F32) {                             \
+      using T = float;                                     \
+      __VA_ARGS__;                                         \
+    } else if ((code) == YALIS_BF16) {                     \
+      using T = __nv_bfloat16;                             \
+      __VA_ARGS__;                                         \
+    } else {                                               \
+      return YALIS_ERR_DTYPE;                              \
+    }                                                      \
+  } while (0)

@@ -1,0 +1,48 @@
+"""Trace replay on top of ``Engine.step``: no forward pass, cache or loader of its own.
+
+A trace is a sequence of steps; each step lists, per request, its next tokens
+and the places whose logits are wanted, plus the requests that end after the
+step.  Tokens are given, nothing is sampled and nothing is scheduled: the
+replayer only creates requests on first sight, calls the engine's step function
+with exactly the step's entries, and finishes the requests named in ``end``.
+The reference's nearest hook is ``get_logits=True`` of its generate loop
+(yalis/engine.py:519-520, 570-571).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import numpy as np
+
+from .engine import Engine, StepEntry
+
+
+class Replayer:
+    def __init__(self, model_dir: str, dtype: str, max_tokens: int, page_size: int = 16, max_live: int = 4,
+                 engine: Optional[Engine] = None):
+        if 64 % page_size and page_size % 64:
+            raise ValueError("page_size must divide 64 or be a multiple of it")
+        # The pool holds max_tokens, with each live request rounded up to whole pages.
+        unit = max(page_size, 64)
+        pool_tokens = -(-max_tokens // unit) * unit
+        self.engine = engine or Engine(model_dir, dtype=dtype, page_size=page_size,
+                                       num_pages=pool_tokens // page_size, max_slots=max_live)
+
+    def run_step(self, step: Dict) -> Optional[np.ndarray]:
+        entries: List[StepEntry] = []
+        for e in step.get("entries", []):
+            if not self.engine.has_request(e["id"]):
+                if self.engine.add_request(e["id"]) is None:
+                    raise RuntimeError(f"step {step.get('step')}: no free slot for request {e['id']!r}")
+            entries.append(StepEntry(e["id"], e["tokens"], e.get("want", [])))
+        logits = None
+        if entries:
+            out = self.engine.step(entries)
+            if out is not None:
+                logits = out.float().cpu().numpy()
+            self.engine.check_device_errors()
+        for rid in step.get("end", []):
+            if self.engine.has_request(rid):
+                self.engine.finish_request(rid)
+        return logits

@@ -1,0 +1,80 @@
+"""ctypes plumbing shared by the kernel wrappers.
+
+Every wrapper checks its tensors on the host (device, dtype, contiguity,
+shapes) before it hands raw pointers to the library, and raises
+``KernelError`` when a launcher returns a non-zero status.  There is no
+PyTorch or CPU fallback behind any wrapper: without the CUDA library the
+import of a wrapper's first call fails with ``NativeBuildError``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from yalis_b200 import native
+
+F32, BF16 = 0, 1
+
+_STATUS = {
+    -1: "dtype not handled by this kernel",
+    -2: "a size this kernel refuses",
+    -3: "the launch failed (cudaGetLastError)",
+    -4: "a pointer or stride is not aligned as the kernel needs",
+    -5: "the problem exceeds the kernel's fixed scratch memory",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    return native.load("cuda")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"dtype {dt} is not supported (float32 and bfloat16 only)")
+
+
+def ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def check(status: int, name: str, detail: str = "") -> None:
+    if status != 0:
+        why = _STATUS.get(status, f"status {status}")
+        raise KernelError(f"{name}: {why}{(' (' + detail + ')') if detail else ''}")
+
+
+def need(cond: bool, name: str, msg: str) -> None:
+    if not cond:
+        raise KernelError(f"{name}: {msg}")
+
+
+def need_cuda(name: str, *tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError(f"{name}: every tensor must be on the GPU (there is no CPU path)")
+
+
+def i32(v: int) -> ctypes.c_int:
+    return ctypes.c_int(int(v))
+
+
+def i64(v: int) -> ctypes.c_longlong:
+    return ctypes.c_longlong(int(v))
+
+
+def f32(v: float) -> ctypes.c_float:
+    return ctypes.c_float(float(v))

@@ -1,0 +1,49 @@
+"""Wrappers of the token-selection kernels (csrc/sampling.cu)."""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ._lib import check, i32, i64, lib, need, need_cuda, ptr, stream
+
+
+def _check_logits(name: str, logits: torch.Tensor) -> None:
+    need_cuda(name, logits)
+    need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1, name,
+         "logits must be float32 [rows, vocab] with unit inner stride")
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Index of the largest logit of each row; ties go to the lowest index. int32 [rows]."""
+    name = "argmax"
+    _check_logits(name, logits)
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    need(out.dtype == torch.int32 and out.shape == (rows,) and out.is_contiguous(), name, "bad out tensor")
+    check(lib().yalis_argmax(ptr(logits), i64(logits.stride(0)), i32(rows), i32(vocab), ptr(out), stream()), name)
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           seed: torch.Tensor, draw_index: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row with per-row parameters (all device tensors of length rows).
+
+    temperature float32, top_k int32 (0 = off), top_p float32, seed and draw_index
+    int64 (read as unsigned).  A row with temperature 0 and top_p 0 is greedy.
+    """
+    name = "sample"
+    _check_logits(name, logits)
+    rows, vocab = logits.shape
+    need_cuda(name, temperature, top_k, top_p, seed, draw_index, out)
+    for t, dt in ((temperature, torch.float32), (top_k, torch.int32), (top_p, torch.float32), (seed, torch.int64),
+                  (draw_index, torch.int64)):
+        need(t.dtype == dt and t.shape == (rows,) and t.is_contiguous(), name, f"per-row parameter must be {dt} [rows]")
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    need(out.dtype == torch.int32 and out.shape == (rows,) and out.is_contiguous(), name, "bad out tensor")
+    check(lib().yalis_sample(ptr(logits), i64(logits.stride(0)), i32(rows), i32(vocab), ptr(temperature), ptr(top_k),
+                             ptr(top_p), ptr(seed), ptr(draw_index), ptr(out), stream()), name)
+    return out

@@ -1,0 +1,69 @@
+"""Grouped-query causal attention over the paged cache.
+
+qkv = x Wqkv^T; positions are encoded into Q and K and K, V stored (the position
+part does both in one kernel); every token attends to the cached keys of its
+request up to its own position; the heads are projected back with Wo
+(yalis/external/model.py:540-608).  The three projections are stored
+concatenated [Wq; Wk; Wv] (the reference interleaves them per KV group,
+model.py:544-557, which only serves its tensor-parallel split).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from yalis_b200.config.spec import PartSpec
+from yalis_b200.ops import attention as attn_ops
+from yalis_b200.ops.linear import linear
+from .base import Mixer, PagedKV, PagedKVCache, ParamSpec, PositionEncoding, register_part
+
+
+class PagedAttention(Mixer):
+    """Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``,
+    ``window`` (None = all keys), ``scale`` (None = 1/sqrt(head_dim))."""
+
+    def __init__(self, spec: PartSpec, position: Optional[PositionEncoding] = None):
+        super().__init__(spec, position)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.nh = int(p["num_heads"])
+        self.g = int(p["num_kv_heads"])
+        self.hs = int(p["head_dim"])
+        self.window = p.get("window")
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hs)
+        if self.nh % self.g:
+            raise ValueError(f"num_heads {self.nh} is not a multiple of num_kv_heads {self.g}")
+        if self.hs % 2 or self.hs > 256:
+            raise ValueError(f"head_dim {self.hs} is not supported (even, at most 256)")
+        if position is None:
+            raise ValueError("paged_attention needs a position part (use kind 'none' for no encoding)")
+        self.w_qkv: Optional[torch.Tensor] = None
+        self.w_o: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {
+            "q_proj": ParamSpec((self.nh * self.hs, self.hidden)),
+            "k_proj": ParamSpec((self.g * self.hs, self.hidden)),
+            "v_proj": ParamSpec((self.g * self.hs, self.hidden)),
+            "o_proj": ParamSpec((self.hidden, self.nh * self.hs)),
+        }
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w_qkv = torch.cat([tensors["q_proj"], tensors["k_proj"], tensors["v_proj"]], dim=0).contiguous()
+        self.w_o = tensors["o_proj"].contiguous()
+
+    def cache_request(self) -> PagedKV:
+        return PagedKV(self.g, self.hs, self.window)
+
+    def forward(self, x: torch.Tensor, ctx, cache: PagedKVCache) -> torch.Tensor:
+        qkv = linear(x, self.w_qkv)
+        self.position.encode_and_store(qkv, self.nh, self.g, self.hs, ctx, cache)
+        y = attn_ops.paged_attention(qkv, cache.k, cache.v, ctx, cache.group, self.nh, self.g, self.hs,
+                                     scale=self.scale, window=self.window)
+        return linear(y, self.w_o)
+
+
+register_part("mixer", "paged_attention", PagedAttention)

@@ -1,0 +1,210 @@
+"""Interfaces of the parts a layer is put together from, and their registry.
+
+Five categories, each with one small interface:
+
+``norm``          ``forward(stream, rows=None) -> Tensor``: applies the pending
+                  residual delta, returns the normed rows in the model dtype.
+``position``      ``encode_and_store(qkv, heads, kv_heads, head_dim, ctx, cache)``:
+                  encodes positions into Q and K of a fused qkv matrix and puts
+                  K, V into the layer's cache pages.
+``mixer``         ``cache_request() -> PagedKV | SlotState | None`` and
+                  ``forward(x, ctx, cache) -> Tensor [N, hidden]``.
+``feed_forward``  ``forward(x, ctx) -> Tensor [N, hidden]``.
+``block``         ``forward(stream, ctx, cache) -> None``: the arrangement of the
+                  four above around the residual stream.
+
+Every part is constructed from a ``PartSpec`` (kind + parameters) alone, names
+its tensors with ``param_specs()`` and receives them in ``load()``.  A part
+never sees the model configuration, the architecture's name or another layer.
+New kinds are added with ``register_part(category, kind, cls)``; nothing else in
+the package has to change.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, Optional, Tuple
+
+import torch
+
+from yalis_b200.config.spec import PartSpec
+
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block")
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    """One tensor a part needs.
+
+    ``init`` says what the random-weights mode writes: ``normal`` = N(0, 0.02)
+    (the reference's GPT._init_weights, yalis/external/model.py:113-120),
+    ``ones`` or ``zeros``.  ``keep_float32``: held in float32 whatever the
+    engine's dtype (norm scales).  ``integer``: an integer table, held as int32.
+    """
+
+    shape: Tuple[int, ...]
+    init: str = "normal"
+    keep_float32: bool = False
+    integer: bool = False
+
+
+# ---- what a mixer may ask of the cache manager ---------------------------------
+
+@dataclass(frozen=True)
+class PagedKV:
+    """Keys and values in pages. ``window`` None keeps every key; W keeps, for a
+    query at position p, the keys at positions > p - W."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class SlotState:
+    """A tensor of fixed shape per request (zeroed when the request is admitted)."""
+
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class PagedKVCache:
+    """What a paged mixer gets for one schedule entry: its two pools
+    [pages, kv_heads, page_size, head_dim] and the name of its page group, under
+    which the step context holds the block tables.  ``writable`` is False for an
+    entry that reads the cache of another entry."""
+
+    def __init__(self, k: torch.Tensor, v: torch.Tensor, group: str, writable: bool = True):
+        self.k, self.v, self.group, self.writable = k, v, group, writable
+
+    @property
+    def page_size(self) -> int:
+        return self.k.shape[2]
+
+
+class SlotStateCache:
+    """What a stateful mixer gets: ``state`` [max_slots, *shape]; rows are indexed
+    by the step context's ``slots``."""
+
+    def __init__(self, state: torch.Tensor, writable: bool = True):
+        self.state, self.writable = state, writable
+
+
+# ---- the residual stream ----------------------------------------------------------
+
+class ResidualStream:
+    """The float32 residual stream [N, hidden] with one pending delta.
+
+    A sub-layer's output is not added at once: it is parked in ``pending`` and
+    the next norm adds it while it reads the stream (one pass instead of two).
+    ``pending`` is [N, hidden] in the model dtype, or float32 split partial sums
+    [S, N, hidden] that are added in order.
+    """
+
+    def __init__(self, x: torch.Tensor, dtype: torch.dtype):
+        self.x = x
+        self.dtype = dtype
+        self.pending: Optional[torch.Tensor] = None
+
+    def add(self, delta: torch.Tensor) -> None:
+        self.flush()
+        self.pending = delta
+
+    def flush(self) -> None:
+        if self.pending is not None:
+            from yalis_b200.ops.elementwise import residual_add
+            residual_add(self.x, self.pending)
+            self.pending = None
+
+
+# ---- parts ---------------------------------------------------------------------------
+
+class Part:
+    category = ""
+
+    def __init__(self, spec: PartSpec):
+        self.spec = spec
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Receives the tensors named by param_specs(), on the device, in the engine's dtype."""
+
+
+class Norm(Part):
+    category = "norm"
+
+    def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    category = "position"
+
+    def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, ctx, cache: PagedKVCache) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    category = "mixer"
+
+    def __init__(self, spec: PartSpec, position: Optional[PositionEncoding] = None):
+        super().__init__(spec)
+        self.position = position
+
+    def cache_request(self):
+        return None
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    category = "feed_forward"
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    category = "block"
+
+    def __init__(self, spec: PartSpec, mixer: Mixer, feed_forward: FeedForward, norm_1: Norm, norm_2: Norm):
+        super().__init__(spec)
+        self.mixer, self.feed_forward, self.norm_1, self.norm_2 = mixer, feed_forward, norm_1, norm_2
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        raise NotImplementedError
+
+
+# ---- registry ---------------------------------------------------------------------------
+
+_REGISTRY: Dict[str, Dict[str, Callable[..., Part]]] = {c: {} for c in CATEGORIES}
+
+
+def register_part(category: str, kind: str, factory: Callable[..., Part], *, replace: bool = False) -> None:
+    if category not in _REGISTRY:
+        raise ValueError(f"unknown part category {category!r} (one of {', '.join(CATEGORIES)})")
+    if kind in _REGISTRY[category] and not replace:
+        raise ValueError(f"{category} kind {kind!r} is already registered")
+    _REGISTRY[category][kind] = factory
+
+
+def make_part(category: str, spec: PartSpec, **kwargs: Any) -> Part:
+    _ensure_builtin()
+    try:
+        factory = _REGISTRY[category][spec.kind]
+    except KeyError:
+        known = ", ".join(sorted(_REGISTRY.get(category, {}))) or "none"
+        raise ValueError(f"no {category} of kind {spec.kind!r} is registered (known: {known})") from None
+    return factory(spec, **kwargs)
+
+
+def registered(category: str) -> Tuple[str, ...]:
+    _ensure_builtin()
+    return tuple(sorted(_REGISTRY[category]))
+
+
+def _ensure_builtin() -> None:
+    from yalis_b200.parts import attention, block, norm, rotary, swiglu  # noqa: F401
