@@ -1,0 +1,188 @@
+"""Replay of the same requests cut four ways, in float32 and bfloat16, against the plain
+implementation: each request whole; most of it in one step and the last 32 tokens one by
+one; portions of changing size down to two tokens; and up to four live requests mixed, with
+so few pages that they are used again.  One run goes through ``bin/trace_run`` as a
+program; the rest use the same replayer in-process."""
+
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+import traces
+from tiny import page_size_of, tiny_model_dir
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# relative to the largest |logit| of the request
+TOL = {"float32": 1e-4, "bfloat16": 2e-2}
+STD = {"float32": 0.2, "bfloat16": 0.02}     # wide weights in float32 make attention far from uniform
+
+
+def make_requests(cfg, lengths, seed):
+    g = torch.Generator().manual_seed(seed)
+    return {f"r{i}": torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for i, n in enumerate(lengths)}
+
+
+def lengths_for(which):
+    return [5, 17, 33, 70, 100, 128] if which == "A" else [1, 40, 100, 64, 203, 90]
+
+
+_oracle_cache = {}
+
+
+def oracle(which, std, requests):
+    key = (which, std, tuple(sorted((k, tuple(v)) for k, v in requests.items())))
+    if key not in _oracle_cache:
+        d = tiny_model_dir(which, std)
+        cfg, w = plain.read_config(d), plain.read_weights(d)
+        _oracle_cache[key] = {rid: plain.forward_logits(t, w, cfg).numpy() for rid, t in requests.items()}
+    return _oracle_cache[key]
+
+
+def replay_in_process(model_dir, dtype, page_size, steps, max_tokens):
+    from yalis_b200.engine.replay import Replayer
+    rep = Replayer(model_dir, dtype, max_tokens, page_size=page_size)
+    out = {}
+    for s in steps:
+        r = rep.run_step(s)
+        if r is not None:
+            out[s["step"]] = r
+    rep.engine.manager.check()
+    for g in rep.engine.groups:
+        assert rep.engine.manager.free_pages(g.name) == g.num_pages     # every page came back
+    return out, rep
+
+
+def compare(got, want, tol, what):
+    assert set(got) == set(want), what
+    worst = 0.0
+    for rid in want:
+        assert got[rid].shape == want[rid].shape, (what, rid)
+        scale = np.abs(want[rid]).max()
+        err = np.abs(got[rid] - want[rid]).max() / scale
+        worst = max(worst, err)
+        if err > tol:
+            bad = np.argwhere(np.abs(got[rid] - want[rid]).max(axis=1) / scale > tol)
+            raise AssertionError(f"{what}: request {rid} differs by {err:.3e} (tolerance {tol}); "
+                                 f"first wrong position {int(bad[0])} of {want[rid].shape[0]}")
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["A", "B"])
+@pytest.mark.parametrize("cut", ["whole", "tail_decoded", "portions", "mixed"])
+def test_cuttings_match_plain(which, dtype, cut):
+    std = STD[dtype]
+    d = tiny_model_dir(which, std)
+    cfg = plain.read_config(d)
+    requests = make_requests(cfg, lengths_for(which), seed=11)
+    want = oracle(which, std, requests)
+    build = {"whole": traces.whole, "tail_decoded": traces.tail_decoded, "portions": traces.portions,
+             "mixed": traces.mixed}[cut]
+    steps = traces.number(build(requests))
+    peak = traces.peak_tokens(steps)
+    out, rep = replay_in_process(d, dtype, page_size_of(which), steps, peak)
+    got = traces.collect(steps, out, cfg["vocab_size"])
+    compare(got, want, TOL[dtype], f"{which}/{dtype}/{cut}")
+    if cut == "mixed":
+        # the pool was smaller than the sum of all requests: pages were used again
+        assert peak < sum(traces.round_up(len(t)) for t in requests.values())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuttings_agree_with_each_other(dtype):
+    """The logits at a position do not depend on the cutting beyond rounding: in float32
+    every kernel sums in a fixed order, so the four ways agree to the last bit or two."""
+    which, std = "B", 0.2
+    d = tiny_model_dir(which, std)
+    cfg = plain.read_config(d)
+    requests = make_requests(cfg, [3, 61, 130, 77, 18], seed=5)
+    results = []
+    for build in (traces.whole, traces.tail_decoded, traces.portions, traces.mixed):
+        steps = traces.number(build(requests))
+        out, _ = replay_in_process(d, dtype, page_size_of(which), steps, traces.peak_tokens(steps))
+        results.append(traces.collect(steps, out, cfg["vocab_size"]))
+    tol = 1e-6 if dtype == "float32" else 2e-2
+    for other in results[1:]:
+        compare(other, results[0], tol, f"cut vs whole ({dtype})")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype):
+    """The program itself: JSON lines in, ``done <step>`` lines and <step>.f32 files out."""
+    which = "A"
+    std = STD[dtype]
+    d = tiny_model_dir(which, std)
+    cfg = plain.read_config(d)
+    requests = make_requests(cfg, [9, 64, 65, 120, 30], seed=3)
+    steps = traces.number(traces.whole(requests) + traces.tail_decoded(requests) + traces.portions(requests)
+                          + traces.mixed(requests))
+    # the four phases reuse the ids r0.. one after the other; every phase ends its requests
+    peak = traces.peak_tokens(steps)
+    with tempfile.TemporaryDirectory() as out_dir:
+        proc = subprocess.run(
+            [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype, "--out", out_dir,
+             "--max-tokens", str(peak), "--page-size", str(page_size_of(which))],
+            input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        done = [l for l in proc.stdout.splitlines() if l.startswith("done ")]
+        assert done == [f"done {s['step']}" for s in steps]
+        out = {s["step"]: np.fromfile(os.path.join(out_dir, f"{s['step']}.f32"), dtype="<f4") for s in steps}
+    want = oracle(which, std, requests)
+    # split the concatenated trace back into its four phases
+    phase_starts = []
+    n_whole = len(traces.whole(requests)); n_tail = len(traces.tail_decoded(requests)); n_port = len(traces.portions(requests))
+    bounds = [0, n_whole, n_whole + n_tail, n_whole + n_tail + n_port, len(steps)]
+    for a, b in zip(bounds[:-1], bounds[1:]):
+        got = traces.collect(steps[a:b], out, cfg["vocab_size"])
+        compare(got, want, TOL[dtype], f"trace_run/{dtype}/steps {a}-{b}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(dtype):
+    """One prompt token, then 250 tokens one by one (positions across many pages); and the
+    first tokens of a sequence asked for alone."""
+    which, std = "B", STD[dtype]
+    d = tiny_model_dir(which, std)
+    cfg = plain.read_config(d)
+    requests = make_requests(cfg, [251], seed=8)
+    steps = traces.number(traces.tail_decoded(requests, tail=250))
+    out, _ = replay_in_process(d, dtype, page_size_of(which), steps, traces.peak_tokens(steps))
+    got = traces.collect(steps, out, cfg["vocab_size"])
+    want = oracle(which, std, requests)
+    compare(got, want, TOL[dtype], f"long decoding {dtype}")
+    toks = requests["r0"]
+    first = traces.number([{"entries": [{"id": "f", "tokens": toks[:1], "want": [0]}], "end": []},
+                           {"entries": [{"id": "f", "tokens": toks[1:3], "want": [0, 1]}], "end": ["f"]}])
+    out, _ = replay_in_process(d, dtype, page_size_of(which), first, 64)
+    got = traces.collect(first, out, cfg["vocab_size"])
+    compare(got, {"f": want["r0"][:3]}, TOL[dtype], f"first tokens {dtype}")
+
+
+def test_wanted_subset_and_skipped_logits():
+    """``want`` may be empty or a subset; rows come back in the order of entries and want."""
+    which, dtype, std = "A", "float32", 0.2
+    d = tiny_model_dir(which, std)
+    cfg = plain.read_config(d)
+    requests = make_requests(cfg, [20, 12], seed=4)
+    want = oracle(which, std, requests)
+    a, b = requests["r0"], requests["r1"]
+    steps = traces.number([
+        {"entries": [{"id": "a", "tokens": a[:10], "want": []}, {"id": "b", "tokens": b[:5], "want": [4, 0]}], "end": []},
+        {"entries": [{"id": "b", "tokens": b[5:], "want": [6]}, {"id": "a", "tokens": a[10:], "want": [9, 3]}], "end": ["a", "b"]},
+    ])
+    out, _ = replay_in_process(d, dtype, 16, steps, 128)
+    s0, s1 = out[0].reshape(-1, cfg["vocab_size"]), out[1].reshape(-1, cfg["vocab_size"])
+    ref = lambda rid, pos: want[rid][pos]
+    for got, exp in ((s0[0], ref("r1", 4)), (s0[1], ref("r1", 0)), (s1[0], ref("r1", 11)), (s1[1], ref("r0", 19)),
+                     (s1[2], ref("r0", 13))):
+        assert np.abs(got - exp).max() <= 1e-4 * np.abs(exp).max()
+    assert s0.shape[0] == 2 and s1.shape[0] == 3

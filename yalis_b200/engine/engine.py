@@ -171,8 +171,7 @@ class Engine:
         self._staging[i] = (buf, None)
         return buf, i
 
-    def _build_context(self, entries: Sequence[StepEntry]) -> StepContext:
-        slots = [self._slot_of[e.request] for e in entries]
+    def _build_context(self, slots: Sequence[int], entries: Sequence[StepEntry]) -> StepContext:
         q_lens = [len(e.tokens) for e in entries]
         before = [self.manager.length(s) for s in slots]
         n, r = sum(q_lens), len(entries)
@@ -235,16 +234,12 @@ class Engine:
                           max_kv_len=max_kv),
             error_flag=self._error_flag, decode_only=all(q == 1 for q in q_lens))
 
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
+    def _validate(self, slots: Sequence[int], entries: Sequence[StepEntry]) -> None:
         if not entries:
             raise StepError("a step needs at least one entry")
-        seen = set()
-        for e in entries:
-            if e.request not in self._slot_of:
-                raise StepError(f"request {e.request!r} is not live (add_request first)")
-            if e.request in seen:
-                raise StepError(f"request {e.request!r} appears twice in one step")
-            seen.add(e.request)
+        if len(set(slots)) != len(slots):
+            raise StepError("a request appears twice in one step")
+        for s, e in zip(slots, entries):
             if len(e.tokens) == 0:
                 raise StepError(f"request {e.request!r} brings no tokens")
             lo, hi = min(e.tokens), max(e.tokens)
@@ -253,29 +248,37 @@ class Engine:
             for j in e.want:
                 if not 0 <= j < len(e.tokens):
                     raise StepError(f"request {e.request!r}: wanted place {j} is outside its {len(e.tokens)} tokens")
-            new_len = self.length(e.request) + len(e.tokens)
+            new_len = self.manager.length(s) + len(e.tokens)
             if new_len > self.max_context or not self.manager.fits(new_len):
                 raise StepError(f"request {e.request!r} would hold {new_len} tokens, more than the limit {self.max_context}")
 
-    @torch.no_grad()
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        """Run one batch; returns float32 logits [wanted, vocab] on the device in the
-        order of the entries and of their ``want`` (None if nothing is wanted)."""
-        self._validate(entries)
-        slots = [self._slot_of[e.request] for e in entries]
+        """Run one batch of live requests (by the ids given to ``add_request``); returns
+        float32 logits [wanted, vocab] on the device in the order of the entries and of
+        their ``want`` (None if nothing is wanted)."""
+        for e in entries:
+            if e.request not in self._slot_of:
+                raise StepError(f"request {e.request!r} is not live (add_request first)")
+        return self.step_slots([self._slot_of[e.request] for e in entries], entries)
+
+    @torch.no_grad()
+    def step_slots(self, slots: Sequence[int], entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """The step function proper, for callers that manage slots themselves (the
+        scheduler): entry i belongs to the request that holds ``slots[i]``."""
+        self._validate(slots, entries)
         new_lens = [self.manager.length(s) + len(e.tokens) for s, e in zip(slots, entries)]
         for s, e, nl in zip(slots, entries, new_lens):
             if not self.manager.reserve(s, nl):
                 raise OutOfPages(f"no pages left for request {e.request!r} to reach {nl} tokens "
                                  f"(free: {self.free_pages()})")
-        ctx = self._build_context(entries)
+        ctx = self._build_context(slots, entries)
         stream = self.model.forward(ctx, self.storage.entries)
         logits = self.model.logits(stream, ctx.logit_rows) if ctx.logit_rows.numel() else None
         for s, nl in zip(slots, new_lens):
             self.manager.commit(s, nl)
         self.steps_run += 1
-        if os.environ.get("YALIS_B200_CHECK") and int(self._error_flag.item()):
-            raise StepError("a kernel reported a token id or page outside its range")
+        if os.environ.get("YALIS_B200_CHECK"):
+            self.check_device_errors()
         return logits
 
     def check_device_errors(self) -> None:

@@ -50,10 +50,11 @@ class SafetensorsFile:
                 raise RuntimeError(f"{path}: tensor {name} has unsupported dtype {info['dtype']}")
             b, e = info["data_offsets"]
             self.entries[name] = (_DTYPES[info["dtype"]], tuple(info["shape"]), b, e)
-        self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ) if size > 0 else None
+        self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_COPY) if size > 0 else None
 
     def get(self, name: str) -> torch.Tensor:
-        """A CPU tensor that views the mapped file (clone or move it before the file is closed)."""
+        """A CPU tensor that views the mapped file (clone or move it before the file is closed).
+        The mapping is private (copy-on-write), so nothing written through the view reaches the file."""
         dtype, shape, b, e = self.entries[name]
         count = 1
         for s in shape:
