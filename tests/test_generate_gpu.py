@@ -1,0 +1,124 @@
+"""Greedy and sampled generation through the Python entry point and the command line."""
+
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+from tiny import page_size_of, tiny_model_dir
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def prompts_for(cfg, lengths, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lengths]
+
+
+def engine_for(model_dir, precision, **kw):
+    from yalis_b200 import InferenceConfig, LLMEngine, ModelConfig
+    opts = dict(max_batch_size=4, max_length_of_generated_sequences=128, temperature=0.0, top_p=0.0)
+    opts.update(kw)
+    return LLMEngine(ModelConfig(model_name="tiny", model_path=model_dir, precision=precision), InferenceConfig(**opts))
+
+
+@pytest.mark.parametrize("which, lengths, new, chunk", [("A", [5, 17, 33], 16, None), ("B", [1, 40, 100], 12, 24)])
+def test_greedy_generation_equals_plain_float32(which, lengths, new, chunk):
+    d = tiny_model_dir(which, 0.3)
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    prompts = prompts_for(cfg, lengths)
+    eng = engine_for(d, "fp32", page_size=page_size_of(which), prefill_chunk=chunk, max_tokens_per_step=64)
+    tokens, metrics, logits = eng.generate(prompts, tokens_to_generate=new, get_logits=True)
+    assert tokens.shape == (len(prompts), new) and tokens.dtype == torch.int64 and tokens.is_cuda
+    for p, row, lg in zip(prompts, tokens.tolist(), logits):
+        assert row == plain.greedy_generate(p, new, w, cfg)
+        ref = plain.forward_logits(p + row[:-1], w, cfg)[len(p) - 1:]
+        assert np.abs(lg.cpu().numpy() - ref.numpy()).max() <= 1e-4 * float(ref.abs().max())
+    assert metrics["BatchSize"] == len(prompts) and metrics["DecodeLength"] == new and metrics["FinishedReason"] == "Max Token Length"
+    assert metrics["Throughput"] > 0 and metrics["E2E"] > 0
+    eng.engine.manager.check()
+    assert all(eng.engine.manager.free_pages(g.name) == g.num_pages for g in eng.engine.groups)
+
+
+def test_greedy_generation_bfloat16_follows_the_oracle():
+    """In bfloat16 every generated token is the oracle's best or within rounding of it
+    (the reference's own criterion is top-5 containment: tests/basic_correctness/test_yalis_vs_hf.py:163-185)."""
+    d = tiny_model_dir("A", 0.02)
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    prompts = prompts_for(cfg, [5, 17, 33])
+    eng = engine_for(d, "bf16")
+    tokens, _ = eng.generate(prompts, tokens_to_generate=16)
+    for p, row in zip(prompts, tokens.tolist()):
+        seq = list(p)
+        for tok in row:
+            ref = plain.forward_logits(seq, w, cfg)[-1]
+            assert tok in torch.topk(ref, 5).indices.tolist()
+            assert float(ref.max() - ref[tok]) <= 2e-2 * float(ref.abs().max())
+            seq.append(tok)
+
+
+def test_more_prompts_than_slots_and_few_pages():
+    """Nine prompts, three slots, a pool that forces waiting and preemption: the tokens are
+    those of each prompt generated alone."""
+    d = tiny_model_dir("B", 0.3)
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    prompts = prompts_for(cfg, [30, 3, 61, 12, 45, 8, 70, 22, 5], seed=4)
+    eng = engine_for(d, "fp32", max_batch_size=3, page_size=8, cache_tokens=104, prefill_chunk=16, max_tokens_per_step=40)
+    tokens, metrics = eng.generate(prompts, tokens_to_generate=10)
+    for p, row in zip(prompts, tokens.tolist()):
+        assert row == plain.greedy_generate(p, 10, w, cfg)
+    assert metrics["Preemptions"] > 0
+    eng.engine.manager.check()
+
+
+def test_eos_stops_a_row_and_pads_it():
+    d = tiny_model_dir("A", 0.3)
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    prompts = prompts_for(cfg, [9, 20], seed=2)
+    free = [plain.greedy_generate(p, 12, w, cfg) for p in prompts]
+    eos = free[0][4]                                        # make the 5th token of row 0 the EOS id
+    eng = engine_for(d, "fp32")
+    eng.engine.spec = type(eng.engine.spec)(**{**{f: getattr(eng.engine.spec, f) for f in eng.engine.spec.__dataclass_fields__},
+                                               "eos_token_id": eos})
+    tokens, metrics = eng.generate(prompts, tokens_to_generate=12, ignore_eos=False)
+    row0 = tokens[0].tolist()
+    stop = free[0].index(eos)
+    assert row0[:stop + 1] == free[0][:stop + 1] and all(t == eos for t in row0[stop + 1:])
+    if eos not in free[1]:
+        assert tokens[1].tolist() == free[1]
+
+
+def test_sampling_is_reproducible_and_independent_of_the_batch():
+    d = tiny_model_dir("A", 0.3)
+    cfg = plain.read_config(d)
+    prompts = prompts_for(cfg, [7, 19, 4], seed=6)
+    kw = dict(temperature=0.8, top_p=0.9, top_k=50, seed=99)
+    a, _ = engine_for(d, "fp32", **kw).generate(prompts, tokens_to_generate=12)
+    b, _ = engine_for(d, "fp32", **kw).generate(prompts, tokens_to_generate=12)
+    assert torch.equal(a, b)
+    # request 0 alone draws what it drew in the batch (its seed and draw counter are its own)
+    alone, _ = engine_for(d, "fp32", **kw).generate(prompts[:1], tokens_to_generate=12)
+    assert alone[0].tolist() == a[0].tolist()
+    c, _ = engine_for(d, "fp32", **dict(kw, seed=100)).generate(prompts, tokens_to_generate=12)
+    assert not torch.equal(a, c)
+
+
+def test_generate_shortcut_and_command_line():
+    from yalis_b200 import generate
+    d = tiny_model_dir("A", 0.3)
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    prompts = prompts_for(cfg, [6, 11], seed=8)
+    out = generate(d, prompts, max_new_tokens=5, precision="fp32")
+    assert out == [plain.greedy_generate(p, 5, w, cfg) for p in prompts]
+    proc = subprocess.run([sys.executable, "-m", "yalis_b200.cli", "--model", d, "--precision", "fp32", "--temperature", "0",
+                           "--top-p", "0", "--tokens-to-gen", "5", "--max-length", "64",
+                           "--prompt-ids", ",".join(map(str, prompts[0])), "--prompt-ids", ",".join(map(str, prompts[1]))],
+                          capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [l for l in proc.stdout.splitlines() if l.startswith("output = ")]
+    assert [eval(l[len("output = "):]) for l in lines] == out

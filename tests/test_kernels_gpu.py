@@ -1,0 +1,332 @@
+"""Each kernel alone against a plain torch float32 reference of the same operation, at
+sizes other than the tiny models': head sizes in steps of 16, odd head and group counts,
+widths and vocabularies that are no power of two."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("vocab, width", [(37, 24), (1000, 520)])
+def test_embedding(dtype, vocab, width):
+    from yalis_b200.ops.elementwise import embedding
+    table = rnd(vocab, width, dtype=dtype)
+    ids = torch.tensor([0, vocab - 1, 5, 5, 17], dtype=torch.int32, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = embedding(table, ids, bad_flag=flag)
+    assert out.dtype == torch.float32 and torch.equal(out, table[ids.long()].float())
+    assert int(flag) == 0
+    embedding(table, torch.tensor([vocab], dtype=torch.int32, device=DEV), bad_flag=flag)
+    assert int(flag) == 1                                   # an id out of range is flagged, not read
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n, width, eps", [(5, 96, 1e-6), (3, 4100, 1e-5), (1, 16, 1e-2)])
+def test_add_rmsnorm(dtype, n, width, eps):
+    from yalis_b200.ops.elementwise import add_rmsnorm
+    x = rnd(n, width, seed=1, scale=3.0)
+    delta = rnd(n, width, dtype=dtype, seed=2)
+    w = rnd(width, seed=3).abs() + 0.5
+    h = x + delta.float()
+    ref = plain.rms_norm(h, w, eps)
+    x1 = x.clone()
+    y = add_rmsnorm(x1, delta, w, eps, dtype)
+    torch.testing.assert_close(x1, h, rtol=1e-6, atol=1e-6)              # the stream got the sum
+    torch.testing.assert_close(y.float(), ref.to(dtype).float(), **tol(dtype))
+    # without delta; and on chosen rows only (stream untouched)
+    y0 = add_rmsnorm(x.clone(), None, w, eps, dtype)
+    torch.testing.assert_close(y0.float(), plain.rms_norm(x, w, eps).to(dtype).float(), **tol(dtype))
+    rows = torch.tensor([n - 1, 0], dtype=torch.int32, device=DEV)
+    x2 = x.clone()
+    yr = add_rmsnorm(x2, delta, w, eps, dtype, rows=rows)
+    assert torch.equal(x2, x)
+    torch.testing.assert_close(yr.float(), ref[rows.long()].to(dtype).float(), **tol(dtype))
+    # split partial sums [S, n, width] are added in order
+    parts = torch.stack([delta.float() * 0.25, delta.float() * 0.75]).contiguous()
+    x3 = x.clone()
+    add_rmsnorm(x3, parts, w, eps, dtype)
+    torch.testing.assert_close(x3, x + parts[0] + parts[1], rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n, inter", [(4, 176), (3, 1000)])
+def test_silu_mul(dtype, n, inter):
+    from yalis_b200.ops.elementwise import silu_mul
+    x = rnd(n, 2 * inter, dtype=dtype, scale=2.0)
+    xf = x.float()
+    ref = torch.nn.functional.silu(xf[:, :inter]) * xf[:, inter:]
+    torch.testing.assert_close(silu_mul(x).float(), ref.to(dtype).float(), **tol(dtype))
+    ref_i = torch.nn.functional.silu(xf[:, 0::2]) * xf[:, 1::2]          # the reference's interleaved layout
+    torch.testing.assert_close(silu_mul(x, interleaved=True).float(), ref_i.to(dtype).float(), **tol(dtype))
+
+
+def paged_setup(n_req, lens, g, hs, page, dtype, seed=0, extra_pages=3):
+    """Random K/V for requests of the given lengths scattered into shuffled pages."""
+    gen = torch.Generator().manual_seed(seed)
+    pages_per = [-(-l // page) for l in lens]
+    num_pages = sum(pages_per) + extra_pages
+    perm = torch.randperm(num_pages, generator=gen).tolist()
+    width = max(pages_per) + 1
+    table = torch.full((n_req, width), -1, dtype=torch.int32)
+    k_pool = torch.full((num_pages, g, page, hs), float("nan"))          # unwritten places must never be read
+    v_pool = torch.full((num_pages, g, page, hs), float("nan"))
+    ks, vs = [], []
+    it = iter(perm)
+    for r, l in enumerate(lens):
+        k = torch.randn(l, g, hs, generator=gen)
+        v = torch.randn(l, g, hs, generator=gen)
+        ks.append(k); vs.append(v)
+        for i in range(pages_per[r]):
+            p = next(it)
+            table[r, i] = p
+            n = min(page, l - i * page)
+            k_pool[p, :, :n] = k[i * page:i * page + n].transpose(0, 1)
+            v_pool[p, :, :n] = v[i * page:i * page + n].transpose(0, 1)
+    return ks, vs, k_pool.to(dtype).to(DEV), v_pool.to(dtype).to(DEV), table.to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh, g, hs, page, window", [
+    (4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 4, None), (5, 5, 80, 16, None),
+    (8, 2, 128, 16, None), (2, 1, 256, 32, None), (4, 2, 64, 16, 7), (4, 4, 96, 8, 33),
+])
+def test_paged_attention_generic(dtype, nh, g, hs, page, window):
+    from yalis_b200.ops.attention import paged_attention_generic
+    lens = [1, 37, 130]
+    q_lens = [1, 5, 130]                                     # a decode, a portion at an offset, a whole prompt
+    ks, vs, k_pool, v_pool, table = paged_setup(3, lens, g, hs, page, dtype, seed=hs)
+    gen = torch.Generator().manual_seed(1)
+    qs, pos, req = [], [], []
+    for r, (l, ql) in enumerate(zip(lens, q_lens)):
+        qs.append(torch.randn(ql, nh, hs, generator=gen))
+        pos += list(range(l - ql, l))
+        req += [r] * ql
+    q = torch.cat(qs).to(dtype)
+    positions = torch.tensor(pos, dtype=torch.int32, device=DEV)
+    req_of_token = torch.tensor(req, dtype=torch.int32, device=DEV)
+    out = paged_attention_generic(q.view(-1, nh * hs).to(DEV), k_pool, v_pool, positions, req_of_token, table, nh, g, hs,
+                                  window=window)
+    o = 0
+    for r, (l, ql) in enumerate(zip(lens, q_lens)):
+        kk, vv = ks[r].to(dtype).float(), vs[r].to(dtype).float()
+        ref = plain.causal_attention(q[o:o + ql].float(), kk, vv, torch.arange(l - ql, l), torch.arange(l), window=window)
+        got = out[o:o + ql].float().cpu().view(ql, nh, hs)
+        assert not torch.isnan(got).any()
+        torch.testing.assert_close(got, ref.to(dtype).float(), **tol(dtype))
+        o += ql
+
+
+def test_paged_attention_far_key_stands_out():
+    """One key among hundreds, scaled so that it takes nearly all the weight, for a query far
+    behind it and across many pages: the output must be that key's value."""
+    from yalis_b200.ops.attention import paged_attention_generic
+    nh, g, hs, page, l = 2, 1, 32, 8, 777
+    ks, vs, k_pool, v_pool, table = paged_setup(1, [l], g, hs, page, torch.float32, seed=9)
+    for target in (0, 7, 8, 391, l - 1):                     # first key, page edges, middle, the query itself
+        q = ks[0][target, 0] * 8.0                           # aligned with that key, large
+        qq = q.repeat(nh).view(1, nh * hs).to(DEV)
+        out = paged_attention_generic(qq, k_pool, v_pool, torch.tensor([l - 1], dtype=torch.int32, device=DEV),
+                                      torch.zeros(1, dtype=torch.int32, device=DEV), table, nh, g, hs)
+        ref = plain.causal_attention(q.repeat(nh).view(1, nh, hs), ks[0], vs[0], torch.tensor([l - 1]), torch.arange(l))
+        torch.testing.assert_close(out.cpu().view(1, nh, hs), ref, rtol=1e-4, atol=1e-4)
+        assert torch.allclose(out.cpu().view(nh, hs)[0], vs[0][target, 0], atol=5e-2)
+
+
+def test_window_edge_is_exact():
+    """With a window of W the key at distance W-1 is seen and the one at distance W is not."""
+    from yalis_b200.ops.attention import paged_attention_generic
+    nh, g, hs, page, l, w = 1, 1, 16, 4, 40, 9
+    ks, vs, k_pool, v_pool, table = paged_setup(1, [l], g, hs, page, torch.float32, seed=2)
+    p = l - 1
+    for target, seen in ((p - w + 1, True), (p - w, False)):
+        q = (ks[0][target, 0] * 20.0).view(1, hs).to(DEV)
+        out = paged_attention_generic(q, k_pool, v_pool, torch.tensor([p], dtype=torch.int32, device=DEV),
+                                      torch.zeros(1, dtype=torch.int32, device=DEV), table, nh, g, hs, window=w)
+        close = torch.allclose(out.cpu()[0], vs[0][target, 0], atol=5e-2)
+        assert close == seen
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh, g, hs, page", [(4, 2, 16, 16), (3, 1, 32, 8), (5, 5, 80, 4), (8, 2, 128, 16)])
+@pytest.mark.parametrize("scaled", [False, True])
+def test_rope_kv_write(dtype, nh, g, hs, page, scaled):
+    from yalis_b200.ops.elementwise import rope_kv_write
+    from yalis_b200.parts.rotary import inverse_frequencies
+    scaling = dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=32) if scaled else None
+    theta = 500000.0 if scaled else 10000.0
+    inv = inverse_frequencies(hs, theta, scaling)
+    torch.testing.assert_close(inv, plain.rope_inverse_frequencies(hs, theta, None if not scaled else scaling), rtol=0, atol=0)
+    pos_list = [0, 1, 7, 8, 100, 4095, 3, 4]
+    req_list = [0, 0, 0, 0, 0, 0, 1, 1]
+    n = len(pos_list)
+    qkv = rnd(n, (nh + 2 * g) * hs, dtype=dtype, seed=4)
+    num_pages = 4096 // page + 4
+    table = torch.full((2, 4096 // page), -1, dtype=torch.int32)
+    gen = torch.Generator().manual_seed(0)
+    perm = torch.randperm(num_pages, generator=gen)
+    for i, (p, r) in enumerate(zip(pos_list, req_list)):
+        table[r, p // page] = perm[(p // page) * 2 + r] if (p // page) * 2 + r < num_pages else perm[i]
+    table = table.to(DEV)
+    k_pool = torch.zeros(num_pages, g, page, hs, dtype=dtype, device=DEV)
+    v_pool = torch.zeros_like(k_pool)
+    positions = torch.tensor(pos_list, dtype=torch.int32, device=DEV)
+    reqs = torch.tensor(req_list, dtype=torch.int32, device=DEV)
+    before = qkv.clone()
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    rope_kv_write(qkv, positions, reqs, inv.to(DEV), k_pool, v_pool, table, nh, g, hs, bad_flag=flag)
+    assert int(flag) == 0
+    cos, sin = plain.rope_tables(torch.tensor(pos_list), inv)
+    bq = before[:, :nh * hs].float().cpu().view(n, nh, hs)
+    bk = before[:, nh * hs:(nh + g) * hs].float().cpu().view(n, g, hs)
+    bv = before[:, (nh + g) * hs:].float().cpu().view(n, g, hs)
+    t = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(qkv[:, :nh * hs].float().cpu().view(n, nh, hs), plain.apply_rope(bq, cos, sin).to(dtype).float(), **t)
+    assert torch.equal(qkv[:, nh * hs:], before[:, nh * hs:])            # K and V in the row are left alone
+    rk = plain.apply_rope(bk, cos, sin)
+    for i, (p, r) in enumerate(zip(pos_list, req_list)):
+        page_id, off = int(table[r, p // page]), p % page
+        torch.testing.assert_close(k_pool[page_id, :, off].float().cpu(), rk[i].to(dtype).float(), **t)
+        assert torch.equal(v_pool[page_id, :, off].float().cpu(), bv[i])
+    assert int((k_pool != 0).any(dim=-1).sum()) <= n * g                  # nothing else was written
+    # an unmapped page is flagged and skipped
+    rope_kv_write(before.clone(), torch.tensor([9 * page], dtype=torch.int32, device=DEV).repeat(n)[:n], reqs * 0 + 1,
+                  inv.to(DEV), k_pool, v_pool, table, nh, g, hs, bad_flag=flag)
+    assert int(flag) == 1
+
+
+def test_rope_large_positions_match_float32_table():
+    """Angles are float32 products as in the reference's table: at position 100000 a float64
+    angle would differ visibly; the kernel must agree with the float32 table."""
+    from yalis_b200.ops.elementwise import rope_kv_write
+    from yalis_b200.parts.rotary import inverse_frequencies
+    nh, g, hs, page = 1, 1, 64, 16
+    inv = inverse_frequencies(hs, 500000.0, None)
+    pos = [100000, 131071]
+    qkv = rnd(2, 3 * hs, seed=6)
+    before = qkv.clone()
+    table = torch.zeros(1, 131072 // page, dtype=torch.int32, device=DEV)
+    pool = torch.zeros(1, g, page, hs, device=DEV)
+    rope_kv_write(qkv, torch.tensor(pos, dtype=torch.int32, device=DEV), torch.zeros(2, dtype=torch.int32, device=DEV),
+                  inv.to(DEV), pool, pool.clone(), table, nh, g, hs)
+    cos, sin = plain.rope_tables(torch.tensor(pos), inv)
+    ref = plain.apply_rope(before[:, :hs].cpu().view(2, 1, hs), cos, sin)
+    torch.testing.assert_close(qkv[:, :hs].cpu().view(2, 1, hs), ref, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 7, 5), (33, 130, 96), (70, 64, 1000), (5, 300, 17)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_simt(m, n, k, dtype):
+    from yalis_b200.ops.linear import gemm_simt
+    x, w = rnd(m, k, dtype=dtype, seed=1), rnd(n, k, dtype=dtype, seed=2)
+    ref = x.double() @ w.double().T
+    out = gemm_simt(x, w, out_dtype=torch.float32)
+    torch.testing.assert_close(out.double(), ref, rtol=1e-5, atol=1e-4)
+    out = gemm_simt(x, w)
+    torch.testing.assert_close(out.double(), ref.to(dtype).double(), **(dict(rtol=1e-5, atol=1e-4) if dtype == torch.float32
+                                                                        else dict(rtol=2e-2, atol=2e-2)))
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch():
+    from yalis_b200.ops.linear import gemm_simt
+    x, w = rnd(67, 200, seed=1), rnd(150, 200, seed=2)
+    full = gemm_simt(x, w)
+    for rows in ([0], [3, 66], list(range(20, 41))):
+        part = gemm_simt(x[rows].contiguous(), w)
+        assert torch.equal(part, full[rows])                               # the same bits
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 512, 96), (24, 300, 64), (130, 1000, 256)])
+def test_linear_bf16_against_float32(m, n, k):
+    from yalis_b200.ops.linear import linear
+    x, w = rnd(m, k, dtype=torch.bfloat16, seed=1), rnd(n, k, dtype=torch.bfloat16, seed=2)
+    ref = x.float() @ w.float().T
+    torch.testing.assert_close(linear(x, w, out_dtype=torch.float32), ref, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(linear(x, w).float(), ref.to(torch.bfloat16).float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("rows, vocab", [(1, 5), (3, 1000), (2, 128256)])
+def test_argmax_ties_go_to_the_lowest_index(rows, vocab):
+    from yalis_b200.ops.sampling import argmax
+    x = rnd(rows, vocab, seed=3)
+    assert argmax(x).tolist() == x.argmax(dim=-1).tolist()
+    x[:, :] = 0.0
+    x[0, vocab // 2] = 1.0
+    x[0, vocab - 1] = 1.0
+    got = argmax(x).tolist()
+    assert got[0] == vocab // 2 and all(g == 0 for g in got[1:])
+
+
+def draws(logits_row, temperature, top_k, top_p, n, seed=77):
+    from yalis_b200.ops.sampling import sample
+    vocab = logits_row.numel()
+    logits = logits_row.view(1, vocab).repeat(n, 1).contiguous().to(DEV)
+    f = lambda v, dt: torch.full((n,), v, dtype=dt, device=DEV)
+    out = sample(logits, f(temperature, torch.float32), f(top_k or 0, torch.int32), f(top_p, torch.float32),
+                 f(seed, torch.int64), torch.arange(n, dtype=torch.int64, device=DEV))
+    return out.cpu()
+
+
+@pytest.mark.parametrize("temperature, top_k, top_p", [(1.0, None, 1.0), (0.7, None, 1.0), (1.0, 5, 1.0), (1.3, None, 0.8),
+                                                       (0.9, 11, 0.6), (0.0, None, 0.9)])
+def test_sampler_follows_the_reference_distribution(temperature, top_k, top_p):
+    """Chi-square of 20000 draws against the probabilities the reference samples from."""
+    vocab = 40
+    logits = torch.randn(vocab, generator=torch.Generator().manual_seed(5)) * 2.0
+    n = 20000
+    out = draws(logits, temperature, top_k, top_p, n)
+    p = plain.sampling_distribution(logits, temperature, top_k, top_p).double().numpy()
+    counts = np.bincount(out.numpy(), minlength=vocab).astype(np.float64)
+    assert counts[p == 0].sum() == 0                                        # nothing outside the kept set
+    keep = p > 0
+    chi2 = (((counts[keep] - n * p[keep]) ** 2) / (n * p[keep])).sum()
+    dof = keep.sum() - 1
+    assert chi2 < dof + 5 * math.sqrt(2 * max(dof, 1)) + 10, (chi2, dof)
+
+
+def test_sampler_greedy_rule_and_reproducibility():
+    from yalis_b200.ops.sampling import sample
+    vocab = 1000
+    logits = rnd(4, vocab, seed=1)
+    f = lambda vals, dt: torch.tensor(vals, dtype=dt, device=DEV)
+    temp, tk, tp = f([0.0, 1.0, 1.0, 0.0], torch.float32), f([0, 0, 1, 0], torch.int32), f([0.0, 0.0, 1.0, 1.0], torch.float32)
+    seed, draw = f([1, 2, 3, 4], torch.int64), f([0, 0, 0, 0], torch.int64)
+    a = sample(logits, temp, tk, tp, seed, draw).tolist()
+    best = logits.argmax(dim=-1).tolist()
+    assert a[0] == best[0]          # temperature 0 and top_p 0: greedy
+    assert a[1] == best[1]          # top_p 0 keeps the first only
+    assert a[2] == best[2]          # top_k 1
+    b = sample(logits, temp, tk, tp, seed, draw).tolist()
+    assert a == b                   # same seed and draw index: same token
+    # a row's draw does not depend on the rest of the batch
+    one = sample(logits[3:4].contiguous(), temp[3:4].contiguous(), tk[3:4].contiguous(), tp[3:4].contiguous(),
+                 seed[3:4].contiguous(), draw[3:4].contiguous()).tolist()
+    assert one[0] == a[3]
+    many = {int(sample(logits[3:4].contiguous(), temp[3:4].contiguous(), tk[3:4].contiguous(), tp[3:4].contiguous(),
+                       seed[3:4].contiguous(), f([d], torch.int64))) for d in range(30)}
+    assert len(many) > 5            # other draw indices give other tokens
+
+
+def test_top_k_and_top_p_cuts_on_clear_gaps():
+    """Logits with wide gaps: the kept sets are exactly the reference's."""
+    logits = torch.tensor([5.0, 4.0, 3.0, -2.0, -3.0, 1.0, 0.0, -9.0])
+    for temperature, top_k, top_p in ((1.0, 3, 1.0), (1.0, None, 0.7), (1.0, None, 0.95), (2.0, 4, 0.9), (1.0, None, 0.2)):
+        p = plain.sampling_distribution(logits, temperature, top_k, top_p)
+        seen = set(draws(logits, temperature, top_k, top_p, 4000).tolist())
+        assert seen == {i for i in range(8) if p[i] > 1e-4}, (temperature, top_k, top_p, seen)

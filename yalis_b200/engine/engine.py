@@ -111,7 +111,7 @@ class Engine:
         self.num_pages = int(num_pages)
         self.max_slots = int(max_slots)
         requests = self.model.cache_requests()
-        self.groups = plan_groups(self.model.cache_requests_all(), self.page_size, self.num_pages, self.max_context)
+        self.groups = plan_groups(requests, self.page_size, self.num_pages, self.max_context)
         self.manager = CacheManager(self.max_slots, self.groups)
         self.storage = CacheStorage(requests, [e.cache_of for e in self.spec.schedule], self.groups, self.max_slots,
                                     self.device, self.dtype)

@@ -91,11 +91,8 @@ class Model:
 
     # ---- cache -------------------------------------------------------------------------
     def cache_requests(self) -> List[Optional[object]]:
-        """What each schedule entry's mixer wants to keep (None for entries that read another's)."""
-        return [None if e.cache_of is not None else self.blocks[e.layer].mixer.cache_request()
-                for e in self.spec.schedule]
-
-    def cache_requests_all(self) -> List[Optional[object]]:
+        """What the mixer of each schedule entry wants to keep (an entry that reads another
+        entry's cache still says what it expects to find there)."""
         return [self.blocks[e.layer].mixer.cache_request() for e in self.spec.schedule]
 
     # ---- forward -----------------------------------------------------------------------
