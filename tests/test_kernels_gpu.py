@@ -330,3 +330,66 @@ def test_top_k_and_top_p_cuts_on_clear_gaps():
         p = plain.sampling_distribution(logits, temperature, top_k, top_p)
         seen = set(draws(logits, temperature, top_k, top_p, 4000).tolist())
         assert seen == {i for i in range(8) if p[i] > 1e-4}, (temperature, top_k, top_p, seen)
+
+
+@pytest.mark.parametrize("nh, g, hs, page, window", [
+    (4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 4, None), (5, 5, 80, 16, None), (8, 2, 128, 16, None),
+    (2, 1, 256, 32, None), (4, 2, 64, 16, 7), (4, 4, 96, 8, 33), (32, 1, 64, 16, None), (12, 4, 112, 2, None),
+    (6, 2, 160, 64, 100), (3, 3, 192, 16, None), (2, 2, 224, 16, None),
+])
+@pytest.mark.parametrize("mode", ["mixed", "decode", "decode_split"])
+def test_paged_attention_mma_against_plain_and_generic(nh, g, hs, page, window, mode):
+    """The tensor-core kernel: a decode, a portion at an offset and a whole prompt in one
+    launch; decode-only batches with and without key splitting; against the plain float32
+    attention and against the exact generic kernel."""
+    from yalis_b200.ops.attention import paged_attention_generic, paged_attention_mma
+    dtype = torch.bfloat16
+    if mode == "mixed":
+        lens, q_lens = [1, 37, 130, 300], [1, 5, 130, 67]
+    else:
+        lens, q_lens = [1, 64, 65, 130, 517], [1, 1, 1, 1, 1]
+    ks, vs, k_pool, v_pool, table = paged_setup(len(lens), lens, g, hs, page, dtype, seed=hs + nh)
+    gen = torch.Generator().manual_seed(1)
+    qs, pos, req, q_start = [], [], [], [0]
+    for r, (l, ql) in enumerate(zip(lens, q_lens)):
+        qs.append(torch.randn(ql, nh, hs, generator=gen))
+        pos += list(range(l - ql, l))
+        req += [r] * ql
+        q_start.append(q_start[-1] + ql)
+    q = torch.cat(qs).to(dtype)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    positions, req_of_token, q_start_d = i32(pos), i32(req), i32(q_start)
+    qd = q.view(-1, nh * hs).to(DEV)
+    splits = 5 if mode == "decode_split" else 1
+    if mode != "mixed" and nh // g > 16:
+        splits = 1
+    out = paged_attention_mma(qd, k_pool, v_pool, positions, q_start_d, req_of_token, table, max(q_lens), nh, g, hs,
+                              window=window, n_splits=splits if nh // g <= 16 else 1)
+    gen_out = paged_attention_generic(qd, k_pool, v_pool, positions, req_of_token, table, nh, g, hs, window=window)
+    assert not torch.isnan(out.float()).any()
+    torch.testing.assert_close(out.float(), gen_out.float(), rtol=2e-2, atol=2e-2)
+    o = 0
+    for r, (l, ql) in enumerate(zip(lens, q_lens)):
+        kk, vv = ks[r].to(dtype).float(), vs[r].to(dtype).float()
+        ref = plain.causal_attention(q[o:o + ql].float(), kk, vv, torch.arange(l - ql, l), torch.arange(l), window=window)
+        torch.testing.assert_close(out[o:o + ql].float().cpu().view(ql, nh, hs), ref, rtol=2e-2, atol=2e-2)
+        o += ql
+
+
+def test_paged_attention_mma_far_key_and_padding_rows():
+    """A far key that takes nearly all the weight, through the tensor-core kernel in split
+    decode mode; and padding tokens (request index -1) are left alone."""
+    from yalis_b200.ops.attention import paged_attention_mma
+    nh, g, hs, page, l = 8, 2, 64, 16, 1500
+    ks, vs, k_pool, v_pool, table = paged_setup(1, [l], g, hs, page, torch.bfloat16, seed=9)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    for target in (0, 15, 16, 777, l - 1):
+        q = torch.cat([ks[0][target, h // (nh // g)] * 6.0 for h in range(nh)]).view(1, nh * hs)
+        qq = torch.cat([q, torch.zeros(3, nh * hs)]).to(torch.bfloat16).to(DEV)         # three padding rows behind
+        out = torch.full((4, nh * hs), 7.0, dtype=torch.bfloat16, device=DEV)
+        paged_attention_mma(qq, k_pool, v_pool, i32([l - 1, 0, 0, 0]), i32([0, 1]), i32([0, -1, -1, -1]), table, 1, nh, g, hs,
+                            n_splits=7, out=out)
+        got = out[0].float().cpu().view(nh, hs)
+        for h in range(nh):
+            assert torch.allclose(got[h], vs[0][target, h // (nh // g)].to(torch.bfloat16).float(), atol=6e-2), (target, h)
+        assert torch.all(out[1:] == 7.0)

@@ -1,0 +1,139 @@
+"""Pieces of the benchmark that drive the engine below the scheduler: a batch of requests
+prefilled to a given length and then decoded for K steps with the chosen tokens fed back
+on the device, a timed prefill, and the byte and flop counts of the model for rooflines."""
+
+from __future__ import annotations
+
+from typing import Callable, Dict, List
+
+import torch
+
+from yalis_b200.engine.engine import Engine, StepEntry
+from yalis_b200.ops.sampling import argmax
+from yalis_b200.parts.base import PagedKV
+
+
+def model_numbers(engine: Engine) -> Dict[str, object]:
+    """Bytes a decode step must read and flops of a prefill, from the built model."""
+    m = engine.model
+    elt = 2 if engine.dtype == torch.bfloat16 else 4
+    emb_bytes = m.embedding.numel() * m.embedding.element_size()
+    tied = m.head.data_ptr() == m.embedding.data_ptr()
+    # every weight a step uses once: all layer matrices and norms, the output matrix; of the
+    # embedding table only the rows of the step's tokens are read
+    weight_bytes = m.weight_bytes() - (0 if tied else emb_bytes)
+    kv_per_token = 0
+    for req, cache in zip(m.cache_requests(), engine.storage.entries):
+        if isinstance(req, PagedKV) and getattr(cache, "writable", False):
+            kv_per_token += 2 * req.num_kv_heads * req.head_dim * elt
+    matrix_params = 0
+    attn_dims: List[tuple] = []
+    for entry in engine.spec.schedule:
+        b = m.blocks[entry.layer]
+        for part in (b.mixer, b.feed_forward):
+            for ps in part.param_specs().values():
+                if len(ps.shape) == 2:
+                    matrix_params += ps.shape[0] * ps.shape[1]
+        req = b.mixer.cache_request()
+        if isinstance(req, PagedKV):
+            attn_dims.append((b.mixer.nh, req.head_dim))
+    head_params = m.head.shape[0] * m.head.shape[1]
+
+    def flops_prefill(tokens: int, logit_rows: int = 1) -> float:
+        linear = 2.0 * tokens * matrix_params
+        attn = sum(4.0 * nh * hs * tokens * (tokens + 1) / 2 for nh, hs in attn_dims)    # causal QK^T and PV
+        return linear + attn + 2.0 * logit_rows * head_params
+
+    return {"weight_bytes_per_step": weight_bytes, "kv_bytes_per_token": kv_per_token, "flops_prefill": flops_prefill,
+            "matrix_params": matrix_params}
+
+
+class DecodeBench:
+    """``batch`` requests with ``prompt_len`` cached tokens each, decoded step by step through
+    the captured decode graph with device-side feedback of the chosen tokens (greedy)."""
+
+    def __init__(self, engine: Engine, batch: int, prompt_len: int, seed: int = 0, prefill_tokens_per_step: int = 2048):
+        self.engine, self.batch, self.prompt_len, self.seed = engine, batch, prompt_len, seed
+        self.per_step = prefill_tokens_per_step
+        self.ids = [("bench", seed, i) for i in range(batch)]
+        self.slots: List[int] = []
+        self.steps_done = 0
+        self.launches_per_step = 0
+
+    def prepare(self) -> None:
+        eng = self.engine
+        gen = torch.Generator().manual_seed(self.seed)
+        first = []
+        for rid in self.ids:
+            slot = eng.add_request(rid)
+            if slot is None:
+                raise RuntimeError("no free slot for the benchmark batch")
+            self.slots.append(slot)
+        group, group_tokens = [], 0
+        prompts = [torch.randint(0, eng.vocab_size, (self.prompt_len,), generator=gen).tolist() for _ in self.ids]
+
+        def flush():
+            nonlocal group, group_tokens
+            if group:
+                logits = eng.step([StepEntry(rid, p, [len(p) - 1]) for rid, p in group])
+                first.append(argmax(logits))
+                group, group_tokens = [], 0
+
+        for rid, p in zip(self.ids, prompts):
+            if group_tokens + len(p) > self.per_step:
+                flush()
+            group.append((rid, p))
+            group_tokens += len(p)
+        flush()
+        self.first_tokens = torch.cat(first).tolist()
+        # first decode step takes its tokens from the host; later ones from the device
+        self.engine.decoder.step(self.slots, tokens=self.first_tokens)
+        self.steps_done = 1
+
+    def run(self, steps: int) -> None:
+        dec = self.engine.decoder
+        for _ in range(steps):
+            b = dec.step(self.slots)
+        self.steps_done += steps
+        self.launches_per_step = b.launches if steps else self.launches_per_step
+
+    def run_timed(self, steps: int) -> float:
+        """Milliseconds of ``steps`` decode steps on the device (CUDA events, synchronised on both sides)."""
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self._timed_from = self.steps_done
+        start.record()
+        self.run(steps)
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end)
+
+    def mean_context(self, steps: int) -> float:
+        """Mean number of cached tokens per request that the timed steps attended to."""
+        first = self.prompt_len + self._timed_from + 1
+        return first + (steps - 1) / 2.0
+
+    def finish(self) -> None:
+        for rid in self.ids:
+            self.engine.finish_request(rid)
+        self.slots = []
+
+
+def prefill_bench(engine: Engine, tokens: int, warmup: int = 2, iters: int = 3) -> float:
+    """Milliseconds of one step that prefills a single ``tokens``-token prompt (logits of its last token)."""
+    gen = torch.Generator().manual_seed(7)
+    prompt = torch.randint(0, engine.vocab_size, (tokens,), generator=gen).tolist()
+    times = []
+    for i in range(warmup + iters):
+        rid = ("prefill", i)
+        engine.add_request(rid)
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.step([StepEntry(rid, prompt, [tokens - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        engine.finish_request(rid)
+        if i >= warmup:
+            times.append(start.elapsed_time(end))
+    return sum(times) / len(times)

@@ -1,0 +1,480 @@
+// Paged causal attention on the tensor cores (bfloat16 in, float32 softmax and
+// accumulation), one kernel for prompt portions, single decoded tokens and any
+// mix of them.
+//
+// Work is cut by (request, KV head): all query heads that share a KV head and
+// all tokens the request brings to this step form the rows of one problem,
+// row = token * heads_per_group + head_in_group, so a K/V tile read from the
+// cache serves every one of them (for a decode step that is the whole GQA group
+// of one token).  A block takes 64 rows (4 warps x 16) and walks the visible
+// keys in tiles of 64: K and V tiles are gathered page by page with cp.async
+// into padded shared memory (double buffered), S = Q K^T and O += P V run on
+// mma.sync.m16n8k16 with ldmatrix operand loads, the online softmax is kept in
+// registers in the exp2 domain.  The mask is by absolute position: the row of a
+// token at position p sees keys j with p - window < j <= p
+// (yalis/attention/backend_impl/sdpa_and_flex.py:15-19, 301-307).
+//
+// When a (request, KV head) has at most 16 rows (a decode step: one token, up to 16 heads per
+// group) the four warps do not own rows: all work on the same 16 rows and each takes a
+// quarter of every key tile, and their four partial softmax states are merged through
+// shared memory at the end.
+//
+// With n_splits > 1 (decode steps of few requests) the keys of a request are
+// divided among blocks; each writes an unnormalised partial result with its
+// running maximum and sum, and a second kernel merges the splits in index order.
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 64;   // rows per block
+constexpr int BN = 64;   // keys per tile
+constexpr int NWARPS = 4;
+
+struct AttnParams {
+  const __nv_bfloat16* q;      // [N, q_stride], head h at column h*HS
+  int q_stride;
+  __nv_bfloat16* out;          // [N, out_stride]
+  int out_stride;
+  const __nv_bfloat16* k_pool; // [pages, g, page_size, HS]
+  const __nv_bfloat16* v_pool;
+  const int32_t* positions;    // [N]
+  const int32_t* q_start;      // [R+1]
+  const int32_t* block_table;  // [R, table_width]
+  int table_width, page_size, num_pages;
+  int nh, g, per;              // per = nh / g
+  float scale_log2;            // scale * log2(e)
+  int window;                  // 0: none
+  int n_splits;
+  float* part_o;               // [N, nh, n_splits, HS] (split mode)
+  float* part_ml;              // [N, nh, n_splits, 2]
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Gathers keys [key0, key0 + BN) of one KV head into a [BN][HS + 8] tile; rows
+// outside [lo_key, hi_key] or on an unmapped page are zero-filled.
+template <int HS>
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* dst, const __nv_bfloat16* pool, const int32_t* bt,
+                                             const AttnParams& p, int kvh, int key0, int lo_key, int hi_key) {
+  constexpr int CHUNKS = HS / 8;        // 16-byte chunks per row
+  constexpr int LD = HS + 8;
+  for (int c = threadIdx.x; c < BN * CHUNKS; c += NWARPS * 32) {
+    const int row = c / CHUNKS, ch = c - row * CHUNKS;
+    const int key = key0 + row;
+    __nv_bfloat16* d = dst + row * LD + ch * 8;
+    int page = -1, off = 0;
+    if (key >= lo_key && key <= hi_key) {
+      const int pi = key / p.page_size;
+      off = key - pi * p.page_size;
+      page = pi < p.table_width ? bt[pi] : -1;
+      if (page >= p.num_pages) page = -1;
+    }
+    if (page >= 0) {
+      cp_async16(d, pool + (((size_t)page * p.g + kvh) * p.page_size + off) * HS + ch * 8);
+    } else {
+      *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+}
+
+// DEC: the block has at most 16 rows; warps split the keys of a tile instead of the rows.
+template <int HS, bool DEC>
+__global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const AttnParams p) {
+  constexpr int LD = HS + 8;            // padded row: ldmatrix rows fall into distinct banks
+  constexpr int KSTEPS = HS / 16;       // k-steps of Q K^T
+  constexpr int DT = HS / 8;            // n8 tiles of the output along the head dimension
+  constexpr int WKEYS = DEC ? BN / NWARPS : BN;   // keys of a tile that one warp handles
+  constexpr int ST = WKEYS / 8;         // n8 tiles of S along this warp's keys
+  constexpr int RB = DEC ? 16 : BM;     // rows per block
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [BM][LD]
+  __nv_bfloat16* k_s = q_s + BM * LD;                                 // [2][BN][LD]
+  __nv_bfloat16* v_s = k_s + 2 * BN * LD;                             // [2][BN][LD]
+
+  const int req = blockIdx.y / p.g, kvh = blockIdx.y - req * p.g;
+  const int tok0 = p.q_start[req], q_len = p.q_start[req + 1] - tok0;
+  const int n_rows = q_len * p.per;
+  const int row0 = blockIdx.x * RB;
+  if (row0 >= n_rows) return;
+  const int split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int wrow = DEC ? 0 : warp * 16;           // first row of this warp within the block's tile
+  const int wkey = DEC ? warp * WKEYS : 0;        // first key of this warp within a key tile
+  const int32_t* bt = p.block_table + (size_t)req * p.table_width;
+
+  // Positions of the tile's first and last token bound the keys this block needs.
+  const int first_tok = row0 / p.per;
+  const int last_row = min(row0 + RB, n_rows) - 1;
+  const int last_tok = last_row / p.per;
+  const int pos_first = p.positions[tok0 + first_tok];
+  const int pos_last = p.positions[tok0 + last_tok];
+  const int lo_key = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+  const int hi_key = pos_last;
+  int tile_lo = lo_key / BN, tile_hi = hi_key / BN + 1;     // key tiles [tile_lo, tile_hi)
+  if (p.n_splits > 1) {
+    const int total = tile_hi - tile_lo;
+    const int per_split = (total + p.n_splits - 1) / p.n_splits;
+    tile_lo = tile_lo + split * per_split;
+    tile_hi = min(tile_hi, tile_lo + per_split);
+  }
+  const int n_tiles = max(0, tile_hi - tile_lo);
+
+  // ---- Q tile -> shared memory, then this warp's A fragments ----------------------
+  {
+    constexpr int CHUNKS = HS / 8;
+    for (int c = threadIdx.x; c < RB * CHUNKS; c += NWARPS * 32) {
+      const int r = c / CHUNKS, ch = c - r * CHUNKS;
+      const int row = row0 + r;
+      __nv_bfloat16* d = q_s + r * LD + ch * 8;
+      if (row < n_rows) {
+        const int t = row / p.per, h = row - t * p.per;
+        cp_async16(d, p.q + (size_t)(tok0 + t) * p.q_stride + (size_t)(kvh * p.per + h) * HS + ch * 8);
+      } else {
+        *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  }
+  if (n_tiles > 0) {
+    load_kv_tile<HS>(k_s, p.k_pool, bt, p, kvh, tile_lo * BN, lo_key, hi_key);
+    load_kv_tile<HS>(v_s, p.v_pool, bt, p, kvh, tile_lo * BN, lo_key, hi_key);
+  }
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  unsigned qf[KSTEPS][4];
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    const int r = wrow + (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int c = ks * 16 + (lane >> 4) * 8;
+    ldmatrix_x4(qf[ks], q_s + r * LD + c);
+  }
+  // Rows of this thread: gid and gid + 8 of the warp's 16.
+  int row_pos[2];
+  bool row_ok[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = row0 + wrow + gid + i * 8;
+    row_ok[i] = row < n_rows;
+    row_pos[i] = row_ok[i] ? p.positions[tok0 + row / p.per] : -1;
+  }
+
+  float o[DT][4];
+#pragma unroll
+  for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int buf = it & 1;
+    const int key0 = (tile_lo + it) * BN;
+    // prefetch the next tile into the other buffer
+    if (it + 1 < n_tiles) {
+      load_kv_tile<HS>(k_s + (buf ^ 1) * BN * LD, p.k_pool, bt, p, kvh, key0 + BN, lo_key, hi_key);
+      load_kv_tile<HS>(v_s + (buf ^ 1) * BN * LD, p.v_pool, bt, p, kvh, key0 + BN, lo_key, hi_key);
+    }
+    cp_async_commit();
+    const __nv_bfloat16* kt = k_s + buf * BN * LD;
+    const __nv_bfloat16* vt = v_s + buf * BN * LD;
+
+    // ---- S = Q K^T ------------------------------------------------------------------
+    float s[ST][4];
+#pragma unroll
+    for (int j = 0; j < ST; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+      for (int j = 0; j < ST; j += 2) {
+        unsigned kb[4];
+        const int key = wkey + j * 8 + (lane & 7) + (lane >> 4) * 8;
+        const int dim = ks * 16 + ((lane >> 3) & 1) * 8;
+        ldmatrix_x4(kb, kt + key * LD + dim);
+        mma_bf16(s[j], qf[ks], kb[0], kb[1]);
+        mma_bf16(s[j + 1], qf[ks], kb[2], kb[3]);
+      }
+    }
+    // ---- mask, online softmax (exp2 domain) -----------------------------------------
+    float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int j = 0; j < ST; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const int key = key0 + wkey + j * 8 + tig * 2 + (e & 1);
+        const bool vis = row_ok[i] && key <= row_pos[i] && (p.window <= 0 || key > row_pos[i] - p.window);
+        const float v = vis ? s[j][e] * p.scale_log2 : -INFINITY;
+        s[j][e] = v;
+        m_new[i] = fmaxf(m_new[i], v);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
+      m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
+    }
+    float corr[2], base[2], l_add[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      base[i] = (m_new[i] == -INFINITY) ? 0.f : m_new[i];
+      corr[i] = exp2f(m_run[i] - base[i]);          // m_run = -inf gives 0
+      m_run[i] = m_new[i];
+    }
+    unsigned pf[ST / 2][4];
+#pragma unroll
+    for (int j = 0; j < ST; ++j) {
+      const float p0 = exp2f(s[j][0] - base[0]), p1 = exp2f(s[j][1] - base[0]);
+      const float p2 = exp2f(s[j][2] - base[1]), p3 = exp2f(s[j][3] - base[1]);
+      l_add[0] += p0 + p1;
+      l_add[1] += p2 + p3;
+      pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
+      pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * corr[i] + l_add[i];
+#pragma unroll
+    for (int d = 0; d < DT; ++d) {
+      o[d][0] *= corr[0]; o[d][1] *= corr[0];
+      o[d][2] *= corr[1]; o[d][3] *= corr[1];
+    }
+    // ---- O += P V -------------------------------------------------------------------
+#pragma unroll
+    for (int kk = 0; kk < ST / 2; ++kk) {
+#pragma unroll
+      for (int d = 0; d < DT; d += 2) {
+        unsigned vb[4];
+        const int key = wkey + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int dim = d * 8 + (lane >> 4) * 8;
+        ldmatrix_x4_trans(vb, vt + key * LD + dim);
+        mma_bf16(o[d], pf[kk], vb[0], vb[1]);
+        mma_bf16(o[d + 1], pf[kk], vb[2], vb[3]);
+      }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+  }
+
+  // ---- finish -----------------------------------------------------------------------
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+  }
+  if constexpr (DEC) {
+    // The four warps hold partial states of the same 16 rows: merge them in warp order.
+    float* mo = reinterpret_cast<float*>(k_s);        // [NWARPS][16][HS]
+    float* mml = reinterpret_cast<float*>(v_s);       // [NWARPS][16][2]
+    __syncthreads();                                    // every warp is done with the K/V tiles
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = gid + i * 8;
+#pragma unroll
+      for (int d = 0; d < DT; ++d)
+        *reinterpret_cast<float2*>(mo + ((size_t)warp * 16 + r) * HS + d * 8 + tig * 2) =
+            make_float2(o[d][i * 2], o[d][i * 2 + 1]);
+      if (tig == 0) {
+        mml[(warp * 16 + r) * 2] = m_run[i];
+        mml[(warp * 16 + r) * 2 + 1] = l_run[i];
+      }
+    }
+    __syncthreads();
+    const int rows_here = min(16, n_rows - row0);
+    for (int e = threadIdx.x; e < rows_here * HS; e += NWARPS * 32) {
+      const int r = e / HS, d = e - r * HS;
+      float mm = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < NWARPS; ++w) mm = fmaxf(mm, mml[(w * 16 + r) * 2]);
+      float ll = 0.f, acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < NWARPS; ++w) {
+        const float m = mml[(w * 16 + r) * 2];
+        const float f = (m == -INFINITY) ? 0.f : exp2f(m - mm);
+        ll += mml[(w * 16 + r) * 2 + 1] * f;
+        acc += mo[((size_t)w * 16 + r) * HS + d] * f;
+      }
+      const int row = row0 + r;
+      const int t = row / p.per, h = row - t * p.per;
+      const int tok = tok0 + t, head = kvh * p.per + h;
+      if (p.n_splits == 1) {
+        p.out[(size_t)tok * p.out_stride + (size_t)head * HS + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+      } else {
+        const size_t slot = ((size_t)tok * p.nh + head) * p.n_splits + split;
+        p.part_o[slot * HS + d] = acc;
+        if (d == 0) {
+          p.part_ml[slot * 2] = mm;
+          p.part_ml[slot * 2 + 1] = ll;
+        }
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (!row_ok[i]) continue;
+    const int row = row0 + wrow + gid + i * 8;
+    const int t = row / p.per, h = row - t * p.per;
+    const int tok = tok0 + t, head = kvh * p.per + h;
+    if (p.n_splits == 1) {
+      const float inv = l_run[i] > 0.f ? 1.0f / l_run[i] : 0.f;
+      __nv_bfloat16* dst = p.out + (size_t)tok * p.out_stride + (size_t)head * HS;
+#pragma unroll
+      for (int d = 0; d < DT; ++d) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(o[d][i * 2] * inv, o[d][i * 2 + 1] * inv);
+        *reinterpret_cast<__nv_bfloat162*>(dst + d * 8 + tig * 2) = v;
+      }
+    } else {
+      const size_t slot = ((size_t)tok * p.nh + head) * p.n_splits + split;
+      float* dst = p.part_o + slot * HS;
+#pragma unroll
+      for (int d = 0; d < DT; ++d) {
+        *reinterpret_cast<float2*>(dst + d * 8 + tig * 2) = make_float2(o[d][i * 2], o[d][i * 2 + 1]);
+      }
+      if (tig == 0) {
+        p.part_ml[slot * 2] = m_run[i];
+        p.part_ml[slot * 2 + 1] = l_run[i];
+      }
+    }
+  }
+}
+
+// Merges split partial results in split order: out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
+// Every (row, split) slot of a live request is written by the attention kernel, a split without
+// keys writes m = -inf and l = 0; rows of padding tokens are skipped here as they are there.
+__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         __nv_bfloat16* __restrict__ out, int out_stride, int nh, int hs,
+                                         int n_splits, const int32_t* __restrict__ req_of_token) {
+  const int tok = blockIdx.x, head = blockIdx.y;
+  if (req_of_token && req_of_token[tok] < 0) return;
+  const size_t base = ((size_t)tok * nh + head) * n_splits;
+  float mm = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
+  float ll = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float m = part_ml[(base + s) * 2];
+    if (m != -INFINITY) ll += part_ml[(base + s) * 2 + 1] * exp2f(m - mm);
+  }
+  const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+  for (int d = threadIdx.x; d < hs; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float m = part_ml[(base + s) * 2];
+      if (m != -INFINITY) acc += part_o[(base + s) * hs + d] * exp2f(m - mm);
+    }
+    out[(size_t)tok * out_stride + (size_t)head * hs + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int HS, bool DEC>
+int launch_mode(const AttnParams& p, int n_requests, int max_rows, cudaStream_t stream) {
+  constexpr int LD = HS + 8;
+  const size_t smem = (size_t)(BM + 4 * BN) * LD * sizeof(__nv_bfloat16);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(paged_attention_mma_kernel<HS, DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return YALIS_ERR_LAUNCH;
+    configured = true;
+  }
+  const int rows_per_block = DEC ? 16 : BM;
+  dim3 grid((max_rows + rows_per_block - 1) / rows_per_block, n_requests * p.g, p.n_splits);
+  if (grid.y > 65535 || grid.z > 65535) return YALIS_ERR_SHAPE;
+  paged_attention_mma_kernel<HS, DEC><<<grid, NWARPS * 32, smem, stream>>>(p);
+  return yalis_launch_status();
+}
+
+template <int HS>
+int launch(const AttnParams& p, int n_requests, int max_rows, cudaStream_t stream) {
+  return max_rows <= 16 ? launch_mode<HS, true>(p, n_requests, max_rows, stream)
+                        : launch_mode<HS, false>(p, n_requests, max_rows, stream);
+}
+
+}  // namespace
+
+// Head sizes this kernel is built for.
+YALIS_API int yalis_attention_mma_supports(int hs) {
+  switch (hs) {
+    case 16: case 32: case 48: case 64: case 80: case 96: case 112: case 128: case 160: case 192: case 224: case 256:
+      return 1;
+    default:
+      return 0;
+  }
+}
+
+// Scratch floats needed for n_splits > 1: part_o then part_ml.
+YALIS_API long long yalis_attention_mma_scratch_floats(int n_tokens, int nh, int hs, int n_splits) {
+  return n_splits > 1 ? (long long)n_tokens * nh * n_splits * (hs + 2) : 0;
+}
+
+YALIS_API int yalis_paged_attention_mma(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
+                                        const void* v_pool, const int32_t* positions, const int32_t* q_start,
+                                        const int32_t* req_of_token, const int32_t* block_table, int table_width,
+                                        int page_size, int num_pages, int n_tokens, int n_requests, int max_q_len,
+                                        int nh, int g, int hs, float scale, int window, int n_splits, float* scratch,
+                                        cudaStream_t stream) {
+  if (n_tokens <= 0 || n_requests <= 0) return YALIS_OK;
+  if (g <= 0 || nh % g != 0 || n_splits < 1 || max_q_len < 1) return YALIS_ERR_SHAPE;
+  if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) return YALIS_ERR_ALIGN;
+  if ((q_stride % 8) || (out_stride % 2)) return YALIS_ERR_ALIGN;
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
+  p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
+  p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;
+  p.positions = positions; p.q_start = q_start; p.block_table = block_table;
+  p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages;
+  p.nh = nh; p.g = g; p.per = nh / g;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window; p.n_splits = n_splits;
+  p.part_o = nullptr; p.part_ml = nullptr;
+  if (n_splits > 1) {
+    if (scratch == nullptr) return YALIS_ERR_SHAPE;
+    p.part_o = scratch;
+    p.part_ml = scratch + (size_t)n_tokens * nh * n_splits * hs;
+  }
+  const int max_rows = max_q_len * p.per;
+  int st;
+  switch (hs) {
+    case 16: st = launch<16>(p, n_requests, max_rows, stream); break;
+    case 32: st = launch<32>(p, n_requests, max_rows, stream); break;
+    case 48: st = launch<48>(p, n_requests, max_rows, stream); break;
+    case 64: st = launch<64>(p, n_requests, max_rows, stream); break;
+    case 80: st = launch<80>(p, n_requests, max_rows, stream); break;
+    case 96: st = launch<96>(p, n_requests, max_rows, stream); break;
+    case 112: st = launch<112>(p, n_requests, max_rows, stream); break;
+    case 128: st = launch<128>(p, n_requests, max_rows, stream); break;
+    case 160: st = launch<160>(p, n_requests, max_rows, stream); break;
+    case 192: st = launch<192>(p, n_requests, max_rows, stream); break;
+    case 224: st = launch<224>(p, n_requests, max_rows, stream); break;
+    case 256: st = launch<256>(p, n_requests, max_rows, stream); break;
+    default: return YALIS_ERR_SHAPE;
+  }
+  if (st != YALIS_OK || n_splits == 1) return st;
+  dim3 grid(n_tokens, nh);
+  attention_combine_kernel<<<grid, 128, 0, stream>>>(p.part_o, p.part_ml, p.out, out_stride, nh, hs, n_splits,
+                                                     req_of_token);
+  return yalis_launch_status();
+}

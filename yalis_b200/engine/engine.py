@@ -120,6 +120,23 @@ class Engine:
         self._staging: List[Tuple[torch.Tensor, Optional[torch.cuda.Event]]] = []
         self._staging_next = 0
         self.steps_run = 0
+        self.last_h2d_bytes = 0
+        self._graph_pool = None
+        self._decoder = None
+
+    def graph_pool(self):
+        """One memory pool shared by all captured decode graphs."""
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        return self._graph_pool
+
+    @property
+    def decoder(self):
+        """The CUDA-graph runner of decode-only steps (made on first use)."""
+        if self._decoder is None:
+            from yalis_b200.engine.decode_graph import GraphedDecoder
+            self._decoder = GraphedDecoder(self)
+        return self._decoder
 
     # ---- requests ------------------------------------------------------------------------
     def has_request(self, request: Hashable) -> bool:
@@ -215,6 +232,7 @@ class Engine:
             o += r * u
         dev = torch.empty(total, dtype=torch.int32, device=self.device)
         dev.copy_(pinned[:total], non_blocking=True)
+        self.last_h2d_bytes = 4 * total
         ev = torch.cuda.Event()
         ev.record()
         self._staging[which] = (pinned, ev)

@@ -11,6 +11,7 @@ slots and pages allow, prefilled in portions beside the decoding of others.
 
 from __future__ import annotations
 
+import os
 import time
 from typing import Dict, List, Optional, Sequence, Union
 
@@ -44,6 +45,7 @@ class LLMEngine:
         self.sampler = Sampler(self.device)
         self.tokenizer = None
         self._requests_made = 0
+        self.use_graphs = os.environ.get("YALIS_DISABLE_DECODE_CUDAGRAPHS", "0") != "1"
 
     # ---- tokenizer (optional sugar; token ids are the interface) -----------------------
     def _tokenize(self, prompts: Sequence[str]) -> List[List[int]]:
@@ -154,7 +156,19 @@ class LLMEngine:
         return out, metrics
 
     def _run_plan(self, plan: StepPlan, logits_out) -> List[int]:
-        """One engine step for the plan, then one draw per entry that reached its last token."""
+        """One engine step for the plan, then one draw per entry that reached its last token.
+        A step of single tokens only goes through the captured decode graph (unless
+        YALIS_DISABLE_DECODE_CUDAGRAPHS=1, the reference's switch, yalis/engine.py:44-48)."""
+        if self.use_graphs and all(e.count == 1 and e.samples for e in plan.entries):
+            reqs = [e.request for e in plan.entries]
+            bucket = self.engine.decoder.step(
+                [r.slot for r in reqs], tokens=[r.tokens[-1] for r in reqs], params=[r.sampling for r in reqs],
+                draws=[len(r.output) for r in reqs], keep_logits=logits_out is not None)
+            toks = bucket.tokens[:len(reqs)].tolist()
+            if logits_out is not None:
+                for i, r in enumerate(reqs):
+                    logits_out[r.id].append(bucket.logits[i].clone())
+            return toks
         entries, slots, samplers = [], [], []
         for e in plan.entries:
             toks = e.request.tokens[e.start:e.start + e.count]

@@ -51,7 +51,11 @@ def stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+LAUNCHES = [0]   # kernels of this library launched by this process (one per successful launcher call)
+
+
 def check(status: int, name: str, detail: str = "") -> None:
+    LAUNCHES[0] += 1
     if status != 0:
         why = _STATUS.get(status, f"status {status}")
         raise KernelError(f"{name}: {why}{(' (' + detail + ')') if detail else ''}")

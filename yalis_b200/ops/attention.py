@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+import ctypes
 import math
 from typing import Optional
 
@@ -53,11 +54,72 @@ def paged_attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch
     return out
 
 
+SM_COUNT = 148   # B200
+
+
+def mma_supports(head_dim: int) -> bool:
+    """Whether the tensor-core kernel is built for this head size (multiples of 16 up to 128, of 32 up to 256)."""
+    return bool(lib().yalis_attention_mma_supports(i32(head_dim)))
+
+
+def decode_splits(n_requests: int, num_kv_heads: int) -> int:
+    """How many blocks share the keys of one (request, KV head) in a decode step, so that
+    few requests still fill the GPU.  Depends on the batch shape only, never on lengths,
+    so a captured step can be replayed."""
+    blocks = max(1, n_requests * num_kv_heads)
+    return max(1, min(16, -(-2 * SM_COUNT // blocks)))
+
+
+def paged_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, positions: torch.Tensor,
+                        q_start: torch.Tensor, req_of_token: torch.Tensor, block_table: torch.Tensor, max_q_len: int,
+                        num_heads: int, num_kv_heads: int, head_dim: int, scale: Optional[float] = None,
+                        window: Optional[int] = None, n_splits: int = 1,
+                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Tensor-core attention (bfloat16) of the step's tokens over the cache; the same
+    semantics as ``paged_attention_generic``.  ``q_start`` int32 [R+1] gives each request's
+    token range; ``max_q_len`` bounds the launch grid.  ``n_splits`` > 1 divides the keys of
+    a request among blocks (decode steps) and needs scratch memory for the partial results.
+    """
+    name = "paged_attention_mma"
+    _check_common(name, q, k_pool, v_pool, positions, req_of_token, block_table, num_heads, num_kv_heads, head_dim)
+    need(q.dtype == torch.bfloat16, name, "bfloat16 only (float32 goes to the generic kernel)")
+    need(mma_supports(head_dim), name, f"head_dim {head_dim} is not built (multiples of 16 to 128, of 32 to 256)")
+    n, r = q.shape[0], q_start.numel() - 1
+    need(q_start.dtype == torch.int32 and q_start.is_contiguous() and q_start.is_cuda, name, "q_start must be int32 [R+1]")
+    need(block_table.shape[0] >= r, name, "block_table has fewer rows than requests")
+    if out is None:
+        out = torch.empty((n, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    need(out.shape == (n, num_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous(), name, "bad out tensor")
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    scratch = None
+    if n_splits > 1:
+        need(max_q_len * (num_heads // num_kv_heads) <= 16, name, "splitting the keys is for decode steps only")
+        floats = lib().yalis_attention_mma_scratch_floats
+        floats.restype = ctypes.c_longlong
+        scratch = torch.empty(int(floats(i32(n), i32(num_heads), i32(head_dim), i32(n_splits))), dtype=torch.float32,
+                              device=q.device)
+    check(lib().yalis_paged_attention_mma(
+        ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(k_pool), ptr(v_pool), ptr(positions), ptr(q_start),
+        ptr(req_of_token), ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]), i32(k_pool.shape[0]),
+        i32(n), i32(r), i32(max_q_len), i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), i32(window or 0),
+        i32(n_splits), ptr(scratch), stream()), name)
+    return out
+
+
 def paged_attention(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: str, num_heads: int,
                     num_kv_heads: int, head_dim: int, scale: Optional[float] = None,
                     window: Optional[int] = None) -> torch.Tensor:
-    """Attention of the step's tokens over the cache of their requests: picks the
-    kernel for the step's shape and dtype.  ``ctx`` is the step context."""
+    """Attention of the step's tokens over the cache of their requests: picks the kernel
+    for the step's shape and dtype.  ``ctx`` is the step context.  bfloat16 with a head
+    size the tensor-core kernel is built for goes there; everything else (float32, odd
+    head sizes) to the exact generic kernel."""
     table = ctx.block_tables[group]
+    if qkv.dtype == torch.bfloat16 and mma_supports(head_dim):
+        per = num_heads // num_kv_heads
+        splits = decode_splits(ctx.n_requests, num_kv_heads) if ctx.host.max_q_len * per <= 16 else 1
+        return paged_attention_mma(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, ctx.req_of_token, table,
+                                   ctx.host.max_q_len, num_heads, num_kv_heads, head_dim, scale=scale, window=window,
+                                   n_splits=splits)
     return paged_attention_generic(qkv, k_pool, v_pool, ctx.positions, ctx.req_of_token, table, num_heads,
                                    num_kv_heads, head_dim, scale=scale, window=window)
