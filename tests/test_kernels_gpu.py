@@ -190,15 +190,22 @@ def test_rope_kv_write(dtype, nh, g, hs, page, scaled):
     reqs = torch.tensor(req_list, dtype=torch.int32, device=DEV)
     before = qkv.clone()
     flag = torch.zeros(1, dtype=torch.int32, device=DEV)
-    rope_kv_write(qkv, positions, reqs, inv.to(DEV), k_pool, v_pool, table, nh, g, hs, bad_flag=flag)
+    q_out = rope_kv_write(qkv, positions, reqs, inv.to(DEV), k_pool, v_pool, table, nh, g, hs, bad_flag=flag)
     assert int(flag) == 0
     cos, sin = plain.rope_tables(torch.tensor(pos_list), inv)
     bq = before[:, :nh * hs].float().cpu().view(n, nh, hs)
     bk = before[:, nh * hs:(nh + g) * hs].float().cpu().view(n, g, hs)
     bv = before[:, (nh + g) * hs:].float().cpu().view(n, g, hs)
     t = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
-    torch.testing.assert_close(qkv[:, :nh * hs].float().cpu().view(n, nh, hs), plain.apply_rope(bq, cos, sin).to(dtype).float(), **t)
-    assert torch.equal(qkv[:, nh * hs:], before[:, nh * hs:])            # K and V in the row are left alone
+    torch.testing.assert_close(q_out.float().cpu().view(n, nh, hs), plain.apply_rope(bq, cos, sin).to(dtype).float(), **t)
+    assert torch.equal(qkv, before)                                       # the source row is left alone
+    # the same from float32 partial sums of a split product
+    parts = torch.stack([before.float() * 0.5, before.float() * 0.25, before.float() * 0.25]).contiguous()
+    k2, v2 = torch.zeros_like(k_pool), torch.zeros_like(v_pool)
+    q2 = rope_kv_write(parts, positions, reqs, inv.to(DEV), k2, v2, table, nh, g, hs, out_dtype=dtype, bad_flag=flag)
+    torch.testing.assert_close(q2.float(), q_out.float(), **t)
+    torch.testing.assert_close(k2.float(), k_pool.float(), **t)
+    assert torch.equal(v2, v_pool)
     rk = plain.apply_rope(bk, cos, sin)
     for i, (p, r) in enumerate(zip(pos_list, req_list)):
         page_id, off = int(table[r, p // page]), p % page
@@ -223,11 +230,11 @@ def test_rope_large_positions_match_float32_table():
     before = qkv.clone()
     table = torch.zeros(1, 131072 // page, dtype=torch.int32, device=DEV)
     pool = torch.zeros(1, g, page, hs, device=DEV)
-    rope_kv_write(qkv, torch.tensor(pos, dtype=torch.int32, device=DEV), torch.zeros(2, dtype=torch.int32, device=DEV),
-                  inv.to(DEV), pool, pool.clone(), table, nh, g, hs)
+    q = rope_kv_write(qkv, torch.tensor(pos, dtype=torch.int32, device=DEV), torch.zeros(2, dtype=torch.int32, device=DEV),
+                      inv.to(DEV), pool, pool.clone(), table, nh, g, hs)
     cos, sin = plain.rope_tables(torch.tensor(pos), inv)
     ref = plain.apply_rope(before[:, :hs].cpu().view(2, 1, hs), cos, sin)
-    torch.testing.assert_close(qkv[:, :hs].cpu().view(2, 1, hs), ref, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(q.cpu().view(2, 1, hs), ref, rtol=1e-5, atol=1e-5)
 
 
 @pytest.mark.parametrize("m, n, k", [(1, 7, 5), (33, 130, 96), (70, 64, 1000), (5, 300, 17)])
@@ -393,3 +400,23 @@ def test_paged_attention_mma_far_key_and_padding_rows():
         for h in range(nh):
             assert torch.allclose(got[h], vs[0][target, h // (nh // g)].to(torch.bfloat16).float(), atol=6e-2), (target, h)
         assert torch.all(out[1:] == 7.0)
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 128, 64), (8, 384, 1024), (17, 200, 520), (64, 1000, 4096), (100, 130, 72),
+                                     (256, 512, 2048), (3, 4096, 14336)])
+def test_gemm_wstream_tcgen05(m, n, k):
+    """The tcgen05 weight-streaming product against a float32 product of the same bfloat16
+    operands: whole and as split partial sums; its rows do not depend on the batch."""
+    from yalis_b200.ops.linear import gemm_simt, gemm_wstream, wstream_error_flag, wstream_splits
+    x, w = rnd(m, k, dtype=torch.bfloat16, seed=1, scale=0.5), rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.5)
+    ref = gemm_simt(x, w, out_dtype=torch.float32)
+    out32 = gemm_wstream(x, w, out_dtype=torch.float32)
+    torch.testing.assert_close(out32, ref, rtol=1e-4, atol=1e-3 * math.sqrt(k / 64))
+    out16 = gemm_wstream(x, w)
+    torch.testing.assert_close(out16.float(), ref.to(torch.bfloat16).float(), rtol=2e-2, atol=2e-2)
+    parts = gemm_wstream(x, w, split=True)
+    assert parts.shape == (wstream_splits(n, k), m, n) and parts.dtype == torch.float32
+    torch.testing.assert_close(parts.sum(0), ref, rtol=1e-4, atol=1e-3 * math.sqrt(k / 64))
+    one = gemm_wstream(x[m - 1:].contiguous(), w, out_dtype=torch.float32)
+    assert torch.equal(one[0], out32[m - 1])                               # the same bits alone and in the batch
+    assert int(wstream_error_flag(DEV)) == 0

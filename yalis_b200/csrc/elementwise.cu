@@ -45,7 +45,8 @@ YALIS_API int yalis_embedding(const void* table, int dtype, const int32_t* ids, 
 // One block per output row; the mean is a fixed-order block reduction, so a
 // row's result does not depend on which other rows are in the launch.
 // --------------------------------------------------------------------------
-template <typename T, typename TD>
+// MAXV: values a thread keeps in registers (the row is read once); 0 = re-read variant for wide rows.
+template <typename T, typename TD, int MAXV>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_delta,
                                    size_t delta_stride, const float* __restrict__ w, T* __restrict__ y,
                                    const int32_t* __restrict__ rows, int width, float eps, int write_back) {
@@ -55,24 +56,74 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
   if (r < 0) return;  // padded row
   float* xr = x + (size_t)r * width;
   const TD* dr = delta ? delta + (size_t)r * width : nullptr;
-  float ss = 0.f;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    float h = xr[c];
-    if (dr) {
-      for (int s = 0; s < n_delta; ++s) h += to_f32<TD>(dr[(size_t)s * delta_stride + c]);
-      if (write_back) xr[c] = h;
-    }
-    ss += h * h;
-  }
-  ss = block_sum(ss, scratch);
-  const float inv = rsqrtf(ss / (float)width + eps);
   T* yr = y + (size_t)i * width;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    float h = xr[c];
-    if (dr && !write_back)
-      for (int s = 0; s < n_delta; ++s) h += to_f32<TD>(dr[(size_t)s * delta_stride + c]);
-    yr[c] = from_f32<T>((h * inv) * w[c]);
+  float ss = 0.f;
+  if constexpr (MAXV > 0) {
+    float h[MAXV];
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int c = threadIdx.x + v * blockDim.x;
+      h[v] = c < width ? xr[c] : 0.f;
+    }
+    if (dr) {
+      for (int s = 0; s < n_delta; ++s) {
+#pragma unroll
+        for (int v = 0; v < MAXV; ++v) {
+          const int c = threadIdx.x + v * blockDim.x;
+          if (c < width) h[v] += to_f32<TD>(dr[(size_t)s * delta_stride + c]);
+        }
+      }
+      if (write_back) {
+#pragma unroll
+        for (int v = 0; v < MAXV; ++v) {
+          const int c = threadIdx.x + v * blockDim.x;
+          if (c < width) xr[c] = h[v];
+        }
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) ss += h[v] * h[v];
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)width + eps);
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int c = threadIdx.x + v * blockDim.x;
+      if (c < width) yr[c] = from_f32<T>((h[v] * inv) * w[c]);
+    }
+  } else {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      float h = xr[c];
+      if (dr) {
+        for (int s = 0; s < n_delta; ++s) h += to_f32<TD>(dr[(size_t)s * delta_stride + c]);
+        if (write_back) xr[c] = h;
+      }
+      ss += h * h;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      float h = xr[c];
+      if (dr && !write_back)
+        for (int s = 0; s < n_delta; ++s) h += to_f32<TD>(dr[(size_t)s * delta_stride + c]);
+      yr[c] = from_f32<T>((h * inv) * w[c]);
+    }
   }
+}
+
+template <typename T, typename TD>
+void launch_add_rmsnorm(float* x, const void* delta, int n_delta, size_t delta_stride, const float* w, void* y,
+                        const int32_t* rows, int n_out_rows, int width, float eps, int write_back,
+                        cudaStream_t stream) {
+  const int threads = width >= 4096 ? 1024 : width >= 1024 ? 512 : 256;
+  const int per_thread = (width + threads - 1) / threads;
+#define YALIS_NORM_LAUNCH(V)                                                                                   \
+  add_rmsnorm_kernel<T, TD, V><<<n_out_rows, threads, 0, stream>>>(x, (const TD*)delta, n_delta, delta_stride, w, \
+                                                                    (T*)y, rows, width, eps, write_back)
+  if (per_thread <= 4) YALIS_NORM_LAUNCH(4);
+  else if (per_thread <= 8) YALIS_NORM_LAUNCH(8);
+  else if (per_thread <= 16) YALIS_NORM_LAUNCH(16);
+  else YALIS_NORM_LAUNCH(0);
+#undef YALIS_NORM_LAUNCH
 }
 
 // delta_dtype: type of delta (YALIS_F32 for split-K partials, else the model type).
@@ -80,15 +131,14 @@ YALIS_API int yalis_add_rmsnorm(float* x, const void* delta, int delta_dtype, in
                                 const float* w, void* y, int out_dtype, const int32_t* rows, int n_out_rows,
                                 int width, float eps, int write_back, cudaStream_t stream) {
   if (n_out_rows <= 0) return YALIS_OK;
-  const int threads = width >= 2048 ? 512 : 256;
   YALIS_DISPATCH_DTYPE(
       out_dtype, T,
       if (delta_dtype == YALIS_F32) {
-        add_rmsnorm_kernel<T, float><<<n_out_rows, threads, 0, stream>>>(
-            x, (const float*)delta, n_delta, (size_t)delta_stride, w, (T*)y, rows, width, eps, write_back);
+        launch_add_rmsnorm<T, float>(x, delta, n_delta, (size_t)delta_stride, w, y, rows, n_out_rows, width, eps,
+                                     write_back, stream);
       } else if (delta_dtype == YALIS_BF16) {
-        add_rmsnorm_kernel<T, __nv_bfloat16><<<n_out_rows, threads, 0, stream>>>(
-            x, (const __nv_bfloat16*)delta, n_delta, (size_t)delta_stride, w, (T*)y, rows, width, eps, write_back);
+        launch_add_rmsnorm<T, __nv_bfloat16>(x, delta, n_delta, (size_t)delta_stride, w, y, rows, n_out_rows, width,
+                                             eps, write_back, stream);
       } else { return YALIS_ERR_DTYPE; });
   return yalis_launch_status();
 }
@@ -127,91 +177,86 @@ YALIS_API int yalis_residual_add(float* x, const void* delta, int delta_dtype, i
 //   reference's table, yalis/external/model.py:810-820)
 //   out[i]        = x[i]*cos - x[i+hs/2]*sin
 //   out[i+hs/2]   = x[i+hs/2]*cos + x[i]*sin  (half-split, model.py:894-909)
-// Q is rotated in place inside the fused qkv row; K (rotated) and V go to
+// The source is the fused qkv row [Q heads | K heads | V heads] of each token,
+// either in the model type or as `n_parts` float32 partial sums of a split-K
+// product (added in order).  Rotated Q goes to q_out [N, nh*hs]; K (rotated)
+// and V go to
 //   pool[page][kv_head][pos % page_size][:], page = block_table[req][pos / page_size]
 // (the reference's paged scatter: yalis/attention/utils/flash_utils.py:33-43).
 // inv_freq == null means "no rotation" (K and V are still stored); k_pool == null
 // means "store nothing" (Q is still rotated).
 // A token whose request index is negative is padding and is skipped; a token
 // whose page is unmapped raises *bad_page and is not stored.
-// One block per token.
+// One block per (token, head of the fused row).
 // --------------------------------------------------------------------------
-template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, const int32_t* __restrict__ positions,
+template <typename T, typename TS>
+__global__ void rope_kv_write_kernel(const TS* __restrict__ src, int src_stride, int n_parts, size_t part_stride,
+                                     T* __restrict__ q_out, const int32_t* __restrict__ positions,
                                      const int32_t* __restrict__ req_of_token, const float* __restrict__ inv_freq,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool,
                                      const int32_t* __restrict__ block_table, int table_width, int page_size,
                                      int num_pages, int nh, int g, int hs, int32_t* bad_page) {
-  extern __shared__ float cs[];  // cos[hs/2], sin[hs/2]
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, head = blockIdx.y;   // head: [0, nh) Q, [nh, nh+g) K, [nh+g, nh+2g) V
   const int req = req_of_token[t];
   if (req < 0) return;
   const int pos = positions[t];
   const int half = hs >> 1;
-  if (inv_freq) {
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-      const float angle = (float)pos * inv_freq[i];
-      float s, c;
-      sincosf(angle, &s, &c);
-      cs[i] = c;
-      cs[half + i] = s;
-    }
-  }
-  __syncthreads();
-  T* row = qkv + (size_t)t * qkv_stride;
-  const int page_idx = pos / page_size;
-  int page = -1;
-  if (k_pool != nullptr) {  // a layer that reads another layer's cache stores nothing
-    page = (page_idx < table_width) ? block_table[(size_t)req * table_width + page_idx] : -1;
+  const bool is_q = head < nh, is_v = head >= nh + g;
+  T* dst;
+  if (is_q) {
+    dst = q_out + ((size_t)t * nh + head) * hs;
+  } else {
+    if (k_pool == nullptr) return;               // a layer that reads another layer's cache stores nothing
+    const int page_idx = pos / page_size;
+    const int page = (page_idx < table_width) ? block_table[(size_t)req * table_width + page_idx] : -1;
     if (page < 0 || page >= num_pages) {
       if (threadIdx.x == 0 && bad_page) atomicExch(bad_page, 1);
-      page = -1;
+      return;
     }
+    const int kvh = is_v ? head - nh - g : head - nh;
+    dst = (is_v ? v_pool : k_pool) + (((size_t)page * g + kvh) * page_size + (pos - page_idx * page_size)) * hs;
   }
-  const int off = pos - page_idx * page_size;
-  // Q heads then K heads: (nh + g) * half rotation pairs.
-  const int n_pairs = (nh + g) * half;
-  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
-    const int head = p / half, i = p - head * half;
-    T* src = row + (size_t)head * hs;  // K heads follow the Q heads in the fused row
-    float x1 = to_f32<T>(src[i]), x2 = to_f32<T>(src[i + half]);
+  const TS* row = src + (size_t)t * src_stride + (size_t)head * hs;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float x1 = 0.f, x2 = 0.f;
+    for (int s = 0; s < n_parts; ++s) {
+      x1 += to_f32<TS>(row[s * part_stride + i]);
+      x2 += to_f32<TS>(row[s * part_stride + i + half]);
+    }
     float o1 = x1, o2 = x2;
-    if (inv_freq) {
-      const float c = cs[i], s = cs[half + i];
-      o1 = x1 * c - x2 * s;
-      o2 = x2 * c + x1 * s;
+    if (!is_v && inv_freq) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[i], &sn, &cs);
+      o1 = x1 * cs - x2 * sn;
+      o2 = x2 * cs + x1 * sn;
     }
-    if (head < nh) {
-      src[i] = from_f32<T>(o1);
-      src[i + half] = from_f32<T>(o2);
-    } else if (page >= 0) {
-      const int kvh = head - nh;
-      T* dst = k_pool + (((size_t)page * g + kvh) * page_size + off) * hs;
-      dst[i] = from_f32<T>(o1);
-      dst[i + half] = from_f32<T>(o2);
-    }
-  }
-  if (page >= 0) {
-    const T* vsrc = row + (size_t)(nh + g) * hs;
-    for (int p = threadIdx.x; p < g * hs; p += blockDim.x) {
-      const int kvh = p / hs, d = p - kvh * hs;
-      v_pool[(((size_t)page * g + kvh) * page_size + off) * hs + d] = vsrc[p];
-    }
+    dst[i] = from_f32<T>(o1);
+    dst[i + half] = from_f32<T>(o2);
   }
 }
 
-YALIS_API int yalis_rope_kv_write(void* qkv, int dtype, int qkv_stride, const int32_t* positions,
-                                  const int32_t* req_of_token, const float* inv_freq, void* k_pool, void* v_pool,
-                                  const int32_t* block_table, int table_width, int page_size, int num_pages, int nh,
-                                  int g, int hs, int n_tokens, int32_t* bad_page, cudaStream_t stream) {
+// src_dtype: the model type (n_parts must be 1) or YALIS_F32 partial sums [n_parts, N, src_stride].
+YALIS_API int yalis_rope_kv_write(const void* src, int src_dtype, int src_stride, int n_parts, long long part_stride,
+                                  void* q_out, int dtype, const int32_t* positions, const int32_t* req_of_token,
+                                  const float* inv_freq, void* k_pool, void* v_pool, const int32_t* block_table,
+                                  int table_width, int page_size, int num_pages, int nh, int g, int hs, int n_tokens,
+                                  int32_t* bad_page, cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
-  if (hs <= 0 || (hs & 1)) return YALIS_ERR_SHAPE;
-  const size_t smem = (size_t)hs * sizeof(float);
-  if (smem > 48 * 1024) return YALIS_ERR_SHAPE;
-  YALIS_DISPATCH_DTYPE(dtype, T,
-                       rope_kv_write_kernel<T><<<n_tokens, 256, smem, stream>>>(
-                           (T*)qkv, qkv_stride, positions, req_of_token, inv_freq, (T*)k_pool, (T*)v_pool, block_table,
-                           table_width, page_size, num_pages, nh, g, hs, bad_page));
+  if (hs <= 0 || (hs & 1) || n_parts < 1) return YALIS_ERR_SHAPE;
+  if (nh + 2 * g > 65535) return YALIS_ERR_SHAPE;
+  dim3 grid(n_tokens, nh + 2 * g);
+  const int threads = (hs / 2 + 31) / 32 * 32;
+  YALIS_DISPATCH_DTYPE(
+      dtype, T,
+      if (src_dtype == dtype && n_parts == 1) {
+        rope_kv_write_kernel<T, T><<<grid, threads, 0, stream>>>(
+            (const T*)src, src_stride, 1, 0, (T*)q_out, positions, req_of_token, inv_freq, (T*)k_pool, (T*)v_pool,
+            block_table, table_width, page_size, num_pages, nh, g, hs, bad_page);
+      } else if (src_dtype == YALIS_F32) {
+        rope_kv_write_kernel<T, float><<<grid, threads, 0, stream>>>(
+            (const float*)src, src_stride, n_parts, (size_t)part_stride, (T*)q_out, positions, req_of_token, inv_freq,
+            (T*)k_pool, (T*)v_pool, block_table, table_width, page_size, num_pages, nh, g, hs, bad_page);
+      } else { return YALIS_ERR_DTYPE; });
   return yalis_launch_status();
 }
 

@@ -80,16 +80,24 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, req_of_token: torch.Tensor,
                   inv_freq: Optional[torch.Tensor], k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
                   block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
-                  bad_flag: Optional[torch.Tensor] = None) -> None:
-    """Rotate Q (in place in ``qkv``) and K, and store K, V into their pages.
+                  out_dtype: Optional[torch.dtype] = None, bad_flag: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rotate Q and K of the fused qkv rows, store K and V into their pages, return Q.
 
-    qkv [N, (nh + 2g) * hs]; pools [num_pages, g, page_size, hs]; block_table int32 [R, width].
+    ``qkv`` is [N, (nh + 2g) * hs] in the model dtype, or float32 partial sums
+    [S, N, (nh + 2g) * hs] of a split product (summed in order).  Pools are
+    [num_pages, g, page_size, hs]; block_table int32 [R, width].  Returns the rotated
+    Q [N, nh * hs] in ``out_dtype`` (default: qkv's dtype).
     """
     name = "rope_kv_write"
     need_cuda(name, qkv, positions, req_of_token, inv_freq, k_pool, v_pool, block_table, bad_flag)
-    n = qkv.shape[0]
-    need(qkv.dim() == 2 and qkv.is_contiguous() and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim, name,
-         "qkv must be contiguous [N, (heads + 2*kv_heads) * head_dim]")
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    need(qkv.is_contiguous() and qkv.shape[-1] == width and qkv.dim() in (2, 3), name,
+         "qkv must be contiguous [N, (heads + 2*kv_heads) * head_dim] or [S, N, ...]")
+    parts = qkv.shape[0] if qkv.dim() == 3 else 1
+    n = qkv.shape[-2]
+    need(qkv.dim() == 2 or qkv.dtype == torch.float32, name, "split partial sums must be float32")
+    out_dtype = out_dtype or qkv.dtype
+    need(qkv.dim() == 3 or qkv.dtype == out_dtype, name, "an unsplit qkv must have the output dtype")
     need(head_dim % 2 == 0, name, f"head_dim {head_dim} must be even")
     for t in (positions, req_of_token):
         need(t.dtype == torch.int32 and t.shape == (n,) and t.is_contiguous(), name, "positions/req_of_token: int32 [N]")
@@ -98,20 +106,21 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, req_of_token: torc
              "inv_freq must be float32 [head_dim / 2]")
     need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(), name,
          "block_table must be contiguous int32 [R, width]")
-    page_size = num_pages = 0
+    page_size, num_pages = 1, 0
     if k_pool is not None:
-        need(v_pool is not None and k_pool.shape == v_pool.shape and k_pool.dtype == qkv.dtype == v_pool.dtype, name,
-             "pools must match each other and qkv in dtype")
+        need(v_pool is not None and k_pool.shape == v_pool.shape and k_pool.dtype == out_dtype == v_pool.dtype, name,
+             "pools must match each other and the output dtype")
         need(k_pool.dim() == 4 and k_pool.shape[1] == num_kv_heads and k_pool.shape[3] == head_dim
              and k_pool.is_contiguous() and v_pool.is_contiguous(), name,
              "pools must be contiguous [pages, kv_heads, page_size, head_dim]")
         num_pages, page_size = k_pool.shape[0], k_pool.shape[2]
-    else:
-        page_size = 1
-    check(lib().yalis_rope_kv_write(ptr(qkv), i32(dtype_code(qkv.dtype)), i32(qkv.shape[1]), ptr(positions),
-                                    ptr(req_of_token), ptr(inv_freq), ptr(k_pool), ptr(v_pool), ptr(block_table),
+    q_out = torch.empty((n, num_heads * head_dim), dtype=out_dtype, device=qkv.device)
+    check(lib().yalis_rope_kv_write(ptr(qkv), i32(dtype_code(qkv.dtype)), i32(width), i32(parts), i64(n * width),
+                                    ptr(q_out), i32(dtype_code(out_dtype)), ptr(positions), ptr(req_of_token),
+                                    ptr(inv_freq), ptr(k_pool), ptr(v_pool), ptr(block_table),
                                     i32(block_table.shape[1]), i32(page_size), i32(num_pages), i32(num_heads),
                                     i32(num_kv_heads), i32(head_dim), i32(n), ptr(bad_flag), stream()), name)
+    return q_out
 
 
 def silu_mul(x: torch.Tensor, interleaved: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:

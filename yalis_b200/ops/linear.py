@@ -17,7 +17,12 @@ from typing import Optional
 
 import torch
 
+import os
+
 from ._lib import check, dtype_code, i32, i64, lib, need, need_cuda, ptr, stream
+
+# YALIS_B200_NO_WSTREAM=1 sends every bfloat16 product to the library (for comparisons).
+USE_WSTREAM = os.environ.get("YALIS_B200_NO_WSTREAM", "0") != "1"
 
 
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
@@ -41,13 +46,74 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype]
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """The projection used by the parts: picks the kernel by dtype (see module docstring)."""
+    """The projection used by the parts: picks the kernel by dtype and size (see module docstring)."""
     need_cuda("linear", x, w)
     out_dtype = out_dtype or x.dtype
     if x.dtype == torch.float32:
         return gemm_simt(x, w, out_dtype)
     need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear", "operands must both be bfloat16 or float32")
+    if USE_WSTREAM and wstream_supports(x, w):
+        return gemm_wstream(x, w, out_dtype=out_dtype)
     if out_dtype == torch.bfloat16:
         return torch.matmul(x, w.t())
     need(out_dtype == torch.float32, "linear", f"unsupported output dtype {out_dtype}")
     return torch.mm(x, w.t(), out_dtype=torch.float32)
+
+
+def linear_partial(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """A projection whose consumer can add partial sums: returns [M, N] in x's dtype, or
+    float32 partial sums [S, M, N] when the weight-streaming kernel divides K among blocks."""
+    if x.dtype == torch.bfloat16 and USE_WSTREAM and wstream_supports(x, w) and wstream_splits(w.shape[0], w.shape[1]) > 1:
+        return gemm_wstream(x, w, split=True)
+    return linear(x, w)
+
+
+# ---- the tcgen05 weight-streaming product (csrc/gemm_tcgen05.cu) -------------------------------
+
+WSTREAM_MAX_TOKENS = 256
+_wstream_error = {}
+
+
+def wstream_error_flag(device) -> torch.Tensor:
+    """int32 [1] on the device; a kernel raises it if one of its bounded waits ran out."""
+    key = torch.device(device)
+    if key not in _wstream_error:
+        _wstream_error[key] = torch.zeros(1, dtype=torch.int32, device=key)
+    return _wstream_error[key]
+
+
+def wstream_splits(n: int, k: int) -> int:
+    return int(lib().yalis_gemm_wstream_splits(i32(n), i32(k)))
+
+
+def wstream_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """bfloat16, at most 256 tokens, K a multiple of 8 (16-byte rows for TMA), aligned bases."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
+            and 0 < x.shape[0] <= WSTREAM_MAX_TOKENS and x.shape[1] % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_wstream(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                 split: bool = False) -> torch.Tensor:
+    """x [M <= 256, K] . w [N, K]^T on tcgen05 tensor cores with TMA-streamed weights.
+
+    ``split=False``: returns [M, N] in ``out_dtype``.  ``split=True``: the K range may be
+    divided among blocks (decided by the shape); returns float32 partial sums [S, M, N]
+    that the consumer adds in order (S may be 1)."""
+    name = "gemm_wstream"
+    need_cuda(name, x, w)
+    need(wstream_supports(x, w), name, "needs bfloat16, at most 256 tokens, K % 8 == 0, 16-byte aligned rows")
+    need(x.shape[1] == w.shape[1], name, f"shapes {tuple(x.shape)} and {tuple(w.shape)} do not agree in K")
+    m, k = x.shape
+    n = w.shape[0]
+    splits = wstream_splits(n, k) if split else 1
+    if split:
+        out = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
+        code = dtype_code(torch.float32)
+    else:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        code = dtype_code(out_dtype)
+    check(lib().yalis_gemm_wstream(ptr(x), i64(x.stride(0)), ptr(w), i64(w.stride(0)), ptr(out), i32(code), i64(n),
+                                   i32(m), i32(n), i32(k), i32(splits), ptr(wstream_error_flag(x.device)), stream()),
+          name)
+    return out

@@ -17,7 +17,7 @@ import torch
 
 from yalis_b200.config.spec import PartSpec
 from yalis_b200.ops import attention as attn_ops
-from yalis_b200.ops.linear import linear
+from yalis_b200.ops.linear import linear_partial
 from .base import Mixer, PagedKV, PagedKVCache, ParamSpec, PositionEncoding, register_part
 
 
@@ -59,11 +59,11 @@ class PagedAttention(Mixer):
         return PagedKV(self.g, self.hs, self.window)
 
     def forward(self, x: torch.Tensor, ctx, cache: PagedKVCache) -> torch.Tensor:
-        qkv = linear(x, self.w_qkv)
-        self.position.encode_and_store(qkv, self.nh, self.g, self.hs, ctx, cache)
-        y = attn_ops.paged_attention(qkv, cache.k, cache.v, ctx, cache.group, self.nh, self.g, self.hs,
+        qkv = linear_partial(x, self.w_qkv)          # [N, width], or float32 partial sums [S, N, width]
+        q = self.position.encode_and_store(qkv, self.nh, self.g, self.hs, ctx, cache, dtype=x.dtype)
+        y = attn_ops.paged_attention(q, cache.k, cache.v, ctx, cache.group, self.nh, self.g, self.hs,
                                      scale=self.scale, window=self.window)
-        return linear(y, self.w_o)
+        return linear_partial(y, self.w_o)             # the residual stream adds the partial sums
 
 
 register_part("mixer", "paged_attention", PagedAttention)

@@ -4,9 +4,10 @@ Five categories, each with one small interface:
 
 ``norm``          ``forward(stream, rows=None) -> Tensor``: applies the pending
                   residual delta, returns the normed rows in the model dtype.
-``position``      ``encode_and_store(qkv, heads, kv_heads, head_dim, ctx, cache)``:
-                  encodes positions into Q and K of a fused qkv matrix and puts
-                  K, V into the layer's cache pages.
+``position``      ``encode_and_store(qkv, heads, kv_heads, head_dim, ctx, cache, dtype) -> q``:
+                  encodes positions into Q and K of a fused qkv matrix (given in
+                  the model dtype or as float32 partial sums [S, N, width]), puts
+                  K, V into the layer's cache pages and returns Q [N, heads*head_dim].
 ``mixer``         ``cache_request() -> PagedKV | SlotState | None`` and
                   ``forward(x, ctx, cache) -> Tensor [N, hidden]``.
 ``feed_forward``  ``forward(x, ctx) -> Tensor [N, hidden]``.
@@ -142,7 +143,7 @@ class Norm(Part):
 class PositionEncoding(Part):
     category = "position"
 
-    def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, ctx, cache: PagedKVCache) -> None:
+    def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, ctx, cache: PagedKVCache, dtype=None):
         raise NotImplementedError
 
 

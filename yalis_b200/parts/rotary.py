@@ -47,24 +47,25 @@ class RotaryEncoding(PositionEncoding):
     def to(self, device) -> None:
         self.inv_freq = self.inv_freq_host.to(device)
 
-    def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, ctx, cache: PagedKVCache) -> None:
+    def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, ctx, cache: PagedKVCache, dtype=None):
         if head_dim != self.head_dim:
             raise ValueError(f"rotary encoding built for head_dim {self.head_dim}, used with {head_dim}")
         if self.inv_freq is None or self.inv_freq.device != qkv.device:
             self.to(qkv.device)
         store = cache.writable
-        rope_kv_write(qkv, ctx.positions, ctx.req_of_token, self.inv_freq, cache.k if store else None,
-                      cache.v if store else None, ctx.block_tables[cache.group], num_heads, num_kv_heads, head_dim,
-                      bad_flag=ctx.error_flag)
+        return rope_kv_write(qkv, ctx.positions, ctx.req_of_token, self.inv_freq, cache.k if store else None,
+                             cache.v if store else None, ctx.block_tables[cache.group], num_heads, num_kv_heads,
+                             head_dim, out_dtype=dtype, bad_flag=ctx.error_flag)
 
 
 class NoPositionEncoding(PositionEncoding):
     """Stores K and V unrotated (a mixer that wants positions handled elsewhere)."""
 
-    def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, ctx, cache: PagedKVCache) -> None:
-        if cache.writable:
-            rope_kv_write(qkv, ctx.positions, ctx.req_of_token, None, cache.k, cache.v, ctx.block_tables[cache.group],
-                          num_heads, num_kv_heads, head_dim, bad_flag=ctx.error_flag)
+    def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, ctx, cache: PagedKVCache, dtype=None):
+        store = cache.writable
+        return rope_kv_write(qkv, ctx.positions, ctx.req_of_token, None, cache.k if store else None,
+                             cache.v if store else None, ctx.block_tables[cache.group], num_heads, num_kv_heads,
+                             head_dim, out_dtype=dtype, bad_flag=ctx.error_flag)
 
 
 register_part("position", "rotary", RotaryEncoding)

@@ -12,7 +12,7 @@ import torch
 
 from yalis_b200.config.spec import PartSpec
 from yalis_b200.ops.elementwise import silu_mul
-from yalis_b200.ops.linear import linear
+from yalis_b200.ops.linear import linear, linear_partial
 from .base import FeedForward, ParamSpec, register_part
 
 
@@ -38,7 +38,7 @@ class SwiGLU(FeedForward):
         self.w_down = tensors["down_proj"].contiguous()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        return linear(silu_mul(linear(x, self.w_gate_up)), self.w_down)
+        return linear_partial(silu_mul(linear(x, self.w_gate_up)), self.w_down)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
