@@ -27,6 +27,8 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, int q_st
                                                int page_size, int num_pages, int nh, int g, int hs, float scale,
                                                int window) {
   extern __shared__ float smem[];  // [kWarps][hs] accumulators, then m[kWarps], l[kWarps]
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const int req = req_of_token[t];
   if (req < 0) return;
@@ -116,8 +118,9 @@ YALIS_API int yalis_paged_attention_generic(const void* q, int q_stride, void* o
   const size_t smem = ((size_t)kWarps * hs + 2 * kWarps) * sizeof(float);
   dim3 grid(n_tokens, nh);
   YALIS_DISPATCH_DTYPE(dtype, T,
-                       paged_attention_generic_kernel<T><<<grid, kWarps * 32, smem, stream>>>(
-                           (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool, (const T*)v_pool, positions,
-                           req_of_token, block_table, table_width, page_size, num_pages, nh, g, hs, scale, window));
-  return yalis_launch_status();
+                       return yalis_launch(paged_attention_generic_kernel<T>, grid, dim3(kWarps * 32), smem, stream,
+                                           (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool,
+                                           (const T*)v_pool, positions, req_of_token, block_table, table_width,
+                                           page_size, num_pages, nh, g, hs, scale, window));
+  return YALIS_OK;
 }

@@ -21,7 +21,10 @@
 //
 // With n_splits > 1 (decode steps of few requests) the keys of a request are
 // divided among blocks; each writes an unnormalised partial result with its
-// running maximum and sum, and a second kernel merges the splits in index order.
+// running maximum and sum to scratch memory and takes a ticket from a counter of
+// its (request, KV head); the block that draws the last ticket merges all splits
+// in index order (so the result does not depend on which block came last) and
+// resets the counter for the next launch.
 #include "common.cuh"
 
 namespace {
@@ -41,12 +44,14 @@ struct AttnParams {
   const int32_t* q_start;      // [R+1]
   const int32_t* block_table;  // [R, table_width]
   int table_width, page_size, num_pages;
+  int page_shift;              // log2(page_size) if it is a power of two, else -1
   int nh, g, per;              // per = nh / g
   float scale_log2;            // scale * log2(e)
   int window;                  // 0: none
   int n_splits;
   float* part_o;               // [N, nh, n_splits, HS] (split mode)
   float* part_ml;              // [N, nh, n_splits, 2]
+  int32_t* tickets;            // [R * g] zero before the launch and zero again after it (split mode)
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -77,28 +82,44 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
-// Gathers keys [key0, key0 + BN) of one KV head into a [BN][HS + 8] tile; rows
-// outside [lo_key, hi_key] or on an unmapped page are zero-filled.
+// Gathers keys [key0, key0 + BN) of one KV head into two [BN][HS + 8] tiles (K and V); rows
+// outside [lo_key, hi_key] or on an unmapped page are zero-filled.  Consecutive threads copy
+// consecutive 16-byte chunks of a row (coalesced); all page lookups of a thread are done
+// before its first copy is issued, so that they overlap.
 template <int HS>
-__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* dst, const __nv_bfloat16* pool, const int32_t* bt,
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst, const int32_t* bt,
                                              const AttnParams& p, int kvh, int key0, int lo_key, int hi_key) {
-  constexpr int CHUNKS = HS / 8;        // 16-byte chunks per row
+  constexpr int CHUNKS = HS / 8;                          // 16-byte chunks per row
   constexpr int LD = HS + 8;
-  for (int c = threadIdx.x; c < BN * CHUNKS; c += NWARPS * 32) {
+  constexpr int ITERS = BN * CHUNKS / (NWARPS * 32);      // chunks per thread (HS % 16 == 0 makes it whole)
+  static_assert(BN * CHUNKS % (NWARPS * 32) == 0, "tile chunks must divide among the threads");
+  long long src[ITERS];
+  const int head_stride = p.page_size * HS;               // elements of one (page, kv head) block
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) {
+    const int c = threadIdx.x + i * (NWARPS * 32);
     const int row = c / CHUNKS, ch = c - row * CHUNKS;
     const int key = key0 + row;
-    __nv_bfloat16* d = dst + row * LD + ch * 8;
-    int page = -1, off = 0;
+    src[i] = -1;
     if (key >= lo_key && key <= hi_key) {
-      const int pi = key / p.page_size;
-      off = key - pi * p.page_size;
-      page = pi < p.table_width ? bt[pi] : -1;
-      if (page >= p.num_pages) page = -1;
+      const int pi = p.page_shift >= 0 ? (key >> p.page_shift) : (key / p.page_size);
+      const int page = pi < p.table_width ? bt[pi] : -1;
+      if (page >= 0 && page < p.num_pages)
+        src[i] = (long long)(page * p.g + kvh) * head_stride + (key - pi * p.page_size) * HS + ch * 8;
     }
-    if (page >= 0) {
-      cp_async16(d, pool + (((size_t)page * p.g + kvh) * p.page_size + off) * HS + ch * 8);
+  }
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) {
+    const int c = threadIdx.x + i * (NWARPS * 32);
+    const int row = c / CHUNKS, ch = c - row * CHUNKS;
+    __nv_bfloat16* kd = k_dst + row * LD + ch * 8;
+    __nv_bfloat16* vd = v_dst + row * LD + ch * 8;
+    if (src[i] >= 0) {
+      cp_async16(kd, p.k_pool + src[i]);
+      cp_async16(vd, p.v_pool + src[i]);
     } else {
-      *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(kd) = make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(vd) = make_uint4(0u, 0u, 0u, 0u);
     }
   }
 }
@@ -112,10 +133,13 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
   constexpr int WKEYS = DEC ? BN / NWARPS : BN;   // keys of a tile that one warp handles
   constexpr int ST = WKEYS / 8;         // n8 tiles of S along this warp's keys
   constexpr int RB = DEC ? 16 : BM;     // rows per block
+  constexpr int NST = DEC ? 3 : 2;      // K/V tiles in flight: decode blocks are latency bound
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [BM][LD]
-  __nv_bfloat16* k_s = q_s + BM * LD;                                 // [2][BN][LD]
-  __nv_bfloat16* v_s = k_s + 2 * BN * LD;                             // [2][BN][LD]
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [RB][LD]
+  __nv_bfloat16* k_s = q_s + RB * LD;                                 // [NST][BN][LD]
+  __nv_bfloat16* v_s = k_s + NST * BN * LD;                           // [NST][BN][LD]
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int req = blockIdx.y / p.g, kvh = blockIdx.y - req * p.g;
   const int tok0 = p.q_start[req], q_len = p.q_start[req + 1] - tok0;
@@ -161,12 +185,14 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
       }
     }
   }
-  if (n_tiles > 0) {
-    load_kv_tile<HS>(k_s, p.k_pool, bt, p, kvh, tile_lo * BN, lo_key, hi_key);
-    load_kv_tile<HS>(v_s, p.v_pool, bt, p, kvh, tile_lo * BN, lo_key, hi_key);
+  // Prologue: Q and the first tile form one group, then NST-2 further tiles one group each.
+#pragma unroll
+  for (int t = 0; t < NST - 1; ++t) {
+    if (t < n_tiles)
+      load_kv_tile<HS>(k_s + t * BN * LD, v_s + t * BN * LD, bt, p, kvh, (tile_lo + t) * BN, lo_key, hi_key);
+    cp_async_commit();
   }
-  cp_async_commit();
-  cp_async_wait<0>();
+  cp_async_wait<NST - 2>();     // the group with Q and tile 0 has landed
   __syncthreads();
 
   unsigned qf[KSTEPS][4];
@@ -192,12 +218,12 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
   for (int it = 0; it < n_tiles; ++it) {
-    const int buf = it & 1;
+    const int buf = it % NST;
     const int key0 = (tile_lo + it) * BN;
-    // prefetch the next tile into the other buffer
-    if (it + 1 < n_tiles) {
-      load_kv_tile<HS>(k_s + (buf ^ 1) * BN * LD, p.k_pool, bt, p, kvh, key0 + BN, lo_key, hi_key);
-      load_kv_tile<HS>(v_s + (buf ^ 1) * BN * LD, p.v_pool, bt, p, kvh, key0 + BN, lo_key, hi_key);
+    // prefetch tile it + NST - 1 into the buffer that tile it - 1 has left
+    if (it + NST - 1 < n_tiles) {
+      const int nb = (it + NST - 1) % NST;
+      load_kv_tile<HS>(k_s + nb * BN * LD, v_s + nb * BN * LD, bt, p, kvh, key0 + (NST - 1) * BN, lo_key, hi_key);
     }
     cp_async_commit();
     const __nv_bfloat16* kt = k_s + buf * BN * LD;
@@ -221,16 +247,30 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
     }
     // ---- mask, online softmax (exp2 domain) -----------------------------------------
     float m_new[2] = {m_run[0], m_run[1]};
+    // A tile strictly inside every row's visible range needs no mask (the common case in decode).
+    const bool inner = key0 + BN - 1 <= pos_first && (p.window <= 0 || key0 > pos_last - p.window) &&
+                       row0 + RB <= n_rows;
+    if (inner) {
 #pragma unroll
-    for (int j = 0; j < ST; ++j) {
+      for (int j = 0; j < ST; ++j) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = e >> 1;
-        const int key = key0 + wkey + j * 8 + tig * 2 + (e & 1);
-        const bool vis = row_ok[i] && key <= row_pos[i] && (p.window <= 0 || key > row_pos[i] - p.window);
-        const float v = vis ? s[j][e] * p.scale_log2 : -INFINITY;
-        s[j][e] = v;
-        m_new[i] = fmaxf(m_new[i], v);
+        for (int e = 0; e < 4; ++e) {
+          s[j][e] *= p.scale_log2;
+          m_new[e >> 1] = fmaxf(m_new[e >> 1], s[j][e]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < ST; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1;
+          const int key = key0 + wkey + j * 8 + tig * 2 + (e & 1);
+          const bool vis = row_ok[i] && key <= row_pos[i] && (p.window <= 0 || key > row_pos[i] - p.window);
+          const float v = vis ? s[j][e] * p.scale_log2 : -INFINITY;
+          s[j][e] = v;
+          m_new[i] = fmaxf(m_new[i], v);
+        }
       }
     }
 #pragma unroll
@@ -275,7 +315,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
         mma_bf16(o[d + 1], pf[kk], vb[2], vb[3]);
       }
     }
-    cp_async_wait<0>();
+    cp_async_wait<NST - 2>();   // tile it + 1 has landed (later ones may still fly)
     __syncthreads();
   }
 
@@ -331,68 +371,60 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_mma_kernel(const 
         }
       }
     }
-    return;
-  }
+    if (p.n_splits > 1) {
+      // Ticket: the block that finds every other split already done merges them all.
+      __shared__ int s_last;
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) s_last = (atomicAdd(&p.tickets[blockIdx.y], 1) == p.n_splits - 1) ? 1 : 0;
+      __syncthreads();
+      if (s_last) {
+        __threadfence();
+        for (int e = threadIdx.x; e < rows_here * HS; e += NWARPS * 32) {
+          const int r = e / HS, d = e - r * HS;
+          const int row = row0 + r;
+          const int t = row / p.per, h = row - t * p.per;
+          const int tok = tok0 + t, head = kvh * p.per + h;
+          const size_t base = ((size_t)tok * p.nh + head) * p.n_splits;
+          const volatile float* ml = p.part_ml;
+          const volatile float* po = p.part_o;
+          float mm = -INFINITY;
+          for (int sp = 0; sp < p.n_splits; ++sp) mm = fmaxf(mm, ml[(base + sp) * 2]);
+          float ll = 0.f, acc = 0.f;
+          for (int sp = 0; sp < p.n_splits; ++sp) {
+            const float m = ml[(base + sp) * 2];
+            const float f = (m == -INFINITY) ? 0.f : exp2f(m - mm);
+            ll += ml[(base + sp) * 2 + 1] * f;
+            acc += po[(base + sp) * HS + d] * f;
+          }
+          p.out[(size_t)tok * p.out_stride + (size_t)head * HS + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+        }
+        if (threadIdx.x == 0) p.tickets[blockIdx.y] = 0;
+      }
+    }
+  } else {
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     if (!row_ok[i]) continue;
     const int row = row0 + wrow + gid + i * 8;
     const int t = row / p.per, h = row - t * p.per;
     const int tok = tok0 + t, head = kvh * p.per + h;
-    if (p.n_splits == 1) {
-      const float inv = l_run[i] > 0.f ? 1.0f / l_run[i] : 0.f;
-      __nv_bfloat16* dst = p.out + (size_t)tok * p.out_stride + (size_t)head * HS;
+    const float inv = l_run[i] > 0.f ? 1.0f / l_run[i] : 0.f;
+    __nv_bfloat16* dst = p.out + (size_t)tok * p.out_stride + (size_t)head * HS;
 #pragma unroll
-      for (int d = 0; d < DT; ++d) {
-        __nv_bfloat162 v = __floats2bfloat162_rn(o[d][i * 2] * inv, o[d][i * 2 + 1] * inv);
-        *reinterpret_cast<__nv_bfloat162*>(dst + d * 8 + tig * 2) = v;
-      }
-    } else {
-      const size_t slot = ((size_t)tok * p.nh + head) * p.n_splits + split;
-      float* dst = p.part_o + slot * HS;
-#pragma unroll
-      for (int d = 0; d < DT; ++d) {
-        *reinterpret_cast<float2*>(dst + d * 8 + tig * 2) = make_float2(o[d][i * 2], o[d][i * 2 + 1]);
-      }
-      if (tig == 0) {
-        p.part_ml[slot * 2] = m_run[i];
-        p.part_ml[slot * 2 + 1] = l_run[i];
-      }
+    for (int d = 0; d < DT; ++d) {
+      __nv_bfloat162 v = __floats2bfloat162_rn(o[d][i * 2] * inv, o[d][i * 2 + 1] * inv);
+      *reinterpret_cast<__nv_bfloat162*>(dst + d * 8 + tig * 2) = v;
     }
   }
-}
-
-// Merges split partial results in split order: out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
-// Every (row, split) slot of a live request is written by the attention kernel, a split without
-// keys writes m = -inf and l = 0; rows of padding tokens are skipped here as they are there.
-__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         __nv_bfloat16* __restrict__ out, int out_stride, int nh, int hs,
-                                         int n_splits, const int32_t* __restrict__ req_of_token) {
-  const int tok = blockIdx.x, head = blockIdx.y;
-  if (req_of_token && req_of_token[tok] < 0) return;
-  const size_t base = ((size_t)tok * nh + head) * n_splits;
-  float mm = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
-  float ll = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float m = part_ml[(base + s) * 2];
-    if (m != -INFINITY) ll += part_ml[(base + s) * 2 + 1] * exp2f(m - mm);
-  }
-  const float inv = ll > 0.f ? 1.0f / ll : 0.f;
-  for (int d = threadIdx.x; d < hs; d += blockDim.x) {
-    float acc = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float m = part_ml[(base + s) * 2];
-      if (m != -INFINITY) acc += part_o[(base + s) * hs + d] * exp2f(m - mm);
-    }
-    out[(size_t)tok * out_stride + (size_t)head * hs + d] = __float2bfloat16_rn(acc * inv);
   }
 }
 
 template <int HS, bool DEC>
 int launch_mode(const AttnParams& p, int n_requests, int max_rows, cudaStream_t stream) {
   constexpr int LD = HS + 8;
-  const size_t smem = (size_t)(BM + 4 * BN) * LD * sizeof(__nv_bfloat16);
+  constexpr int RB = DEC ? 16 : BM, NST = DEC ? 3 : 2;
+  const size_t smem = (size_t)(RB + 2 * NST * BN) * LD * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(paged_attention_mma_kernel<HS, DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -400,11 +432,9 @@ int launch_mode(const AttnParams& p, int n_requests, int max_rows, cudaStream_t 
       return YALIS_ERR_LAUNCH;
     configured = true;
   }
-  const int rows_per_block = DEC ? 16 : BM;
-  dim3 grid((max_rows + rows_per_block - 1) / rows_per_block, n_requests * p.g, p.n_splits);
+  dim3 grid((max_rows + RB - 1) / RB, n_requests * p.g, p.n_splits);
   if (grid.y > 65535 || grid.z > 65535) return YALIS_ERR_SHAPE;
-  paged_attention_mma_kernel<HS, DEC><<<grid, NWARPS * 32, smem, stream>>>(p);
-  return yalis_launch_status();
+  return yalis_launch(paged_attention_mma_kernel<HS, DEC>, grid, dim3(NWARPS * 32), smem, stream, p);
 }
 
 template <int HS>
@@ -425,7 +455,8 @@ YALIS_API int yalis_attention_mma_supports(int hs) {
   }
 }
 
-// Scratch floats needed for n_splits > 1: part_o then part_ml.
+// Scratch floats needed for n_splits > 1: part_o then part_ml.  Besides, `tickets` needs
+// n_requests * g int32 that are zero before the first launch (each launch leaves them zero).
 YALIS_API long long yalis_attention_mma_scratch_floats(int n_tokens, int nh, int hs, int n_splits) {
   return n_splits > 1 ? (long long)n_tokens * nh * n_splits * (hs + 2) : 0;
 }
@@ -435,7 +466,7 @@ YALIS_API int yalis_paged_attention_mma(const void* q, int q_stride, void* out, 
                                         const int32_t* req_of_token, const int32_t* block_table, int table_width,
                                         int page_size, int num_pages, int n_tokens, int n_requests, int max_q_len,
                                         int nh, int g, int hs, float scale, int window, int n_splits, float* scratch,
-                                        cudaStream_t stream) {
+                                        int32_t* tickets, cudaStream_t stream) {
   if (n_tokens <= 0 || n_requests <= 0) return YALIS_OK;
   if (g <= 0 || nh % g != 0 || n_splits < 1 || max_q_len < 1) return YALIS_ERR_SHAPE;
   if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) return YALIS_ERR_ALIGN;
@@ -446,12 +477,15 @@ YALIS_API int yalis_paged_attention_mma(const void* q, int q_stride, void* out, 
   p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;
   p.positions = positions; p.q_start = q_start; p.block_table = block_table;
   p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages;
+  p.page_shift = -1;
+  for (int sh = 0; sh < 31; ++sh)
+    if ((1 << sh) == page_size) p.page_shift = sh;
   p.nh = nh; p.g = g; p.per = nh / g;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window; p.n_splits = n_splits;
-  p.part_o = nullptr; p.part_ml = nullptr;
+  p.part_o = nullptr; p.part_ml = nullptr; p.tickets = tickets;
   if (n_splits > 1) {
-    if (scratch == nullptr) return YALIS_ERR_SHAPE;
+    if (scratch == nullptr || tickets == nullptr || max_q_len * p.per > 16) return YALIS_ERR_SHAPE;
     p.part_o = scratch;
     p.part_ml = scratch + (size_t)n_tokens * nh * n_splits * hs;
   }
@@ -472,9 +506,5 @@ YALIS_API int yalis_paged_attention_mma(const void* q, int q_stride, void* out, 
     case 256: st = launch<256>(p, n_requests, max_rows, stream); break;
     default: return YALIS_ERR_SHAPE;
   }
-  if (st != YALIS_OK || n_splits == 1) return st;
-  dim3 grid(n_tokens, nh);
-  attention_combine_kernel<<<grid, 128, 0, stream>>>(p.part_o, p.part_ml, p.out, out_stride, nh, hs, n_splits,
-                                                     req_of_token);
-  return yalis_launch_status();
+  return st;
 }

@@ -23,6 +23,36 @@ inline int yalis_launch_status() {
   return cudaGetLastError() == cudaSuccess ? YALIS_OK : YALIS_ERR_LAUNCH;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------
+// Every kernel of the library is launched with the "programmatic stream serialization"
+// attribute: the next kernel in the stream may be scheduled while this one still runs, do
+// work that does not depend on it (set-up, prefetch of weights) and then block in
+// pdl_wait() until this one has completed and its writes are visible.  Rules kept by every
+// kernel here: (1) pdl_launch_dependents() and pdl_wait() are executed by every thread
+// before any early return and before the first read of an activation or write of an output,
+// so completion of a kernel implies completion of all kernels before it; (2) only constant
+// inputs (weights) are touched before pdl_wait().
+bool yalis_pdl_enabled();   // defined in elementwise.cu; switched by yalis_set_pdl()
+
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline int yalis_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                        Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = yalis_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...) == cudaSuccess ? YALIS_OK : YALIS_ERR_LAUNCH;
+}
+
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
 template <>

@@ -4,6 +4,13 @@
 // stores are in the storage type T (float or bfloat16).
 #include "common.cuh"
 
+namespace {
+bool g_pdl_enabled = true;
+}
+bool yalis_pdl_enabled() { return g_pdl_enabled; }
+// Switches programmatic dependent launch for every kernel of the library (on by default).
+YALIS_API void yalis_set_pdl(int enabled) { g_pdl_enabled = enabled != 0; }
+
 // --------------------------------------------------------------------------
 // Embedding: out[t, :] = float(table[ids[t], :])      (yalis/external/model.py:137)
 // The residual stream is float32 whatever the weight type.
@@ -12,6 +19,8 @@
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids,
                                  float* __restrict__ out, int width, int vocab, int32_t* bad_id) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * width;
@@ -28,9 +37,9 @@ YALIS_API int yalis_embedding(const void* table, int dtype, const int32_t* ids, 
                               int width, int vocab, int32_t* bad_id, cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
   YALIS_DISPATCH_DTYPE(dtype, T,
-                       embedding_kernel<T><<<n_tokens, 256, 0, stream>>>((const T*)table, ids, out, width, vocab,
-                                                                         bad_id));
-  return yalis_launch_status();
+                       return yalis_launch(embedding_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)table,
+                                           ids, out, width, vocab, bad_id));
+  return YALIS_OK;
 }
 
 // --------------------------------------------------------------------------
@@ -51,6 +60,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
                                    size_t delta_stride, const float* __restrict__ w, T* __restrict__ y,
                                    const int32_t* __restrict__ rows, int width, float eps, int write_back) {
   __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x;
   const int r = rows ? rows[i] : i;
   if (r < 0) return;  // padded row
@@ -111,14 +122,14 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
 }
 
 template <typename T, typename TD>
-void launch_add_rmsnorm(float* x, const void* delta, int n_delta, size_t delta_stride, const float* w, void* y,
+int launch_add_rmsnorm(float* x, const void* delta, int n_delta, size_t delta_stride, const float* w, void* y,
                         const int32_t* rows, int n_out_rows, int width, float eps, int write_back,
                         cudaStream_t stream) {
   const int threads = width >= 4096 ? 1024 : width >= 1024 ? 512 : 256;
   const int per_thread = (width + threads - 1) / threads;
-#define YALIS_NORM_LAUNCH(V)                                                                                   \
-  add_rmsnorm_kernel<T, TD, V><<<n_out_rows, threads, 0, stream>>>(x, (const TD*)delta, n_delta, delta_stride, w, \
-                                                                    (T*)y, rows, width, eps, write_back)
+#define YALIS_NORM_LAUNCH(V)                                                                                  \
+  return yalis_launch(add_rmsnorm_kernel<T, TD, V>, dim3(n_out_rows), dim3(threads), 0, stream, x, (const TD*)delta, \
+                      n_delta, delta_stride, w, (T*)y, rows, width, eps, write_back)
   if (per_thread <= 4) YALIS_NORM_LAUNCH(4);
   else if (per_thread <= 8) YALIS_NORM_LAUNCH(8);
   else if (per_thread <= 16) YALIS_NORM_LAUNCH(16);
@@ -134,13 +145,13 @@ YALIS_API int yalis_add_rmsnorm(float* x, const void* delta, int delta_dtype, in
   YALIS_DISPATCH_DTYPE(
       out_dtype, T,
       if (delta_dtype == YALIS_F32) {
-        launch_add_rmsnorm<T, float>(x, delta, n_delta, (size_t)delta_stride, w, y, rows, n_out_rows, width, eps,
-                                     write_back, stream);
+        return launch_add_rmsnorm<T, float>(x, delta, n_delta, (size_t)delta_stride, w, y, rows, n_out_rows, width,
+                                            eps, write_back, stream);
       } else if (delta_dtype == YALIS_BF16) {
-        launch_add_rmsnorm<T, __nv_bfloat16>(x, delta, n_delta, (size_t)delta_stride, w, y, rows, n_out_rows, width,
-                                             eps, write_back, stream);
+        return launch_add_rmsnorm<T, __nv_bfloat16>(x, delta, n_delta, (size_t)delta_stride, w, y, rows, n_out_rows,
+                                                    width, eps, write_back, stream);
       } else { return YALIS_ERR_DTYPE; });
-  return yalis_launch_status();
+  return YALIS_OK;
 }
 
 // Plain residual add without a norm: x[r] += sum_s delta[s][r]. Used to flush a
@@ -148,6 +159,8 @@ YALIS_API int yalis_add_rmsnorm(float* x, const void* delta, int delta_dtype, in
 template <typename TD>
 __global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_delta,
                                     size_t delta_stride, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float h = x[i];
@@ -161,14 +174,12 @@ YALIS_API int yalis_residual_add(float* x, const void* delta, int delta_dtype, i
   const int threads = 256;
   const unsigned blocks = (unsigned)((n + threads - 1) / threads);
   if (delta_dtype == YALIS_F32)
-    residual_add_kernel<float><<<blocks, threads, 0, stream>>>(x, (const float*)delta, n_delta, (size_t)delta_stride,
-                                                              (size_t)n);
-  else if (delta_dtype == YALIS_BF16)
-    residual_add_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(x, (const __nv_bfloat16*)delta, n_delta,
-                                                                      (size_t)delta_stride, (size_t)n);
-  else
-    return YALIS_ERR_DTYPE;
-  return yalis_launch_status();
+    return yalis_launch(residual_add_kernel<float>, dim3(blocks), dim3(threads), 0, stream, x, (const float*)delta,
+                        n_delta, (size_t)delta_stride, (size_t)n);
+  if (delta_dtype == YALIS_BF16)
+    return yalis_launch(residual_add_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, x,
+                        (const __nv_bfloat16*)delta, n_delta, (size_t)delta_stride, (size_t)n);
+  return YALIS_ERR_DTYPE;
 }
 
 // --------------------------------------------------------------------------
@@ -196,6 +207,8 @@ __global__ void rope_kv_write_kernel(const TS* __restrict__ src, int src_stride,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool,
                                      const int32_t* __restrict__ block_table, int table_width, int page_size,
                                      int num_pages, int nh, int g, int hs, int32_t* bad_page) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x, head = blockIdx.y;   // head: [0, nh) Q, [nh, nh+g) K, [nh+g, nh+2g) V
   const int req = req_of_token[t];
   if (req < 0) return;
@@ -249,15 +262,16 @@ YALIS_API int yalis_rope_kv_write(const void* src, int src_dtype, int src_stride
   YALIS_DISPATCH_DTYPE(
       dtype, T,
       if (src_dtype == dtype && n_parts == 1) {
-        rope_kv_write_kernel<T, T><<<grid, threads, 0, stream>>>(
-            (const T*)src, src_stride, 1, 0, (T*)q_out, positions, req_of_token, inv_freq, (T*)k_pool, (T*)v_pool,
-            block_table, table_width, page_size, num_pages, nh, g, hs, bad_page);
+        return yalis_launch(rope_kv_write_kernel<T, T>, grid, dim3(threads), 0, stream, (const T*)src, src_stride, 1,
+                            (size_t)0, (T*)q_out, positions, req_of_token, inv_freq, (T*)k_pool, (T*)v_pool,
+                            block_table, table_width, page_size, num_pages, nh, g, hs, bad_page);
       } else if (src_dtype == YALIS_F32) {
-        rope_kv_write_kernel<T, float><<<grid, threads, 0, stream>>>(
-            (const float*)src, src_stride, n_parts, (size_t)part_stride, (T*)q_out, positions, req_of_token, inv_freq,
-            (T*)k_pool, (T*)v_pool, block_table, table_width, page_size, num_pages, nh, g, hs, bad_page);
+        return yalis_launch(rope_kv_write_kernel<T, float>, grid, dim3(threads), 0, stream, (const float*)src,
+                            src_stride, n_parts, (size_t)part_stride, (T*)q_out, positions, req_of_token, inv_freq,
+                            (T*)k_pool, (T*)v_pool, block_table, table_width, page_size, num_pages, nh, g, hs,
+                            bad_page);
       } else { return YALIS_ERR_DTYPE; });
-  return yalis_launch_status();
+  return YALIS_OK;
 }
 
 // --------------------------------------------------------------------------
@@ -270,6 +284,8 @@ YALIS_API int yalis_rope_kv_write(const void* src, int src_dtype, int src_stride
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int interleaved,
                                 size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / inter;
@@ -288,14 +304,16 @@ YALIS_API int yalis_silu_mul(const void* in, void* out, int dtype, int n_tokens,
   const int threads = 256;
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
   YALIS_DISPATCH_DTYPE(dtype, T,
-                       silu_mul_kernel<T><<<blocks, threads, 0, stream>>>((const T*)in, (T*)out, inter, interleaved,
-                                                                          total));
-  return yalis_launch_status();
+                       return yalis_launch(silu_mul_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (const T*)in,
+                                           (T*)out, inter, interleaved, total));
+  return YALIS_OK;
 }
 
 // Gather rows of a float32 matrix: out[i, :] = x[rows[i], :].
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
                                    float* __restrict__ out, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = rows[blockIdx.x];
   if (r < 0) return;
   for (int c = threadIdx.x; c < width; c += blockDim.x) out[(size_t)blockIdx.x * width + c] = x[(size_t)r * width + c];
@@ -304,6 +322,5 @@ __global__ void gather_rows_kernel(const float* __restrict__ x, const int32_t* _
 YALIS_API int yalis_gather_rows_f32(const float* x, const int32_t* rows, float* out, int n_rows, int width,
                                     cudaStream_t stream) {
   if (n_rows <= 0) return YALIS_OK;
-  gather_rows_kernel<<<n_rows, 256, 0, stream>>>(x, rows, out, width);
-  return yalis_launch_status();
+  return yalis_launch(gather_rows_kernel, dim3(n_rows), dim3(256), 0, stream, x, rows, out, width);
 }

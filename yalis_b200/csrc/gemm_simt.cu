@@ -23,6 +23,8 @@ gemm_tn_simt_kernel(const TA* __restrict__ A, long long lda, const TW* __restric
                     TO* __restrict__ O, long long ldo, int M, int N, int K) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -74,8 +76,8 @@ int launch(const void* A, long long lda, const void* W, long long ldw, void* O, 
            cudaStream_t stream) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return YALIS_ERR_SHAPE;
-  gemm_tn_simt_kernel<TA, TW, TO><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, (TO*)O, ldo, M, N, K);
-  return yalis_launch_status();
+  return yalis_launch(gemm_tn_simt_kernel<TA, TW, TO>, grid, dim3(256), 0, stream, (const TA*)A, lda, (const TW*)W, ldw,
+                      (TO*)O, ldo, M, N, K);
 }
 
 }  // namespace

@@ -34,6 +34,7 @@ constexpr int TILE_K = 64;       // bfloat16 elements per stage along K: one 128
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;    // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
 constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kSMs = 148;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -110,17 +111,20 @@ struct GemmParams {
   int32_t* error;       // set to 1 if a wait ran out
 };
 
-template <int NTOK>
+// Ring depth. A stage is 16 KB of W plus NTOK * 128 bytes of x.  DEEP: one block per SM with a
+// ring of ~190 KB, for grids that fit the GPU in one wave of single blocks; otherwise two blocks
+// per SM with ~95 KB each, so that grids between one and two blocks per SM run as one wave.
+template <int NTOK, bool DEEP>
 __host__ __device__ constexpr int stages_for() {
-  // stage = 16 KB of W + NTOK * 128 bytes of x; keep the ring under ~200 KB
-  return NTOK <= 16 ? 10 : NTOK <= 32 ? 9 : NTOK <= 64 ? 8 : NTOK <= 128 ? 6 : 4;
+  return DEEP ? (NTOK <= 16 ? 10 : NTOK <= 32 ? 9 : NTOK <= 64 ? 8 : NTOK <= 128 ? 6 : 4)
+              : (NTOK <= 32 ? 5 : NTOK <= 64 ? 4 : NTOK <= 128 ? 3 : 4);
 }
 
-template <int NTOK>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int NTOK, bool DEEP>
+__global__ void __launch_bounds__(kThreads, (DEEP || NTOK > 128) ? 1 : 2)
 gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const GemmParams p) {
-  constexpr int STAGES = stages_for<NTOK>();
+  constexpr int STAGES = stages_for<NTOK, DEEP>();
   constexpr int A_BYTES = TILE_N * TILE_K * 2;
   constexpr int B_BYTES = NTOK * TILE_K * 2;
   constexpr int TMEM_COLS = NTOK < 32 ? 32 : NTOK;
@@ -143,6 +147,7 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const int kt_end = min(kt_total, kt_begin + p.kt_per_split);
   const int n_kt = max(0, kt_end - kt_begin);
 
+  pdl_launch_dependents();      // the next kernel may be scheduled and do its own set-up
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -165,7 +170,18 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   int armed = 0;   // producer: stages armed so far (for the drain on abort)
   if (warp == 0) {
     if (lane == 0) {
-      for (int kt = 0; kt < n_kt; ++kt) {
+      // Weights do not depend on the kernel before this one: fill the ring with W tiles at once,
+      // and only then wait for that kernel before the first read of x.
+      const int n_pre = min(n_kt, STAGES);
+      for (int kt = 0; kt < n_pre; ++kt) {
+        mbar_expect_tx(&full[kt], A_BYTES + B_BYTES);
+        tma_load_2d(a_s + kt * A_BYTES, &map_w, (kt_begin + kt) * TILE_K, n0, &full[kt]);
+      }
+      armed = n_pre;
+      pdl_wait();
+      for (int kt = 0; kt < n_pre; ++kt)
+        tma_load_2d(b_s + kt * B_BYTES, &map_x, (kt_begin + kt) * TILE_K, 0, &full[kt]);
+      for (int kt = n_pre; kt < n_kt; ++kt) {
         const int s = kt % STAGES;
         const uint32_t ph = (kt / STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
@@ -176,8 +192,10 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         armed = kt + 1;
       }
     }
+    else pdl_wait();
     __syncwarp();
   } else if (warp == 1) {
+    pdl_wait();
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(NTOK);
       int kt = 0;
@@ -200,6 +218,7 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncwarp();
   } else {
     // Epilogue: warp w may touch the 32 tensor-memory lanes of its quarter (w % 4).
+    pdl_wait();
     const int q = warp & 3;
     int ok = 1;
     if (n_kt > 0 && lane == 0) ok = mbar_wait(acc_full, 0, abort_flag) ? 1 : 0;
@@ -291,31 +310,54 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, lo
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int NTOK>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t stream) {
-  constexpr int STAGES = stages_for<NTOK>();
+template <int NTOK, bool DEEP>
+int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t stream) {
+  constexpr int STAGES = stages_for<NTOK, DEEP>();
   const size_t smem = 1024 + (size_t)STAGES * (TILE_N * TILE_K * 2 + NTOK * TILE_K * 2) + (2 * STAGES + 1) * 8 + 16;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_wstream_kernel<NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_wstream_kernel<NTOK, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
       return YALIS_ERR_LAUNCH;
     configured = true;
   }
   dim3 grid((p.N + TILE_N - 1) / TILE_N, p.splits);
-  gemm_wstream_kernel<NTOK><<<grid, kThreads, smem, stream>>>(mw, mx, p);
-  return yalis_launch_status();
+  return yalis_launch(gemm_wstream_kernel<NTOK, DEEP>, grid, dim3(kThreads), smem, stream, mw, mx, p);
+}
+
+template <int NTOK>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t stream) {
+  const int blocks = ((p.N + TILE_N - 1) / TILE_N) * p.splits;
+  return blocks <= kSMs ? launch_cfg<NTOK, true>(mw, mx, p, stream) : launch_cfg<NTOK, false>(mw, mx, p, stream);
 }
 
 }  // namespace
 
 // How many K splits the launcher would use for this shape (so callers can size `out`).
+// Chosen so that the grid fills the GPU without a mostly empty last wave: grids of up to two
+// blocks per SM run as one wave; every split costs a little (a partial output to write and add).
 YALIS_API int yalis_gemm_wstream_splits(int N, int K) {
   const int tiles = (N + TILE_N - 1) / TILE_N;
   const int kt = (K + TILE_K - 1) / TILE_K;
-  int splits = 1;
-  while (tiles * splits < 120 && splits < 16 && kt / (splits + 1) >= 8) ++splits;
-  return splits;
+  int best = 1;
+  double best_cost = 1e30;
+  for (int s = 1; s <= 16; ++s) {
+    if (s > 1 && kt / s < 8) break;
+    const int blocks = tiles * s;
+    double cost;
+    if (blocks <= 2 * kSMs) {
+      cost = blocks >= kSMs ? 1.0 : (double)kSMs / blocks;
+    } else {
+      const int waves = (blocks + 2 * kSMs - 1) / (2 * kSMs);
+      cost = (double)waves * 2 * kSMs / blocks;
+    }
+    cost += 0.03 * s;
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
 }
 
 // out = x[M, K] . w[N, K]^T, bfloat16 operands.  splits must be yalis_gemm_wstream_splits(N, K) or 1;

@@ -88,6 +88,8 @@ __device__ ArgMax block_argmax(ArgMax a, ArgMax* scratch) {
 __global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restrict__ logits, long long row_stride,
                                                           int vocab, int32_t* __restrict__ out) {
   __shared__ ArgMax scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const float* row = logits + (size_t)blockIdx.x * row_stride;
   ArgMax a;
   a.v = 0.f;
@@ -116,6 +118,8 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
   __shared__ unsigned long long sh_above;
   __shared__ int sh_remaining;
   __shared__ int sh_done;
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
@@ -280,8 +284,7 @@ YALIS_API int yalis_argmax(const float* logits, long long row_stride, int n_rows
                            cudaStream_t stream) {
   if (n_rows <= 0) return YALIS_OK;
   if (vocab <= 0) return YALIS_ERR_SHAPE;
-  argmax_kernel<<<n_rows, kThreads, 0, stream>>>(logits, row_stride, vocab, out);
-  return yalis_launch_status();
+  return yalis_launch(argmax_kernel, dim3(n_rows), dim3(kThreads), 0, stream, logits, row_stride, vocab, out);
 }
 
 YALIS_API int yalis_sample(const float* logits, long long row_stride, int n_rows, int vocab, const float* temperature,
@@ -289,7 +292,6 @@ YALIS_API int yalis_sample(const float* logits, long long row_stride, int n_rows
                            const unsigned long long* draw_index, int32_t* out, cudaStream_t stream) {
   if (n_rows <= 0) return YALIS_OK;
   if (vocab <= 0) return YALIS_ERR_SHAPE;
-  sample_kernel<<<n_rows, kThreads, 0, stream>>>(logits, row_stride, vocab, temperature, top_k, top_p, seed,
-                                                 draw_index, out);
-  return yalis_launch_status();
+  return yalis_launch(sample_kernel, dim3(n_rows), dim3(kThreads), 0, stream, logits, row_stride, vocab, temperature,
+                      top_k, top_p, seed, draw_index, out);
 }

@@ -125,7 +125,8 @@ def _compile_all(compiler: List[str], sources: List[str], flags: List[str], out_
     objects = []
     for src in sources:
         path = os.path.join(_CSRC, src)
-        key = _digest([path] + headers, compiler + flags)
+        # the include path differs between checkouts of the same sources: keep it out of the key
+        key = _digest([path] + headers, [os.path.basename(compiler[0])] + [f for f in flags if f != _CSRC])
         obj = os.path.join(out_dir, f"{tag}_{os.path.basename(src)}.{key}.o")
         objects.append(obj)
         if not os.path.exists(obj):
@@ -157,6 +158,19 @@ def _link(linker: List[str], objects: List[str], out: str) -> None:
     os.replace(tmp, out)
 
 
+def _sweep(out_dir: str, prefix: str, lib_prefix: str, keep: List[str]) -> None:
+    """Remove objects and libraries of older source versions (best effort)."""
+    keep_names = {os.path.basename(k) for k in keep}
+    try:
+        for name in os.listdir(out_dir):
+            stale_obj = name.startswith(prefix + "_") and name.endswith(".o")
+            stale_lib = name.startswith(lib_prefix + ".") and name.endswith(".so")
+            if (stale_obj or stale_lib) and name not in keep_names:
+                os.remove(os.path.join(out_dir, name))
+    except OSError:
+        pass
+
+
 def _build(kind: str) -> str:
     out_dir = build_dir()
     if kind == "host":
@@ -166,6 +180,7 @@ def _build(kind: str) -> str:
         lib = os.path.join(out_dir, f"libyalis_host.{key}.so")
         if not os.path.exists(lib):
             _link([cxx, "-shared"], objs, lib)
+            _sweep(out_dir, "host", "libyalis_host", objs + [lib])
         return lib
     nvcc = _find("nvcc", "NVCC", "/usr/local/cuda/bin/nvcc")
     flags = CUDA_ARCH_FLAGS + NVCC_FLAGS + ["-I", _CSRC]
@@ -174,7 +189,8 @@ def _build(kind: str) -> str:
     lib = os.path.join(out_dir, f"libyalis_cuda.{key}.so")
     if not os.path.exists(lib):
         _log("linking libyalis_cuda ...")
-        _link([nvcc, "-shared"] + CUDA_ARCH_FLAGS + ["-lcuda"], objs, lib)
+        _link([nvcc, "-shared"] + CUDA_ARCH_FLAGS, objs, lib)
+        _sweep(out_dir, "cuda", "libyalis_cuda", objs + [lib])
     return lib
 
 

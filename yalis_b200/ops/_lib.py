@@ -10,6 +10,7 @@ import of a wrapper's first call fails with ``NativeBuildError``.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -31,8 +32,17 @@ class KernelError(RuntimeError):
     pass
 
 
+_configured = False
+
+
 def lib() -> ctypes.CDLL:
-    return native.load("cuda")
+    global _configured
+    handle = native.load("cuda")
+    if not _configured:
+        _configured = True
+        # Kernels are chained with programmatic dependent launch; YALIS_B200_NO_PDL=1 turns it off.
+        handle.yalis_set_pdl(ctypes.c_int(0 if os.environ.get("YALIS_B200_NO_PDL", "0") == "1" else 1))
+    return handle
 
 
 def dtype_code(dt: torch.dtype) -> int:

@@ -67,7 +67,20 @@ def decode_splits(n_requests: int, num_kv_heads: int) -> int:
     few requests still fill the GPU.  Depends on the batch shape only, never on lengths,
     so a captured step can be replayed."""
     blocks = max(1, n_requests * num_kv_heads)
-    return max(1, min(16, -(-2 * SM_COUNT // blocks)))
+    return max(1, min(32, -(-4 * SM_COUNT // blocks)))
+
+
+_ticket_cache = {}
+
+
+def _tickets(device, n: int) -> torch.Tensor:
+    """Zeroed int32 counters, one per (request, KV head): every split launch leaves them zero,
+    so one buffer per device is allocated once (outside any graph capture) and shared."""
+    key = torch.device(device)
+    t = _ticket_cache.get(key)
+    if t is None or t.numel() < n:
+        t = _ticket_cache[key] = torch.zeros(max(n, 4096), dtype=torch.int32, device=key)
+    return t
 
 
 def paged_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, positions: torch.Tensor,
@@ -92,18 +105,19 @@ def paged_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Ten
     need(out.shape == (n, num_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous(), name, "bad out tensor")
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
-    scratch = None
+    scratch = tickets = None
     if n_splits > 1:
         need(max_q_len * (num_heads // num_kv_heads) <= 16, name, "splitting the keys is for decode steps only")
         floats = lib().yalis_attention_mma_scratch_floats
         floats.restype = ctypes.c_longlong
         scratch = torch.empty(int(floats(i32(n), i32(num_heads), i32(head_dim), i32(n_splits))), dtype=torch.float32,
                               device=q.device)
+        tickets = _tickets(q.device, r * num_kv_heads)
     check(lib().yalis_paged_attention_mma(
         ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(k_pool), ptr(v_pool), ptr(positions), ptr(q_start),
         ptr(req_of_token), ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]), i32(k_pool.shape[0]),
         i32(n), i32(r), i32(max_q_len), i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), i32(window or 0),
-        i32(n_splits), ptr(scratch), stream()), name)
+        i32(n_splits), ptr(scratch), ptr(tickets), stream()), name)
     return out
 
 

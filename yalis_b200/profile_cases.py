@@ -1,0 +1,101 @@
+"""Small, self-contained workloads of single kernels, for timing and for profiler captures.
+
+    python -m yalis_b200.profile_cases attention_decode --batch 64 --ctx 1040 --launches 8
+    python -m yalis_b200.profile_cases gemm_wstream --tokens 8 --n 28672 --k 4096 --launches 8
+
+Each case allocates inputs larger than the L2 cache but at most a few GB, launches the
+kernel a few times, and prints the mean time per launch measured with CUDA events.
+"""
+
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+
+def _time(fn, launches: int) -> float:
+    fn()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(launches):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / launches * 1e3
+
+
+def attention_decode(args) -> None:
+    from yalis_b200.ops.attention import decode_splits, paged_attention_mma
+    dev = "cuda:0"
+    nh, g, hs, page, b, ctx = args.heads, args.kv_heads, args.head_dim, args.page_size, args.batch, args.ctx
+    pages_per = -(-ctx // page)
+    num_pages = b * pages_per
+    layers = max(2, min(8, int(400e6 // max(1, num_pages * g * page * hs * 4)) + 1))    # rotate pools: > L2 in total
+    pools = [(torch.randn(num_pages, g, page, hs, device=dev).to(torch.bfloat16),
+              torch.randn(num_pages, g, page, hs, device=dev).to(torch.bfloat16)) for _ in range(layers)]
+    table = torch.randperm(num_pages, device=dev).to(torch.int32).view(b, pages_per).contiguous()
+    q = torch.randn(b, nh * hs, device=dev).to(torch.bfloat16)
+    pos = torch.full((b,), ctx - 1, dtype=torch.int32, device=dev)
+    q_start = torch.arange(b + 1, dtype=torch.int32, device=dev)
+    req = torch.arange(b, dtype=torch.int32, device=dev)
+    splits = args.splits or decode_splits(b, g)
+    state = {"i": 0}
+
+    def fn():
+        k, v = pools[state["i"] % layers]
+        state["i"] += 1
+        paged_attention_mma(q, k, v, pos, q_start, req, table, 1, nh, g, hs, n_splits=splits)
+
+    us = _time(fn, args.launches)
+    kv_bytes = b * ctx * 2 * g * hs * 2
+    print(f"attention_decode batch {b} ctx {ctx} splits {splits}: {us:.1f} us per launch, "
+          f"{kv_bytes / us / 1e6:.2f} TB/s of K/V")
+
+
+def gemm_wstream(args) -> None:
+    from yalis_b200.ops.linear import gemm_wstream as gemm, wstream_splits
+    dev = "cuda:0"
+    m, n, k = args.tokens, args.n, args.k
+    copies = max(2, min(8, int(400e6 // (n * k * 2)) + 1))
+    ws = [(torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+    state = {"i": 0}
+
+    def fn():
+        w = ws[state["i"] % copies]
+        state["i"] += 1
+        gemm(x, w, split=args.split)
+
+    us = _time(fn, args.launches)
+    print(f"gemm_wstream tokens {m} n {n} k {k} splits {wstream_splits(n, k) if args.split else 1}: "
+          f"{us:.1f} us per launch, {n * k * 2 / us / 1e6:.2f} TB/s of weights")
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="case", required=True)
+    a = sub.add_parser("attention_decode")
+    a.add_argument("--batch", type=int, default=64)
+    a.add_argument("--ctx", type=int, default=1040)
+    a.add_argument("--heads", type=int, default=32)
+    a.add_argument("--kv-heads", type=int, default=8)
+    a.add_argument("--head-dim", type=int, default=128)
+    a.add_argument("--page-size", type=int, default=16)
+    a.add_argument("--splits", type=int, default=0)
+    a.add_argument("--launches", type=int, default=8)
+    a.set_defaults(fn=attention_decode)
+    gm = sub.add_parser("gemm_wstream")
+    gm.add_argument("--tokens", type=int, default=8)
+    gm.add_argument("--n", type=int, default=28672)
+    gm.add_argument("--k", type=int, default=4096)
+    gm.add_argument("--split", action="store_true")
+    gm.add_argument("--launches", type=int, default=8)
+    gm.set_defaults(fn=gemm_wstream)
+    args = ap.parse_args()
+    args.fn(args)
+
+
+if __name__ == "__main__":
+    main()
