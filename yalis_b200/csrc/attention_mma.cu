@@ -508,3 +508,70 @@ YALIS_API int yalis_paged_attention_mma(const void* q, int q_stride, void* out, 
   }
   return st;
 }
+
+// ---------------------------------------------------------------------------------------
+// The same kernel with its temporary memory in a fixed array of the library, for callers that
+// must not allocate (see attention_noalloc.h for who they are and for the rules).
+// ---------------------------------------------------------------------------------------
+#include "attention_noalloc.h"
+
+namespace {
+
+// Counters first (must be zero when a launch starts), then the partial results.  The name is
+// usable as an address in device code only; host code has to ask the runtime for its address.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[YALIS_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_noalloc_ptr[kMaxDevices] = {nullptr};   // device address of the array, per device
+
+// Device address of the array on the current device; looked up on the first call there.
+int noalloc_scratch(unsigned char** ptr) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return YALIS_ERR_LAUNCH;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return YALIS_ERR_LAUNCH;
+    g_noalloc_ptr[dev] = p;
+  }
+  *ptr = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
+  return YALIS_OK;
+}
+
+}  // namespace
+
+YALIS_API long long yalis_paged_attention_mma_noalloc_needed(int n_tokens, int n_requests, int nh, int g, int hs,
+                                                             int n_splits, long long* ticket_bytes,
+                                                             long long* partial_bytes) {
+  const long long t = n_splits > 1 ? (long long)n_requests * g * (long long)sizeof(int32_t) : 0;
+  const long long f = yalis_attention_mma_scratch_floats(n_tokens, nh, hs, n_splits) * (long long)sizeof(float);
+  if (ticket_bytes) *ticket_bytes = t;
+  if (partial_bytes) *partial_bytes = f;
+  return t + f;
+}
+
+YALIS_API int yalis_paged_attention_mma_noalloc(const void* q, int q_stride, void* out, int out_stride,
+                                                const void* k_pool, const void* v_pool, const int32_t* positions,
+                                                const int32_t* q_start, const int32_t* req_of_token,
+                                                const int32_t* block_table, int table_width, int page_size,
+                                                int num_pages, int n_tokens, int n_requests, int max_q_len, int nh,
+                                                int g, int hs, float scale, int window, int n_splits,
+                                                cudaStream_t stream) {
+  if (n_tokens <= 0 || n_requests <= 0) return YALIS_OK;
+  if (n_splits < 1 || g <= 0) return YALIS_ERR_SHAPE;
+  long long ticket_bytes = 0, partial_bytes = 0;
+  yalis_paged_attention_mma_noalloc_needed(n_tokens, n_requests, nh, g, hs, n_splits, &ticket_bytes, &partial_bytes);
+  if (ticket_bytes > YALIS_NOALLOC_TICKET_BYTES || partial_bytes > YALIS_NOALLOC_PARTIAL_BYTES)
+    return YALIS_ERR_SCRATCH;                       // refused: nothing was launched
+  unsigned char* base = nullptr;
+  if (int st = noalloc_scratch(&base)) return st;
+  int32_t* tickets = reinterpret_cast<int32_t*>(base);
+  float* partials = reinterpret_cast<float*>(base + YALIS_NOALLOC_TICKET_BYTES);
+  if (n_splits > 1) {
+    // The array keeps what the last call left: the counters have to start at zero.
+    if (cudaMemsetAsync(tickets, 0, (size_t)ticket_bytes, stream) != cudaSuccess) return YALIS_ERR_LAUNCH;
+  }
+  return yalis_paged_attention_mma(q, q_stride, out, out_stride, k_pool, v_pool, positions, q_start, req_of_token,
+                                   block_table, table_width, page_size, num_pages, n_tokens, n_requests, max_q_len, nh,
+                                   g, hs, scale, window, n_splits, n_splits > 1 ? partials : nullptr,
+                                   n_splits > 1 ? tickets : nullptr, stream);
+}
