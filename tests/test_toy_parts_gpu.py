@@ -82,6 +82,9 @@ class ToyArchitecture:
         for i, kind in enumerate(c["mixers"]):
             if kind == "attention":
                 mixer, names = attn, dict(attn_names, **common)
+            elif kind == "window_attention":
+                mixer = PartSpec("paged_attention", dict(attn.params, window=c["window"]))
+                names = dict(attn_names, **common)
             else:
                 mixer, names = PartSpec("running_mean", {"hidden_size": h}), dict({"mixer.mix": "mean.mix.weight"}, **common)
             layers.append(LayerSpec(PartSpec("pre_norm_residual"), mixer, ffn, norm, norm, rot, f"toy.{i}.", names))
@@ -95,9 +98,9 @@ def setup_module(module):
     registry.register_architecture("ToyForCausalLM", ToyArchitecture, replace=True)
 
 
-def toy_config(mixers, schedule):
-    return dict(architectures=["ToyForCausalLM"], width=40, heads=4, kv_heads=2, head_dim=8, inner=56, vocab=97, max_len=160,
-                eps=1e-5, mixers=mixers, schedule=schedule, torch_dtype="bfloat16")
+def toy_config(mixers, schedule, window=None, head_dim=8):
+    return dict(architectures=["ToyForCausalLM"], width=40, heads=4, kv_heads=2, head_dim=head_dim, inner=56, vocab=97,
+                max_len=160, eps=1e-5, mixers=mixers, schedule=schedule, window=window, torch_dtype="bfloat16")
 
 
 def plain_toy(tokens, w, c):
@@ -111,7 +114,8 @@ def plain_toy(tokens, w, c):
     for idx, (layer, cache_of) in enumerate(c["schedule"]):
         p = f"toy.{layer}."
         h = plain.rms_norm(x, w[p + "n1.weight"], c["eps"])
-        if c["mixers"][layer] == "attention":
+        if c["mixers"][layer] in ("attention", "window_attention"):
+            window = c["window"] if c["mixers"][layer] == "window_attention" else None
             nh, g, hs = c["heads"], c["kv_heads"], c["head_dim"]
             cos, sin = plain.rope_tables(pos, plain.rope_inverse_frequencies(hs, 10000.0, None))
             q = plain.apply_rope((h @ w[p + "attn.q.weight"].T).view(t, nh, hs), cos, sin)
@@ -121,7 +125,7 @@ def plain_toy(tokens, w, c):
                 kept[idx] = (k, v)
             else:
                 k, v = kept[cache_of]
-            y = plain.causal_attention(q, k, v, pos, pos).reshape(t, nh * hs) @ w[p + "attn.o.weight"].T
+            y = plain.causal_attention(q, k, v, pos, pos, window=window).reshape(t, nh * hs) @ w[p + "attn.o.weight"].T
         else:
             means = torch.cumsum(h, dim=0) / torch.arange(1, t + 1)[:, None]
             y = means @ w[p + "mean.mix.weight"].T
@@ -157,6 +161,47 @@ def test_toy_model_steps_like_a_builtin(dtype, mixers, schedule):
                 r = rep.run_step(s)
                 if r is not None:
                     out[s["step"]] = r
+            got = traces.collect(steps, out, c["vocab"])
+            tol = 1e-4 if dtype == "float32" else 3e-2
+            for rid in want:
+                err = np.abs(got[rid] - want[rid]).max() / np.abs(want[rid]).max()
+                assert err < tol, (build.__name__, rid, err)
+            rep.engine.manager.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_window_layers_have_pages_of_their_own(dtype):
+    """A toy model with one layer over all keys and one over a window of 20: two page groups;
+    the window group gives pages back while a request grows, and the logits match the plain
+    model at every position (a wrong edge of the window would show at once)."""
+    from yalis_b200.engine.replay import Replayer
+    from yalis_b200.weights.loader import write_random_model
+    c = toy_config(["window_attention", "attention"], [(0, None), (1, None)], window=20, head_dim=16)
+    std = 0.2 if dtype == "float32" else 0.05
+    with tempfile.TemporaryDirectory() as d:
+        write_random_model(c, d, seed=5, std=std)
+        w = plain.read_weights(d)
+        g = torch.Generator().manual_seed(2)
+        requests = {f"r{i}": torch.randint(0, c["vocab"], (n,), generator=g).tolist() for i, n in enumerate([150, 33, 97])}
+        want = {rid: plain_toy(t, w, c).numpy() for rid, t in requests.items()}
+        for build in (traces.whole, traces.tail_decoded, traces.portions, traces.mixed):
+            steps = traces.number(build(requests))
+            rep = Replayer(d, dtype, traces.peak_tokens(steps), page_size=8, max_live=4)
+            names = sorted(g.name for g in rep.engine.groups)
+            assert names == ["kv_all", "kv_window_20"]
+            out, low_water = {}, None
+            for s in steps:
+                r = rep.run_step(s)
+                if r is not None:
+                    out[s["step"]] = r
+                if build is traces.tail_decoded and any(e["id"] == "r0" for e in s["entries"]) and rep.engine.has_request("r0"):
+                    slot = rep.engine.slot_of("r0")
+                    lo, hi = rep.engine.manager.held_range("kv_window_20", slot)
+                    held_all = rep.engine.manager.held_range("kv_all", slot)
+                    assert (hi - lo) * 8 <= 20 + 2 * 8 and held_all[0] == 0        # the window group lets go, the other keeps all
+                    low_water = lo
+            if build is traces.tail_decoded:
+                assert low_water and low_water > 10
             got = traces.collect(steps, out, c["vocab"])
             tol = 1e-4 if dtype == "float32" else 3e-2
             for rid in want:
