@@ -420,3 +420,50 @@ def test_gemm_wstream_tcgen05(m, n, k):
     one = gemm_wstream(x[m - 1:].contiguous(), w, out_dtype=torch.float32)
     assert torch.equal(one[0], out32[m - 1])                               # the same bits alone and in the batch
     assert int(wstream_error_flag(DEV)) == 0
+
+
+@pytest.mark.parametrize("nh, g, hs, page", [(32, 8, 128, 16), (8, 2, 64, 8), (4, 4, 64, 32), (16, 1, 128, 64), (6, 2, 192, 16),
+                                             (2, 1, 256, 16), (5, 5, 128, 16)])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_decode_attention_tma_against_plain_and_generic(nh, g, hs, page, splits):
+    """The TMA-fed decode kernel: lengths around tile and page edges, pools poisoned with NaN
+    where nothing was written, against the plain float32 attention and the exact kernel."""
+    from yalis_b200.ops.attention import decode_attention_tma, paged_attention_generic
+    dtype = torch.bfloat16
+    lens = [1, 15, 16, 17, 63, 64, 65, 130, 517, 1200]
+    ks, vs, k_pool, v_pool, table = paged_setup(len(lens), lens, g, hs, page, dtype, seed=hs + nh + page)
+    gen = torch.Generator().manual_seed(3)
+    q = torch.randn(len(lens), nh, hs, generator=gen).to(dtype)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    positions, q_start, req = i32([l - 1 for l in lens]), i32(list(range(len(lens) + 1))), i32(list(range(len(lens))))
+    qd = q.view(-1, nh * hs).to(DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = decode_attention_tma(qd, k_pool, v_pool, positions, q_start, table, nh, g, hs, n_splits=splits, error_flag=flag)
+    assert int(flag) == 0 and not torch.isnan(out.float()).any()
+    ref_gen = paged_attention_generic(qd, k_pool, v_pool, positions, req, table, nh, g, hs)
+    torch.testing.assert_close(out.float(), ref_gen.float(), rtol=2e-2, atol=2e-2)
+    for r, l in enumerate(lens):
+        ref = plain.causal_attention(q[r:r + 1].float(), ks[r].to(dtype).float(), vs[r].to(dtype).float(),
+                                     torch.tensor([l - 1]), torch.arange(l))
+        torch.testing.assert_close(out[r].float().cpu().view(1, nh, hs), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_decode_attention_tma_far_key_and_padding_requests():
+    """A far key with nearly all the weight at page and tile edges; requests without tokens
+    (padding of a captured batch) are left alone."""
+    from yalis_b200.ops.attention import decode_attention_tma
+    nh, g, hs, page, l = 8, 2, 128, 16, 2000
+    ks, vs, k_pool, v_pool, table = paged_setup(1, [l], g, hs, page, torch.bfloat16, seed=11)
+    table = torch.cat([table, torch.full_like(table, -1), torch.full_like(table, -1)])
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    for target in (0, 15, 16, 63, 64, 1023, l - 1):
+        q = torch.cat([ks[0][target, h // (nh // g)] * 4.0 for h in range(nh)]).view(1, nh * hs)
+        qq = torch.cat([q, torch.zeros(2, nh * hs)]).to(torch.bfloat16).to(DEV)
+        out = torch.full((3, nh * hs), 7.0, dtype=torch.bfloat16, device=DEV)
+        flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+        decode_attention_tma(qq, k_pool, v_pool, i32([l - 1, 0, 0]), i32([0, 1, 1, 1]), table, nh, g, hs, n_splits=6,
+                             error_flag=flag, out=out)
+        got = out[0].float().cpu().view(nh, hs)
+        for h in range(nh):
+            assert torch.allclose(got[h], vs[0][target, h // (nh // g)].to(torch.bfloat16).float(), atol=6e-2), (target, h)
+        assert torch.all(out[1:] == 7.0) and int(flag) == 0

@@ -1,0 +1,485 @@
+// Decode attention with TMA-fed key/value tiles: one query token per request, the keys of a
+// (request, KV head) divided among `n_splits` blocks.
+//
+// It computes what paged_attention_mma_kernel<HS, true> computes (attention_mma.cu) and merges
+// splits the same way (tickets, last block merges in split order); what differs is how K and V
+// reach shared memory.  There every thread computes page addresses and issues 16-byte
+// cp.async copies, which made the kernel instruction-bound.  Here one producer thread walks the
+// block table and issues one TMA box copy per (page, 64-column half) for K and for V
+// (cp.async.bulk.tensor.2d over the pool seen as a matrix [pages*kv_heads*page_size, head_dim],
+// 128-byte swizzle), completion is counted by an mbarrier per stage, and the four consumer
+// warps only wait, run ldmatrix on the swizzled tiles and mma.sync.  The ring has three stages.
+//
+// Limits (the launcher refuses anything else, the caller then uses the cp.async kernel):
+// bfloat16, head_dim a multiple of 64 up to 256, page_size 8, 16, 32 or 64, no window, at most
+// 16 query heads per KV head, one token per request.
+//
+// Keys beyond the query's position share the last page with visible ones and may hold anything:
+// their scores are masked by index and their V rows are zeroed in shared memory before use.
+// Every mbarrier wait is bounded; on a timeout the block raises the error word, drains its
+// outstanding copies and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BN = 64;            // keys per tile
+constexpr int CWARPS = 4;         // consumer warps; warp CWARPS is the producer
+constexpr int kThreads = (CWARPS + 1) * 32;
+constexpr int STAGES = 3;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+struct DecParams {
+  const __nv_bfloat16* q;      // [N, q_stride]
+  int q_stride;
+  __nv_bfloat16* out;          // [N, out_stride]
+  int out_stride;
+  const int32_t* positions;    // [N]
+  const int32_t* q_start;      // [R+1]
+  const int32_t* block_table;  // [R, table_width]
+  int table_width, page_size, num_pages;
+  int nh, g, per;
+  float scale_log2;
+  int n_splits;
+  float* part_o;               // [N, nh, n_splits, HS]
+  float* part_ml;              // [N, nh, n_splits, 2]
+  int32_t* tickets;            // [R * g]
+  int32_t* error;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], uint32_t saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], uint32_t saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CWARPS * 32) : "memory"); }
+
+// Byte offset of element (row, dim) inside a swizzled tile [HS/64 halves][BN rows][128 bytes].
+__device__ __forceinline__ uint32_t tile_off(int row, int dim) {
+  const int half = dim >> 6, chunk = (dim & 63) >> 3;
+  return (uint32_t)(half * (BN * 128) + row * 128 + (((chunk ^ (row & 7)) << 4)));
+}
+
+template <int HS>
+__global__ void __launch_bounds__(kThreads)
+decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const DecParams p) {
+  constexpr int H2 = HS / 64;                  // 64-column halves of a row
+  constexpr int TILE_BYTES = BN * HS * 2;      // one K (or V) tile
+  constexpr int LDQ = HS + 8;                  // padded Q rows
+  constexpr int KSTEPS = HS / 16, DT = HS / 8;
+  constexpr int WKEYS = BN / CWARPS;           // 16 keys of a tile per consumer warp
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* k_s = base;                                 // [STAGES][TILE_BYTES]
+  unsigned char* v_s = base + STAGES * TILE_BYTES;           // [STAGES][TILE_BYTES]
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(v_s + STAGES * TILE_BYTES);   // [16][LDQ]
+  uint64_t* full = reinterpret_cast<uint64_t*>(q_s + 16 * LDQ);
+  uint64_t* empty = full + STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + STAGES);
+  int* s_last = const_cast<int*>(abort_flag) + 1;
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int req = blockIdx.x / p.g, kvh = blockIdx.x - req * p.g;
+  const int split = blockIdx.y;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], CWARPS);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  pdl_wait();
+  __syncthreads();
+
+  const int tok = p.q_start[req];
+  const int n_tok = p.q_start[req + 1] - tok;
+  if (n_tok <= 0) return;                      // padding request (uniform for the block)
+  const int pos = p.positions[tok];
+  const int hi_key = pos;
+  const int total = hi_key / BN + 1;
+  const int per_split = (total + p.n_splits - 1) / p.n_splits;
+  const int tile_lo = split * per_split;
+  const int tile_hi = min(total, tile_lo + per_split);
+  const int n_tiles = max(0, tile_hi - tile_lo);
+  const int32_t* bt = p.block_table + (size_t)req * p.table_width;
+
+  int armed = 0;
+  if (warp == CWARPS) {
+    // ---- producer -------------------------------------------------------------------------
+    if (lane == 0) {
+      const int pages_per_tile = BN / p.page_size;
+      const uint32_t page_bytes = (uint32_t)p.page_size * HS * 2;
+      for (int it = 0; it < n_tiles; ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
+        const int key0 = (tile_lo + it) * BN;
+        const int n_pages = min(pages_per_tile, (hi_key - key0) / p.page_size + 1);
+        mbar_expect_tx(&full[s], 2u * page_bytes * (uint32_t)n_pages);
+        for (int i = 0; i < n_pages; ++i) {
+          const int pi = key0 / p.page_size + i;
+          int page = pi < p.table_width ? bt[pi] : -1;
+          if (page < 0 || page >= p.num_pages) {   // a visible key without a page: a caller's bug
+            if (p.error) atomicExch(p.error, 1);
+            page = 0;
+          }
+          const int y = (page * p.g + kvh) * p.page_size;
+#pragma unroll
+          for (int h = 0; h < H2; ++h) {
+            const int off = h * (BN * 128) + i * p.page_size * 128;
+            tma_load_2d(k_s + s * TILE_BYTES + off, &map_k, h * 64, y, &full[s]);
+            tma_load_2d(v_s + s * TILE_BYTES + off, &map_v, h * 64, y, &full[s]);
+          }
+        }
+        armed = it + 1;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---- consumers ---------------------------------------------------------------------------
+    const int gid = lane >> 2, tig = lane & 3;
+    const int wkey = warp * WKEYS;
+    const int n_rows = p.per;                  // rows = query heads of this KV head
+    {
+      constexpr int CHUNKS = HS / 8;
+      for (int c = threadIdx.x; c < 16 * CHUNKS; c += CWARPS * 32) {
+        const int r = c / CHUNKS, ch = c - r * CHUNKS;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < n_rows)
+          v = *reinterpret_cast<const uint4*>(p.q + (size_t)tok * p.q_stride + (size_t)(kvh * p.per + r) * HS + ch * 8);
+        *reinterpret_cast<uint4*>(q_s + r * LDQ + ch * 8) = v;
+      }
+    }
+    consumer_sync();
+    unsigned qf[KSTEPS][4];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int c = ks * 16 + (lane >> 4) * 8;
+      ldmatrix_x4(qf[ks], smem_u32(q_s + r * LDQ + c));
+    }
+    float o[DT][4];
+#pragma unroll
+    for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const bool row_ok[2] = {gid < n_rows, gid + 8 < n_rows};
+
+    bool alive = true;
+    for (int it = 0; it < n_tiles && alive; ++it) {
+      const int s = it % STAGES;
+      const uint32_t ph = (it / STAGES) & 1;
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(&full[s], ph, abort_flag) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { alive = false; break; }
+      const int key0 = (tile_lo + it) * BN;
+      const uint32_t kt = smem_u32(k_s + s * TILE_BYTES), vt = smem_u32(v_s + s * TILE_BYTES);
+      const bool last = key0 + BN - 1 > hi_key;
+      if (last) {
+        // Zero this warp's V rows past the query's position (they may hold anything).
+        unsigned char* vrow = v_s + s * TILE_BYTES;
+        for (int e = lane; e < WKEYS * (HS / 8); e += 32) {
+          const int r = wkey + e / (HS / 8), c = e % (HS / 8);
+          if (key0 + r > hi_key) *reinterpret_cast<uint4*>(vrow + tile_off(r, c * 8)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        __syncwarp();
+      }
+      // S = Q K^T for this warp's 16 keys
+      float sc[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        unsigned kb[4];
+        const int key = wkey + (lane & 7) + (lane >> 4) * 8;
+        const int dim = ks * 16 + ((lane >> 3) & 1) * 8;
+        ldmatrix_x4(kb, kt + tile_off(key, dim));
+        mma_bf16(sc[0], qf[ks], kb[0], kb[1]);
+        mma_bf16(sc[1], qf[ks], kb[2], kb[3]);
+      }
+      float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1;
+          const int key = key0 + wkey + j * 8 + tig * 2 + (e & 1);
+          const float v = (row_ok[i] && (!last || key <= hi_key)) ? sc[j][e] * p.scale_log2 : -INFINITY;
+          sc[j][e] = v;
+          m_new[i] = fmaxf(m_new[i], v);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
+        m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
+      }
+      float corr[2], bs[2], l_add[2] = {0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        bs[i] = (m_new[i] == -INFINITY) ? 0.f : m_new[i];
+        corr[i] = exp2f(m_run[i] - bs[i]);
+        m_run[i] = m_new[i];
+      }
+      unsigned pf[4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float p0 = exp2f(sc[j][0] - bs[0]), p1 = exp2f(sc[j][1] - bs[0]);
+        const float p2 = exp2f(sc[j][2] - bs[1]), p3 = exp2f(sc[j][3] - bs[1]);
+        l_add[0] += p0 + p1;
+        l_add[1] += p2 + p3;
+        pf[j * 2 + 0] = pack_bf16(p0, p1);
+        pf[j * 2 + 1] = pack_bf16(p2, p3);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * corr[i] + l_add[i];
+#pragma unroll
+      for (int d = 0; d < DT; ++d) {
+        o[d][0] *= corr[0]; o[d][1] *= corr[0];
+        o[d][2] *= corr[1]; o[d][3] *= corr[1];
+      }
+      // O += P V over the warp's 16 keys
+#pragma unroll
+      for (int d = 0; d < DT; d += 2) {
+        unsigned vb[4];
+        const int key = wkey + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int dim = d * 8 + (lane >> 4) * 8;
+        ldmatrix_x4_trans(vb, vt + tile_off(key, dim));
+        mma_bf16(o[d], pf, vb[0], vb[1]);
+        mma_bf16(o[d + 1], pf, vb[2], vb[3]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+
+    // ---- merge the four warps, write the split's partial or the result ---------------------
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+      l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    }
+    consumer_sync();                                        // all warps are done with the tiles
+    float* mo = reinterpret_cast<float*>(k_s);             // [CWARPS][16][HS]
+    float* mml = reinterpret_cast<float*>(v_s);            // [CWARPS][16][2]
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = gid + i * 8;
+#pragma unroll
+      for (int d = 0; d < DT; ++d)
+        *reinterpret_cast<float2*>(mo + ((size_t)warp * 16 + r) * HS + d * 8 + tig * 2) = make_float2(o[d][i * 2], o[d][i * 2 + 1]);
+      if (tig == 0) {
+        mml[(warp * 16 + r) * 2] = m_run[i];
+        mml[(warp * 16 + r) * 2 + 1] = l_run[i];
+      }
+    }
+    consumer_sync();
+    for (int e = threadIdx.x; e < n_rows * HS; e += CWARPS * 32) {
+      const int r = e / HS, d = e - r * HS;
+      float mm = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < CWARPS; ++w) mm = fmaxf(mm, mml[(w * 16 + r) * 2]);
+      float ll = 0.f, acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < CWARPS; ++w) {
+        const float m = mml[(w * 16 + r) * 2];
+        const float f = (m == -INFINITY) ? 0.f : exp2f(m - mm);
+        ll += mml[(w * 16 + r) * 2 + 1] * f;
+        acc += mo[((size_t)w * 16 + r) * HS + d] * f;
+      }
+      const int head = kvh * p.per + r;
+      if (p.n_splits == 1) {
+        p.out[(size_t)tok * p.out_stride + (size_t)head * HS + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+      } else {
+        const size_t slot = ((size_t)tok * p.nh + head) * p.n_splits + split;
+        p.part_o[slot * HS + d] = acc;
+        if (d == 0) {
+          p.part_ml[slot * 2] = mm;
+          p.part_ml[slot * 2 + 1] = ll;
+        }
+      }
+    }
+    if (p.n_splits > 1) {
+      __threadfence();
+      consumer_sync();
+      if (threadIdx.x == 0) *s_last = (atomicAdd(&p.tickets[blockIdx.x], 1) == p.n_splits - 1) ? 1 : 0;
+      consumer_sync();
+      if (*s_last) {
+        __threadfence();
+        const volatile float* ml = p.part_ml;
+        const volatile float* po = p.part_o;
+        for (int e = threadIdx.x; e < n_rows * HS; e += CWARPS * 32) {
+          const int r = e / HS, d = e - r * HS;
+          const int head = kvh * p.per + r;
+          const size_t sb = ((size_t)tok * p.nh + head) * p.n_splits;
+          float mm = -INFINITY;
+          for (int sp = 0; sp < p.n_splits; ++sp) mm = fmaxf(mm, ml[(sb + sp) * 2]);
+          float ll = 0.f, acc = 0.f;
+          for (int sp = 0; sp < p.n_splits; ++sp) {
+            const float m = ml[(sb + sp) * 2];
+            const float f = (m == -INFINITY) ? 0.f : exp2f(m - mm);
+            ll += ml[(sb + sp) * 2 + 1] * f;
+            acc += po[(sb + sp) * HS + d] * f;
+          }
+          p.out[(size_t)tok * p.out_stride + (size_t)head * HS + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+        }
+        if (threadIdx.x == 0) p.tickets[blockIdx.x] = 0;
+      }
+    }
+  }
+
+  // ---- exit: on an abort wait (bounded) for copies in flight so none lands after the block ---
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == CWARPS * 32) {
+    if (p.error) atomicExch(p.error, 1);
+    for (int it = max(0, armed - STAGES); it < armed; ++it) {
+      const int s = it % STAGES;
+      const uint32_t ph = (it / STAGES) & 1;
+      for (uint32_t i = 0; i < kSpinLimit; ++i)
+        if (mbar_try_wait(&full[s], ph)) break;
+    }
+  }
+  __syncthreads();
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// The pool [pages, g, page_size, hs] as a matrix [pages*g*page_size, hs]; boxes of [page_size rows, 64 columns].
+bool make_pool_map(CUtensorMap* map, const void* pool, long long rows, int hs, int page_size) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)hs, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)hs * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)page_size};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int HS>
+int launch(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int n_requests, cudaStream_t stream) {
+  const size_t smem = 1024 + (size_t)2 * STAGES * BN * HS * 2 + (size_t)16 * (HS + 8) * 2 + 2 * STAGES * 8 + 16;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(decode_attention_tma_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return YALIS_ERR_LAUNCH;
+    configured = true;
+  }
+  dim3 grid(n_requests * p.g, p.n_splits);
+  if (grid.y > 65535) return YALIS_ERR_SHAPE;
+  return yalis_launch(decode_attention_tma_kernel<HS>, grid, dim3(kThreads), smem, stream, mk, mv, p);
+}
+
+}  // namespace
+
+// Whether the TMA decode kernel takes this shape.
+YALIS_API int yalis_decode_attention_tma_supports(int hs, int page_size, int per) {
+  const bool hs_ok = hs == 64 || hs == 128 || hs == 192 || hs == 256;
+  const bool page_ok = page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64;
+  return (hs_ok && page_ok && per >= 1 && per <= 16) ? 1 : 0;
+}
+
+// One query token per request.  scratch: n_tokens*nh*n_splits*(hs+2) floats and tickets: n_requests*g zeroed
+// int32 when n_splits > 1 (as for yalis_paged_attention_mma).  error: device int32 raised on a timed-out wait or
+// an unmapped page.
+YALIS_API int yalis_decode_attention_tma(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
+                                         const void* v_pool, const int32_t* positions, const int32_t* q_start,
+                                         const int32_t* block_table, int table_width, int page_size, int num_pages,
+                                         int n_tokens, int n_requests, int nh, int g, int hs, float scale,
+                                         int n_splits, float* scratch, int32_t* tickets, int32_t* error,
+                                         cudaStream_t stream) {
+  if (n_tokens <= 0 || n_requests <= 0) return YALIS_OK;
+  if (g <= 0 || nh % g != 0 || n_splits < 1) return YALIS_ERR_SHAPE;
+  if (!yalis_decode_attention_tma_supports(hs, page_size, nh / g)) return YALIS_ERR_SHAPE;
+  if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) return YALIS_ERR_ALIGN;
+  if ((q_stride % 8) || (out_stride % 2)) return YALIS_ERR_ALIGN;
+  if (n_splits > 1 && (scratch == nullptr || tickets == nullptr)) return YALIS_ERR_SHAPE;
+  CUtensorMap mk, mv;
+  const long long rows = (long long)num_pages * g * page_size;
+  if (!make_pool_map(&mk, k_pool, rows, hs, page_size) || !make_pool_map(&mv, v_pool, rows, hs, page_size))
+    return YALIS_ERR_LAUNCH;
+  DecParams p;
+  p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
+  p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
+  p.positions = positions; p.q_start = q_start; p.block_table = block_table;
+  p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages;
+  p.nh = nh; p.g = g; p.per = nh / g;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.n_splits = n_splits;
+  p.part_o = scratch;
+  p.part_ml = scratch ? scratch + (size_t)n_tokens * nh * n_splits * hs : nullptr;
+  p.tickets = tickets;
+  p.error = error;
+  switch (hs) {
+    case 64: return launch<64>(mk, mv, p, n_requests, stream);
+    case 128: return launch<128>(mk, mv, p, n_requests, stream);
+    case 192: return launch<192>(mk, mv, p, n_requests, stream);
+    default: return launch<256>(mk, mv, p, n_requests, stream);
+  }
+}

@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Optional
 
 import torch
@@ -55,6 +56,8 @@ def paged_attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch
 
 
 SM_COUNT = 148   # B200
+# YALIS_B200_NO_DECODE_TMA=1 keeps decode steps on the cp.async kernel (for comparisons).
+USE_DECODE_TMA = os.environ.get("YALIS_B200_NO_DECODE_TMA", "0") != "1"
 
 
 def mma_supports(head_dim: int) -> bool:
@@ -121,6 +124,46 @@ def paged_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Ten
     return out
 
 
+def decode_tma_supports(head_dim: int, page_size: int, heads_per_group: int) -> bool:
+    """Whether the TMA-fed decode kernel takes this shape (head_dim 64/128/192/256, pages of 8..64, <= 16 heads per group)."""
+    return bool(lib().yalis_decode_attention_tma_supports(i32(head_dim), i32(page_size), i32(heads_per_group)))
+
+
+def decode_attention_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, positions: torch.Tensor,
+                         q_start: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int,
+                         head_dim: int, scale: Optional[float] = None, n_splits: int = 1,
+                         error_flag: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode attention (one token per request, no window) with TMA-fed K/V tiles; same result as
+    ``paged_attention_mma`` for such a step.  ``q`` is [R, heads*head_dim] (one row per request)."""
+    name = "decode_attention_tma"
+    n, r = q.shape[0], q_start.numel() - 1
+    req_dummy = positions      # only shapes and dtypes are checked through the common helper
+    _check_common(name, q, k_pool, v_pool, positions, req_dummy, block_table, num_heads, num_kv_heads, head_dim)
+    need(q.dtype == torch.bfloat16, name, "bfloat16 only")
+    need(decode_tma_supports(head_dim, k_pool.shape[2], num_heads // num_kv_heads), name,
+         "needs head_dim 64/128/192/256, page_size 8/16/32/64 and at most 16 heads per KV head")
+    need(q_start.dtype == torch.int32 and q_start.is_contiguous() and q_start.is_cuda, name, "q_start must be int32 [R+1]")
+    need(block_table.shape[0] >= r, name, "block_table has fewer rows than requests")
+    if out is None:
+        out = torch.empty((n, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    need(out.shape == (n, num_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous(), name, "bad out tensor")
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    scratch = tickets = None
+    if n_splits > 1:
+        floats = lib().yalis_attention_mma_scratch_floats
+        floats.restype = ctypes.c_longlong
+        scratch = torch.empty(int(floats(i32(n), i32(num_heads), i32(head_dim), i32(n_splits))), dtype=torch.float32,
+                              device=q.device)
+        tickets = _tickets(q.device, r * num_kv_heads)
+    check(lib().yalis_decode_attention_tma(
+        ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(k_pool), ptr(v_pool), ptr(positions), ptr(q_start),
+        ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]), i32(k_pool.shape[0]), i32(n), i32(r),
+        i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), i32(n_splits), ptr(scratch), ptr(tickets),
+        ptr(error_flag), stream()), name)
+    return out
+
+
 def paged_attention(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: str, num_heads: int,
                     num_kv_heads: int, head_dim: int, scale: Optional[float] = None,
                     window: Optional[int] = None) -> torch.Tensor:
@@ -129,8 +172,13 @@ def paged_attention(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     size the tensor-core kernel is built for goes there; everything else (float32, odd
     head sizes) to the exact generic kernel."""
     table = ctx.block_tables[group]
+    per = num_heads // num_kv_heads
+    if (qkv.dtype == torch.bfloat16 and USE_DECODE_TMA and ctx.decode_only and ctx.host.max_q_len == 1 and window is None
+            and decode_tma_supports(head_dim, k_pool.shape[2], per)):
+        return decode_attention_tma(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, num_heads, num_kv_heads,
+                                    head_dim, scale=scale, n_splits=decode_splits(ctx.n_requests, num_kv_heads),
+                                    error_flag=ctx.error_flag)
     if qkv.dtype == torch.bfloat16 and mma_supports(head_dim):
-        per = num_heads // num_kv_heads
         splits = decode_splits(ctx.n_requests, num_kv_heads) if ctx.host.max_q_len * per <= 16 else 1
         return paged_attention_mma(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, ctx.req_of_token, table,
                                    ctx.host.max_q_len, num_heads, num_kv_heads, head_dim, scale=scale, window=window,

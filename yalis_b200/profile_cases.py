@@ -14,16 +14,32 @@ import argparse
 import torch
 
 
-def _time(fn, launches: int) -> float:
+def _time(fn, launches: int, graph: bool = True) -> float:
+    """Microseconds per launch.  With ``graph`` the launches are captured into one CUDA graph
+    and replayed, so that host launch cost does not hide the kernels' own time."""
     fn()
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if not graph:
+        start.record()
+        for _ in range(launches):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / launches * 1e3
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(launches):
+            fn()
+    g.replay()
+    torch.cuda.synchronize()
+    reps = 5
     start.record()
-    for _ in range(launches):
-        fn()
+    for _ in range(reps):
+        g.replay()
     end.record()
     torch.cuda.synchronize()
-    return start.elapsed_time(end) / launches * 1e3
+    return start.elapsed_time(end) / (reps * launches) * 1e3
 
 
 def attention_decode(args) -> None:
@@ -48,7 +64,7 @@ def attention_decode(args) -> None:
         state["i"] += 1
         paged_attention_mma(q, k, v, pos, q_start, req, table, 1, nh, g, hs, n_splits=splits)
 
-    us = _time(fn, args.launches)
+    us = _time(fn, args.launches, graph=not args.eager)
     kv_bytes = b * ctx * 2 * g * hs * 2
     print(f"attention_decode batch {b} ctx {ctx} splits {splits}: {us:.1f} us per launch, "
           f"{kv_bytes / us / 1e6:.2f} TB/s of K/V")
@@ -68,13 +84,14 @@ def gemm_wstream(args) -> None:
         state["i"] += 1
         gemm(x, w, split=args.split)
 
-    us = _time(fn, args.launches)
+    us = _time(fn, args.launches, graph=not args.eager)
     print(f"gemm_wstream tokens {m} n {n} k {k} splits {wstream_splits(n, k) if args.split else 1}: "
           f"{us:.1f} us per launch, {n * k * 2 / us / 1e6:.2f} TB/s of weights")
 
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--eager", action="store_true", help="launch one by one instead of replaying a CUDA graph")
     sub = ap.add_subparsers(dest="case", required=True)
     a = sub.add_parser("attention_decode")
     a.add_argument("--batch", type=int, default=64)
