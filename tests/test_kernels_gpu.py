@@ -66,7 +66,7 @@ def test_add_rmsnorm(dtype, n, width, eps):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n, inter", [(4, 176), (3, 1000)])
+@pytest.mark.parametrize("n, inter", [(4, 176), (3, 1000), (5, 100), (300, 14336 // 8)])
 def test_silu_mul(dtype, n, inter):
     from yalis_b200.ops.elementwise import silu_mul
     x = rnd(n, 2 * inter, dtype=dtype, scale=2.0)
@@ -467,3 +467,32 @@ def test_decode_attention_tma_far_key_and_padding_requests():
         for h in range(nh):
             assert torch.allclose(got[h], vs[0][target, h // (nh // g)].to(torch.bfloat16).float(), atol=6e-2), (target, h)
         assert torch.all(out[1:] == 7.0) and int(flag) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_kv_write_many_tokens(dtype):
+    """Steps with many tokens take the one-block-per-token variant: same results."""
+    from yalis_b200.ops.elementwise import rope_kv_write
+    from yalis_b200.parts.rotary import inverse_frequencies
+    nh, g, hs, page, n = 6, 2, 48, 8, 333
+    inv = inverse_frequencies(hs, 10000.0, None)
+    qkv = rnd(n, (nh + 2 * g) * hs, dtype=dtype, seed=8)
+    pos_list = list(range(5, 5 + n))
+    num_pages = (5 + n) // page + 2
+    table = torch.arange(num_pages, dtype=torch.int32).flip(0).view(1, -1).contiguous().to(DEV)
+    k_pool = torch.zeros(num_pages, g, page, hs, dtype=dtype, device=DEV)
+    v_pool = torch.zeros_like(k_pool)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q_out = rope_kv_write(qkv, torch.tensor(pos_list, dtype=torch.int32, device=DEV), torch.zeros(n, dtype=torch.int32, device=DEV),
+                          inv.to(DEV), k_pool, v_pool, table, nh, g, hs, bad_flag=flag)
+    assert int(flag) == 0
+    cos, sin = plain.rope_tables(torch.tensor(pos_list), inv)
+    src = qkv.float().cpu()
+    t = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(q_out.float().cpu().view(n, nh, hs), plain.apply_rope(src[:, :nh * hs].view(n, nh, hs), cos, sin).to(dtype).float(), **t)
+    rk = plain.apply_rope(src[:, nh * hs:(nh + g) * hs].view(n, g, hs), cos, sin).to(dtype).float()
+    tab = table.cpu()[0]
+    for i in (0, 1, 7, 100, n - 1):
+        p = pos_list[i]
+        torch.testing.assert_close(k_pool[int(tab[p // page]), :, p % page].float().cpu(), rk[i], **t)
+        assert torch.equal(v_pool[int(tab[p // page]), :, p % page].float().cpu(), src[i, (nh + g) * hs:].view(g, hs).to(dtype).float())

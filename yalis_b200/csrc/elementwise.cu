@@ -248,6 +248,73 @@ __global__ void rope_kv_write_kernel(const TS* __restrict__ src, int src_stride,
   }
 }
 
+// The same for steps with many tokens: one block per token walks all heads, with the token's
+// cosines and sines computed once in shared memory.
+template <typename T, typename TS>
+__global__ void rope_kv_write_token_kernel(const TS* __restrict__ src, int src_stride, int n_parts, size_t part_stride,
+                                           T* __restrict__ q_out, const int32_t* __restrict__ positions,
+                                           const int32_t* __restrict__ req_of_token,
+                                           const float* __restrict__ inv_freq, T* __restrict__ k_pool,
+                                           T* __restrict__ v_pool, const int32_t* __restrict__ block_table,
+                                           int table_width, int page_size, int num_pages, int nh, int g, int hs,
+                                           int32_t* bad_page) {
+  extern __shared__ float cs[];   // cos[hs/2], sin[hs/2]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int req = req_of_token[t];
+  if (req < 0) return;
+  const int pos = positions[t];
+  const int half = hs >> 1;
+  if (inv_freq) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      float sn, c;
+      sincosf((float)pos * inv_freq[i], &sn, &c);
+      cs[i] = c;
+      cs[half + i] = sn;
+    }
+  }
+  int page = -1, off = 0;
+  if (k_pool != nullptr) {
+    const int page_idx = pos / page_size;
+    off = pos - page_idx * page_size;
+    page = (page_idx < table_width) ? block_table[(size_t)req * table_width + page_idx] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0 && bad_page) atomicExch(bad_page, 1);
+      page = -1;
+    }
+  }
+  __syncthreads();
+  const TS* row = src + (size_t)t * src_stride;
+  const int n_heads = nh + 2 * g;
+  for (int e = threadIdx.x; e < n_heads * half; e += blockDim.x) {
+    const int head = e / half, i = e - head * half;
+    const bool is_q = head < nh, is_v = head >= nh + g;
+    T* dst;
+    if (is_q) {
+      dst = q_out + ((size_t)t * nh + head) * hs;
+    } else {
+      if (page < 0) continue;
+      const int kvh = is_v ? head - nh - g : head - nh;
+      dst = (is_v ? v_pool : k_pool) + (((size_t)page * g + kvh) * page_size + off) * hs;
+    }
+    const TS* h = row + (size_t)head * hs;
+    float x1 = 0.f, x2 = 0.f;
+    for (int s = 0; s < n_parts; ++s) {
+      x1 += to_f32<TS>(h[s * part_stride + i]);
+      x2 += to_f32<TS>(h[s * part_stride + i + half]);
+    }
+    float o1 = x1, o2 = x2;
+    if (!is_v && inv_freq) {
+      const float c = cs[i], sn = cs[half + i];
+      o1 = x1 * c - x2 * sn;
+      o2 = x2 * c + x1 * sn;
+    }
+    dst[i] = from_f32<T>(o1);
+    dst[i + half] = from_f32<T>(o2);
+  }
+}
+
 // src_dtype: the model type (n_parts must be 1) or YALIS_F32 partial sums [n_parts, N, src_stride].
 YALIS_API int yalis_rope_kv_write(const void* src, int src_dtype, int src_stride, int n_parts, long long part_stride,
                                   void* q_out, int dtype, const int32_t* positions, const int32_t* req_of_token,
@@ -257,20 +324,28 @@ YALIS_API int yalis_rope_kv_write(const void* src, int src_dtype, int src_stride
   if (n_tokens <= 0) return YALIS_OK;
   if (hs <= 0 || (hs & 1) || n_parts < 1) return YALIS_ERR_SHAPE;
   if (nh + 2 * g > 65535) return YALIS_ERR_SHAPE;
-  dim3 grid(n_tokens, nh + 2 * g);
-  const int threads = (hs / 2 + 31) / 32 * 32;
+  const bool per_token = n_tokens >= 128;      // enough tokens to fill the GPU with one block each
+  dim3 grid(n_tokens, per_token ? 1 : nh + 2 * g);
+  const int threads = per_token ? 256 : (hs / 2 + 31) / 32 * 32;
+  const size_t smem = per_token ? (size_t)hs * sizeof(float) : 0;
+  if (smem > 48 * 1024) return YALIS_ERR_SHAPE;
+#define YALIS_ROPE_ARGS(TS_)                                                                                         \
+  (const TS_*)src, src_stride, n_parts, (size_t)part_stride, (T*)q_out, positions, req_of_token, inv_freq, (T*)k_pool, \
+      (T*)v_pool, block_table, table_width, page_size, num_pages, nh, g, hs, bad_page
   YALIS_DISPATCH_DTYPE(
       dtype, T,
       if (src_dtype == dtype && n_parts == 1) {
-        return yalis_launch(rope_kv_write_kernel<T, T>, grid, dim3(threads), 0, stream, (const T*)src, src_stride, 1,
-                            (size_t)0, (T*)q_out, positions, req_of_token, inv_freq, (T*)k_pool, (T*)v_pool,
-                            block_table, table_width, page_size, num_pages, nh, g, hs, bad_page);
+        return per_token ? yalis_launch(rope_kv_write_token_kernel<T, T>, grid, dim3(threads), smem, stream,
+                                        YALIS_ROPE_ARGS(T))
+                         : yalis_launch(rope_kv_write_kernel<T, T>, grid, dim3(threads), smem, stream,
+                                        YALIS_ROPE_ARGS(T));
       } else if (src_dtype == YALIS_F32) {
-        return yalis_launch(rope_kv_write_kernel<T, float>, grid, dim3(threads), 0, stream, (const float*)src,
-                            src_stride, n_parts, (size_t)part_stride, (T*)q_out, positions, req_of_token, inv_freq,
-                            (T*)k_pool, (T*)v_pool, block_table, table_width, page_size, num_pages, nh, g, hs,
-                            bad_page);
+        return per_token ? yalis_launch(rope_kv_write_token_kernel<T, float>, grid, dim3(threads), smem, stream,
+                                        YALIS_ROPE_ARGS(float))
+                         : yalis_launch(rope_kv_write_kernel<T, float>, grid, dim3(threads), smem, stream,
+                                        YALIS_ROPE_ARGS(float));
       } else { return YALIS_ERR_DTYPE; });
+#undef YALIS_ROPE_ARGS
   return YALIS_OK;
 }
 
@@ -297,11 +372,41 @@ __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, i
   out[idx] = from_f32<T>(act * up);
 }
 
+// bfloat16, halves layout, inter % 8 == 0: eight elements per thread with 16-byte accesses.
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                       int inter, size_t total_vec) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= total_vec) return;
+  const int vec_per_row = inter >> 3;
+  const size_t t = v / vec_per_row;
+  const int i = (int)(v - t * vec_per_row) << 3;
+  const __nv_bfloat16* row = in + t * 2 * (size_t)inter;
+  const uint4 g4 = *reinterpret_cast<const uint4*>(row + i);
+  const uint4 u4 = *reinterpret_cast<const uint4*>(row + inter + i);
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+  const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+  uint4 o4;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+    o2[k] = __floats2bfloat162_rn((g.x / (1.0f + expf(-g.x))) * u.x, (g.y / (1.0f + expf(-g.y))) * u.y);
+  }
+  *reinterpret_cast<uint4*>(out + t * (size_t)inter + i) = o4;
+}
+
 YALIS_API int yalis_silu_mul(const void* in, void* out, int dtype, int n_tokens, int inter, int interleaved,
                              cudaStream_t stream) {
   const size_t total = (size_t)n_tokens * inter;
   if (total == 0) return YALIS_OK;
   const int threads = 256;
+  if (dtype == YALIS_BF16 && !interleaved && inter % 8 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+    const size_t total_vec = total >> 3;
+    return yalis_launch(silu_mul_bf16x8_kernel, dim3((unsigned)((total_vec + threads - 1) / threads)), dim3(threads), 0,
+                        stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter, total_vec);
+  }
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
   YALIS_DISPATCH_DTYPE(dtype, T,
                        return yalis_launch(silu_mul_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (const T*)in,

@@ -280,11 +280,68 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
 
 }  // namespace
 
+constexpr int kArgmaxChunks = 32;   // blocks per row in the first phase for wide rows
+
+// Phase 1 of the wide argmax: block (row, chunk) finds the best entry of its slice.
+__global__ void __launch_bounds__(kThreads) argmax_partial_kernel(const float* __restrict__ logits, long long row_stride,
+                                                                  int vocab, float* __restrict__ part_v,
+                                                                  int32_t* __restrict__ part_i) {
+  __shared__ ArgMax scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const float* row = logits + (size_t)blockIdx.x * row_stride;
+  const int per = (vocab + kArgmaxChunks - 1) / kArgmaxChunks;
+  const int lo = blockIdx.y * per, hi = min(vocab, lo + per);
+  ArgMax a;
+  a.v = 0.f;
+  a.i = -1;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    ArgMax b;
+    b.v = row[i];
+    b.i = i;
+    if (b.v == b.v) a = better(a, b);
+  }
+  a = block_argmax(a, scratch);
+  if (threadIdx.x == 0) {
+    part_v[blockIdx.x * kArgmaxChunks + blockIdx.y] = a.v;
+    part_i[blockIdx.x * kArgmaxChunks + blockIdx.y] = a.i;
+  }
+}
+
+// Phase 2: one warp per row merges the slices (ties still go to the lowest index).
+__global__ void argmax_merge_kernel(const float* __restrict__ part_v, const int32_t* __restrict__ part_i,
+                                    int32_t* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  ArgMax a;
+  a.v = part_v[blockIdx.x * kArgmaxChunks + threadIdx.x];
+  a.i = part_i[blockIdx.x * kArgmaxChunks + threadIdx.x];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax b;
+    b.v = __shfl_xor_sync(0xffffffffu, a.v, o);
+    b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
+    a = better(a, b);
+  }
+  if (threadIdx.x == 0) out[blockIdx.x] = a.i < 0 ? 0 : a.i;
+}
+
+// scratch: n_rows * 32 floats followed by n_rows * 32 int32 for rows wider than 16384 (may be null
+// for narrower rows, which one block per row handles).
 YALIS_API int yalis_argmax(const float* logits, long long row_stride, int n_rows, int vocab, int32_t* out,
-                           cudaStream_t stream) {
+                           float* scratch, cudaStream_t stream) {
+  static_assert(kArgmaxChunks == 32, "the merge kernel is one warp wide");
   if (n_rows <= 0) return YALIS_OK;
   if (vocab <= 0) return YALIS_ERR_SHAPE;
-  return yalis_launch(argmax_kernel, dim3(n_rows), dim3(kThreads), 0, stream, logits, row_stride, vocab, out);
+  if (vocab <= 16384 || scratch == nullptr)
+    return yalis_launch(argmax_kernel, dim3(n_rows), dim3(kThreads), 0, stream, logits, row_stride, vocab, out);
+  float* part_v = scratch;
+  int32_t* part_i = reinterpret_cast<int32_t*>(scratch + (size_t)n_rows * kArgmaxChunks);
+  int st = yalis_launch(argmax_partial_kernel, dim3(n_rows, kArgmaxChunks), dim3(kThreads), 0, stream, logits,
+                        row_stride, vocab, part_v, part_i);
+  if (st != YALIS_OK) return st;
+  return yalis_launch(argmax_merge_kernel, dim3(n_rows), dim3(32), 0, stream, (const float*)part_v,
+                      (const int32_t*)part_i, out);
 }
 
 YALIS_API int yalis_sample(const float* logits, long long row_stride, int n_rows, int vocab, const float* temperature,

@@ -23,7 +23,10 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     need(out.dtype == torch.int32 and out.shape == (rows,) and out.is_contiguous(), name, "bad out tensor")
-    check(lib().yalis_argmax(ptr(logits), i64(logits.stride(0)), i32(rows), i32(vocab), ptr(out), stream()), name)
+    # wide rows are searched by 32 blocks each, then merged: needs a little scratch memory
+    scratch = torch.empty((rows * 64,), dtype=torch.float32, device=logits.device) if vocab > 16384 else None
+    check(lib().yalis_argmax(ptr(logits), i64(logits.stride(0)), i32(rows), i32(vocab), ptr(out), ptr(scratch),
+                             stream()), name)
     return out
 
 

@@ -89,6 +89,21 @@ def gemm_wstream(args) -> None:
           f"{us:.1f} us per launch, {n * k * 2 / us / 1e6:.2f} TB/s of weights")
 
 
+def prefill(args) -> None:
+    """One prompt of ``--tokens`` tokens through the whole engine (Llama-3-8B shape, ``--layers`` layers)."""
+    from yalis_b200.bench_support import prefill_bench
+    from yalis_b200.config.presets import preset
+    from yalis_b200.engine.engine import Engine
+    cfg = preset(args.preset)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    engine = Engine(config=cfg, seed=0, dtype=args.dtype, page_size=16, cache_tokens=args.tokens + 64, max_slots=2,
+                    max_context=args.tokens + 64)
+    ms = prefill_bench(engine, args.tokens, warmup=1, iters=args.launches)
+    print(f"prefill {args.preset} layers {cfg['num_hidden_layers']} tokens {args.tokens} {args.dtype}: {ms:.3f} ms, "
+          f"{args.tokens / ms * 1e3:.0f} tokens/s")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--eager", action="store_true", help="launch one by one instead of replaying a CUDA graph")
@@ -110,6 +125,13 @@ def main() -> None:
     gm.add_argument("--split", action="store_true")
     gm.add_argument("--launches", type=int, default=8)
     gm.set_defaults(fn=gemm_wstream)
+    pf = sub.add_parser("prefill")
+    pf.add_argument("--preset", default="Llama-3-8B")
+    pf.add_argument("--layers", type=int, default=4)
+    pf.add_argument("--tokens", type=int, default=2048)
+    pf.add_argument("--dtype", default="bfloat16")
+    pf.add_argument("--launches", type=int, default=2)
+    pf.set_defaults(fn=prefill)
     args = ap.parse_args()
     args.fn(args)
 
