@@ -43,7 +43,7 @@ def _time(fn, launches: int, graph: bool = True) -> float:
 
 
 def attention_decode(args) -> None:
-    from yalis_b200.ops.attention import decode_splits, paged_attention_mma
+    from yalis_b200.ops.attention import decode_attention_tma, decode_splits, paged_attention_mma
     dev = "cuda:0"
     nh, g, hs, page, b, ctx = args.heads, args.kv_heads, args.head_dim, args.page_size, args.batch, args.ctx
     pages_per = -(-ctx // page)
@@ -62,11 +62,14 @@ def attention_decode(args) -> None:
     def fn():
         k, v = pools[state["i"] % layers]
         state["i"] += 1
-        paged_attention_mma(q, k, v, pos, q_start, req, table, 1, nh, g, hs, n_splits=splits)
+        if args.kernel == "tma":
+            decode_attention_tma(q, k, v, pos, q_start, table, nh, g, hs, n_splits=splits)
+        else:
+            paged_attention_mma(q, k, v, pos, q_start, req, table, 1, nh, g, hs, n_splits=splits)
 
     us = _time(fn, args.launches, graph=not args.eager)
     kv_bytes = b * ctx * 2 * g * hs * 2
-    print(f"attention_decode batch {b} ctx {ctx} splits {splits}: {us:.1f} us per launch, "
+    print(f"attention_decode ({args.kernel}) batch {b} ctx {ctx} splits {splits}: {us:.1f} us per launch, "
           f"{kv_bytes / us / 1e6:.2f} TB/s of K/V")
 
 
@@ -116,6 +119,7 @@ def main() -> None:
     a.add_argument("--head-dim", type=int, default=128)
     a.add_argument("--page-size", type=int, default=16)
     a.add_argument("--splits", type=int, default=0)
+    a.add_argument("--kernel", default="tma", choices=["tma", "mma"], help="TMA-fed decode kernel or the cp.async one")
     a.add_argument("--launches", type=int, default=8)
     a.set_defaults(fn=attention_decode)
     gm = sub.add_parser("gemm_wstream")
