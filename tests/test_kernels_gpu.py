@@ -496,3 +496,59 @@ def test_rope_kv_write_many_tokens(dtype):
         p = pos_list[i]
         torch.testing.assert_close(k_pool[int(tab[p // page]), :, p % page].float().cpu(), rk[i], **t)
         assert torch.equal(v_pool[int(tab[p // page]), :, p % page].float().cpu(), src[i, (nh + g) * hs:].view(g, hs).to(dtype).float())
+
+
+@pytest.mark.parametrize("nh, g, hs, page", [(8, 2, 128, 16), (4, 4, 64, 8), (6, 2, 128, 32), (3, 1, 64, 64), (32, 8, 128, 16),
+                                             (5, 1, 128, 128)])
+def test_prefill_attention_tcgen05_against_plain_and_generic(nh, g, hs, page):
+    """The tcgen05 prompt kernel: a whole prompt, a portion at an offset that ends inside a page,
+    a short portion and a decode token in one launch; pools poisoned with NaN where nothing was
+    written; against the plain float32 attention and the exact kernel."""
+    from yalis_b200.ops.attention import paged_attention_generic, prefill_attention_tcgen05
+    dtype = torch.bfloat16
+    lens, q_lens = [300, 517, 40, 130, 1], [300, 67, 33, 128, 1]
+    ks, vs, k_pool, v_pool, table = paged_setup(len(lens), lens, g, hs, page, dtype, seed=hs + nh)
+    gen = torch.Generator().manual_seed(1)
+    qs, pos, req, q_start = [], [], [], [0]
+    for r, (l, ql) in enumerate(zip(lens, q_lens)):
+        qs.append(torch.randn(ql, nh, hs, generator=gen))
+        pos += list(range(l - ql, l))
+        req += [r] * ql
+        q_start.append(q_start[-1] + ql)
+    q = torch.cat(qs).to(dtype)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    positions, req_of_token, q_start_d = i32(pos), i32(req), i32(q_start)
+    qd = q.view(-1, nh * hs).to(DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = prefill_attention_tcgen05(qd, k_pool, v_pool, positions, q_start_d, table, max(q_lens), nh, g, hs, error_flag=flag)
+    torch.cuda.synchronize()
+    assert int(flag) == 0
+    assert not torch.isnan(out.float()).any()
+    gen_out = paged_attention_generic(qd, k_pool, v_pool, positions, req_of_token, table, nh, g, hs)
+    torch.testing.assert_close(out.float(), gen_out.float(), rtol=2e-2, atol=2e-2)
+    o = 0
+    for r, (l, ql) in enumerate(zip(lens, q_lens)):
+        kk, vv = ks[r].to(dtype).float(), vs[r].to(dtype).float()
+        ref = plain.causal_attention(q[o:o + ql].float(), kk, vv, torch.arange(l - ql, l), torch.arange(l))
+        torch.testing.assert_close(out[o:o + ql].float().cpu().view(ql, nh, hs), ref, rtol=2e-2, atol=2e-2)
+        o += ql
+
+
+def test_prefill_attention_tcgen05_far_key_and_causal_edge():
+    """One key takes nearly all the weight: each query row must return that key's value if it
+    can see the key, and must not if the key lies after it (causal edge inside a tile)."""
+    from yalis_b200.ops.attention import prefill_attention_tcgen05
+    nh, g, hs, page, l = 4, 1, 128, 16, 700
+    ks, vs, k_pool, v_pool, table = paged_setup(1, [l], g, hs, page, torch.bfloat16, seed=21)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    for target in (0, 127, 128, 300, 555):
+        q_len = 200                                          # queries at positions 500..699
+        q = (ks[0][target, 0] * 4.0).repeat(q_len * nh).view(q_len, nh * hs).to(torch.bfloat16).to(DEV)
+        out = prefill_attention_tcgen05(q, k_pool, v_pool, i32(list(range(l - q_len, l))), i32([0, q_len]), table, q_len,
+                                        nh, g, hs)
+        got = out.float().cpu().view(q_len, nh, hs)
+        want = vs[0][target, 0].to(torch.bfloat16).float()
+        for t in (0, 54, 55, 56, 199):
+            sees = target <= l - q_len + t
+            close = torch.allclose(got[t, 0], want, atol=8e-2)
+            assert close == sees, (target, t, sees)

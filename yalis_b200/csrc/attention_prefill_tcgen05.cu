@@ -1,0 +1,550 @@
+// Paged causal attention for prompt portions on the 5th-generation tensor cores.
+//
+// One block owns up to 128 rows of one (request, KV head) -- row = token * heads_per_group +
+// head_in_group, so the whole GQA group of a token shares the K/V tiles -- and walks the visible
+// keys in tiles of 128:
+//
+//   S = Q K^T      tcgen05.mma (cta_group::1, kind::f16), Q and K tiles in 128B-swizzled shared
+//                  memory (fed by TMA: Q through a 3-D map [head_dim, heads_per_group, tokens],
+//                  K and V one box per cache page), S in tensor memory, double buffered;
+//   P = softmax    four warps, one thread per row: tcgen05.ld of its S row into registers, mask
+//                  by absolute position, running max and sum in float32 (exp2 domain), P packed
+//                  to bfloat16 and written back to tensor memory (tcgen05.st);
+//   O += P V       tcgen05.mma with A = P from tensor memory and B = the V tile read as an
+//                  MN-major operand (V is stored [key][dim]); O stays in tensor memory for the
+//                  whole key loop.  When a row's maximum grows by more than 2^8 the softmax
+//                  threads rescale O in place (tcgen05.ld / st); smaller growth is absorbed by
+//                  keeping the older maximum, which is exact as long as exp2 stays in range.
+//
+// One thread issues all TMA copies, one thread issues all MMAs, completion travels over
+// mbarriers (tcgen05.commit for the MMAs); QK^T of tile j+1 runs while the softmax of tile j is
+// computed.  Same semantics as paged_attention_generic (mask by absolute position,
+// yalis/attention/backend_impl/sdpa_and_flex.py:15-19, 301-307) without a window.
+//
+// Limits (else the caller uses the mma.sync kernel): bfloat16, head_dim 64 or 128, page_size 8,
+// 16, 32, 64 or 128, at most 128 heads per KV head, no window.
+// Rows of V past a tile's last visible key may hold anything; they are zeroed in shared memory
+// before they are multiplied.  All mbarrier waits are bounded (error word, tensor memory freed).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;           // rows (tensor-memory lanes) per block
+constexpr int BN = 128;           // keys per tile
+constexpr int kThreads = 192;     // warps 0-3 softmax, warp 4 TMA, warp 5 MMA + tensor memory
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int TMEM_COLS = 512;
+constexpr int COL_S = 0, COL_P = 2 * BN, COL_O = 2 * BN + BN;   // S0,S1 | P0,P1 (BN/2 each) | O
+
+struct PrefillParams {
+  __nv_bfloat16* out;
+  int out_stride;
+  const int32_t* positions;    // [N]
+  const int32_t* q_start;      // [R+1]
+  const int32_t* block_table;  // [R, table_width]
+  int table_width, page_size, num_pages;
+  int nh, g, per;
+  int tokens_per_tile;         // 128 / per
+  float scale_log2;
+  int32_t* error;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+// One lane polls, the warp stays convergent.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane) {
+  int ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+      : "memory");
+}
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+  return ((uint64_t)(saddr >> 4) & 0x3FFFull) | (1ull << 16) | ((1024ull >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand (V stored [key][dim]), 128-byte swizzle: 64 dims (128 bytes) contiguous per key,
+// 8-key groups 1024 bytes apart (stride byte offset), the next 64 dims `lbo_bytes` further (leading byte offset).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((uint64_t)(saddr >> 4) & 0x3FFFull) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+         ((1024ull >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16, D float32, A/B bfloat16, M = 128; b_mn selects an MN-major B.
+__device__ __forceinline__ uint32_t idesc_f16(int n, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+// 2^x in one instruction; the softmax arguments are <= 8 and -inf gives 0.
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+template <int HS>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                 const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
+  constexpr int H2 = HS / 64;
+  constexpr int Q_BYTES = BM * HS * 2;
+  constexpr int KV_BYTES = BN * HS * 2;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* q_s = base;                       // [H2][128 rows][128 B]
+  unsigned char* k_s = q_s + Q_BYTES;              // [2][H2][128 keys][128 B]
+  unsigned char* v_s = k_s + 2 * KV_BYTES;         // [2][H2][128 keys][128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * KV_BYTES);
+  uint64_t* q_full = bars;                         // 1
+  uint64_t* k_full = bars + 1;                     // 2
+  uint64_t* k_empty = bars + 3;                    // 2
+  uint64_t* v_full = bars + 5;                     // 2
+  uint64_t* v_empty = bars + 7;                    // 2
+  uint64_t* s_full = bars + 9;                     // 2
+  uint64_t* s_empty = bars + 11;                   // 2
+  uint64_t* p_full = bars + 13;                    // 2
+  uint64_t* o_full = bars + 15;                    // 1
+  uint64_t* o_done = bars + 16;                    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int req = blockIdx.y / p.g, kvh = blockIdx.y - req * p.g;
+  const int tok0 = p.q_start[req], q_len = p.q_start[req + 1] - tok0;
+  const int t0 = blockIdx.x * p.tokens_per_tile;           // first token of this block within the request
+  if (t0 >= q_len) return;                                  // uniform: nothing allocated yet
+  const int n_tok = min(p.tokens_per_tile, q_len - t0);
+  const int n_rows = n_tok * p.per;
+  const int pos_first = p.positions[tok0 + t0];
+  const int hi_key = p.positions[tok0 + t0 + n_tok - 1];
+  const int n_tiles = hi_key / BN + 1;
+  const int32_t* bt = p.block_table + (size_t)req * p.table_width;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&k_full[b], 1); mbar_init(&k_empty[b], 1);
+      mbar_init(&v_full[b], 1); mbar_init(&v_empty[b], 1);
+      mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 4);
+      mbar_init(&p_full[b], 4);
+    }
+    mbar_init(o_full, 1);
+    mbar_init(o_done, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  int k_armed = 0, v_armed = 0;
+  if (warp == 4) {
+    // ---------------------------------- TMA producer ------------------------------------------
+    if (lane == 0) {
+      mbar_expect_tx(q_full, (uint32_t)(p.tokens_per_tile * p.per) * HS * 2);
+#pragma unroll
+      for (int h = 0; h < H2; ++h)
+        tma_load_3d(q_s + h * (BM * 128), &map_q, h * 64, kvh * p.per, tok0 + t0, q_full);
+      const int pages_per_tile = BN / p.page_size;
+      const uint32_t page_bytes = (uint32_t)p.page_size * HS * 2;
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int b = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int key0 = j * BN;
+        const int n_pages = min(pages_per_tile, (hi_key - key0) / p.page_size + 1);
+        for (int kv = 0; kv < 2 && ok; ++kv) {
+          uint64_t* full = kv == 0 ? &k_full[b] : &v_full[b];
+          uint64_t* empty = kv == 0 ? &k_empty[b] : &v_empty[b];
+          unsigned char* dst = (kv == 0 ? k_s : v_s) + b * KV_BYTES;
+          const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
+          if (!mbar_wait(empty, ph ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(full, page_bytes * (uint32_t)n_pages);
+          for (int i = 0; i < n_pages; ++i) {
+            const int pi = key0 / p.page_size + i;
+            int page = pi < p.table_width ? bt[pi] : -1;
+            if (page < 0 || page >= p.num_pages) {
+              if (p.error) atomicExch(p.error, 1);
+              page = 0;
+            }
+            const int y = (page * p.g + kvh) * p.page_size;
+#pragma unroll
+            for (int h = 0; h < H2; ++h)
+              tma_load_2d(dst + h * (BN * 128) + i * p.page_size * 128, map, h * 64, y, full);
+          }
+          if (kv == 0) k_armed = j + 1; else v_armed = j + 1;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    // ---------------------------------- MMA issuer --------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc_qk = idesc_f16(BN, false), idesc_pv = idesc_f16(HS, true);
+      const uint32_t q_addr = smem_u32(q_s);
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      auto issue_qk = [&](int j) -> bool {
+        const int b = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_full[b], ph, abort_flag)) return false;
+        if (!mbar_wait(&s_empty[b], ph ^ 1, abort_flag)) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t k_addr = smem_u32(k_s + b * KV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < HS / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * (BM * 128) + (ks & 3) * 32;      // half, then 32 bytes per 16 dims
+          umma_ss(tmem + COL_S + b * BN, desc_kmajor(q_addr + off), desc_kmajor(k_addr + off), idesc_qk, ks > 0);
+        }
+        umma_commit(&s_full[b]);
+        umma_commit(&k_empty[b]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int b = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+        if (!ok) break;
+        if (!mbar_wait(&v_full[b], ph, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&p_full[b], ph, abort_flag)) { ok = false; break; }      // P(j) written, O rescaled if needed
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t v_addr = smem_u32(v_s + b * KV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ++ks) {
+          // 16 keys = two 8-key swizzle groups = 2048 bytes further; P: 16 bfloat16 = 8 columns further
+          umma_ts(tmem + COL_O, tmem + COL_P + b * (BN / 2) + ks * 8, desc_mnmajor(v_addr + ks * 2048, BN * 128),
+                  idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(o_full);
+        umma_commit(&v_empty[b]);
+      }
+      if (ok) umma_commit(o_done);
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------- softmax, one thread per row ----------------------------
+    const int r = threadIdx.x;                        // row of the tile = tensor-memory lane
+    const bool valid = r < n_rows;
+    const int t_in = r / p.per, head = r - t_in * p.per;
+    const int pos_row = valid ? p.positions[tok0 + t0 + t_in] : -1;
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int b = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      const int key0 = j * BN;
+      if (!warp_wait(&s_full[b], ph, abort_flag, lane)) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float sv[BN];
+      {
+        const uint32_t s_addr = lane_base + COL_S + b * BN;
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 32) tmem_ld32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      }
+      // S is in registers: the buffer may be overwritten by the product after next
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[b]);
+      if (key0 + BN - 1 > pos_first || !valid) {           // some key of the tile is hidden from this row
+#pragma unroll
+        for (int c = 0; c < BN; ++c)
+          if (!valid || key0 + c > pos_row) sv[c] = -INFINITY;
+      }
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < BN; c += 4) {
+        mx[0] = fmaxf(mx[0], sv[c]); mx[1] = fmaxf(mx[1], sv[c + 1]);
+        mx[2] = fmaxf(mx[2], sv[c + 2]); mx[3] = fmaxf(mx[3], sv[c + 3]);
+      }
+      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+      const float m_new = fmaxf(m_run, m_tile);
+      // Keep the older maximum unless the new one is more than 2^8 larger: exp2 of at most 8 is
+      // harmless in float32 and bfloat16, and O then needs no rescaling.
+      const bool grow = (m_new - m_run > 8.0f) || (m_run == -INFINITY && m_new != -INFINITY);
+      const float m_use = grow ? m_new : m_run;
+      const float mb = (m_use == -INFINITY) ? 0.f : m_use;
+      const float corr = grow ? ((m_run == -INFINITY) ? 0.f : ex2(m_run - mb)) : 1.f;
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t p_addr = lane_base + COL_P + b * (BN / 2);
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          const float p0 = ex2(fmaf(sv[c0 + c], p.scale_log2, -mb)), p1 = ex2(fmaf(sv[c0 + c + 1], p.scale_log2, -mb));
+          const float p2 = ex2(fmaf(sv[c0 + c + 2], p.scale_log2, -mb)), p3 = ex2(fmaf(sv[c0 + c + 3], p.scale_log2, -mb));
+          ls[0] += p0; ls[1] += p1; ls[2] += p2; ls[3] += p3;
+          pk[c >> 1] = pack_bf16(p0, p1);
+          pk[(c >> 1) + 1] = pack_bf16(p2, p3);
+        }
+        tmem_st16(p_addr + (c0 >> 1), pk);
+      }
+      l_run = l_run * corr + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
+      m_run = m_use;
+      // Rescale O in place if some row of this warp moved its maximum (never for the first tile).
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        if (!warp_wait(o_full, (j - 1) & 1, abort_flag, lane)) { ok = false; break; }     // P V of tile j-1 is done
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+        for (int c0 = 0; c0 < HS; c0 += 16) {
+          uint32_t o[16];
+          tmem_ld16(lane_base + COL_O + c0, o);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
+          tmem_st16(lane_base + COL_O + c0, o);
+        }
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      if (key0 + BN - 1 > hi_key) {
+        // Last tile: rows of V past the last visible key may hold anything (even NaN); zero them
+        // once the tile has landed, and make the writes visible to the tensor core's reads.
+        if (!warp_wait(&v_full[b], ph, abort_flag, lane)) { ok = false; break; }
+        if (key0 + r > hi_key) {
+          unsigned char* vt = v_s + b * KV_BYTES;
+#pragma unroll
+          for (int h = 0; h < H2; ++h)
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              *reinterpret_cast<uint4*>(vt + h * (BN * 128) + r * 128 + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[b]);
+    }
+    // ---- O / l -> global --------------------------------------------------------------------
+    if (ok) ok = warp_wait(o_done, 0, abort_flag, lane);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      __nv_bfloat16* dst = p.out + (size_t)(tok0 + t0 + (valid ? t_in : 0)) * p.out_stride +
+                           (size_t)(kvh * p.per + (valid ? head : 0)) * HS;
+#pragma unroll 1
+      for (int c0 = 0; c0 < HS; c0 += 16) {
+        uint32_t o[16];
+        tmem_ld16(lane_base + COL_O + c0, o);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (valid) {
+          uint4 v0, v1;
+          v0.x = pack_bf16(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
+          v0.y = pack_bf16(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
+          v0.z = pack_bf16(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
+          v0.w = pack_bf16(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
+          v1.x = pack_bf16(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
+          v1.y = pack_bf16(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
+          v1.z = pack_bf16(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
+          v1.w = pack_bf16(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
+          *reinterpret_cast<uint4*>(dst + c0) = v0;
+          *reinterpret_cast<uint4*>(dst + c0 + 8) = v1;
+        }
+      }
+    }
+  }
+
+  // ---- exit: drain on abort, free tensor memory -----------------------------------------------
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 4 * 32) {
+      if (p.error) atomicExch(p.error, 1);
+      for (uint32_t i = 0; i < kSpinLimit; ++i)
+        if (mbar_try_wait(q_full, 0)) break;
+      for (int j = max(0, k_armed - 2); j < k_armed; ++j)
+        for (uint32_t i = 0; i < kSpinLimit; ++i)
+          if (mbar_try_wait(&k_full[j & 1], (j >> 1) & 1)) break;
+      for (int j = max(0, v_armed - 2); j < v_armed; ++j)
+        for (uint32_t i = 0; i < kSpinLimit; ++i)
+          if (mbar_try_wait(&v_full[j & 1], (j >> 1) & 1)) break;
+    }
+    __syncthreads();
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// The pool [pages, g, page_size, hs] as a matrix [pages*g*page_size, hs]; boxes of [page_size rows, 64 columns].
+bool make_pool_map(CUtensorMap* map, const void* pool, long long rows, int hs, int page_size) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)hs, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)hs * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)page_size};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// q [N, q_stride] with head h at column h*hs, seen as [tokens][heads][hs]; a box is
+// [tokens_per_tile][heads_per_group][64 columns], i.e. the rows of a tile in (token, head) order.
+bool make_q_map(CUtensorMap* map, const void* q, long long n_tokens, int q_stride, int nh, int hs, int per,
+                int tokens_per_tile) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)hs, (cuuint64_t)nh, (cuuint64_t)n_tokens};
+  cuuint64_t strides[2] = {(cuuint64_t)hs * 2, (cuuint64_t)q_stride * 2};
+  cuuint32_t box[3] = {64u, (cuuint32_t)per, (cuuint32_t)tokens_per_tile};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int HS>
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, int n_requests,
+           int max_q_len, cudaStream_t stream) {
+  const size_t smem = 1024 + (size_t)BM * HS * 2 + (size_t)4 * BN * HS * 2 + 17 * 8 + 16;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(prefill_attention_tcgen05_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return YALIS_ERR_LAUNCH;
+    configured = true;
+  }
+  dim3 grid((max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile, n_requests * p.g);
+  if (grid.y > 65535) return YALIS_ERR_SHAPE;
+  return yalis_launch(prefill_attention_tcgen05_kernel<HS>, grid, dim3(kThreads), smem, stream, mq, mk, mv, p);
+}
+
+}  // namespace
+
+YALIS_API int yalis_prefill_attention_tcgen05_supports(int hs, int page_size, int per) {
+  const bool page_ok = page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
+  return ((hs == 64 || hs == 128) && page_ok && per >= 1 && per <= 128) ? 1 : 0;
+}
+
+// q: [N, q_stride] (head h at column h*hs); out [N, out_stride].  error: device int32 raised on a timed-out
+// wait or an unmapped page.  No window.
+YALIS_API int yalis_prefill_attention_tcgen05(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
+                                              const void* v_pool, const int32_t* positions, const int32_t* q_start,
+                                              const int32_t* block_table, int table_width, int page_size,
+                                              int num_pages, int n_tokens, int n_requests, int max_q_len, int nh,
+                                              int g, int hs, float scale, int32_t* error, cudaStream_t stream) {
+  if (n_tokens <= 0 || n_requests <= 0) return YALIS_OK;
+  if (g <= 0 || nh % g != 0 || max_q_len < 1) return YALIS_ERR_SHAPE;
+  if (!yalis_prefill_attention_tcgen05_supports(hs, page_size, nh / g)) return YALIS_ERR_SHAPE;
+  if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) return YALIS_ERR_ALIGN;
+  if ((q_stride % 8) || (out_stride % 8)) return YALIS_ERR_ALIGN;
+  PrefillParams p;
+  p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
+  p.positions = positions; p.q_start = q_start; p.block_table = block_table;
+  p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages;
+  p.nh = nh; p.g = g; p.per = nh / g;
+  p.tokens_per_tile = BM / p.per;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.error = error;
+  CUtensorMap mq, mk, mv;
+  const long long rows = (long long)num_pages * g * page_size;
+  if (!make_q_map(&mq, q, n_tokens, q_stride, nh, hs, p.per, p.tokens_per_tile) ||
+      !make_pool_map(&mk, k_pool, rows, hs, page_size) || !make_pool_map(&mv, v_pool, rows, hs, page_size))
+    return YALIS_ERR_LAUNCH;
+  return hs == 64 ? launch<64>(mq, mk, mv, p, n_requests, max_q_len, stream)
+                  : launch<128>(mq, mk, mv, p, n_requests, max_q_len, stream);
+}

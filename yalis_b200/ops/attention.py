@@ -58,6 +58,8 @@ def paged_attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch
 SM_COUNT = 148   # B200
 # YALIS_B200_NO_DECODE_TMA=1 keeps decode steps on the cp.async kernel (for comparisons).
 USE_DECODE_TMA = os.environ.get("YALIS_B200_NO_DECODE_TMA", "0") != "1"
+# YALIS_B200_NO_PREFILL_TCGEN05=1 keeps prompt portions on the mma.sync kernel.
+USE_PREFILL_TCGEN05 = os.environ.get("YALIS_B200_NO_PREFILL_TCGEN05", "0") != "1"
 
 
 def mma_supports(head_dim: int) -> bool:
@@ -164,6 +166,38 @@ def decode_attention_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
     return out
 
 
+def prefill_tcgen05_supports(head_dim: int, page_size: int, heads_per_group: int) -> bool:
+    """Whether the tcgen05 prompt-attention kernel takes this shape (head_dim 64/128, pages of 8..128)."""
+    return bool(lib().yalis_prefill_attention_tcgen05_supports(i32(head_dim), i32(page_size), i32(heads_per_group)))
+
+
+def prefill_attention_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, positions: torch.Tensor,
+                              q_start: torch.Tensor, block_table: torch.Tensor, max_q_len: int, num_heads: int,
+                              num_kv_heads: int, head_dim: int, scale: Optional[float] = None,
+                              error_flag: Optional[torch.Tensor] = None,
+                              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal paged attention of prompt portions on tcgen05 tensor cores (no window); the same
+    semantics as ``paged_attention_generic``.  ``q`` is [N, >= heads*head_dim]."""
+    name = "prefill_attention_tcgen05"
+    n, r = q.shape[0], q_start.numel() - 1
+    _check_common(name, q, k_pool, v_pool, positions, positions, block_table, num_heads, num_kv_heads, head_dim)
+    need(q.dtype == torch.bfloat16, name, "bfloat16 only")
+    need(prefill_tcgen05_supports(head_dim, k_pool.shape[2], num_heads // num_kv_heads), name,
+         "needs head_dim 64 or 128, page_size 8..128 (power of two) and at most 128 heads per KV head")
+    need(q_start.dtype == torch.int32 and q_start.is_contiguous() and q_start.is_cuda, name, "q_start must be int32 [R+1]")
+    need(block_table.shape[0] >= r, name, "block_table has fewer rows than requests")
+    if out is None:
+        out = torch.empty((n, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    need(out.shape == (n, num_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous(), name, "bad out tensor")
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    check(lib().yalis_prefill_attention_tcgen05(
+        ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(k_pool), ptr(v_pool), ptr(positions), ptr(q_start),
+        ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]), i32(k_pool.shape[0]), i32(n), i32(r),
+        i32(max_q_len), i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), ptr(error_flag), stream()), name)
+    return out
+
+
 def paged_attention(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: str, num_heads: int,
                     num_kv_heads: int, head_dim: int, scale: Optional[float] = None,
                     window: Optional[int] = None) -> torch.Tensor:
@@ -178,6 +212,10 @@ def paged_attention(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
         return decode_attention_tma(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, num_heads, num_kv_heads,
                                     head_dim, scale=scale, n_splits=decode_splits(ctx.n_requests, num_kv_heads),
                                     error_flag=ctx.error_flag)
+    if (qkv.dtype == torch.bfloat16 and USE_PREFILL_TCGEN05 and window is None and ctx.host.max_q_len >= 16
+            and prefill_tcgen05_supports(head_dim, k_pool.shape[2], per)):
+        return prefill_attention_tcgen05(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, ctx.host.max_q_len,
+                                         num_heads, num_kv_heads, head_dim, scale=scale, error_flag=ctx.error_flag)
     if qkv.dtype == torch.bfloat16 and mma_supports(head_dim):
         splits = decode_splits(ctx.n_requests, num_kv_heads) if ctx.host.max_q_len * per <= 16 else 1
         return paged_attention_mma(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, ctx.req_of_token, table,

@@ -73,6 +73,32 @@ def attention_decode(args) -> None:
           f"{kv_bytes / us / 1e6:.2f} TB/s of K/V")
 
 
+def attention_prefill(args) -> None:
+    """One prompt of ``--tokens`` tokens attending to itself (causal), one layer's worth of heads."""
+    from yalis_b200.ops.attention import paged_attention_mma, prefill_attention_tcgen05
+    dev = "cuda:0"
+    nh, g, hs, page, n = args.heads, args.kv_heads, args.head_dim, args.page_size, args.tokens
+    pages = -(-n // page)
+    k_pool = torch.randn(pages, g, page, hs, device=dev).to(torch.bfloat16)
+    v_pool = torch.randn(pages, g, page, hs, device=dev).to(torch.bfloat16)
+    table = torch.randperm(pages, device=dev).to(torch.int32).view(1, pages).contiguous()
+    q = torch.randn(n, nh * hs, device=dev).to(torch.bfloat16)
+    pos = torch.arange(n, dtype=torch.int32, device=dev)
+    q_start = torch.tensor([0, n], dtype=torch.int32, device=dev)
+    req = torch.zeros(n, dtype=torch.int32, device=dev)
+
+    def fn():
+        if args.kernel == "tcgen05":
+            prefill_attention_tcgen05(q, k_pool, v_pool, pos, q_start, table, n, nh, g, hs)
+        else:
+            paged_attention_mma(q, k_pool, v_pool, pos, q_start, req, table, n, nh, g, hs)
+
+    us = _time(fn, args.launches, graph=not args.eager)
+    flops = 4.0 * nh * hs * n * (n + 1) / 2
+    print(f"attention_prefill ({args.kernel}) tokens {n} heads {nh}/{g} head_dim {hs}: {us:.1f} us per launch, "
+          f"{flops / us / 1e6:.1f} TFLOP/s (causal flops)")
+
+
 def gemm_wstream(args) -> None:
     from yalis_b200.ops.linear import gemm_wstream as gemm, wstream_splits
     dev = "cuda:0"
@@ -129,6 +155,15 @@ def main() -> None:
     gm.add_argument("--split", action="store_true")
     gm.add_argument("--launches", type=int, default=8)
     gm.set_defaults(fn=gemm_wstream)
+    ap_ = sub.add_parser("attention_prefill")
+    ap_.add_argument("--tokens", type=int, default=2048)
+    ap_.add_argument("--heads", type=int, default=32)
+    ap_.add_argument("--kv-heads", type=int, default=8)
+    ap_.add_argument("--head-dim", type=int, default=128)
+    ap_.add_argument("--page-size", type=int, default=16)
+    ap_.add_argument("--kernel", default="tcgen05", choices=["tcgen05", "mma"])
+    ap_.add_argument("--launches", type=int, default=4)
+    ap_.set_defaults(fn=attention_prefill)
     pf = sub.add_parser("prefill")
     pf.add_argument("--preset", default="Llama-3-8B")
     pf.add_argument("--layers", type=int, default=4)
