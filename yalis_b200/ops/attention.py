@@ -69,10 +69,11 @@ def mma_supports(head_dim: int) -> bool:
 
 def decode_splits(n_requests: int, num_kv_heads: int) -> int:
     """How many blocks share the keys of one (request, KV head) in a decode step, so that
-    few requests still fill the GPU.  Depends on the batch shape only, never on lengths,
-    so a captured step can be replayed."""
+    few requests still fill the GPU: as many as fit in ONE wave of two blocks per SM (a second,
+    nearly empty wave would double the kernel's time).  Depends on the batch shape only, never
+    on lengths, so a captured step can be replayed."""
     blocks = max(1, n_requests * num_kv_heads)
-    return max(1, min(32, -(-4 * SM_COUNT // blocks)))
+    return max(1, min(32, (2 * SM_COUNT) // blocks))
 
 
 _ticket_cache = {}
