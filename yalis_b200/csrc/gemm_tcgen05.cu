@@ -310,6 +310,8 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, lo
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+int g_force_ring = -1;   // -1: by grid size; 0: always the half-SM ring; 1: always the whole-SM ring (experiments)
+
 template <int NTOK, bool DEEP>
 int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t stream) {
   constexpr int STAGES = stages_for<NTOK, DEEP>();
@@ -328,12 +330,15 @@ int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p
 template <int NTOK>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t stream) {
   const int blocks = ((p.N + TILE_N - 1) / TILE_N) * p.splits;
-  return blocks <= kSMs ? launch_cfg<NTOK, true>(mw, mx, p, stream) : launch_cfg<NTOK, false>(mw, mx, p, stream);
+  const bool deep = g_force_ring < 0 ? blocks <= kSMs : g_force_ring == 1;
+  return deep ? launch_cfg<NTOK, true>(mw, mx, p, stream) : launch_cfg<NTOK, false>(mw, mx, p, stream);
 }
 
 }  // namespace
 
 // How many K splits the launcher would use for this shape (so callers can size `out`).
+YALIS_API void yalis_gemm_wstream_force_ring(int mode) { g_force_ring = mode; }
+
 // Chosen so that the grid fills the GPU without a mostly empty last wave: grids of up to two
 // blocks per SM run as one wave; every split costs a little (a partial output to write and add).
 YALIS_API int yalis_gemm_wstream_splits(int N, int K) {

@@ -25,6 +25,18 @@ from yalis_b200.engine.timers import Timers
 from yalis_b200.sampling.sampler import Sampler, SamplingParams, request_seed
 
 
+class _PendingTokens:
+    """A decode step whose chosen tokens are on their way to the host."""
+
+    def __init__(self, requests, slots, host, event):
+        self.requests, self.slots, self.host, self.event = requests, slots, host, event
+        self.positions = None          # index of the placeholder in each request's output
+
+    def read(self) -> List[int]:
+        self.event.synchronize()
+        return self.host[:len(self.requests)].tolist()
+
+
 class LLMEngine:
     def __init__(self, model_config: ModelConfig, inference_config: InferenceConfig, device: str = "cuda:0"):
         self.model_config = model_config
@@ -46,6 +58,8 @@ class LLMEngine:
         self.tokenizer = None
         self._requests_made = 0
         self.use_graphs = os.environ.get("YALIS_DISABLE_DECODE_CUDAGRAPHS", "0") != "1"
+        self.max_steps_in_flight = 2        # decode steps the host may run ahead of the tokens it has read
+        self._token_buffers: List[torch.Tensor] = []
 
     # ---- tokenizer (optional sugar; token ids are the interface) -----------------------
     def _tokenize(self, prompts: Sequence[str]) -> List[List[int]]:
@@ -102,8 +116,11 @@ class LLMEngine:
         n_decode_steps = 0
         timers.start("generate")
         t0 = time.perf_counter()
+        pending: List[_PendingTokens] = []      # decode steps whose tokens the host has not read yet
         while sched.has_work():
             plan = sched.plan()
+            if plan.preempted:
+                self._resolve(pending)          # a preempted request is recomputed from its real tokens
             if not plan.entries:
                 if plan.failed or plan.preempted:
                     continue
@@ -113,7 +130,11 @@ class LLMEngine:
             if nvtx:
                 nvtx.range_push("Decode" if decode_only else "Prefill")
             timers.start(name)
-            sampled = self._run_plan(plan, logits_out if get_logits else None)
+            if self.use_graphs and all(e.count == 1 and e.samples for e in plan.entries):
+                sampled = self._run_decode(plan, pending, logits_out if get_logits else None)
+            else:
+                self._resolve(pending)
+                sampled = self._run_plan(plan, logits_out if get_logits else None)
             timers.stop(name)
             if nvtx:
                 nvtx.range_pop()
@@ -121,6 +142,9 @@ class LLMEngine:
                 first_token_ms = (time.perf_counter() - t0) * 1e3
             n_decode_steps += decode_only
             sched.update(plan, sampled)
+            if pending and pending[-1].positions is None:
+                pending[-1].positions = [len(r.output) - 1 for r in pending[-1].requests]
+        self._resolve(pending)
         timers.stop("generate")
         times, counts = timers.get_times()
         n_cols = max(len(r.output) for r in requests)
@@ -155,20 +179,51 @@ class LLMEngine:
             return out, metrics, [torch.stack(logits_out[r.id]) if logits_out[r.id] else None for r in requests]
         return out, metrics
 
+    def _run_decode(self, plan: StepPlan, pending: List["_PendingTokens"], logits_out) -> List[int]:
+        """A step of single tokens through the captured decode graph (unless
+        YALIS_DISABLE_DECODE_CUDAGRAPHS=1, the reference's switch, yalis/engine.py:44-48).
+
+        The host does not wait for the step: the chosen tokens are copied to pinned memory
+        asynchronously and read one or two steps later, and the next step of the same batch
+        takes its input ids from the device.  That is possible while nothing the host decides
+        depends on the token values: requests that stop at an EOS id are read at once.
+        Returns the tokens, or -1 placeholders that ``_resolve`` fills in later."""
+        reqs = [e.request for e in plan.entries]
+        slots = [r.slot for r in reqs]
+        n = len(reqs)
+        same_batch = bool(pending) and pending[-1].slots == slots
+        if pending and not same_batch:
+            self._resolve(pending)
+        bucket = self.engine.decoder.step(
+            slots, tokens=None if same_batch else [r.last_token for r in reqs], params=[r.sampling for r in reqs],
+            draws=[len(r.output) for r in reqs], keep_logits=logits_out is not None)
+        host = self._token_buffers.pop() if self._token_buffers else torch.empty(self.engine.max_slots, dtype=torch.int32).pin_memory()
+        host[:n].copy_(bucket.tokens[:n], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        if logits_out is not None:
+            for i, r in enumerate(reqs):
+                logits_out[r.id].append(bucket.logits[i].clone())
+        entry = _PendingTokens(reqs, slots, host, event)
+        if any(r.eos_id is not None for r in reqs):
+            tokens = entry.read()
+            self._token_buffers.append(host)
+            return tokens
+        pending.append(entry)
+        if len(pending) > self.max_steps_in_flight:
+            self._resolve(pending, keep=self.max_steps_in_flight)
+        return [-1] * n
+
+    def _resolve(self, pending: List["_PendingTokens"], keep: int = 0) -> None:
+        """Read the tokens of all but the newest ``keep`` pending steps into the requests' outputs."""
+        while len(pending) > keep:
+            entry = pending.pop(0)
+            for r, pos, tok in zip(entry.requests, entry.positions, entry.read()):
+                r.output[pos] = tok
+            self._token_buffers.append(entry.host)
+
     def _run_plan(self, plan: StepPlan, logits_out) -> List[int]:
-        """One engine step for the plan, then one draw per entry that reached its last token.
-        A step of single tokens only goes through the captured decode graph (unless
-        YALIS_DISABLE_DECODE_CUDAGRAPHS=1, the reference's switch, yalis/engine.py:44-48)."""
-        if self.use_graphs and all(e.count == 1 and e.samples for e in plan.entries):
-            reqs = [e.request for e in plan.entries]
-            bucket = self.engine.decoder.step(
-                [r.slot for r in reqs], tokens=[r.tokens[-1] for r in reqs], params=[r.sampling for r in reqs],
-                draws=[len(r.output) for r in reqs], keep_logits=logits_out is not None)
-            toks = bucket.tokens[:len(reqs)].tolist()
-            if logits_out is not None:
-                for i, r in enumerate(reqs):
-                    logits_out[r.id].append(bucket.logits[i].clone())
-            return toks
+        """One engine step for the plan, then one draw per entry that reached its last token."""
         entries, slots, samplers = [], [], []
         for e in plan.entries:
             toks = e.request.tokens[e.start:e.start + e.count]

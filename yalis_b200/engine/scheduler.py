@@ -69,6 +69,10 @@ class Request:
     def total(self) -> int:
         return len(self.prompt) + len(self.output)
 
+    @property
+    def last_token(self) -> int:
+        return self.output[-1] if self.output else self.prompt[-1]
+
 
 @dataclass
 class PlannedEntry:
