@@ -13,11 +13,14 @@
 // own draw count and its own logits, not on the batch it sits in.
 //
 // No sort: the k-th largest logit and the top-p cut are found by a radix
-// descent over order-preserving 32-bit keys (four passes of 256 bins each).
-// Bin masses are accumulated as 64-bit fixed point, so every sum is exact in
-// its order and the kernel is deterministic.  Entries tied with the k-th value
-// are all kept; entries tied with the top-p boundary value are all dropped
-// (unless that value is the maximum).  One block per row.
+// descent over order-preserving 32-bit keys (digits of 12, 12 and 8 bits, one
+// block per row; the wide first digit spreads the entries over enough bins that
+// shared-memory atomics rarely collide).  Bin masses are accumulated as 64-bit fixed point, so
+// every sum is exact in its order and the result is deterministic.  Entries
+// tied with the k-th value are all kept; entries tied with the top-p boundary
+// value are all dropped (unless that value is the maximum).  The draw itself is
+// an argmax of perturbed logits and runs on 32 blocks per row with a merge, as
+// the plain argmax does for wide rows.
 #include "common.cuh"
 
 namespace {
@@ -45,6 +48,43 @@ __device__ __forceinline__ uint4 philox4x32(uint4 ctr, uint2 key) {
 
 // Uniform in (0, 1) with 24 random bits.
 __device__ __forceinline__ float uniform_open(uint32_t x) { return ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f); }
+
+// Calls f(value, index) for every entry of row[0, n) that this thread owns, with many loads in
+// flight at once: one block walking a wide row is bound by load latency otherwise.  Which thread
+// sees which entry is unspecified; every entry is seen exactly once by the block.
+template <class F>
+__device__ __forceinline__ void for_each_entry(const float* __restrict__ row, int n, F f) {
+  const int step = blockDim.x;
+  int done = 0;
+  if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
+    const float4* __restrict__ row4 = reinterpret_cast<const float4*>(row);
+    const int n4 = n >> 2;
+    constexpr int U = 4;
+    int i = threadIdx.x;
+    for (; i + (U - 1) * step < n4; i += U * step) {
+      float4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[u] = row4[i + u * step];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int at = 4 * (i + u * step);
+        f(v[u].x, at);
+        f(v[u].y, at + 1);
+        f(v[u].z, at + 2);
+        f(v[u].w, at + 3);
+      }
+    }
+    for (; i < n4; i += step) {
+      const float4 v = row4[i];
+      f(v.x, 4 * i);
+      f(v.y, 4 * i + 1);
+      f(v.z, 4 * i + 2);
+      f(v.w, 4 * i + 3);
+    }
+    done = n4 << 2;
+  }
+  for (int i = done + threadIdx.x; i < n; i += step) f(row[i], i);
+}
 
 struct ArgMax {
   float v;
@@ -94,30 +134,100 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restric
   ArgMax a;
   a.v = 0.f;
   a.i = -1;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  for_each_entry(row, vocab, [&](float v, int i) {
     ArgMax b;
-    b.v = row[i];
+    b.v = v;
     b.i = i;
-    if (b.v == b.v) a = better(a, b);  // NaN never wins
-  }
+    if (v == v) a = better(a, b);  // NaN never wins
+  });
   a = block_argmax(a, scratch);
   if (threadIdx.x == 0) out[blockIdx.x] = a.i < 0 ? 0 : a.i;
 }
 
-constexpr double kFixedOne = 1099511627776.0;  // 2^40
+constexpr double kFixedOne = 549755813888.0;  // 2^39
+constexpr float kFixedOneF = 549755813888.0f;  // the same in float32: a power of two, the product is exact
 
+// Per-row result of the threshold search: which entries survive top-k and top-p.
+struct Cut {
+  uint32_t k_key;       // keep order_key >= k_key
+  uint32_t p_key;       // and order_key > p_key ...
+  uint32_t keep_equal;  // ... or == p_key if this is 1
+  uint32_t use_p;       // 0: no top-p cut
+};
+
+constexpr int kBins = 4096;            // bins of the first two passes (12 bits each); the third has 256
+
+// Width and shift of the three digits of a 32-bit key: 12 + 12 + 8 bits, most significant first.
+__device__ __forceinline__ int digit_bits(int pass) { return pass < 2 ? 12 : 8; }
+__device__ __forceinline__ int digit_shift(int pass) { return pass == 0 ? 20 : pass == 1 ? 8 : 0; }
+
+// Exclusive prefix sum over the block's threads (in thread order) of 64-bit values.
+__device__ unsigned long long block_exclusive_scan(unsigned long long v, unsigned long long* warp_totals) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  unsigned long long inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  __syncthreads();
+  if (lane == 31) warp_totals[warp] = inc;
+  __syncthreads();
+  unsigned long long base = 0;
+  for (int w = 0; w < warp; ++w) base += warp_totals[w];
+  (void)nwarps;
+  return base + inc - v;
+}
+
+// Walks the bins from the highest down and finds the first one at which `above` + the bins so
+// far exceeds `limit`.  Returns the bin (or -1 if the total never exceeds it) in *chosen and the
+// sum of the bins above it in *above_out; every thread gets the same answer.
+__device__ void find_crossing(const unsigned long long* hist, int nb, unsigned long long above, unsigned long long limit,
+                              unsigned long long* warp_totals, int* sh_pick, unsigned long long* sh_above_pick,
+                              int* chosen, unsigned long long* above_out) {
+  const int per = (nb + blockDim.x - 1) / blockDim.x;          // bins per thread, walked downwards
+  const int first = nb - 1 - threadIdx.x * per;                 // this thread's highest bin
+  unsigned long long mine = 0;
+  for (int j = 0; j < per; ++j) {
+    const int b = first - j;
+    if (b >= 0) mine += hist[b];
+  }
+  if (threadIdx.x == 0) *sh_pick = 0x7fffffff;
+  const unsigned long long before = above + block_exclusive_scan(mine, warp_totals);   // includes a __syncthreads
+  unsigned long long run = before;
+  for (int j = 0; j < per; ++j) {
+    const int b = first - j;
+    if (b < 0) break;
+    if (run + hist[b] > limit) {
+      atomicMin(sh_pick, threadIdx.x * per + j);                // position in walking order
+      break;
+    }
+    run += hist[b];
+  }
+  __syncthreads();
+  const int pick = *sh_pick;
+  if (pick != 0x7fffffff && pick / per == (int)threadIdx.x) *sh_above_pick = run;   // the owner of the first crossing
+  __syncthreads();
+  if (pick == 0x7fffffff) {
+    *chosen = -1;
+    *above_out = above;
+  } else {
+    *chosen = nb - 1 - pick;
+    *above_out = *sh_above_pick;
+  }
+  __syncthreads();
+}
+
+// One block per row: the top-k and top-p cuts of the rows that ask for one.
 __global__ void __launch_bounds__(kThreads)
-sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
-              const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
-              const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
-              const unsigned long long* __restrict__ draw_index, int32_t* __restrict__ out) {
-  __shared__ ArgMax scratch[32];
+sample_cut_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
+                  const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
+                  const float* __restrict__ top_p, Cut* __restrict__ cuts) {
+  extern __shared__ unsigned long long hist[];          // [kBins] 64-bit bins, then [3][kBins] 32-bit pieces
   __shared__ float fscratch[32];
-  __shared__ unsigned long long hist[256];
-  __shared__ uint32_t sh_prefix;
-  __shared__ unsigned long long sh_above;
-  __shared__ int sh_remaining;
-  __shared__ int sh_done;
+  __shared__ unsigned long long warp_totals[32];
+  __shared__ int sh_pick;
+  __shared__ unsigned long long sh_above_pick;
   pdl_launch_dependents();
   pdl_wait();
 
@@ -126,156 +236,176 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
   const float temp = temperature[r];
   const float tp = top_p[r];
   const int tk = top_k[r];
-
-  if (!(temp > 0.f) && !(tp > 0.f)) {  // greedy
-    ArgMax a;
-    a.v = 0.f;
-    a.i = -1;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-      ArgMax b;
-      b.v = row[i];
-      b.i = i;
-      if (b.v == b.v) a = better(a, b);
-    }
-    a = block_argmax(a, scratch);
-    if (threadIdx.x == 0) out[r] = a.i < 0 ? 0 : a.i;
+  const bool greedy = !(temp > 0.f) && !(tp > 0.f);
+  const bool want_k = tk > 0 && tk < vocab, want_p = tp < 1.0f;
+  if (greedy || (!want_k && !want_p)) {
+    if (threadIdx.x == 0) cuts[r] = Cut{0u, 0u, 1u, 0u};
     return;
   }
 
-  // ---- 1. top-k: key of the k-th largest logit --------------------------------
-  uint32_t k_key = 0;  // keep entries with order_key >= k_key
-  if (tk > 0 && tk < vocab) {
-    if (threadIdx.x == 0) {
-      sh_prefix = 0;
-      sh_remaining = tk;
-    }
-    for (int pass = 3; pass >= 0; --pass) {
-      for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0;
+  // ---- top-k: key of the k-th largest logit ---------------------------------------
+  uint32_t k_key = 0;
+  if (want_k) {
+    uint32_t prefix = 0;
+    unsigned long long remaining = (unsigned long long)tk;
+    int done_bits = 0;
+    for (int pass = 0; pass < 3; ++pass) {
+      const int nb = 1 << digit_bits(pass), shift = digit_shift(pass);
+      // counts fit 32 bits: count in the upper half of the buffer (kBins * 4 bytes) with native 32-bit atomics, then widen
+      unsigned int* counts = reinterpret_cast<unsigned int*>(hist + kBins / 2);   // [kBins] 32-bit: the upper half
+      for (int b = threadIdx.x; b < nb; b += blockDim.x) counts[b] = 0;
       __syncthreads();
-      const uint32_t prefix = sh_prefix;
-      const int shift = 8 * pass;
-      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const uint32_t key = order_key(row[i]);
-        const bool match = (pass == 3) || ((key >> (shift + 8)) == (prefix >> (shift + 8)));
-        if (match) atomicAdd(&hist[(key >> shift) & 255u], 1ull);
-      }
+      for_each_entry(row, vocab, [&](float v, int) {
+        const uint32_t key = order_key(v);
+        if (done_bits == 0 || (key >> (32 - done_bits)) == (prefix >> (32 - done_bits)))
+          atomicAdd(&counts[(key >> shift) & (nb - 1)], 1u);
+      });
       __syncthreads();
-      if (threadIdx.x == 0) {
-        int remaining = sh_remaining;
-        unsigned long long cum = 0;
-        int chosen = 0;
-        for (int b = 255; b >= 0; --b) {
-          if (cum + hist[b] >= (unsigned long long)remaining) {
-            chosen = b;
-            break;
-          }
-          cum += hist[b];
+      {   // widen to the 64-bit bins the scan reads, staged through registers (the arrays overlap)
+        constexpr int kPer = kBins / kThreads;
+        unsigned int c[kPer];
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+          const int b = threadIdx.x + j * kThreads;
+          c[j] = b < nb ? counts[b] : 0u;
         }
-        sh_remaining = remaining - (int)cum;
-        sh_prefix = prefix | ((uint32_t)chosen << shift);
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+          const int b = threadIdx.x + j * kThreads;
+          if (b < nb) hist[b] = c[j];
+        }
+        __syncthreads();
       }
-      __syncthreads();
+      int chosen;
+      unsigned long long above;
+      find_crossing(hist, nb, 0ull, remaining - 1, warp_totals, &sh_pick, &sh_above_pick, &chosen, &above);
+      if (chosen < 0) chosen = 0;                        // cannot happen: k < vocab entries exist
+      remaining -= above;
+      prefix |= (uint32_t)chosen << shift;
+      done_bits += digit_bits(pass);
     }
-    k_key = sh_prefix;
-    __syncthreads();
+    k_key = prefix;
   }
 
-  // ---- 2. scale, max and normaliser over the kept entries ----------------------
-  const float inv_t = temp > 0.f ? 1.0f / temp : 1.0f;
-  float mx = -INFINITY;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = row[i];
-    if (order_key(v) >= k_key && v == v) mx = fmaxf(mx, v);
-  }
-  mx = block_max(mx, fscratch);
-  float z = 0.f;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = row[i];
-    if (order_key(v) >= k_key && v == v) z += expf((v - mx) * inv_t);
-  }
-  z = block_sum(z, fscratch);
-  const float inv_z = 1.0f / z;
-
-  // ---- 3. top-p: the key at which the cumulative probability passes top_p -------
-  uint32_t p_key = 0;       // keep entries with order_key > p_key ...
-  bool keep_equal = true;   // ... and those equal to it if this is set
-  if (tp < 1.0f) {
+  uint32_t p_key = 0;
+  uint32_t keep_equal = 1;
+  if (want_p) {
+    // ---- scale, max and normaliser over the entries that survive top-k ---------------
+    const float inv_t = temp > 0.f ? 1.0f / temp : 1.0f;
+    float mx = -INFINITY;
+    for_each_entry(row, vocab, [&](float v, int) {
+      if (order_key(v) >= k_key && v == v) mx = fmaxf(mx, v);
+    });
+    mx = block_max(mx, fscratch);
+    float z = 0.f;
+    for_each_entry(row, vocab, [&](float v, int) {
+      if (order_key(v) >= k_key && v == v) z += expf((v - mx) * inv_t);
+    });
+    z = block_sum(z, fscratch);
+    const float inv_z = 1.0f / z;
+    // ---- top-p: the key at which the cumulative probability passes top_p ---------------
     const unsigned long long limit = (unsigned long long)((double)tp * kFixedOne);
-    if (threadIdx.x == 0) {
-      sh_prefix = 0;
-      sh_above = 0;
-      sh_done = 0;
-    }
-    __syncthreads();
-    for (int pass = 3; pass >= 0; --pass) {
-      for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0;
+    uint32_t prefix = 0;
+    unsigned long long above = 0;
+    int done_bits = 0;
+    bool all_fit = false;
+    for (int pass = 0; pass < 3 && !all_fit; ++pass) {
+      const int nb = 1 << digit_bits(pass), shift = digit_shift(pass);
+      // A probability is a 39-bit fixed-point mass; it is added as three 13-bit pieces with native
+      // 32-bit shared atomics (64-bit ones are compare-and-swap loops, slow where bins are hot).
+      // A piece sum stays under 2^32 for rows of up to 2^19 entries.
+      unsigned int* pieces = reinterpret_cast<unsigned int*>(hist + kBins);   // [3][kBins]
+      for (int b = threadIdx.x; b < 3 * kBins; b += blockDim.x) pieces[b] = 0;
       __syncthreads();
-      const uint32_t prefix = sh_prefix;
-      const int shift = 8 * pass;
-      if (!sh_done) {
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-          const float v = row[i];
-          const uint32_t key = order_key(v);
-          if (key < k_key || v != v) continue;
-          const bool match = (pass == 3) || ((key >> (shift + 8)) == (prefix >> (shift + 8)));
-          if (match) {
-            const double p = (double)(expf((v - mx) * inv_t) * inv_z);
-            atomicAdd(&hist[(key >> shift) & 255u], (unsigned long long)(p * kFixedOne));
-          }
+      for_each_entry(row, vocab, [&](float v, int) {
+        const uint32_t key = order_key(v);
+        if (key < k_key || v != v) return;
+        if (done_bits == 0 || (key >> (32 - done_bits)) == (prefix >> (32 - done_bits))) {
+          const unsigned long long mass = __float2ull_rz(expf((v - mx) * inv_t) * inv_z * kFixedOneF);
+          const int b = (key >> shift) & (nb - 1);
+          if (mass & 0x1fffull) atomicAdd(&pieces[b], (unsigned int)(mass & 0x1fffull));
+          if ((mass >> 13) & 0x1fffull) atomicAdd(&pieces[kBins + b], (unsigned int)((mass >> 13) & 0x1fffull));
+          if (mass >> 26) atomicAdd(&pieces[2 * kBins + b], (unsigned int)(mass >> 26));
         }
+      });
+      __syncthreads();
+      for (int b = threadIdx.x; b < nb; b += blockDim.x)
+        hist[b] = (unsigned long long)pieces[b] + ((unsigned long long)pieces[kBins + b] << 13) +
+                  ((unsigned long long)pieces[2 * kBins + b] << 26);
+      __syncthreads();
+      int chosen;
+      unsigned long long new_above;
+      find_crossing(hist, nb, above, limit, warp_totals, &sh_pick, &sh_above_pick, &chosen, &new_above);
+      if (chosen < 0) {
+        // Only possible in the first pass (later passes split a bin whose mass is already known
+        // to cross the limit, and the fixed-point masses add up exactly): the whole row fits
+        // under top_p, nothing is dropped.
+        all_fit = true;
+        prefix = 0;
+      } else {
+        above = new_above;
+        prefix |= (uint32_t)chosen << shift;
+        done_bits += digit_bits(pass);
       }
-      __syncthreads();
-      if (threadIdx.x == 0 && !sh_done) {
-        unsigned long long above = sh_above;
-        int chosen = -1;
-        for (int b = 255; b >= 0; --b) {
-          if (above + hist[b] > limit) {
-            chosen = b;
-            break;
-          }
-          above += hist[b];
-        }
-        if (chosen < 0) {
-          // Only possible in the first pass (later passes split a bin whose mass is already
-          // known to cross the limit, and the fixed-point masses add up exactly): the whole
-          // row fits under top_p, nothing is dropped.
-          sh_done = 1;
-          sh_prefix = 0u;
-        } else {
-          sh_above = above;
-          sh_prefix = prefix | ((uint32_t)chosen << shift);
-        }
-      }
-      __syncthreads();
     }
-    p_key = sh_prefix;
+    p_key = prefix;
     // Either nothing is dropped (p_key 0, equal kept), or p_key is the exact key whose entries
     // carry the sum past top_p: they are dropped unless nothing lies above them (the first
     // entry is always kept).
-    keep_equal = sh_done ? true : (sh_above == 0);
-    __syncthreads();
+    keep_equal = all_fit ? 1u : (above == 0 ? 1u : 0u);
   }
+  if (threadIdx.x == 0) cuts[r] = Cut{k_key, p_key, keep_equal, want_p ? 1u : 0u};
+}
 
-  // ---- 4. the draw ---------------------------------------------------------------
+// The draw, spread over kChunks blocks per row: each finds the best perturbed logit of its slice
+// among the entries the cut keeps (greedy rows: the plain maximum); a second kernel merges.
+// argmax_i (l_i / T + Gumbel_i) needs neither the maximum nor the normaliser.
+constexpr int kDrawChunks = 32;
+
+__global__ void __launch_bounds__(kThreads)
+sample_draw_partial_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
+                           const float* __restrict__ temperature, const float* __restrict__ top_p,
+                           const unsigned long long* __restrict__ seed,
+                           const unsigned long long* __restrict__ draw_index, const Cut* __restrict__ cuts,
+                           float* __restrict__ part_v, int32_t* __restrict__ part_i) {
+  __shared__ ArgMax scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * row_stride;
+  const float temp = temperature[r];
+  const bool greedy = !(temp > 0.f) && !(top_p[r] > 0.f);
+  const float inv_t = temp > 0.f ? 1.0f / temp : 1.0f;
+  const Cut cut = cuts[r];
   const unsigned long long sd = seed[r], ctr = draw_index[r];
   const uint2 key2 = make_uint2((uint32_t)sd, (uint32_t)(sd >> 32));
+  const int per = (vocab + kDrawChunks - 1) / kDrawChunks;
+  const int lo = blockIdx.y * per, hi = min(vocab, lo + per);
   ArgMax a;
   a.v = 0.f;
   a.i = -1;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
     const float v = row[i];
-    const uint32_t key = order_key(v);
-    if (v != v || key < k_key) continue;
-    if (tp < 1.0f && !(key > p_key || (keep_equal && key == p_key))) continue;
-    const uint4 rnd = philox4x32(make_uint4((uint32_t)i, (uint32_t)ctr, (uint32_t)(ctr >> 32), 0x59414c49u), key2);
-    const float u = uniform_open(rnd.x);
+    if (v != v) continue;
     ArgMax b;
-    b.v = (v - mx) * inv_t - logf(-logf(u));  // log p_i - log e_i, up to a constant
     b.i = i;
+    if (greedy) {
+      b.v = v;
+    } else {
+      const uint32_t key = order_key(v);
+      if (key < cut.k_key) continue;
+      if (cut.use_p && !(key > cut.p_key || (cut.keep_equal && key == cut.p_key))) continue;
+      const uint4 rnd = philox4x32(make_uint4((uint32_t)i, (uint32_t)ctr, (uint32_t)(ctr >> 32), 0x59414c49u), key2);
+      b.v = v * inv_t - logf(-logf(uniform_open(rnd.x)));     // log p_i - log e_i, up to a constant
+    }
     a = better(a, b);
   }
   a = block_argmax(a, scratch);
-  if (threadIdx.x == 0) out[r] = a.i < 0 ? 0 : a.i;
+  if (threadIdx.x == 0) {
+    part_v[r * kDrawChunks + blockIdx.y] = a.v;
+    part_i[r * kDrawChunks + blockIdx.y] = a.i;
+  }
 }
 
 }  // namespace
@@ -344,11 +474,29 @@ YALIS_API int yalis_argmax(const float* logits, long long row_stride, int n_rows
                       (const int32_t*)part_i, out);
 }
 
+// scratch: n_rows * (64 + 4) 32-bit words (partial results of the draw, then the cuts).
 YALIS_API int yalis_sample(const float* logits, long long row_stride, int n_rows, int vocab, const float* temperature,
                            const int32_t* top_k, const float* top_p, const unsigned long long* seed,
-                           const unsigned long long* draw_index, int32_t* out, cudaStream_t stream) {
+                           const unsigned long long* draw_index, int32_t* out, float* scratch, cudaStream_t stream) {
+  static_assert(kDrawChunks == kArgmaxChunks, "the merge kernel is shared with argmax");
   if (n_rows <= 0) return YALIS_OK;
-  if (vocab <= 0) return YALIS_ERR_SHAPE;
-  return yalis_launch(sample_kernel, dim3(n_rows), dim3(kThreads), 0, stream, logits, row_stride, vocab, temperature,
-                      top_k, top_p, seed, draw_index, out);
+  if (vocab <= 0 || vocab > (1 << 19) || scratch == nullptr) return YALIS_ERR_SHAPE;   // see the piece sums of top-p
+  float* part_v = scratch;
+  int32_t* part_i = reinterpret_cast<int32_t*>(scratch + (size_t)n_rows * kDrawChunks);
+  Cut* cuts = reinterpret_cast<Cut*>(scratch + (size_t)n_rows * 2 * kDrawChunks);
+  const size_t smem = (size_t)kBins * (sizeof(unsigned long long) + 3 * sizeof(unsigned int));
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(sample_cut_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return YALIS_ERR_LAUNCH;
+    configured = true;
+  }
+  int st = yalis_launch(sample_cut_kernel, dim3(n_rows), dim3(kThreads), smem, stream, logits, row_stride, vocab,
+                        temperature, top_k, top_p, cuts);
+  if (st != YALIS_OK) return st;
+  st = yalis_launch(sample_draw_partial_kernel, dim3(n_rows, kDrawChunks), dim3(kThreads), 0, stream, logits, row_stride,
+                    vocab, temperature, top_p, seed, draw_index, (const Cut*)cuts, part_v, part_i);
+  if (st != YALIS_OK) return st;
+  return yalis_launch(argmax_merge_kernel, dim3(n_rows), dim3(32), 0, stream, (const float*)part_v,
+                      (const int32_t*)part_i, out);
 }

@@ -40,6 +40,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     name = "sample"
     _check_logits(name, logits)
     rows, vocab = logits.shape
+    need(vocab <= 1 << 19, name, f"rows of at most {1 << 19} logits are supported, got {vocab}")
     need_cuda(name, temperature, top_k, top_p, seed, draw_index, out)
     for t, dt in ((temperature, torch.float32), (top_k, torch.int32), (top_p, torch.float32), (seed, torch.int64),
                   (draw_index, torch.int64)):
@@ -47,6 +48,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     need(out.dtype == torch.int32 and out.shape == (rows,) and out.is_contiguous(), name, "bad out tensor")
+    scratch = torch.empty((rows * 68,), dtype=torch.float32, device=logits.device)   # partial draws and the cuts
     check(lib().yalis_sample(ptr(logits), i64(logits.stride(0)), i32(rows), i32(vocab), ptr(temperature), ptr(top_k),
-                             ptr(top_p), ptr(seed), ptr(draw_index), ptr(out), stream()), name)
+                             ptr(top_p), ptr(seed), ptr(draw_index), ptr(out), ptr(scratch), stream()), name)
     return out
