@@ -183,7 +183,7 @@ def main() -> int:
     step_bytes = numbers["weight_bytes_per_step"] + args.batch * main_r["kv_tokens"] * numbers["kv_bytes_per_token"]
     achieved = step_bytes / (main_r["ms_per_step"] / 1e3) / 1e9
     line = {
-        "metric": "decode tok/s (Llama-3-8B shape, batch 8, 1024-token prompts)",
+        "metric": f"decode tok/s (Llama-3-8B shape, batch {args.batch}, {PROMPT_LEN}-token prompts)",
         "value": round(main_r["tok_s"], 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main_r["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: uniform random token ids, random weights N(0, 0.02)", "impl": "ours",

@@ -424,8 +424,8 @@ def test_gemm_wstream_tcgen05(m, n, k):
 
 @pytest.mark.parametrize("nh, g, hs, page", [(32, 8, 128, 16), (8, 2, 64, 8), (4, 4, 64, 32), (16, 1, 128, 64), (6, 2, 192, 16),
                                              (2, 1, 256, 16), (5, 5, 128, 16)])
-@pytest.mark.parametrize("splits", [1, 3, 8])
-def test_decode_attention_tma_against_plain_and_generic(nh, g, hs, page, splits):
+@pytest.mark.parametrize("splits, early", [(1, False), (3, True), (8, False), (8, True), (1, True), (11, True), (20, False)])
+def test_decode_attention_tma_against_plain_and_generic(nh, g, hs, page, splits, early):
     """The TMA-fed decode kernel: lengths around tile and page edges, pools poisoned with NaN
     where nothing was written, against the plain float32 attention and the exact kernel."""
     from yalis_b200.ops.attention import decode_attention_tma, paged_attention_generic
@@ -438,7 +438,9 @@ def test_decode_attention_tma_against_plain_and_generic(nh, g, hs, page, splits)
     positions, q_start, req = i32([l - 1 for l in lens]), i32(list(range(len(lens) + 1))), i32(list(range(len(lens))))
     qd = q.view(-1, nh * hs).to(DEV)
     flag = torch.zeros(1, dtype=torch.int32, device=DEV)
-    out = decode_attention_tma(qd, k_pool, v_pool, positions, q_start, table, nh, g, hs, n_splits=splits, error_flag=flag)
+    torch.cuda.synchronize()      # early fetching wants the pool and the index arrays complete before the launch
+    out = decode_attention_tma(qd, k_pool, v_pool, positions, q_start, table, nh, g, hs, n_splits=splits, error_flag=flag,
+                               early_fetch=early)
     assert int(flag) == 0 and not torch.isnan(out.float()).any()
     ref_gen = paged_attention_generic(qd, k_pool, v_pool, positions, req, table, nh, g, hs)
     torch.testing.assert_close(out.float(), ref_gen.float(), rtol=2e-2, atol=2e-2)
@@ -461,8 +463,10 @@ def test_decode_attention_tma_far_key_and_padding_requests():
         qq = torch.cat([q, torch.zeros(2, nh * hs)]).to(torch.bfloat16).to(DEV)
         out = torch.full((3, nh * hs), 7.0, dtype=torch.bfloat16, device=DEV)
         flag = torch.zeros(1, dtype=torch.int32, device=DEV)
-        decode_attention_tma(qq, k_pool, v_pool, i32([l - 1, 0, 0]), i32([0, 1, 1, 1]), table, nh, g, hs, n_splits=6,
-                             error_flag=flag, out=out)
+        pos, qs = i32([l - 1, 0, 0]), i32([0, 1, 1, 1])
+        torch.cuda.synchronize()
+        decode_attention_tma(qq, k_pool, v_pool, pos, qs, table, nh, g, hs, n_splits=6, error_flag=flag, out=out,
+                             early_fetch=target % 2 == 0)
         got = out[0].float().cpu().view(nh, hs)
         for h in range(nh):
             assert torch.allclose(got[h], vs[0][target, h // (nh // g)].to(torch.bfloat16).float(), atol=6e-2), (target, h)

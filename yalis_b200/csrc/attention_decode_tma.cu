@@ -42,6 +42,8 @@ struct DecParams {
   int nh, g, per;
   float scale_log2;
   int n_splits;
+  int cluster_merge;           // 1: the splits of a (request, KV head) are one cluster and merge through shared memory
+  int early_fetch;             // 1: keys below the queries' positions and the index arrays are settled (see the entry point)
   float* part_o;               // [N, nh, n_splits, HS]
   float* part_ml;              // [N, nh, n_splits, 2]
   int32_t* tickets;            // [R * g]
@@ -98,6 +100,32 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
 }
+constexpr int kMaxCluster = 8;    // portable cluster size: the most splits merged through shared memory
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, int rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float2 ld_cluster_f2(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Four results scaled and rounded to bfloat16, one 8-byte store.
+__device__ __forceinline__ void store_bf16x4(__nv_bfloat16* dst, float4 v, float scale) {
+  uint2 w;
+  w.x = pack_bf16(v.x * scale, v.y * scale);
+  w.y = pack_bf16(v.z * scale, v.w * scale);
+  *reinterpret_cast<uint2*>(dst) = w;
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CWARPS * 32) : "memory"); }
 
 // Byte offset of element (row, dim) inside a swizzled tile [HS/64 halves][BN rows][128 bytes].
@@ -124,12 +152,17 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   uint64_t* empty = full + STAGES;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + STAGES);
   int* s_last = const_cast<int*>(abort_flag) + 1;
+  constexpr int VEC = HS / 4;                  // float4 groups of a row
+  // after the tiles: per-warp results in k_s, their (max, sum) in v_s, then the block's merged result
+  float* co = reinterpret_cast<float*>(v_s + 1024);          // [16][HS] merged, unnormalised
+  float* cml = co + 16 * HS;                                  // [16][2] max and sum
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int req = blockIdx.x / p.g, kvh = blockIdx.x - req * p.g;
   const int split = blockIdx.y;
-  if (threadIdx.x == 0) {
+  const bool is_producer = threadIdx.x == CWARPS * 32;
+  if (is_producer) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], CWARPS);
@@ -138,12 +171,59 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+
+  int armed = 0;
+  // One tile: wait for the stage to be free, then one box copy per page and 64-column half.
+  auto issue_tile = [&](int it, int tile_lo, int hi_key, const int32_t* bt) -> bool {
+    const int pages_per_tile = BN / p.page_size;
+    const uint32_t page_bytes = (uint32_t)p.page_size * HS * 2;
+    const int s = it % STAGES;
+    const uint32_t ph = (it / STAGES) & 1;
+    if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) return false;
+    const int key0 = (tile_lo + it) * BN;
+    const int n_pages = min(pages_per_tile, (hi_key - key0) / p.page_size + 1);
+    mbar_expect_tx(&full[s], 2u * page_bytes * (uint32_t)n_pages);
+    for (int i = 0; i < n_pages; ++i) {
+      const int pi = key0 / p.page_size + i;
+      int page = pi < p.table_width ? bt[pi] : -1;
+      if (page < 0 || page >= p.num_pages) {   // a visible key without a page: a caller's bug
+        if (p.error) atomicExch(p.error, 1);
+        page = 0;
+      }
+      const int y = (page * p.g + kvh) * p.page_size;
+#pragma unroll
+      for (int h = 0; h < H2; ++h) {
+        const int off = h * (BN * 128) + i * p.page_size * 128;
+        tma_load_2d(k_s + s * TILE_BYTES + off, &map_k, h * 64, y, &full[s]);
+        tma_load_2d(v_s + s * TILE_BYTES + off, &map_v, h * 64, y, &full[s]);
+      }
+    }
+    armed = it + 1;
+    return true;
+  };
+
+  if (p.early_fetch && is_producer) {
+    // Tiles that end below the query's position hold keys of earlier steps only, and the caller
+    // promises that the step's index arrays were complete before the preceding kernel began:
+    // fetch them while that kernel (which writes this step's key and value) is still running.
+    const int tok = p.q_start[req];
+    if (p.q_start[req + 1] - tok > 0) {
+      const int pos = p.positions[tok];
+      const int total = pos / BN + 1;
+      const int per_split = (total + p.n_splits - 1) / p.n_splits;
+      const int tile_lo = split * per_split;
+      const int early = min(min(total - 1, tile_lo + per_split) - tile_lo, STAGES);
+      const int32_t* bt = p.block_table + (size_t)req * p.table_width;
+      for (int it = 0; it < early; ++it)
+        if (!issue_tile(it, tile_lo, pos, bt)) break;
+    }
+  }
   pdl_wait();
   __syncthreads();
 
   const int tok = p.q_start[req];
   const int n_tok = p.q_start[req + 1] - tok;
-  if (n_tok <= 0) return;                      // padding request (uniform for the block)
+  if (n_tok <= 0) return;                      // padding request (uniform for the block; nothing was fetched)
   const int pos = p.positions[tok];
   const int hi_key = pos;
   const int total = hi_key / BN + 1;
@@ -153,36 +233,11 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int n_tiles = max(0, tile_hi - tile_lo);
   const int32_t* bt = p.block_table + (size_t)req * p.table_width;
 
-  int armed = 0;
   if (warp == CWARPS) {
     // ---- producer -------------------------------------------------------------------------
     if (lane == 0) {
-      const int pages_per_tile = BN / p.page_size;
-      const uint32_t page_bytes = (uint32_t)p.page_size * HS * 2;
-      for (int it = 0; it < n_tiles; ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
-        const int key0 = (tile_lo + it) * BN;
-        const int n_pages = min(pages_per_tile, (hi_key - key0) / p.page_size + 1);
-        mbar_expect_tx(&full[s], 2u * page_bytes * (uint32_t)n_pages);
-        for (int i = 0; i < n_pages; ++i) {
-          const int pi = key0 / p.page_size + i;
-          int page = pi < p.table_width ? bt[pi] : -1;
-          if (page < 0 || page >= p.num_pages) {   // a visible key without a page: a caller's bug
-            if (p.error) atomicExch(p.error, 1);
-            page = 0;
-          }
-          const int y = (page * p.g + kvh) * p.page_size;
-#pragma unroll
-          for (int h = 0; h < H2; ++h) {
-            const int off = h * (BN * 128) + i * p.page_size * 128;
-            tma_load_2d(k_s + s * TILE_BYTES + off, &map_k, h * 64, y, &full[s]);
-            tma_load_2d(v_s + s * TILE_BYTES + off, &map_v, h * 64, y, &full[s]);
-          }
-        }
-        armed = it + 1;
-      }
+      for (int it = armed; it < n_tiles; ++it)
+        if (!issue_tile(it, tile_lo, hi_key, bt)) break;
     }
     __syncwarp();
   } else {
@@ -323,58 +378,135 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       }
     }
     consumer_sync();
-    for (int e = threadIdx.x; e < n_rows * HS; e += CWARPS * 32) {
-      const int r = e / HS, d = e - r * HS;
-      float mm = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < CWARPS; ++w) mm = fmaxf(mm, mml[(w * 16 + r) * 2]);
-      float ll = 0.f, acc = 0.f;
+    // The block's result: its four warps merged, four dims per thread.
+    for (int e = threadIdx.x; e < n_rows * VEC; e += CWARPS * 32) {
+      const int r = e / VEC, d = (e - r * VEC) * 4;
+      float mw[CWARPS], mm = -INFINITY;
 #pragma unroll
       for (int w = 0; w < CWARPS; ++w) {
-        const float m = mml[(w * 16 + r) * 2];
-        const float f = (m == -INFINITY) ? 0.f : exp2f(m - mm);
+        mw[w] = mml[(w * 16 + r) * 2];
+        mm = fmaxf(mm, mw[w]);
+      }
+      float ll = 0.f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int w = 0; w < CWARPS; ++w) {
+        const float f = (mw[w] == -INFINITY) ? 0.f : exp2f(mw[w] - mm);
         ll += mml[(w * 16 + r) * 2 + 1] * f;
-        acc += mo[((size_t)w * 16 + r) * HS + d] * f;
+        const float4 v = *reinterpret_cast<const float4*>(mo + ((size_t)w * 16 + r) * HS + d);
+        acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
       }
       const int head = kvh * p.per + r;
       if (p.n_splits == 1) {
-        p.out[(size_t)tok * p.out_stride + (size_t)head * HS + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+        store_bf16x4(p.out + (size_t)tok * p.out_stride + (size_t)head * HS + d, acc, ll > 0.f ? 1.0f / ll : 0.f);
+      } else if (p.cluster_merge) {
+        *reinterpret_cast<float4*>(co + r * HS + d) = acc;
+        if (d == 0) *reinterpret_cast<float2*>(cml + r * 2) = make_float2(mm, ll);
       } else {
         const size_t slot = ((size_t)tok * p.nh + head) * p.n_splits + split;
-        p.part_o[slot * HS + d] = acc;
-        if (d == 0) {
-          p.part_ml[slot * 2] = mm;
-          p.part_ml[slot * 2 + 1] = ll;
-        }
+        *reinterpret_cast<float4*>(p.part_o + slot * HS + d) = acc;
+        if (d == 0) *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(mm, ll);
       }
     }
-    if (p.n_splits > 1) {
+    if (p.n_splits > 1 && !p.cluster_merge) {
+      // ---- splits merged through global memory: the last block to arrive does it ------------
       __threadfence();
       consumer_sync();
       if (threadIdx.x == 0) *s_last = (atomicAdd(&p.tickets[blockIdx.x], 1) == p.n_splits - 1) ? 1 : 0;
       consumer_sync();
       if (*s_last) {
         __threadfence();
-        const volatile float* ml = p.part_ml;
-        const volatile float* po = p.part_o;
-        for (int e = threadIdx.x; e < n_rows * HS; e += CWARPS * 32) {
-          const int r = e / HS, d = e - r * HS;
-          const int head = kvh * p.per + r;
-          const size_t sb = ((size_t)tok * p.nh + head) * p.n_splits;
+        // The other splits' results were written by other blocks: read them past the L1 (ld.global.cg),
+        // many loads in flight at once.  First the (max, sum) pairs of every (row, split) into shared
+        // memory, turned into the weight of each split; then the weighted sum over splits, in split order.
+        const int ns = p.n_splits;
+        float* w_s = reinterpret_cast<float*>(k_s);            // [n_rows][ns] max, then weight
+        float* l_s = w_s + 16 * 64;                             // [n_rows][ns] sums
+        float* inv_s = l_s + 16 * 64;                           // [n_rows] 1 / total
+        for (int e = threadIdx.x; e < n_rows * ns; e += CWARPS * 32) {
+          const int r = e / ns, sp = e - r * ns;
+          const size_t slot = ((size_t)tok * p.nh + kvh * p.per + r) * ns + sp;
+          const float2 v = __ldcg(reinterpret_cast<const float2*>(p.part_ml + slot * 2));
+          w_s[e] = v.x;
+          l_s[e] = v.y;
+        }
+        consumer_sync();
+        if (threadIdx.x < n_rows) {
+          const int r = threadIdx.x;
           float mm = -INFINITY;
-          for (int sp = 0; sp < p.n_splits; ++sp) mm = fmaxf(mm, ml[(sb + sp) * 2]);
-          float ll = 0.f, acc = 0.f;
-          for (int sp = 0; sp < p.n_splits; ++sp) {
-            const float m = ml[(sb + sp) * 2];
+          for (int sp = 0; sp < ns; ++sp) mm = fmaxf(mm, w_s[r * ns + sp]);
+          float ll = 0.f;
+          for (int sp = 0; sp < ns; ++sp) {
+            const float m = w_s[r * ns + sp];
             const float f = (m == -INFINITY) ? 0.f : exp2f(m - mm);
-            ll += ml[(sb + sp) * 2 + 1] * f;
-            acc += po[(sb + sp) * HS + d] * f;
+            w_s[r * ns + sp] = f;
+            ll += l_s[r * ns + sp] * f;
           }
-          p.out[(size_t)tok * p.out_stride + (size_t)head * HS + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+          inv_s[r] = ll > 0.f ? 1.0f / ll : 0.f;
+        }
+        consumer_sync();
+        for (int e = threadIdx.x; e < n_rows * VEC; e += CWARPS * 32) {
+          const int r = e / VEC, d = (e - r * VEC) * 4;
+          const int head = kvh * p.per + r;
+          const float* po = p.part_o + ((size_t)tok * p.nh + head) * ns * HS + d;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int sp0 = 0; sp0 < ns; sp0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              v[j] = sp0 + j < ns ? __ldcg(reinterpret_cast<const float4*>(po + (size_t)(sp0 + j) * HS)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (sp0 + j < ns) {
+                const float f = w_s[r * ns + sp0 + j];
+                acc.x += v[j].x * f; acc.y += v[j].y * f; acc.z += v[j].z * f; acc.w += v[j].w * f;
+              }
+            }
+          }
+          store_bf16x4(p.out + (size_t)tok * p.out_stride + (size_t)head * HS + d, acc, inv_s[r]);
         }
         if (threadIdx.x == 0) p.tickets[blockIdx.x] = 0;
       }
     }
+  }
+
+  if (p.n_splits > 1 && p.cluster_merge) {
+    // ---- splits merged through distributed shared memory: the blocks of a (request, KV head)
+    // form one cluster; each reads every block's merged result and finishes its share of the
+    // (row, dim) outputs, summing in split order.
+    cluster_sync_all();
+    if (warp < CWARPS) {
+      const int ns = p.n_splits, n_rows = p.per;
+      const int n_vec = n_rows * VEC;
+      const int chunk = (n_vec + ns - 1) / ns;
+      const int lo = split * chunk, hi = min(n_vec, lo + chunk);
+      const uint32_t co_a = smem_u32(co), cml_a = smem_u32(cml);
+      for (int e = lo + threadIdx.x; e < hi; e += CWARPS * 32) {
+        const int r = e / VEC, d = (e - r * VEC) * 4;
+        float2 ml[kMaxCluster];
+        float mm = -INFINITY;
+#pragma unroll
+        for (int sp = 0; sp < kMaxCluster; ++sp) {
+          ml[sp] = sp < ns ? ld_cluster_f2(map_to_cta(cml_a + (uint32_t)r * 8u, sp)) : make_float2(-INFINITY, 0.f);
+          mm = fmaxf(mm, ml[sp].x);
+        }
+        float4 v[kMaxCluster];
+#pragma unroll
+        for (int sp = 0; sp < kMaxCluster; ++sp)
+          v[sp] = sp < ns ? ld_cluster_f4(map_to_cta(co_a + (uint32_t)(r * HS + d) * 4u, sp)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float ll = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int sp = 0; sp < kMaxCluster; ++sp) {
+          const float f = (ml[sp].x == -INFINITY) ? 0.f : exp2f(ml[sp].x - mm);
+          ll += ml[sp].y * f;
+          acc.x += v[sp].x * f; acc.y += v[sp].y * f; acc.z += v[sp].z * f; acc.w += v[sp].w * f;
+        }
+        const int head = kvh * p.per + r;
+        store_bf16x4(p.out + (size_t)tok * p.out_stride + (size_t)head * HS + d, acc, ll > 0.f ? 1.0f / ll : 0.f);
+      }
+    }
+    cluster_sync_all();                                     // nobody leaves while its memory may still be read
   }
 
   // ---- exit: on an abort wait (bounded) for copies in flight so none lands after the block ---
@@ -433,6 +565,9 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int
   }
   dim3 grid(n_requests * p.g, p.n_splits);
   if (grid.y > 65535) return YALIS_ERR_SHAPE;
+  if (p.cluster_merge)
+    return yalis_launch_cluster(decode_attention_tma_kernel<HS>, grid, dim3(kThreads), dim3(1, p.n_splits, 1), smem, stream,
+                                mk, mv, p);
   return yalis_launch(decode_attention_tma_kernel<HS>, grid, dim3(kThreads), smem, stream, mk, mv, p);
 }
 
@@ -445,21 +580,28 @@ YALIS_API int yalis_decode_attention_tma_supports(int hs, int page_size, int per
   return (hs_ok && page_ok && per >= 1 && per <= 16) ? 1 : 0;
 }
 
-// One query token per request.  scratch: n_tokens*nh*n_splits*(hs+2) floats and tickets: n_requests*g zeroed
-// int32 when n_splits > 1 (as for yalis_paged_attention_mma).  error: device int32 raised on a timed-out wait or
+// One query token per request.  Up to 8 splits are merged through distributed shared memory (the splits of a
+// (request, KV head) are launched as one thread-block cluster); more go through global memory and need
+// scratch: n_tokens*nh*n_splits*(hs+2) floats and tickets: n_requests*g zeroed int32 (as for
+// yalis_paged_attention_mma).  error: device int32 raised on a timed-out wait or
 // an unmapped page.
+// early_fetch = 1 lets a block fetch the tiles that lie wholly below its query's position before the preceding
+// kernel on the stream has finished (programmatic dependent launch).  The caller then promises that those keys and
+// values, positions, q_start and the block table were written before the preceding kernel began - true inside a
+// model step, where a host copy brings the index arrays and only this step's token is written to the pool.
 YALIS_API int yalis_decode_attention_tma(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
                                          const void* v_pool, const int32_t* positions, const int32_t* q_start,
                                          const int32_t* block_table, int table_width, int page_size, int num_pages,
                                          int n_tokens, int n_requests, int nh, int g, int hs, float scale,
-                                         int n_splits, float* scratch, int32_t* tickets, int32_t* error,
-                                         cudaStream_t stream) {
+                                         int n_splits, int early_fetch, float* scratch, int32_t* tickets,
+                                         int32_t* error, cudaStream_t stream) {
   if (n_tokens <= 0 || n_requests <= 0) return YALIS_OK;
-  if (g <= 0 || nh % g != 0 || n_splits < 1) return YALIS_ERR_SHAPE;
+  if (g <= 0 || nh % g != 0 || n_splits < 1 || n_splits > 64) return YALIS_ERR_SHAPE;   // the merge stages 64 splits
   if (!yalis_decode_attention_tma_supports(hs, page_size, nh / g)) return YALIS_ERR_SHAPE;
   if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) return YALIS_ERR_ALIGN;
-  if ((q_stride % 8) || (out_stride % 2)) return YALIS_ERR_ALIGN;
-  if (n_splits > 1 && (scratch == nullptr || tickets == nullptr)) return YALIS_ERR_SHAPE;
+  if ((q_stride % 8) || (out_stride % 4)) return YALIS_ERR_ALIGN;
+  const bool cluster_merge = n_splits > 1 && n_splits <= kMaxCluster;
+  if (n_splits > 1 && !cluster_merge && (scratch == nullptr || tickets == nullptr)) return YALIS_ERR_SHAPE;
   CUtensorMap mk, mv;
   const long long rows = (long long)num_pages * g * page_size;
   if (!make_pool_map(&mk, k_pool, rows, hs, page_size) || !make_pool_map(&mv, v_pool, rows, hs, page_size))
@@ -472,6 +614,8 @@ YALIS_API int yalis_decode_attention_tma(const void* q, int q_stride, void* out,
   p.nh = nh; p.g = g; p.per = nh / g;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.n_splits = n_splits;
+  p.early_fetch = early_fetch ? 1 : 0;
+  p.cluster_merge = cluster_merge ? 1 : 0;
   p.part_o = scratch;
   p.part_ml = scratch ? scratch + (size_t)n_tokens * nh * n_splits * hs : nullptr;
   p.tickets = tickets;

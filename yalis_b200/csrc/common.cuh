@@ -31,7 +31,9 @@ inline int yalis_launch_status() {
 // kernel here: (1) pdl_launch_dependents() and pdl_wait() are executed by every thread
 // before any early return and before the first read of an activation or write of an output,
 // so completion of a kernel implies completion of all kernels before it; (2) only constant
-// inputs (weights) are touched before pdl_wait().
+// inputs (weights) are touched before pdl_wait() - and, where the caller of a kernel says so
+// explicitly, data that was complete before the preceding kernel began (the cache entries
+// of earlier steps and a step's index arrays: the decode attention's early fetch).
 bool yalis_pdl_enabled();   // defined in elementwise.cu; switched by yalis_set_pdl()
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -50,6 +52,27 @@ inline int yalis_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = yalis_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...) == cudaSuccess ? YALIS_OK : YALIS_ERR_LAUNCH;
+}
+
+// The same with the grid divided into thread-block clusters of `cluster` blocks (each a divisor of the grid).
+template <typename... KArgs, typename... Args>
+inline int yalis_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, dim3 cluster, size_t smem,
+                                cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster.x;
+  attr[0].val.clusterDim.y = cluster.y;
+  attr[0].val.clusterDim.z = cluster.z;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = yalis_pdl_enabled() ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...) == cudaSuccess ? YALIS_OK : YALIS_ERR_LAUNCH;
 }
 

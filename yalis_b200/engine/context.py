@@ -44,4 +44,7 @@ class StepContext:
     host: HostStep
     error_flag: Optional[torch.Tensor] = None   # int32 [1]; a kernel sets it on a bad id or page
     decode_only: bool = False                    # every request contributes exactly one token
+    # The index arrays above reached the device by a copy that finished before the step's first kernel, and the
+    # step writes nothing to the cache but its own tokens: kernels may read both ahead of their predecessor.
+    settled: bool = False
     extras: dict = field(default_factory=dict)   # scratch for kernels (split buffers etc.)

@@ -91,7 +91,7 @@ class _Bucket:
             n_tokens=r, n_requests=r, token_ids=self.tokens, positions=d_pos, req_of_token=d_req, q_start=d_qs,
             kv_len=d_kv, slots=d_slots, logit_rows=d_rows, block_tables=d_tables,
             host=HostStep(slots=[], q_start=list(range(r + 1)), ctx_before=[], max_q_len=1, max_kv_len=0),
-            error_flag=engine._error_flag, decode_only=True)
+            error_flag=engine._error_flag, decode_only=True, settled=True)
 
     def fill(self, slots: Sequence[int], lengths: Sequence[int], params: Optional[Sequence[SamplingParams]],
              draws: Optional[Sequence[int]]) -> None:

@@ -250,7 +250,7 @@ class Engine:
             slots=d_sl, logit_rows=d_rows, block_tables=tables,
             host=HostStep(slots=slots, q_start=[int(x) for x in qs], ctx_before=before, max_q_len=max(q_lens),
                           max_kv_len=max_kv),
-            error_flag=self._error_flag, decode_only=all(q == 1 for q in q_lens))
+            error_flag=self._error_flag, decode_only=all(q == 1 for q in q_lens), settled=True)
 
     def _validate(self, slots: Sequence[int], entries: Sequence[StepEntry]) -> None:
         if not entries:

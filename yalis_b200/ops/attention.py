@@ -135,9 +135,14 @@ def decode_tma_supports(head_dim: int, page_size: int, heads_per_group: int) -> 
 def decode_attention_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, positions: torch.Tensor,
                          q_start: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int,
                          head_dim: int, scale: Optional[float] = None, n_splits: int = 1,
-                         error_flag: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         error_flag: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                         early_fetch: bool = False) -> torch.Tensor:
     """Decode attention (one token per request, no window) with TMA-fed K/V tiles; same result as
-    ``paged_attention_mma`` for such a step.  ``q`` is [R, heads*head_dim] (one row per request)."""
+    ``paged_attention_mma`` for such a step.  ``q`` is [R, heads*head_dim] (one row per request).
+
+    ``early_fetch`` lets the kernel read keys below each query's position, ``positions``, ``q_start`` and the
+    block table while the kernel before it on the stream is still running; pass it only when all of those
+    were complete before that kernel began (inside a model step they are)."""
     name = "decode_attention_tma"
     n, r = q.shape[0], q_start.numel() - 1
     req_dummy = positions      # only shapes and dtypes are checked through the common helper
@@ -153,7 +158,7 @@ def decode_attention_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
     scratch = tickets = None
-    if n_splits > 1:
+    if n_splits > 8:            # up to 8 splits merge inside a thread-block cluster and need no scratch memory
         floats = lib().yalis_attention_mma_scratch_floats
         floats.restype = ctypes.c_longlong
         scratch = torch.empty(int(floats(i32(n), i32(num_heads), i32(head_dim), i32(n_splits))), dtype=torch.float32,
@@ -162,8 +167,8 @@ def decode_attention_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
     check(lib().yalis_decode_attention_tma(
         ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(k_pool), ptr(v_pool), ptr(positions), ptr(q_start),
         ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]), i32(k_pool.shape[0]), i32(n), i32(r),
-        i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), i32(n_splits), ptr(scratch), ptr(tickets),
-        ptr(error_flag), stream()), name)
+        i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), i32(n_splits), i32(1 if early_fetch else 0),
+        ptr(scratch), ptr(tickets), ptr(error_flag), stream()), name)
     return out
 
 
@@ -211,8 +216,8 @@ def paged_attention(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     if (qkv.dtype == torch.bfloat16 and USE_DECODE_TMA and ctx.decode_only and ctx.host.max_q_len == 1 and window is None
             and decode_tma_supports(head_dim, k_pool.shape[2], per)):
         return decode_attention_tma(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, num_heads, num_kv_heads,
-                                    head_dim, scale=scale, n_splits=decode_splits(ctx.n_requests, num_kv_heads),
-                                    error_flag=ctx.error_flag)
+                                    head_dim, scale=scale, n_splits=min(8, decode_splits(ctx.n_requests, num_kv_heads)),
+                                    error_flag=ctx.error_flag, early_fetch=bool(getattr(ctx, "settled", False)))
     if (qkv.dtype == torch.bfloat16 and USE_PREFILL_TCGEN05 and window is None and ctx.host.max_q_len >= 16
             and prefill_tcgen05_supports(head_dim, k_pool.shape[2], per)):
         return prefill_attention_tcgen05(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, ctx.host.max_q_len,
