@@ -90,6 +90,21 @@ __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// Sum of the n partial values p[s * stride], added in index order but loaded eight at a time
+// (a load per addition would cost a trip to the L2 for each).
+template <typename TS>
+__device__ __forceinline__ float sum_parts(const TS* __restrict__ p, int n, size_t stride) {
+  float acc = 0.f;
+  for (int s0 = 0; s0 < n; s0 += 8) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = s0 + j < n ? to_f32<TS>(p[(size_t)(s0 + j) * stride]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += v[j];
+  }
+  return acc;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -56,7 +56,7 @@ YALIS_API int yalis_embedding(const void* table, int dtype, const int32_t* ids, 
 // --------------------------------------------------------------------------
 // MAXV: values a thread keeps in registers (the row is read once); 0 = re-read variant for wide rows.
 template <typename T, typename TD, int MAXV>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_delta,
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_delta,
                                    size_t delta_stride, const float* __restrict__ w, T* __restrict__ y,
                                    const int32_t* __restrict__ rows, int width, float eps, int write_back) {
   __shared__ float scratch[32];
@@ -77,11 +77,23 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
       h[v] = c < width ? xr[c] : 0.f;
     }
     if (dr) {
-      for (int s = 0; s < n_delta; ++s) {
+      // Partial sums are added in index order, but loaded a batch at a time: one load per
+      // addition would cost a trip to the L2 for every partial.
+      constexpr int SB = 32 / MAXV;
+      for (int s0 = 0; s0 < n_delta; s0 += SB) {
+        float t[SB][MAXV];
 #pragma unroll
-        for (int v = 0; v < MAXV; ++v) {
-          const int c = threadIdx.x + v * blockDim.x;
-          if (c < width) h[v] += to_f32<TD>(dr[(size_t)s * delta_stride + c]);
+        for (int j = 0; j < SB; ++j) {
+#pragma unroll
+          for (int v = 0; v < MAXV; ++v) {
+            const int c = threadIdx.x + v * blockDim.x;
+            t[j][v] = (s0 + j < n_delta && c < width) ? to_f32<TD>(dr[(size_t)(s0 + j) * delta_stride + c]) : 0.f;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < SB; ++j) {
+#pragma unroll
+          for (int v = 0; v < MAXV; ++v) h[v] += t[j][v];
         }
       }
       if (write_back) {
@@ -121,10 +133,114 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
   }
 }
 
+// Four consecutive values as float32 (16-byte load for float32 data, 8-byte for bfloat16).
+__device__ __forceinline__ float4 load4_f32(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4_f32(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<unsigned*>(&a);
+  u.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+// The same norm for rows whose width is a multiple of four and whose pointers are 16-byte aligned:
+// every thread keeps NV groups of four columns, all loads of a row are in flight at once, and the
+// norm's weight is fetched before the wait for the preceding kernel.
+template <typename T, typename TD, int NV>
+__global__ void __launch_bounds__(1024) add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+                                                               int n_delta, size_t delta_stride,
+                                                               const float* __restrict__ w, T* __restrict__ y,
+                                                               const int32_t* __restrict__ rows, int width, float eps,
+                                                               int write_back) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  const int n4 = width >> 2;
+  float4 wv[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int c = threadIdx.x + v * blockDim.x;
+    wv[v] = c < n4 ? load4_f32(w + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  if (r < 0) return;  // padded row
+  float* xr = x + (size_t)r * width;
+  const TD* dr = delta ? delta + (size_t)r * width : nullptr;
+  T* yr = y + (size_t)i * width;
+  float4 h[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int c = threadIdx.x + v * blockDim.x;
+    h[v] = c < n4 ? load4_f32(xr + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (dr) {
+    constexpr int SB = 8 / NV;       // partial sums loaded per batch; they are added in index order
+    for (int s0 = 0; s0 < n_delta; s0 += SB) {
+      float4 t[SB][NV];
+#pragma unroll
+      for (int j = 0; j < SB; ++j) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          const int c = threadIdx.x + v * blockDim.x;
+          t[j][v] = (s0 + j < n_delta && c < n4) ? load4_f32(dr + (size_t)(s0 + j) * delta_stride + 4 * c)
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < SB; ++j) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          h[v].x += t[j][v].x; h[v].y += t[j][v].y; h[v].z += t[j][v].z; h[v].w += t[j][v].w;
+        }
+      }
+    }
+    if (write_back) {
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        const int c = threadIdx.x + v * blockDim.x;
+        if (c < n4) store4(xr + 4 * c, h[v]);
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) ss += (h[v].x * h[v].x + h[v].y * h[v].y) + (h[v].z * h[v].z + h[v].w * h[v].w);
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)width + eps);
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int c = threadIdx.x + v * blockDim.x;
+    if (c < n4)
+      store4(yr + 4 * c, make_float4((h[v].x * inv) * wv[v].x, (h[v].y * inv) * wv[v].y, (h[v].z * inv) * wv[v].z,
+                                     (h[v].w * inv) * wv[v].w));
+  }
+}
+
 template <typename T, typename TD>
 int launch_add_rmsnorm(float* x, const void* delta, int n_delta, size_t delta_stride, const float* w, void* y,
                         const int32_t* rows, int n_out_rows, int width, float eps, int write_back,
                         cudaStream_t stream) {
+  const uintptr_t ptrs = (uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)y;
+  if (width % 4 == 0 && width <= 16384 && (ptrs & 15) == 0 && delta_stride % 4 == 0) {
+    const int n4 = width / 4;
+    const int vthreads = n4 >= 1024 ? 1024 : (n4 + 31) / 32 * 32;
+    const int nv = (n4 + vthreads - 1) / vthreads;
+#define YALIS_NORM_VEC(V)                                                                                          \
+  return yalis_launch(add_rmsnorm_vec_kernel<T, TD, V>, dim3(n_out_rows), dim3(vthreads), 0, stream, x,            \
+                      (const TD*)delta, n_delta, delta_stride, w, (T*)y, rows, width, eps, write_back)
+    if (nv == 1) YALIS_NORM_VEC(1);
+    else if (nv == 2) YALIS_NORM_VEC(2);
+    else YALIS_NORM_VEC(4);
+#undef YALIS_NORM_VEC
+  }
   const int threads = width >= 4096 ? 1024 : width >= 1024 ? 512 : 256;
   const int per_thread = (width + threads - 1) / threads;
 #define YALIS_NORM_LAUNCH(V)                                                                                  \
@@ -231,11 +347,8 @@ __global__ void rope_kv_write_kernel(const TS* __restrict__ src, int src_stride,
   }
   const TS* row = src + (size_t)t * src_stride + (size_t)head * hs;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    float x1 = 0.f, x2 = 0.f;
-    for (int s = 0; s < n_parts; ++s) {
-      x1 += to_f32<TS>(row[s * part_stride + i]);
-      x2 += to_f32<TS>(row[s * part_stride + i + half]);
-    }
+    const float x1 = sum_parts<TS>(row + i, n_parts, part_stride);
+    const float x2 = sum_parts<TS>(row + i + half, n_parts, part_stride);
     float o1 = x1, o2 = x2;
     if (!is_v && inv_freq) {
       float sn, cs;
@@ -299,11 +412,8 @@ __global__ void rope_kv_write_token_kernel(const TS* __restrict__ src, int src_s
       dst = (is_v ? v_pool : k_pool) + (((size_t)page * g + kvh) * page_size + off) * hs;
     }
     const TS* h = row + (size_t)head * hs;
-    float x1 = 0.f, x2 = 0.f;
-    for (int s = 0; s < n_parts; ++s) {
-      x1 += to_f32<TS>(h[s * part_stride + i]);
-      x2 += to_f32<TS>(h[s * part_stride + i + half]);
-    }
+    const float x1 = sum_parts<TS>(h + i, n_parts, part_stride);
+    const float x2 = sum_parts<TS>(h + i + half, n_parts, part_stride);
     float o1 = x1, o2 = x2;
     if (!is_v && inv_freq) {
       const float c = cs[i], sn = cs[half + i];
