@@ -8,7 +8,8 @@
 // block table and issues one TMA box copy per (page, 64-column half) for K and for V
 // (cp.async.bulk.tensor.2d over the pool seen as a matrix [pages*kv_heads*page_size, head_dim],
 // 128-byte swizzle), completion is counted by an mbarrier per stage, and the four consumer
-// warps only wait, run ldmatrix on the swizzled tiles and mma.sync.  The ring has three stages.
+// warps only wait, run ldmatrix on the swizzled tiles and mma.sync.  The ring has two stages (two
+// blocks per SM keep four tiles in flight, and a block of the next kernel still fits beside them).
 //
 // Limits (the launcher refuses anything else, the caller then uses the cp.async kernel):
 // bfloat16, head_dim a multiple of 64 up to 256, page_size 8, 16, 32 or 64, no window, at most
@@ -27,7 +28,7 @@ namespace {
 constexpr int BN = 64;            // keys per tile
 constexpr int CWARPS = 4;         // consumer warps; warp CWARPS is the producer
 constexpr int kThreads = (CWARPS + 1) * 32;
-constexpr int STAGES = 3;
+constexpr int STAGES = 2;         // the per-warp results reuse the K ring after the tiles: it must hold CWARPS*16*HS floats
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct DecParams {
@@ -143,6 +144,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   constexpr int LDQ = HS + 8;                  // padded Q rows
   constexpr int KSTEPS = HS / 16, DT = HS / 8;
   constexpr int WKEYS = BN / CWARPS;           // 16 keys of a tile per consumer warp
+  static_assert(STAGES * TILE_BYTES >= CWARPS * 16 * HS * 4, "the K ring is reused for the warps' results");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* k_s = base;                                 // [STAGES][TILE_BYTES]
