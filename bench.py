@@ -34,7 +34,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 PRESET = "Llama-3-8B"
 PROMPT_LEN = 1024
 PREFILL_TOKENS = 2048
-PAGE_SIZE = 16
+PAGE_SIZE = 64
 
 
 def load_peaks():
@@ -122,8 +122,8 @@ def reference_arm(args) -> int:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the preset (named in config)")

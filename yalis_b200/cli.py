@@ -48,7 +48,7 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--tokens-to-gen", "--max-new-tokens", dest="tokens_to_gen", type=int, default=512)
     g.add_argument("--no-ignore-eos", action="store_true", help="stop a request at its EOS token")
     e = ap.add_argument_group("engine")
-    e.add_argument("--page-size", type=int, default=16)
+    e.add_argument("--page-size", type=int, default=64)
     e.add_argument("--cache-tokens", type=int, default=None, help="size of the page pool in tokens")
     e.add_argument("--max-tokens-per-step", type=int, default=2048)
     e.add_argument("--chunk", "--prefill-chunk", dest="prefill_chunk", type=int, default=None)

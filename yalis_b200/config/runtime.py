@@ -82,7 +82,7 @@ class InferenceConfig:
                  attention_backend: str = "paged", use_intra_head_parallelism: bool = False,
                  use_paged_kv_caching: bool = True, prestore_kv_cache: bool = True,
                  symmetric_allreduce_strategy: Optional[str] = None,
-                 page_size: int = 16, cache_tokens: Optional[int] = None, max_tokens_per_step: int = 2048,
+                 page_size: int = 64, cache_tokens: Optional[int] = None, max_tokens_per_step: int = 2048,
                  prefill_chunk: Optional[int] = None, seed: int = 1234):
         self.max_batch_size = max_batch_size
         self.max_length = max_length_of_generated_sequences
