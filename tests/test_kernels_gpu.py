@@ -473,12 +473,14 @@ def test_decode_attention_tma_far_key_and_padding_requests():
         assert torch.all(out[1:] == 7.0) and int(flag) == 0
 
 
+@pytest.mark.parametrize("hs", [48, 20, 128])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_rope_kv_write_many_tokens(dtype):
-    """Steps with many tokens take the one-block-per-token variant: same results."""
+def test_rope_kv_write_many_tokens(dtype, hs):
+    """Steps with many tokens take the one-block-per-token variants (four pairs per thread when the
+    head size is a multiple of 8, else one): same results."""
     from yalis_b200.ops.elementwise import rope_kv_write
     from yalis_b200.parts.rotary import inverse_frequencies
-    nh, g, hs, page, n = 6, 2, 48, 8, 333
+    nh, g, page, n = 6, 2, 8, 333
     inv = inverse_frequencies(hs, 10000.0, None)
     qkv = rnd(n, (nh + 2 * g) * hs, dtype=dtype, seed=8)
     pos_list = list(range(5, 5 + n))
@@ -500,6 +502,13 @@ def test_rope_kv_write_many_tokens(dtype):
         p = pos_list[i]
         torch.testing.assert_close(k_pool[int(tab[p // page]), :, p % page].float().cpu(), rk[i], **t)
         assert torch.equal(v_pool[int(tab[p // page]), :, p % page].float().cpu(), src[i, (nh + g) * hs:].view(g, hs).to(dtype).float())
+    # the same rows as three float32 partial sums of a split product
+    parts = torch.stack([qkv.float() * 0.5, qkv.float() * 0.25, qkv.float() * 0.25]).contiguous()
+    k2, v2 = torch.zeros_like(k_pool), torch.zeros_like(v_pool)
+    q2 = rope_kv_write(parts, torch.tensor(pos_list, dtype=torch.int32, device=DEV), torch.zeros(n, dtype=torch.int32, device=DEV),
+                       inv.to(DEV), k2, v2, table, nh, g, hs, out_dtype=dtype, bad_flag=flag)
+    assert int(flag) == 0
+    assert torch.equal(q2, q_out) and torch.equal(k2, k_pool) and torch.equal(v2, v_pool)   # the halves and quarters add exactly
 
 
 @pytest.mark.parametrize("nh, g, hs, page", [(8, 2, 128, 16), (4, 4, 64, 8), (6, 2, 128, 32), (3, 1, 64, 64), (32, 8, 128, 16),

@@ -425,6 +425,75 @@ __global__ void rope_kv_write_token_kernel(const TS* __restrict__ src, int src_s
   }
 }
 
+// The per-token kernel for head sizes that are multiples of 8 and 16-byte aligned rows: a thread
+// rotates four pairs at once (8- or 16-byte loads and stores).
+template <typename T, typename TS>
+__global__ void rope_kv_write_token_vec_kernel(const TS* __restrict__ src, int src_stride, int n_parts, size_t part_stride,
+                                               T* __restrict__ q_out, const int32_t* __restrict__ positions,
+                                               const int32_t* __restrict__ req_of_token,
+                                               const float* __restrict__ inv_freq, T* __restrict__ k_pool,
+                                               T* __restrict__ v_pool, const int32_t* __restrict__ block_table,
+                                               int table_width, int page_size, int num_pages, int nh, int g, int hs,
+                                               int32_t* bad_page) {
+  extern __shared__ __align__(16) float cs[];   // cos[hs/2], sin[hs/2]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int req = req_of_token[t];
+  if (req < 0) return;
+  const int pos = positions[t];
+  const int half = hs >> 1;
+  if (inv_freq) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      float sn, c;
+      sincosf((float)pos * inv_freq[i], &sn, &c);
+      cs[i] = c;
+      cs[half + i] = sn;
+    }
+  }
+  int page = -1, off = 0;
+  if (k_pool != nullptr) {
+    const int page_idx = pos / page_size;
+    off = pos - page_idx * page_size;
+    page = (page_idx < table_width) ? block_table[(size_t)req * table_width + page_idx] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0 && bad_page) atomicExch(bad_page, 1);
+      page = -1;
+    }
+  }
+  __syncthreads();
+  const TS* row = src + (size_t)t * src_stride;
+  const int n_heads = nh + 2 * g;
+  const int quads = half >> 2;
+  for (int e = threadIdx.x; e < n_heads * quads; e += blockDim.x) {
+    const int head = e / quads, i = (e - head * quads) * 4;
+    const bool is_q = head < nh, is_v = head >= nh + g;
+    T* dst;
+    if (is_q) {
+      dst = q_out + ((size_t)t * nh + head) * hs;
+    } else {
+      if (page < 0) continue;
+      const int kvh = is_v ? head - nh - g : head - nh;
+      dst = (is_v ? v_pool : k_pool) + (((size_t)page * g + kvh) * page_size + off) * hs;
+    }
+    const TS* h = row + (size_t)head * hs;
+    float4 x1 = load4_f32(h + i), x2 = load4_f32(h + i + half);
+    for (int s = 1; s < n_parts; ++s) {     // partial sums in index order
+      const float4 a = load4_f32(h + s * part_stride + i), b = load4_f32(h + s * part_stride + i + half);
+      x1.x += a.x; x1.y += a.y; x1.z += a.z; x1.w += a.w;
+      x2.x += b.x; x2.y += b.y; x2.z += b.z; x2.w += b.w;
+    }
+    float4 o1 = x1, o2 = x2;
+    if (!is_v && inv_freq) {
+      const float4 c = *reinterpret_cast<const float4*>(cs + i), sn = *reinterpret_cast<const float4*>(cs + half + i);
+      o1 = make_float4(x1.x * c.x - x2.x * sn.x, x1.y * c.y - x2.y * sn.y, x1.z * c.z - x2.z * sn.z, x1.w * c.w - x2.w * sn.w);
+      o2 = make_float4(x2.x * c.x + x1.x * sn.x, x2.y * c.y + x1.y * sn.y, x2.z * c.z + x1.z * sn.z, x2.w * c.w + x1.w * sn.w);
+    }
+    store4(dst + i, o1);
+    store4(dst + i + half, o2);
+  }
+}
+
 // src_dtype: the model type (n_parts must be 1) or YALIS_F32 partial sums [n_parts, N, src_stride].
 YALIS_API int yalis_rope_kv_write(const void* src, int src_dtype, int src_stride, int n_parts, long long part_stride,
                                   void* q_out, int dtype, const int32_t* positions, const int32_t* req_of_token,
@@ -439,11 +508,21 @@ YALIS_API int yalis_rope_kv_write(const void* src, int src_dtype, int src_stride
   const int threads = per_token ? 256 : (hs / 2 + 31) / 32 * 32;
   const size_t smem = per_token ? (size_t)hs * sizeof(float) : 0;
   if (smem > 48 * 1024) return YALIS_ERR_SHAPE;
+  const uintptr_t ptrs = (uintptr_t)src | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool;
+  const bool vec_ok = hs % 8 == 0 && src_stride % 4 == 0 && part_stride % 4 == 0 && (ptrs & 15) == 0;
 #define YALIS_ROPE_ARGS(TS_)                                                                                         \
   (const TS_*)src, src_stride, n_parts, (size_t)part_stride, (T*)q_out, positions, req_of_token, inv_freq, (T*)k_pool, \
       (T*)v_pool, block_table, table_width, page_size, num_pages, nh, g, hs, bad_page
   YALIS_DISPATCH_DTYPE(
       dtype, T,
+      if (per_token && vec_ok) {
+        if (src_dtype == dtype && n_parts == 1)
+          return yalis_launch(rope_kv_write_token_vec_kernel<T, T>, grid, dim3(threads), smem, stream, YALIS_ROPE_ARGS(T));
+        if (src_dtype == YALIS_F32)
+          return yalis_launch(rope_kv_write_token_vec_kernel<T, float>, grid, dim3(threads), smem, stream,
+                              YALIS_ROPE_ARGS(float));
+        return YALIS_ERR_DTYPE;
+      }
       if (src_dtype == dtype && n_parts == 1) {
         return per_token ? yalis_launch(rope_kv_write_token_kernel<T, T>, grid, dim3(threads), smem, stream,
                                         YALIS_ROPE_ARGS(T))
