@@ -190,7 +190,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int req = blockIdx.y / p.g, kvh = blockIdx.y - req * p.g;
   const int tok0 = p.q_start[req], q_len = p.q_start[req + 1] - tok0;
-  const int t0 = blockIdx.x * p.tokens_per_tile;           // first token of this block within the request
+  // Later query tiles see more keys: they are given to the first blocks, so the light ones fill the tail.
+  const int t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * p.tokens_per_tile;   // first token of this block within the request
   if (t0 >= q_len) return;                                  // uniform: nothing allocated yet
   const int n_tok = min(p.tokens_per_tile, q_len - t0);
   const int n_rows = n_tok * p.per;
