@@ -56,7 +56,7 @@ def attention_decode(args) -> None:
     pos = torch.full((b,), ctx - 1, dtype=torch.int32, device=dev)
     q_start = torch.arange(b + 1, dtype=torch.int32, device=dev)
     req = torch.arange(b, dtype=torch.int32, device=dev)
-    splits = args.splits or decode_splits(b, g)
+    splits = args.splits or (min(8, decode_splits(b, g)) if args.kernel == "tma" else decode_splits(b, g))   # as the engine chooses
     state = {"i": 0}
 
     def fn():
@@ -126,7 +126,7 @@ def prefill(args) -> None:
     cfg = preset(args.preset)
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
-    engine = Engine(config=cfg, seed=0, dtype=args.dtype, page_size=16, cache_tokens=args.tokens + 64, max_slots=2,
+    engine = Engine(config=cfg, seed=0, dtype=args.dtype, page_size=64, cache_tokens=args.tokens + 64, max_slots=2,
                     max_context=args.tokens + 64)
     ms = prefill_bench(engine, args.tokens, warmup=1, iters=args.launches)
     print(f"prefill {args.preset} layers {cfg['num_hidden_layers']} tokens {args.tokens} {args.dtype}: {ms:.3f} ms, "
@@ -143,7 +143,7 @@ def main() -> None:
     a.add_argument("--heads", type=int, default=32)
     a.add_argument("--kv-heads", type=int, default=8)
     a.add_argument("--head-dim", type=int, default=128)
-    a.add_argument("--page-size", type=int, default=16)
+    a.add_argument("--page-size", type=int, default=64)
     a.add_argument("--splits", type=int, default=0)
     a.add_argument("--kernel", default="tma", choices=["tma", "mma"], help="TMA-fed decode kernel or the cp.async one")
     a.add_argument("--launches", type=int, default=8)
@@ -160,7 +160,7 @@ def main() -> None:
     ap_.add_argument("--heads", type=int, default=32)
     ap_.add_argument("--kv-heads", type=int, default=8)
     ap_.add_argument("--head-dim", type=int, default=128)
-    ap_.add_argument("--page-size", type=int, default=16)
+    ap_.add_argument("--page-size", type=int, default=64)
     ap_.add_argument("--kernel", default="tcgen05", choices=["tcgen05", "mma"])
     ap_.add_argument("--launches", type=int, default=4)
     ap_.set_defaults(fn=attention_prefill)
