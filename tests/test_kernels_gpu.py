@@ -422,6 +422,25 @@ def test_gemm_wstream_tcgen05(m, n, k):
     assert int(wstream_error_flag(DEV)) == 0
 
 
+@pytest.mark.parametrize("m, inter, k", [(1, 64, 64), (8, 448, 256), (5, 200, 136), (16, 1000, 72), (17, 130, 512), (64, 320, 192),
+                                         (100, 96, 1024), (256, 192, 64)])
+def test_gemm_wstream_silu_has_the_bits_of_product_then_activation(m, inter, k):
+    """The gated activation fused into the weight-streaming product: tiles of 64 gate and 64 up rows,
+    sizes that end inside a tile, against the unfused pair of kernels (same bits) and float32."""
+    from yalis_b200.ops.linear import gemm_wstream, gemm_wstream_silu, wstream_error_flag
+    from yalis_b200.ops.elementwise import silu_mul
+    x = rnd(m, k, dtype=torch.bfloat16, seed=m + k)
+    w = rnd(2 * inter, k, dtype=torch.bfloat16, seed=inter, scale=1.0 / math.sqrt(k))
+    fused = gemm_wstream_silu(x, w)
+    pair = silu_mul(gemm_wstream(x, w))
+    assert fused.shape == (m, inter) and torch.equal(fused, pair)
+    prod = x.float().cpu() @ w.float().cpu().t()
+    gate, up = prod[:, :inter], prod[:, inter:]
+    ref = gate / (1.0 + torch.exp(-gate)) * up        # the activation of plain.swiglu, written out
+    torch.testing.assert_close(fused.float().cpu(), ref, rtol=3e-2, atol=3e-2)
+    assert int(wstream_error_flag(DEV)) == 0
+
+
 @pytest.mark.parametrize("nh, g, hs, page", [(32, 8, 128, 16), (8, 2, 64, 8), (4, 4, 64, 32), (16, 1, 128, 64), (6, 2, 192, 16),
                                              (2, 1, 256, 16), (5, 5, 128, 16)])
 @pytest.mark.parametrize("splits, early", [(1, False), (3, True), (8, False), (8, True), (1, True), (11, True), (20, False)])

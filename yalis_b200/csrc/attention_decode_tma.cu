@@ -159,7 +159,6 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   float* co = reinterpret_cast<float*>(v_s + 1024);          // [16][HS] merged, unnormalised
   float* cml = co + 16 * HS;                                  // [16][2] max and sum
 
-  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int req = blockIdx.x / p.g, kvh = blockIdx.x - req * p.g;
   const int split = blockIdx.y;
@@ -240,6 +239,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     if (lane == 0) {
       for (int it = armed; it < n_tiles; ++it)
         if (!issue_tile(it, tile_lo, hi_key, bt)) break;
+      pdl_launch_dependents();     // the last tile is on its way: the next kernel's blocks may start filling their rings
     }
     __syncwarp();
   } else {

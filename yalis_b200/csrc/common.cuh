@@ -28,12 +28,16 @@ inline int yalis_launch_status() {
 // attribute: the next kernel in the stream may be scheduled while this one still runs, do
 // work that does not depend on it (set-up, prefetch of weights) and then block in
 // pdl_wait() until this one has completed and its writes are visible.  Rules kept by every
-// kernel here: (1) pdl_launch_dependents() and pdl_wait() are executed by every thread
-// before any early return and before the first read of an activation or write of an output,
-// so completion of a kernel implies completion of all kernels before it; (2) only constant
-// inputs (weights) are touched before pdl_wait() - and, where the caller of a kernel says so
-// explicitly, data that was complete before the preceding kernel began (the cache entries
-// of earlier steps and a step's index arrays: the decode attention's early fetch).
+// kernel here: (1) pdl_wait() is executed by every thread before any early return and before the
+// first read of an activation or write of an output, so completion of a kernel implies completion
+// of all kernels before it; (2) only constant inputs (weights) are touched before pdl_wait() - and,
+// where the caller of a kernel says so explicitly, data that was complete before the preceding
+// kernel began (the cache entries of earlier steps and a step's index arrays: the decode attention's
+// early fetch); (3) pdl_launch_dependents() is called at the top of short kernels, but by the
+// bandwidth-bound ones (weight-streaming product, decode attention) only when a block has requested
+// its last tile: blocks of the next kernels that start earlier fill their rings with bandwidth that
+// this kernel's own tiles still wait for, and hold registers and shared memory that its later
+// blocks need (measured: 9 % of a batch-64 decode step).
 bool yalis_pdl_enabled();   // defined in elementwise.cu; switched by yalis_set_pdl()
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -101,6 +101,8 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 
+__device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }   // as the activation kernel
+
 struct GemmParams {
   void* out;            // splits == 1: [M, N] of out_dtype; splits > 1: float32 [splits, M, N]
   int out_dtype;
@@ -108,6 +110,7 @@ struct GemmParams {
   int M, N, K;
   int splits;
   int kt_per_split;     // K tiles of 64 per split
+  int silu_inter;       // 0, or I: w is [gate (I rows); up (I rows)] and out[m, i] = silu(gate_i) * up_i, [M, I] bfloat16
   int32_t* error;       // set to 1 if a wait ran out
 };
 
@@ -120,7 +123,9 @@ __host__ __device__ constexpr int stages_for() {
               : (NTOK <= 32 ? 5 : NTOK <= 64 ? 4 : NTOK <= 128 ? 3 : 4);
 }
 
-template <int NTOK, bool DEEP>
+// SILU: the gated-activation epilogue (p.silu_inter > 0).  A variant of its own: its extra registers would also
+// be charged to the plain kernel, which then fits once instead of twice beside the attention blocks it follows.
+template <int NTOK, bool DEEP, bool SILU>
 __global__ void __launch_bounds__(kThreads, (DEEP || NTOK > 128) ? 1 : 2)
 gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const GemmParams p) {
@@ -140,14 +145,15 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * TILE_N;
+  // Plain: 128 rows of w from n0.  SiLU mode: 64 gate rows from n0 (tensor-memory lanes 0-63) and the 64
+  // up rows of the same outputs, I further down (lanes 64-127); the map's box is 64 rows then.
+  const int n0 = blockIdx.x * (SILU ? TILE_N / 2 : TILE_N);
   const int split = blockIdx.y;
   const int kt_total = (p.K + TILE_K - 1) / TILE_K;
   const int kt_begin = split * p.kt_per_split;
   const int kt_end = min(kt_total, kt_begin + p.kt_per_split);
   const int n_kt = max(0, kt_end - kt_begin);
 
-  pdl_launch_dependents();      // the next kernel may be scheduled and do its own set-up
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -175,7 +181,12 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const int n_pre = min(n_kt, STAGES);
       for (int kt = 0; kt < n_pre; ++kt) {
         mbar_expect_tx(&full[kt], A_BYTES + B_BYTES);
-        tma_load_2d(a_s + kt * A_BYTES, &map_w, (kt_begin + kt) * TILE_K, n0, &full[kt]);
+        if constexpr (SILU) {
+          tma_load_2d(a_s + kt * A_BYTES, &map_w, (kt_begin + kt) * TILE_K, n0, &full[kt]);
+          tma_load_2d(a_s + kt * A_BYTES + A_BYTES / 2, &map_w, (kt_begin + kt) * TILE_K, p.silu_inter + n0, &full[kt]);
+        } else {
+          tma_load_2d(a_s + kt * A_BYTES, &map_w, (kt_begin + kt) * TILE_K, n0, &full[kt]);
+        }
       }
       armed = n_pre;
       pdl_wait();
@@ -187,10 +198,18 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
         mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
         const int k = (kt_begin + kt) * TILE_K;
-        tma_load_2d(a_s + s * A_BYTES, &map_w, k, n0, &full[s]);
+        if constexpr (SILU) {
+          tma_load_2d(a_s + s * A_BYTES, &map_w, k, n0, &full[s]);
+          tma_load_2d(a_s + s * A_BYTES + A_BYTES / 2, &map_w, k, p.silu_inter + n0, &full[s]);
+        } else {
+          tma_load_2d(a_s + s * A_BYTES, &map_w, k, n0, &full[s]);
+        }
         tma_load_2d(b_s + s * B_BYTES, &map_x, k, 0, &full[s]);
         armed = kt + 1;
       }
+      // This block has asked for its last tile: from here on the next kernel's blocks may be scheduled and
+      // fill their own rings without taking bandwidth from tiles this kernel still waits for.
+      pdl_launch_dependents();
     }
     else pdl_wait();
     __syncwarp();
@@ -224,7 +243,46 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (n_kt > 0 && lane == 0) ok = mbar_wait(acc_full, 0, abort_flag) ? 1 : 0;
     ok = __shfl_sync(0xffffffffu, ok, 0);      // one poller per warp, so the warp stays convergent
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
+    if constexpr (SILU) {
+      // the four warps meet at barriers below: they must agree on whether the accumulator is there
+      uint32_t all_ok;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
+      ok = (int)all_ok;
+    }
+    if (SILU && ok) {
+      // Warps 0 and 1 of the epilogue hold the gate rows, warps 2 and 3 the up rows of the same 64 outputs:
+      // the up values cross through shared memory (the ring is free by now), 16 tokens at a time, two buffers.
+      float* ex = reinterpret_cast<float*>(a_s);            // [2][16 tokens][64 outputs]
+      const int col = (q & 1) * 32 + lane;                   // output within the tile
+      const int n = n0 + col;
+#pragma unroll
+      for (int c0 = 0; c0 < NTOK; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        float* buf = ex + ((c0 >> 4) & 1) * (16 * 64);
+        if (q >= 2) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) buf[i * 64 + col] = __uint_as_float(r[i]);
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (q < 2 && n < p.silu_inter) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int m = c0 + i;
+            if (m < p.M) {
+              // both factors rounded to bfloat16 first: the same bits as the unfused product followed by the
+              // activation kernel
+              const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));
+              const float u = __bfloat162float(__float2bfloat16_rn(buf[i * 64 + col]));
+              reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(silu_f32(g) * u);
+            }
+          }
+        }
+      }
+    } else if (!SILU && ok) {
       const int n = n0 + q * 32 + lane;
 #pragma unroll
       for (int c0 = 0; c0 < NTOK; c0 += 16) {
@@ -310,35 +368,34 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, lo
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int g_force_ring = -1;   // -1: by grid size; 0: always the half-SM ring; 1: always the whole-SM ring (experiments)
-
-template <int NTOK, bool DEEP>
+template <int NTOK, bool DEEP, bool SILU>
 int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t stream) {
   constexpr int STAGES = stages_for<NTOK, DEEP>();
   const size_t smem = 1024 + (size_t)STAGES * (TILE_N * TILE_K * 2 + NTOK * TILE_K * 2) + (2 * STAGES + 1) * 8 + 16;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_wstream_kernel<NTOK, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_wstream_kernel<NTOK, DEEP, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
       return YALIS_ERR_LAUNCH;
     configured = true;
   }
-  dim3 grid((p.N + TILE_N - 1) / TILE_N, p.splits);
-  return yalis_launch(gemm_wstream_kernel<NTOK, DEEP>, grid, dim3(kThreads), smem, stream, mw, mx, p);
+  const int tile_rows = p.silu_inter ? TILE_N / 2 : TILE_N;
+  const int rows = p.silu_inter ? p.silu_inter : p.N;
+  dim3 grid((rows + tile_rows - 1) / tile_rows, p.splits);
+  return yalis_launch(gemm_wstream_kernel<NTOK, DEEP, SILU>, grid, dim3(kThreads), smem, stream, mw, mx, p);
 }
 
 template <int NTOK>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t stream) {
-  const int blocks = ((p.N + TILE_N - 1) / TILE_N) * p.splits;
-  const bool deep = g_force_ring < 0 ? blocks <= kSMs : g_force_ring == 1;
-  return deep ? launch_cfg<NTOK, true>(mw, mx, p, stream) : launch_cfg<NTOK, false>(mw, mx, p, stream);
+  const int blocks = ((p.N + TILE_N - 1) / TILE_N) * p.splits;      // the same count in SiLU mode (N = 2 I, tiles of 64)
+  const bool deep = blocks <= kSMs;
+  if (p.silu_inter) return deep ? launch_cfg<NTOK, true, true>(mw, mx, p, stream) : launch_cfg<NTOK, false, true>(mw, mx, p, stream);
+  return deep ? launch_cfg<NTOK, true, false>(mw, mx, p, stream) : launch_cfg<NTOK, false, false>(mw, mx, p, stream);
 }
 
 }  // namespace
 
 // How many K splits the launcher would use for this shape (so callers can size `out`).
-YALIS_API void yalis_gemm_wstream_force_ring(int mode) { g_force_ring = mode; }
-
 // Chosen so that the grid fills the GPU without a mostly empty last wave: grids of up to two
 // blocks per SM run as one wave; every split costs a little (a partial output to write and add).
 YALIS_API int yalis_gemm_wstream_splits(int N, int K) {
@@ -367,9 +424,9 @@ YALIS_API int yalis_gemm_wstream_splits(int N, int K) {
 
 // out = x[M, K] . w[N, K]^T, bfloat16 operands.  splits must be yalis_gemm_wstream_splits(N, K) or 1;
 // with splits > 1, out is float32 [splits, M, N] (ldo = N).  error: device int32 raised on a timed-out wait.
-YALIS_API int yalis_gemm_wstream(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
-                                 long long ldo, int M, int N, int K, int splits, int32_t* error,
-                                 cudaStream_t stream) {
+namespace {
+int gemm_wstream_impl(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype, long long ldo,
+                      int M, int N, int K, int splits, int silu_inter, int32_t* error, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return YALIS_OK;
   if (M > 256 || K <= 0 || splits < 1) return YALIS_ERR_SHAPE;
   if ((K % 8) || (ldx % 8) || (ldw % 8)) return YALIS_ERR_ALIGN;          // TMA: 16-byte strides
@@ -378,11 +435,13 @@ YALIS_API int yalis_gemm_wstream(const void* x, long long ldx, const void* w, lo
   if (splits > 1 && out_dtype != YALIS_F32) return YALIS_ERR_DTYPE;
   const int ntok = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   CUtensorMap mw, mx;
-  if (!make_map(&mw, w, N, K, ldw, TILE_N) || !make_map(&mx, x, M, K, ldx, ntok)) return YALIS_ERR_LAUNCH;
+  if (!make_map(&mw, w, N, K, ldw, silu_inter ? TILE_N / 2 : TILE_N) || !make_map(&mx, x, M, K, ldx, ntok))
+    return YALIS_ERR_LAUNCH;
   GemmParams p;
   p.out = out; p.out_dtype = out_dtype; p.ldo = ldo; p.M = M; p.N = N; p.K = K; p.splits = splits;
   const int kt = (K + TILE_K - 1) / TILE_K;
   p.kt_per_split = (kt + splits - 1) / splits;
+  p.silu_inter = silu_inter;
   p.error = error;
   switch (ntok) {
     case 16: return launch<16>(mw, mx, p, stream);
@@ -391,4 +450,21 @@ YALIS_API int yalis_gemm_wstream(const void* x, long long ldx, const void* w, lo
     case 128: return launch<128>(mw, mx, p, stream);
     default: return launch<256>(mw, mx, p, stream);
   }
+}
+}  // namespace
+
+YALIS_API int yalis_gemm_wstream(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
+                                 long long ldo, int M, int N, int K, int splits, int32_t* error,
+                                 cudaStream_t stream) {
+  return gemm_wstream_impl(x, ldx, w, ldw, out, out_dtype, ldo, M, N, K, splits, 0, error, stream);
+}
+
+// The gated activation fused into the product: w is [2 * inter, K] with the gate rows first and the up rows
+// after them; out[m, i] = silu(x . gate_i) * (x . up_i), bfloat16 [M, inter] with row stride ldo.  Both products
+// are rounded to bfloat16 before the activation, so the result has the bits of yalis_gemm_wstream followed by
+// yalis_silu_mul.  The K range is never split.
+YALIS_API int yalis_gemm_wstream_silu(const void* x, long long ldx, const void* w, long long ldw, void* out,
+                                      long long ldo, int M, int inter, int K, int32_t* error, cudaStream_t stream) {
+  if (inter <= 0) return YALIS_ERR_SHAPE;
+  return gemm_wstream_impl(x, ldx, w, ldw, out, YALIS_BF16, ldo, M, 2 * inter, K, 1, inter, error, stream);
 }

@@ -11,8 +11,7 @@ from typing import Dict, Optional
 import torch
 
 from yalis_b200.config.spec import PartSpec
-from yalis_b200.ops.elementwise import silu_mul
-from yalis_b200.ops.linear import linear, linear_partial
+from yalis_b200.ops.linear import linear_partial, linear_silu_mul
 from .base import FeedForward, ParamSpec, register_part
 
 
@@ -38,7 +37,7 @@ class SwiGLU(FeedForward):
         self.w_down = tensors["down_proj"].contiguous()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        return linear_partial(silu_mul(linear(x, self.w_gate_up)), self.w_down)
+        return linear_partial(linear_silu_mul(x, self.w_gate_up), self.w_down)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
