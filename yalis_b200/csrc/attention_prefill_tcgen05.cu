@@ -2,14 +2,14 @@
 //
 // One block owns up to 128 rows of one (request, KV head) -- row = token * heads_per_group +
 // head_in_group, so the whole GQA group of a token shares the K/V tiles -- and walks the visible
-// keys in tiles of 128:
+// keys in tiles of 64 (two blocks share an SM: while one computes a softmax the other's products run):
 //
 //   S = Q K^T      tcgen05.mma (cta_group::1, kind::f16), Q and K tiles in 128B-swizzled shared
 //                  memory (fed by TMA: Q through a 3-D map [head_dim, heads_per_group, tokens],
-//                  K and V one box per cache page), S in tensor memory, double buffered;
+//                  K and V one box per cache page or part of a page), S in tensor memory, double buffered;
 //   P = softmax    four warps, one thread per row: tcgen05.ld of its S row into registers, mask
 //                  by absolute position, running max and sum in float32 (exp2 domain), P packed
-//                  to bfloat16 and written back to tensor memory (tcgen05.st);
+//                  to bfloat16 and written back to tensor memory over the S it came from (tcgen05.st);
 //   O += P V       tcgen05.mma with A = P from tensor memory and B = the V tile read as an
 //                  MN-major operand (V is stored [key][dim]); O stays in tensor memory for the
 //                  whole key loop.  When a row's maximum grows by more than 2^8 the softmax
@@ -32,11 +32,14 @@
 namespace {
 
 constexpr int BM = 128;           // rows (tensor-memory lanes) per block
-constexpr int BN = 128;           // keys per tile
+constexpr int BN = 64;            // keys per tile
 constexpr int kThreads = 192;     // warps 0-3 softmax, warp 4 TMA, warp 5 MMA + tensor memory
 constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr int TMEM_COLS = 512;
-constexpr int COL_S = 0, COL_P = 2 * BN, COL_O = 2 * BN + BN;   // S0,S1 | P0,P1 (BN/2 each) | O
+// Two blocks share an SM (one's softmax runs while the other's products do), so each takes half the tensor
+// memory: S0, S1 (BN columns each) and O (up to 128).  P(j) is written over the first half of S(j): by then S(j)
+// is in registers, and the product that next writes that buffer is issued after the one that reads P(j).
+constexpr int TMEM_COLS = 256;
+constexpr int COL_S = 0, COL_O = 2 * BN;
 
 struct PrefillParams {
   __nv_bfloat16* out;
@@ -160,7 +163,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 
 template <int HS>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
   constexpr int H2 = HS / 64;
@@ -231,32 +234,35 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
       for (int h = 0; h < H2; ++h)
         tma_load_3d(q_s + h * (BM * 128), &map_q, h * 64, kvh * p.per, tok0 + t0, q_full);
-      const int pages_per_tile = BN / p.page_size;
-      const uint32_t page_bytes = (uint32_t)p.page_size * HS * 2;
+      // A tile is fetched in boxes of min(page, BN) keys: several pages, or a part of one.
+      const int box_rows = min(p.page_size, BN);
+      const int boxes_per_tile = BN / box_rows;
+      const uint32_t box_bytes = (uint32_t)box_rows * HS * 2;
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int b = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const int key0 = j * BN;
-        const int n_pages = min(pages_per_tile, (hi_key - key0) / p.page_size + 1);
+        const int n_boxes = min(boxes_per_tile, (hi_key - key0) / box_rows + 1);
         for (int kv = 0; kv < 2 && ok; ++kv) {
           uint64_t* full = kv == 0 ? &k_full[b] : &v_full[b];
           uint64_t* empty = kv == 0 ? &k_empty[b] : &v_empty[b];
           unsigned char* dst = (kv == 0 ? k_s : v_s) + b * KV_BYTES;
           const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
           if (!mbar_wait(empty, ph ^ 1, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(full, page_bytes * (uint32_t)n_pages);
-          for (int i = 0; i < n_pages; ++i) {
-            const int pi = key0 / p.page_size + i;
+          mbar_expect_tx(full, box_bytes * (uint32_t)n_boxes);
+          for (int i = 0; i < n_boxes; ++i) {
+            const int key = key0 + i * box_rows;
+            const int pi = key / p.page_size;
             int page = pi < p.table_width ? bt[pi] : -1;
             if (page < 0 || page >= p.num_pages) {
               if (p.error) atomicExch(p.error, 1);
               page = 0;
             }
-            const int y = (page * p.g + kvh) * p.page_size;
+            const int y = (page * p.g + kvh) * p.page_size + (key - pi * p.page_size);
 #pragma unroll
             for (int h = 0; h < H2; ++h)
-              tma_load_2d(dst + h * (BN * 128) + i * p.page_size * 128, map, h * 64, y, full);
+              tma_load_2d(dst + h * (BN * 128) + i * box_rows * 128, map, h * 64, y, full);
           }
           if (kv == 0) k_armed = j + 1; else v_armed = j + 1;
         }
@@ -278,8 +284,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const uint32_t k_addr = smem_u32(k_s + b * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HS / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * (BM * 128) + (ks & 3) * 32;      // half, then 32 bytes per 16 dims
-          umma_ss(tmem + COL_S + b * BN, desc_kmajor(q_addr + off), desc_kmajor(k_addr + off), idesc_qk, ks > 0);
+          // 64-dim half (BM rows of Q, BN rows of K, 128 bytes each), then 32 bytes per 16 dims
+          const uint32_t q_off = (ks >> 2) * (BM * 128) + (ks & 3) * 32, k_off = (ks >> 2) * (BN * 128) + (ks & 3) * 32;
+          umma_ss(tmem + COL_S + b * BN, desc_kmajor(q_addr + q_off), desc_kmajor(k_addr + k_off), idesc_qk, ks > 0);
         }
         umma_commit(&s_full[b]);
         umma_commit(&k_empty[b]);
@@ -298,7 +305,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
           // 16 keys = two 8-key swizzle groups = 2048 bytes further; P: 16 bfloat16 = 8 columns further
-          umma_ts(tmem + COL_O, tmem + COL_P + b * (BN / 2) + ks * 8, desc_mnmajor(v_addr + ks * 2048, BN * 128),
+          umma_ts(tmem + COL_O, tmem + COL_S + b * BN + ks * 8, desc_mnmajor(v_addr + ks * 2048, BN * 128),
                   idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(o_full);
@@ -353,7 +360,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       const float mb = (m_use == -INFINITY) ? 0.f : m_use;
       const float corr = grow ? ((m_run == -INFINITY) ? 0.f : ex2(m_run - mb)) : 1.f;
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
-      const uint32_t p_addr = lane_base + COL_P + b * (BN / 2);
+      const uint32_t p_addr = lane_base + COL_S + b * BN;          // over the first half of S(j)
 #pragma unroll
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t pk[16];
@@ -388,7 +395,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         // Last tile: rows of V past the last visible key may hold anything (even NaN); zero them
         // once the tile has landed, and make the writes visible to the tensor core's reads.
         if (!warp_wait(&v_full[b], ph, abort_flag, lane)) { ok = false; break; }
-        if (key0 + r > hi_key) {
+        if (r < BN && key0 + r > hi_key) {
           unsigned char* vt = v_s + b * KV_BYTES;
 #pragma unroll
           for (int h = 0; h < H2; ++h)
@@ -476,7 +483,7 @@ bool make_pool_map(CUtensorMap* map, const void* pool, long long rows, int hs, i
   if (fn == nullptr) return false;
   cuuint64_t dims[2] = {(cuuint64_t)hs, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)hs * 2};
-  cuuint32_t box[2] = {64u, (cuuint32_t)page_size};
+  cuuint32_t box[2] = {64u, (cuuint32_t)(page_size < BN ? page_size : BN)};   // a page, or the part of one that a tile covers
   cuuint32_t estr[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
