@@ -192,6 +192,12 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       pdl_wait();
       for (int kt = 0; kt < n_pre; ++kt)
         tma_load_2d(b_s + kt * B_BYTES, &map_x, (kt_begin + kt) * TILE_K, 0, &full[kt]);
+      // When this block is about to ask for its last tiles, the next kernel's blocks may be scheduled and fill
+      // their own rings: earlier they would take bandwidth from tiles this kernel still waits for (and
+      // registers and shared memory from its later blocks); later the hand-over shows.  Measured on a decode
+      // step of the Llama-3-8B shape: 4 tiles ahead is best with 8 tokens, 0 to 2 with 64.
+      constexpr int kTriggerAhead = NTOK <= 32 ? 4 : 1;
+      bool released = false;
       for (int kt = n_pre; kt < n_kt; ++kt) {
         const int s = kt % STAGES;
         const uint32_t ph = (kt / STAGES) & 1;
@@ -206,10 +212,12 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
         tma_load_2d(b_s + s * B_BYTES, &map_x, k, 0, &full[s]);
         armed = kt + 1;
+        if (kt == n_kt - 1 - kTriggerAhead) {
+          pdl_launch_dependents();
+          released = true;
+        }
       }
-      // This block has asked for its last tile: from here on the next kernel's blocks may be scheduled and
-      // fill their own rings without taking bandwidth from tiles this kernel still waits for.
-      pdl_launch_dependents();
+      if (!released) pdl_launch_dependents();
     }
     else pdl_wait();
     __syncwarp();
