@@ -4,9 +4,10 @@ Two precisions, chosen by the operands' dtype:
 
 * float32 operands: the SIMT kernel of csrc/gemm_simt.cu.  True 32-bit FMAs in
   a fixed order, no tensor cores, no TF32.
-* bfloat16 operands: float32 accumulation on the tensor cores.  The engine's
-  own tcgen05 kernels are used where they cover the shape; otherwise the
-  product goes to cuBLAS through ``torch.matmul`` (the reference also leaves
+* bfloat16 operands: float32 accumulation on the tensor cores.  Steps of up
+  to 32 tokens (decode) go to the engine's own tcgen05 weight-streaming kernel,
+  which takes up to 256 tokens but is the faster one only for few; larger
+  steps go to cuBLAS through ``torch.matmul`` (the reference also leaves
   its projections to the library: ``nn.Linear``, yalis/external/model.py:449,
   462, 717, 720).
 """
@@ -55,7 +56,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if x.dtype == torch.float32:
         return gemm_simt(x, w, out_dtype)
     need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear", "operands must both be bfloat16 or float32")
-    if USE_WSTREAM and wstream_supports(x, w):
+    if wstream_preferred(x, w):
         return gemm_wstream(x, w, out_dtype=out_dtype)
     if out_dtype == torch.bfloat16:
         return torch.matmul(x, w.t())
@@ -66,14 +67,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
 def linear_partial(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """A projection whose consumer can add partial sums: returns [M, N] in x's dtype, or
     float32 partial sums [S, M, N] when the weight-streaming kernel divides K among blocks."""
-    if x.dtype == torch.bfloat16 and USE_WSTREAM and wstream_supports(x, w) and wstream_splits(w.shape[0], w.shape[1]) > 1:
+    if wstream_preferred(x, w) and wstream_splits(w.shape[0], w.shape[1]) > 1:
         return gemm_wstream(x, w, split=True)
     return linear(x, w)
 
 
 # ---- the tcgen05 weight-streaming product (csrc/gemm_tcgen05.cu) -------------------------------
 
-WSTREAM_MAX_TOKENS = 256
+WSTREAM_MAX_TOKENS = 256        # what the kernel takes
+# Up to this many tokens the engine's own kernel is the faster one in a decode step (measured on the Llama-3-8B
+# shape: batch 32 4.20 ms against 4.36 ms with the library, batch 64 5.70 ms against 5.32 ms).
+WSTREAM_PREFERRED_TOKENS = int(os.environ.get("YALIS_B200_WSTREAM_TOKENS", "32"))
 _wstream_error = {}
 
 
@@ -94,6 +98,11 @@ def wstream_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
             and 0 < x.shape[0] <= WSTREAM_MAX_TOKENS and x.shape[1] % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1
             and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def wstream_preferred(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the projections of the parts send this product to the engine's own kernel."""
+    return USE_WSTREAM and x.dtype == torch.bfloat16 and x.shape[0] <= WSTREAM_PREFERRED_TOKENS and wstream_supports(x, w)
 
 
 def gemm_wstream(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
@@ -146,7 +155,6 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     # Measured on the Llama-3-8B shape: the fused epilogue wins up to 16 tokens (one chunk of tensor-memory
     # columns); from 17 on its blocks, heavier in registers and TMA requests, slow the products around it by more
     # than the activation kernel costs.
-    if (x.dtype == torch.bfloat16 and USE_WSTREAM and USE_FUSED_SILU and x.shape[0] <= FUSED_SILU_MAX_TOKENS
-            and wstream_supports(x, w_gate_up)):
+    if USE_FUSED_SILU and x.shape[0] <= FUSED_SILU_MAX_TOKENS and wstream_preferred(x, w_gate_up):
         return gemm_wstream_silu(x, w_gate_up)
     return silu_mul(linear(x, w_gate_up))
