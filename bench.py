@@ -200,7 +200,7 @@ def main() -> int:
     }
     if not args.skip_points:
         line["points"] = {f"decode_b{b}": round(r["tok_s"], 2) for b, r in results.items() if b != args.batch}
-        pf = prefill_bench(engine, PREFILL_TOKENS, warmup=2, iters=3)
+        pf = prefill_bench(engine, PREFILL_TOKENS, warmup=3, iters=7)
         flops = numbers["flops_prefill"](PREFILL_TOKENS)
         line["prefill"] = {"value": round(PREFILL_TOKENS / (pf / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf, 3),
                            "frac": round(flops / (pf / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}

@@ -469,6 +469,48 @@ def test_decode_attention_tma_against_plain_and_generic(nh, g, hs, page, splits,
         torch.testing.assert_close(out[r].float().cpu().view(1, nh, hs), ref, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("nh, g, hs, page", [(32, 8, 128, 64), (8, 2, 64, 8), (6, 2, 192, 16), (2, 1, 256, 32), (5, 5, 128, 16)])
+@pytest.mark.parametrize("parts, splits, rotate", [(1, 1, True), (3, 4, True), (2, 8, False), (0, 3, True), (3, 11, True)])
+def test_decode_attention_tma_fused_has_the_bits_of_rotary_kernel_then_attention(nh, g, hs, page, parts, splits, rotate):
+    """The decode kernel that rotates Q and the new K itself and stores K, V: same output and same cache
+    as the rotary / cache-write kernel followed by the plain decode kernel; lengths at page and tile edges;
+    bfloat16 rows (parts 0) and float32 partial sums; and without storing (a cache that another layer filled)."""
+    from yalis_b200.ops.attention import decode_attention_tma, decode_attention_tma_fused
+    from yalis_b200.ops.elementwise import rope_kv_write
+    from yalis_b200.parts.rotary import inverse_frequencies
+    dtype = torch.bfloat16
+    lens = [1, 16, 17, 64, 65, 128, 129, 517]
+    n = len(lens)
+    _, _, k_pool, v_pool, table = paged_setup(n, lens, g, hs, page, dtype, seed=hs + nh + page + parts)
+    width = (nh + 2 * g) * hs
+    if parts == 0:
+        qkv = rnd(n, width, dtype=dtype, seed=5)
+    else:
+        qkv = rnd(parts, n, width, seed=5)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    positions, q_start, req = i32([l - 1 for l in lens]), i32(list(range(n + 1))), i32(list(range(n)))
+    inv = inverse_frequencies(hs, 10000.0, None).to(DEV) if rotate else None
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    k1, v1 = k_pool.clone(), v_pool.clone()
+    q = rope_kv_write(qkv, positions, req, inv, k1, v1, table, nh, g, hs, out_dtype=dtype, bad_flag=flag)
+    ref = decode_attention_tma(q, k1, v1, positions, q_start, table, nh, g, hs, n_splits=splits, error_flag=flag)
+    k2, v2 = k_pool.clone(), v_pool.clone()
+    torch.cuda.synchronize()
+    out = decode_attention_tma_fused(qkv, inv, True, k2, v2, positions, q_start, table, nh, g, hs, n_splits=splits,
+                                     error_flag=flag, early_fetch=True)
+    assert int(flag) == 0
+    assert torch.equal(out, ref)
+    # pools: equal wherever something was written (both started from the same poisoned pools)
+    assert torch.equal(torch.nan_to_num(k2.float(), nan=7.0), torch.nan_to_num(k1.float(), nan=7.0))
+    assert torch.equal(torch.nan_to_num(v2.float(), nan=7.0), torch.nan_to_num(v1.float(), nan=7.0))
+    # a cache that already holds this step's key and value (filled by another layer): nothing is stored
+    k3, v3 = k1.clone(), v1.clone()
+    out3 = decode_attention_tma_fused(qkv, inv, False, k3, v3, positions, q_start, table, nh, g, hs, n_splits=splits,
+                                      error_flag=flag)
+    assert int(flag) == 0 and torch.equal(out3, ref)
+    assert torch.equal(torch.nan_to_num(k3.float(), nan=7.0), torch.nan_to_num(k1.float(), nan=7.0))
+
+
 def test_decode_attention_tma_far_key_and_padding_requests():
     """A far key with nearly all the weight at page and tile edges; requests without tokens
     (padding of a captured batch) are left alone."""

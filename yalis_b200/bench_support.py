@@ -120,7 +120,8 @@ class DecodeBench:
 
 
 def prefill_bench(engine: Engine, tokens: int, warmup: int = 2, iters: int = 3) -> float:
-    """Milliseconds of one step that prefills a single ``tokens``-token prompt (logits of its last token)."""
+    """Milliseconds (median of ``iters``) of one step that prefills a single ``tokens``-token prompt (logits of
+    its last token)."""
     gen = torch.Generator().manual_seed(7)
     prompt = torch.randint(0, engine.vocab_size, (tokens,), generator=gen).tolist()
     times = []
@@ -136,4 +137,5 @@ def prefill_bench(engine: Engine, tokens: int, warmup: int = 2, iters: int = 3) 
         engine.finish_request(rid)
         if i >= warmup:
             times.append(start.elapsed_time(end))
-    return sum(times) / len(times)
+    times.sort()
+    return times[len(times) // 2]        # the median: single steps vary by a few percent with the clocks

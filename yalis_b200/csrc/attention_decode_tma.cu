@@ -32,8 +32,18 @@ constexpr int STAGES = 2;         // the per-warp results reuse the K ring after
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct DecParams {
-  const __nv_bfloat16* q;      // [N, q_stride]
+  const __nv_bfloat16* q;      // [N, q_stride]; null when the kernel rotates the queries itself (fused mode)
   int q_stride;
+  // Fused mode: the step's fused QKV rows [N, (nh + 2 g) * HS] (bfloat16, or n_parts float32 partial sums that are
+  // added in order), rotated here by float(position) * inv_freq (null: no rotation).  The block that owns the tile
+  // of the query's own position also rotates the new key, writes it and the new value to the pools (null: the
+  // cache belongs to another layer, which has written them) and patches them into its tile.
+  const void* qkv;
+  int qkv_f32, n_parts, qkv_stride;
+  size_t part_stride;
+  const float* inv_freq;
+  __nv_bfloat16* k_pool_w;
+  __nv_bfloat16* v_pool_w;
   __nv_bfloat16* out;          // [N, out_stride]
   int out_stride;
   const int32_t* positions;    // [N]
@@ -154,6 +164,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   uint64_t* empty = full + STAGES;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + STAGES);
   int* s_last = const_cast<int*>(abort_flag) + 1;
+  __nv_bfloat16* kv_new = reinterpret_cast<__nv_bfloat16*>(s_last + 3);   // [2][HS] new key and value (16-byte aligned)
   constexpr int VEC = HS / 4;                  // float4 groups of a row
   // after the tiles: per-warp results in k_s, their (max, sum) in v_s, then the block's merged result
   float* co = reinterpret_cast<float*>(v_s + 1024);          // [16][HS] merged, unnormalised
@@ -219,6 +230,22 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         if (!issue_tile(it, tile_lo, pos, bt)) break;
     }
   }
+  // Fused mode: the cosines and sines of the query's position do not depend on the preceding kernel either.
+  // A thread rotates the pairs e = threadIdx.x + 128 k; their frequency index e % (HS/2) repeats with period 3
+  // in k for every head size the kernel takes.
+  constexpr int HALF = HS / 2;
+  static_assert((3 * CWARPS * 32) % HALF == 0, "frequency indices of a thread repeat with period 3");
+  float cs3[3] = {1.f, 1.f, 1.f}, sn3[3] = {0.f, 0.f, 0.f};
+  bool trig_ready = false;
+  if (p.qkv != nullptr && p.inv_freq != nullptr && p.early_fetch && warp < CWARPS) {
+    const int tok_e = p.q_start[req];
+    if (p.q_start[req + 1] - tok_e > 0) {
+      const float fpos = (float)p.positions[tok_e];
+#pragma unroll
+      for (int j = 0; j < 3; ++j) sincosf(fpos * p.inv_freq[(threadIdx.x + CWARPS * 32 * j) % HALF], &sn3[j], &cs3[j]);
+      trig_ready = true;
+    }
+  }
   pdl_wait();
   __syncthreads();
 
@@ -247,7 +274,8 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int gid = lane >> 2, tig = lane & 3;
     const int wkey = warp * WKEYS;
     const int n_rows = p.per;                  // rows = query heads of this KV head
-    {
+    const bool owns_pos = tile_lo < total && tile_hi == total;     // this block's last tile holds the query's own position
+    if (p.qkv == nullptr) {
       constexpr int CHUNKS = HS / 8;
       for (int c = threadIdx.x; c < 16 * CHUNKS; c += CWARPS * 32) {
         const int r = c / CHUNKS, ch = c - r * CHUNKS;
@@ -256,8 +284,66 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
           v = *reinterpret_cast<const uint4*>(p.q + (size_t)tok * p.q_stride + (size_t)(kvh * p.per + r) * HS + ch * 8);
         *reinterpret_cast<uint4*>(q_s + r * LDQ + ch * 8) = v;
       }
+    } else {
+      // Rotate this KV head's queries (and, in the owning block, the new key) as the rotary kernel does:
+      // partial sums in index order, angle float(pos) * inv_freq, accurate sincosf, one rounding to bfloat16.
+      if (p.inv_freq && !trig_ready) {
+#pragma unroll
+        for (int j = 0; j < 3; ++j)
+          sincosf((float)pos * p.inv_freq[(threadIdx.x + CWARPS * 32 * j) % HALF], &sn3[j], &cs3[j]);
+      }
+      const size_t row0 = (size_t)tok * p.qkv_stride;
+      auto load = [&](size_t col) -> float {
+        if (p.qkv_f32) return sum_parts<float>(reinterpret_cast<const float*>(p.qkv) + row0 + col, p.n_parts, p.part_stride);
+        return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.qkv)[row0 + col]);
+      };
+      const int n_q = n_rows * HALF;
+      const int n_kv = (owns_pos && p.k_pool_w != nullptr) ? 2 * HALF : 0;      // HALF key pairs, then HALF value pairs
+      int k3 = 0;                                   // (e - threadIdx.x) / 128 modulo 3
+      for (int e = threadIdx.x; e < 16 * HALF + n_kv; e += CWARPS * 32, k3 = k3 == 2 ? 0 : k3 + 1) {
+        const float cs = k3 == 0 ? cs3[0] : k3 == 1 ? cs3[1] : cs3[2], sn = k3 == 0 ? sn3[0] : k3 == 1 ? sn3[1] : sn3[2];
+        if (e < 16 * HALF) {
+          const int r = e / HALF, i = e - r * HALF;
+          float o1 = 0.f, o2 = 0.f;
+          if (e < n_q) {
+            const size_t col = (size_t)(kvh * p.per + r) * HS + i;
+            const float x1 = load(col), x2 = load(col + HALF);
+            o1 = x1; o2 = x2;
+            if (p.inv_freq) rotate_pair(x1, x2, cs, sn, o1, o2);
+          }
+          q_s[r * LDQ + i] = __float2bfloat16_rn(o1);
+          q_s[r * LDQ + i + HALF] = __float2bfloat16_rn(o2);
+        } else {
+          const int f = e - 16 * HALF;
+          const bool is_v = f >= HALF;
+          const int i = is_v ? f - HALF : f;
+          const size_t col = (size_t)(p.nh + (is_v ? p.g : 0) + kvh) * HS + i;
+          const float x1 = load(col), x2 = load(col + HALF);
+          float o1 = x1, o2 = x2;
+          if (!is_v && p.inv_freq) rotate_pair(x1, x2, cs, sn, o1, o2);
+          __nv_bfloat16* dst = kv_new + (is_v ? HS : 0);
+          dst[i] = __float2bfloat16_rn(o1);
+          dst[i + HALF] = __float2bfloat16_rn(o2);
+        }
+      }
     }
     consumer_sync();
+    if (p.qkv != nullptr && owns_pos && p.k_pool_w != nullptr) {
+      // the new key and value go to their place in the cache (16 bytes per thread)
+      const int pi = pos / p.page_size;
+      int page = pi < p.table_width ? bt[pi] : -1;
+      if (page < 0 || page >= p.num_pages) {
+        if (threadIdx.x == 0 && p.error) atomicExch(p.error, 1);
+      } else {
+        const size_t at = (((size_t)page * p.g + kvh) * p.page_size + (pos - pi * p.page_size)) * HS;
+        for (int c = threadIdx.x; c < 2 * (HS / 8); c += CWARPS * 32) {
+          const bool is_v = c >= HS / 8;
+          const int ch = is_v ? c - HS / 8 : c;
+          *reinterpret_cast<uint4*>((is_v ? p.v_pool_w : p.k_pool_w) + at + ch * 8) =
+              *reinterpret_cast<const uint4*>(kv_new + (is_v ? HS : 0) + ch * 8);
+        }
+      }
+    }
     unsigned qf[KSTEPS][4];
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ++ks) {
@@ -282,6 +368,20 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       const int key0 = (tile_lo + it) * BN;
       const uint32_t kt = smem_u32(k_s + s * TILE_BYTES), vt = smem_u32(v_s + s * TILE_BYTES);
       const bool last = key0 + BN - 1 > hi_key;
+      if (p.qkv != nullptr && p.k_pool_w != nullptr && key0 + BN > hi_key) {
+        // The tile holds the query's own position: what the copy brought for that row is older than this step
+        // (it may have been issued before the row was written).  The warp that owns the row replaces it.
+        const int row = hi_key - key0;
+        if (row >= wkey && row < wkey + WKEYS) {
+          for (int c = lane; c < 2 * (HS / 8); c += 32) {
+            const bool is_v = c >= HS / 8;
+            const int ch = is_v ? c - HS / 8 : c;
+            unsigned char* tile = (is_v ? v_s : k_s) + s * TILE_BYTES;
+            *reinterpret_cast<uint4*>(tile + tile_off(row, ch * 8)) = *reinterpret_cast<const uint4*>(kv_new + (is_v ? HS : 0) + ch * 8);
+          }
+        }
+        __syncwarp();
+      }
       if (last) {
         // Zero this warp's V rows past the query's position (they may hold anything).
         unsigned char* vrow = v_s + s * TILE_BYTES;
@@ -557,7 +657,8 @@ bool make_pool_map(CUtensorMap* map, const void* pool, long long rows, int hs, i
 
 template <int HS>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const DecParams& p, int n_requests, cudaStream_t stream) {
-  const size_t smem = 1024 + (size_t)2 * STAGES * BN * HS * 2 + (size_t)16 * (HS + 8) * 2 + 2 * STAGES * 8 + 16;
+  const size_t smem = 1024 + (size_t)2 * STAGES * BN * HS * 2 + (size_t)16 * (HS + 8) * 2 + 2 * STAGES * 8 + 16 + 32 +
+                      (size_t)2 * HS * 2;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(decode_attention_tma_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
@@ -591,17 +692,28 @@ YALIS_API int yalis_decode_attention_tma_supports(int hs, int page_size, int per
 // kernel on the stream has finished (programmatic dependent launch).  The caller then promises that those keys and
 // values, positions, q_start and the block table were written before the preceding kernel began - true inside a
 // model step, where a host copy brings the index arrays and only this step's token is written to the pool.
-YALIS_API int yalis_decode_attention_tma(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
-                                         const void* v_pool, const int32_t* positions, const int32_t* q_start,
-                                         const int32_t* block_table, int table_width, int page_size, int num_pages,
-                                         int n_tokens, int n_requests, int nh, int g, int hs, float scale,
-                                         int n_splits, int early_fetch, float* scratch, int32_t* tickets,
-                                         int32_t* error, cudaStream_t stream) {
+namespace {
+struct FusedArgs {
+  const void* qkv = nullptr;
+  int qkv_f32 = 0, n_parts = 1, qkv_stride = 0;
+  long long part_stride = 0;
+  const float* inv_freq = nullptr;
+  int store = 0;
+};
+
+int decode_attention_tma_impl(const void* q, int q_stride, const FusedArgs& f, void* out, int out_stride, const void* k_pool,
+                              const void* v_pool, const int32_t* positions, const int32_t* q_start,
+                              const int32_t* block_table, int table_width, int page_size, int num_pages,
+                              int n_tokens, int n_requests, int nh, int g, int hs, float scale,
+                              int n_splits, int early_fetch, float* scratch, int32_t* tickets,
+                              int32_t* error, cudaStream_t stream) {
   if (n_tokens <= 0 || n_requests <= 0) return YALIS_OK;
   if (g <= 0 || nh % g != 0 || n_splits < 1 || n_splits > 64) return YALIS_ERR_SHAPE;   // the merge stages 64 splits
   if (!yalis_decode_attention_tma_supports(hs, page_size, nh / g)) return YALIS_ERR_SHAPE;
   if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) return YALIS_ERR_ALIGN;
   if ((q_stride % 8) || (out_stride % 4)) return YALIS_ERR_ALIGN;
+  if ((q == nullptr) == (f.qkv == nullptr)) return YALIS_ERR_SHAPE;           // queries come one way or the other
+  if (f.qkv != nullptr && (f.n_parts < 1 || (!f.qkv_f32 && f.n_parts != 1))) return YALIS_ERR_SHAPE;
   const bool cluster_merge = n_splits > 1 && n_splits <= kMaxCluster;
   if (n_splits > 1 && !cluster_merge && (scratch == nullptr || tickets == nullptr)) return YALIS_ERR_SHAPE;
   CUtensorMap mk, mv;
@@ -610,6 +722,10 @@ YALIS_API int yalis_decode_attention_tma(const void* q, int q_stride, void* out,
     return YALIS_ERR_LAUNCH;
   DecParams p;
   p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
+  p.qkv = f.qkv; p.qkv_f32 = f.qkv_f32; p.n_parts = f.n_parts; p.qkv_stride = f.qkv_stride;
+  p.part_stride = (size_t)f.part_stride; p.inv_freq = f.inv_freq;
+  p.k_pool_w = f.store ? (__nv_bfloat16*)const_cast<void*>(k_pool) : nullptr;
+  p.v_pool_w = f.store ? (__nv_bfloat16*)const_cast<void*>(v_pool) : nullptr;
   p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
   p.positions = positions; p.q_start = q_start; p.block_table = block_table;
   p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages;
@@ -628,4 +744,38 @@ YALIS_API int yalis_decode_attention_tma(const void* q, int q_stride, void* out,
     case 192: return launch<192>(mk, mv, p, n_requests, stream);
     default: return launch<256>(mk, mv, p, n_requests, stream);
   }
+}
+}  // namespace
+
+YALIS_API int yalis_decode_attention_tma(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
+                                         const void* v_pool, const int32_t* positions, const int32_t* q_start,
+                                         const int32_t* block_table, int table_width, int page_size, int num_pages,
+                                         int n_tokens, int n_requests, int nh, int g, int hs, float scale,
+                                         int n_splits, int early_fetch, float* scratch, int32_t* tickets,
+                                         int32_t* error, cudaStream_t stream) {
+  return decode_attention_tma_impl(q, q_stride, FusedArgs(), out, out_stride, k_pool, v_pool, positions, q_start,
+                                   block_table, table_width, page_size, num_pages, n_tokens, n_requests, nh, g, hs, scale,
+                                   n_splits, early_fetch, scratch, tickets, error, stream);
+}
+
+// The same with the rotary kernel's work done inside: qkv is the step's fused projection [N, (nh + 2 g) * hs] in
+// bfloat16 (qkv_f32 = 0, n_parts = 1) or n_parts float32 partial sums part_stride elements apart; inv_freq
+// [hs / 2] float32 or null for no rotation; store = 1 writes the new key and value to the pools (0: the cache
+// belongs to another layer that has written them in this step).  Bits of yalis_rope_kv_write followed by
+// yalis_decode_attention_tma.
+YALIS_API int yalis_decode_attention_tma_fused(const void* qkv, int qkv_f32, int n_parts, long long part_stride,
+                                               int qkv_stride, const float* inv_freq, int store, void* out,
+                                               int out_stride, void* k_pool, void* v_pool, const int32_t* positions,
+                                               const int32_t* q_start, const int32_t* block_table, int table_width,
+                                               int page_size, int num_pages, int n_tokens, int n_requests, int nh,
+                                               int g, int hs, float scale, int n_splits, int early_fetch,
+                                               float* scratch, int32_t* tickets, int32_t* error, cudaStream_t stream) {
+  if (qkv == nullptr) return YALIS_ERR_SHAPE;
+  if (((uintptr_t)qkv & 15) || (qkv_stride % 8) || (part_stride % 4)) return YALIS_ERR_ALIGN;
+  FusedArgs f;
+  f.qkv = qkv; f.qkv_f32 = qkv_f32; f.n_parts = n_parts; f.part_stride = part_stride; f.qkv_stride = qkv_stride;
+  f.inv_freq = inv_freq; f.store = store;
+  return decode_attention_tma_impl(nullptr, 8, f, out, out_stride, k_pool, v_pool, positions, q_start, block_table,
+                                   table_width, page_size, num_pages, n_tokens, n_requests, nh, g, hs, scale, n_splits,
+                                   early_fetch, scratch, tickets, error, stream);
 }

@@ -109,6 +109,13 @@ __device__ __forceinline__ float sum_parts(const TS* __restrict__ p, int n, size
   return acc;
 }
 
+// (x1, x2) turned by the angle with cosine cs and sine sn.  One pinned instruction sequence, so that every
+// kernel that rotates (the rotary kernels, the decode attention that rotates its own queries) agrees to the bit.
+__device__ __forceinline__ void rotate_pair(float x1, float x2, float cs, float sn, float& o1, float& o2) {
+  o1 = __fmaf_rn(x1, cs, -__fmul_rn(x2, sn));
+  o2 = __fmaf_rn(x2, cs, __fmul_rn(x1, sn));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

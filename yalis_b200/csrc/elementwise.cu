@@ -353,8 +353,7 @@ __global__ void rope_kv_write_kernel(const TS* __restrict__ src, int src_stride,
     if (!is_v && inv_freq) {
       float sn, cs;
       sincosf((float)pos * inv_freq[i], &sn, &cs);
-      o1 = x1 * cs - x2 * sn;
-      o2 = x2 * cs + x1 * sn;
+      rotate_pair(x1, x2, cs, sn, o1, o2);
     }
     dst[i] = from_f32<T>(o1);
     dst[i + half] = from_f32<T>(o2);
@@ -417,8 +416,7 @@ __global__ void rope_kv_write_token_kernel(const TS* __restrict__ src, int src_s
     float o1 = x1, o2 = x2;
     if (!is_v && inv_freq) {
       const float c = cs[i], sn = cs[half + i];
-      o1 = x1 * c - x2 * sn;
-      o2 = x2 * c + x1 * sn;
+      rotate_pair(x1, x2, c, sn, o1, o2);
     }
     dst[i] = from_f32<T>(o1);
     dst[i + half] = from_f32<T>(o2);
@@ -486,8 +484,10 @@ __global__ void rope_kv_write_token_vec_kernel(const TS* __restrict__ src, int s
     float4 o1 = x1, o2 = x2;
     if (!is_v && inv_freq) {
       const float4 c = *reinterpret_cast<const float4*>(cs + i), sn = *reinterpret_cast<const float4*>(cs + half + i);
-      o1 = make_float4(x1.x * c.x - x2.x * sn.x, x1.y * c.y - x2.y * sn.y, x1.z * c.z - x2.z * sn.z, x1.w * c.w - x2.w * sn.w);
-      o2 = make_float4(x2.x * c.x + x1.x * sn.x, x2.y * c.y + x1.y * sn.y, x2.z * c.z + x1.z * sn.z, x2.w * c.w + x1.w * sn.w);
+      rotate_pair(x1.x, x2.x, c.x, sn.x, o1.x, o2.x);
+      rotate_pair(x1.y, x2.y, c.y, sn.y, o1.y, o2.y);
+      rotate_pair(x1.z, x2.z, c.z, sn.z, o1.z, o2.z);
+      rotate_pair(x1.w, x2.w, c.w, sn.w, o1.w, o2.w);
     }
     store4(dst + i, o1);
     store4(dst + i + half, o2);

@@ -114,22 +114,22 @@ struct GemmParams {
   int32_t* error;       // set to 1 if a wait ran out
 };
 
-// Ring depth. A stage is 16 KB of W plus NTOK * 128 bytes of x.  DEEP: one block per SM with a
-// ring of ~190 KB, for grids that fit the GPU in one wave of single blocks; otherwise two blocks
-// per SM with ~95 KB each, so that grids between one and two blocks per SM run as one wave.
-template <int NTOK, bool DEEP>
+// Ring depth. A stage is 16 KB of W plus NTOK * 128 bytes of x.  Two blocks fit an SM with ~95 KB each, so that
+// grids between one and two blocks per SM run as one wave.  (A ring of a whole SM for grids of at most one block
+// per SM is faster for a product alone, but slower inside a decode step: the next kernel's blocks then find no
+// room beside it and cannot fetch ahead.  Measured 3.28 against 3.33 ms for a batch-8 step of Llama-3-8B.)
+template <int NTOK>
 __host__ __device__ constexpr int stages_for() {
-  return DEEP ? (NTOK <= 16 ? 10 : NTOK <= 32 ? 9 : NTOK <= 64 ? 8 : NTOK <= 128 ? 6 : 4)
-              : (NTOK <= 32 ? 5 : NTOK <= 64 ? 4 : NTOK <= 128 ? 3 : 4);
+  return NTOK <= 32 ? 5 : NTOK <= 64 ? 4 : NTOK <= 128 ? 3 : 4;
 }
 
 // SILU: the gated-activation epilogue (p.silu_inter > 0).  A variant of its own: its extra registers would also
 // be charged to the plain kernel, which then fits once instead of twice beside the attention blocks it follows.
-template <int NTOK, bool DEEP, bool SILU>
-__global__ void __launch_bounds__(kThreads, (DEEP || NTOK > 128) ? 1 : 2)
+template <int NTOK, bool SILU>
+__global__ void __launch_bounds__(kThreads, NTOK > 128 ? 1 : 2)
 gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const GemmParams p) {
-  constexpr int STAGES = stages_for<NTOK, DEEP>();
+  constexpr int STAGES = stages_for<NTOK>();
   constexpr int A_BYTES = TILE_N * TILE_K * 2;
   constexpr int B_BYTES = NTOK * TILE_K * 2;
   constexpr int TMEM_COLS = NTOK < 32 ? 32 : NTOK;
@@ -376,13 +376,13 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, lo
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int NTOK, bool DEEP, bool SILU>
+template <int NTOK, bool SILU>
 int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t stream) {
-  constexpr int STAGES = stages_for<NTOK, DEEP>();
+  constexpr int STAGES = stages_for<NTOK>();
   const size_t smem = 1024 + (size_t)STAGES * (TILE_N * TILE_K * 2 + NTOK * TILE_K * 2) + (2 * STAGES + 1) * 8 + 16;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_wstream_kernel<NTOK, DEEP, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_wstream_kernel<NTOK, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
       return YALIS_ERR_LAUNCH;
     configured = true;
@@ -390,15 +390,12 @@ int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p
   const int tile_rows = p.silu_inter ? TILE_N / 2 : TILE_N;
   const int rows = p.silu_inter ? p.silu_inter : p.N;
   dim3 grid((rows + tile_rows - 1) / tile_rows, p.splits);
-  return yalis_launch(gemm_wstream_kernel<NTOK, DEEP, SILU>, grid, dim3(kThreads), smem, stream, mw, mx, p);
+  return yalis_launch(gemm_wstream_kernel<NTOK, SILU>, grid, dim3(kThreads), smem, stream, mw, mx, p);
 }
 
 template <int NTOK>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t stream) {
-  const int blocks = ((p.N + TILE_N - 1) / TILE_N) * p.splits;      // the same count in SiLU mode (N = 2 I, tiles of 64)
-  const bool deep = blocks <= kSMs;
-  if (p.silu_inter) return deep ? launch_cfg<NTOK, true, true>(mw, mx, p, stream) : launch_cfg<NTOK, false, true>(mw, mx, p, stream);
-  return deep ? launch_cfg<NTOK, true, false>(mw, mx, p, stream) : launch_cfg<NTOK, false, false>(mw, mx, p, stream);
+  return p.silu_inter ? launch_cfg<NTOK, true>(mw, mx, p, stream) : launch_cfg<NTOK, false>(mw, mx, p, stream);
 }
 
 }  // namespace

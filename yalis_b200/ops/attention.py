@@ -9,7 +9,7 @@ from typing import Optional
 
 import torch
 
-from ._lib import check, dtype_code, f32, i32, lib, need, need_cuda, ptr, stream
+from ._lib import check, dtype_code, f32, i32, i64, lib, need, need_cuda, ptr, stream
 
 
 def _check_common(name, q, k_pool, v_pool, positions, req_of_token, block_table, num_heads, num_kv_heads, head_dim):
@@ -57,6 +57,8 @@ def paged_attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch
 
 SM_COUNT = 148   # B200
 # YALIS_B200_NO_DECODE_TMA=1 keeps decode steps on the cp.async kernel (for comparisons).
+# YALIS_B200_NO_FUSED_ROPE=1 keeps the rotary / cache-write kernel apart from the decode attention.
+USE_FUSED_ROPE = os.environ.get("YALIS_B200_NO_FUSED_ROPE", "0") != "1"
 USE_DECODE_TMA = os.environ.get("YALIS_B200_NO_DECODE_TMA", "0") != "1"
 # YALIS_B200_NO_PREFILL_TCGEN05=1 keeps prompt portions on the mma.sync kernel.
 USE_PREFILL_TCGEN05 = os.environ.get("YALIS_B200_NO_PREFILL_TCGEN05", "0") != "1"
@@ -172,6 +174,64 @@ def decode_attention_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
     return out
 
 
+def decode_attention_tma_fused(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], store: bool, k_pool: torch.Tensor,
+                               v_pool: torch.Tensor, positions: torch.Tensor, q_start: torch.Tensor,
+                               block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                               scale: Optional[float] = None, n_splits: int = 1,
+                               error_flag: Optional[torch.Tensor] = None, early_fetch: bool = False) -> torch.Tensor:
+    """``decode_attention_tma`` with the rotary kernel's work done inside: ``qkv`` is the step's fused projection
+    [N, (heads + 2 kv_heads) * head_dim] in bfloat16, or float32 partial sums [S, N, ...] that are added in order;
+    queries and the new key are rotated by ``float(position) * inv_freq`` (None: not at all), and with ``store``
+    the new key and value are written to the pools.  Same bits as ``rope_kv_write`` followed by
+    ``decode_attention_tma``."""
+    name = "decode_attention_tma_fused"
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    need_cuda(name, qkv, inv_freq, k_pool, v_pool, positions, q_start, block_table, error_flag)
+    need(qkv.is_contiguous() and qkv.shape[-1] == width and qkv.dim() in (2, 3), name,
+         "qkv must be contiguous [N, (heads + 2*kv_heads) * head_dim] or [S, N, ...]")
+    need((qkv.dim() == 2 and qkv.dtype == torch.bfloat16) or (qkv.dim() == 3 and qkv.dtype == torch.float32), name,
+         "qkv must be bfloat16 rows or float32 partial sums")
+    parts = qkv.shape[0] if qkv.dim() == 3 else 1
+    n, r = qkv.shape[-2], q_start.numel() - 1
+    need(k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16 and k_pool.shape == v_pool.shape
+         and k_pool.dim() == 4 and k_pool.shape[1] == num_kv_heads and k_pool.shape[3] == head_dim
+         and k_pool.is_contiguous() and v_pool.is_contiguous(), name, "pools must be contiguous bfloat16 [pages, kv_heads, page_size, head_dim]")
+    need(decode_tma_supports(head_dim, k_pool.shape[2], num_heads // num_kv_heads), name,
+         "needs head_dim 64/128/192/256, page_size 8/16/32/64 and at most 16 heads per KV head")
+    for t in (positions,):
+        need(t.dtype == torch.int32 and t.shape == (n,) and t.is_contiguous(), name, "positions: int32 [N]")
+    need(q_start.dtype == torch.int32 and q_start.is_contiguous(), name, "q_start must be int32 [R+1]")
+    need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous()
+         and block_table.shape[0] >= r, name, "block_table must be contiguous int32 [>= R, width]")
+    if inv_freq is not None:
+        need(inv_freq.dtype == torch.float32 and inv_freq.shape == (head_dim // 2,) and inv_freq.is_contiguous(), name,
+             "inv_freq must be float32 [head_dim / 2]")
+    out = torch.empty((n, num_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    scratch = tickets = None
+    if n_splits > 8:
+        floats = lib().yalis_attention_mma_scratch_floats
+        floats.restype = ctypes.c_longlong
+        scratch = torch.empty(int(floats(i32(n), i32(num_heads), i32(head_dim), i32(n_splits))), dtype=torch.float32,
+                              device=qkv.device)
+        tickets = _tickets(qkv.device, r * num_kv_heads)
+    check(lib().yalis_decode_attention_tma_fused(
+        ptr(qkv), i32(1 if qkv.dtype == torch.float32 else 0), i32(parts), i64(n * width), i32(width), ptr(inv_freq),
+        i32(1 if store else 0), ptr(out), i32(out.stride(0)), ptr(k_pool), ptr(v_pool), ptr(positions), ptr(q_start),
+        ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]), i32(k_pool.shape[0]), i32(n), i32(r),
+        i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), i32(n_splits), i32(1 if early_fetch else 0),
+        ptr(scratch), ptr(tickets), ptr(error_flag), stream()), name)
+    return out
+
+
+def decode_tma_applicable(dtype: torch.dtype, ctx, head_dim: int, page_size: int, heads_per_group: int,
+                          window: Optional[int]) -> bool:
+    """Whether a step goes to the TMA-fed decode kernel: bfloat16, one token per request, no window, a shape it takes."""
+    return (dtype == torch.bfloat16 and USE_DECODE_TMA and ctx.decode_only and ctx.host.max_q_len == 1 and window is None
+            and decode_tma_supports(head_dim, page_size, heads_per_group))
+
+
 def prefill_tcgen05_supports(head_dim: int, page_size: int, heads_per_group: int) -> bool:
     """Whether the tcgen05 prompt-attention kernel takes this shape (head_dim 64/128, pages of 8..128)."""
     return bool(lib().yalis_prefill_attention_tcgen05_supports(i32(head_dim), i32(page_size), i32(heads_per_group)))
@@ -213,8 +273,7 @@ def paged_attention(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     head sizes) to the exact generic kernel."""
     table = ctx.block_tables[group]
     per = num_heads // num_kv_heads
-    if (qkv.dtype == torch.bfloat16 and USE_DECODE_TMA and ctx.decode_only and ctx.host.max_q_len == 1 and window is None
-            and decode_tma_supports(head_dim, k_pool.shape[2], per)):
+    if decode_tma_applicable(qkv.dtype, ctx, head_dim, k_pool.shape[2], per, window):
         return decode_attention_tma(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, num_heads, num_kv_heads,
                                     head_dim, scale=scale, n_splits=min(8, decode_splits(ctx.n_requests, num_kv_heads)),
                                     error_flag=ctx.error_flag, early_fetch=bool(getattr(ctx, "settled", False)))

@@ -18,7 +18,7 @@ import torch
 from yalis_b200.config.spec import PartSpec
 from yalis_b200.ops import attention as attn_ops
 from yalis_b200.ops.linear import linear_partial
-from .base import Mixer, PagedKV, PagedKVCache, ParamSpec, PositionEncoding, register_part
+from .base import NOT_ROTARY, Mixer, PagedKV, PagedKVCache, ParamSpec, PositionEncoding, register_part
 
 
 class PagedAttention(Mixer):
@@ -60,6 +60,17 @@ class PagedAttention(Mixer):
 
     def forward(self, x: torch.Tensor, ctx, cache: PagedKVCache) -> torch.Tensor:
         qkv = linear_partial(x, self.w_qkv)          # [N, width], or float32 partial sums [S, N, width]
+        if attn_ops.USE_FUSED_ROPE and attn_ops.decode_tma_applicable(x.dtype, ctx, self.hs, cache.k.shape[2],
+                                                                        self.nh // self.g, self.window):
+            # a decode step: the attention kernel rotates Q and the new K itself and stores K, V (one launch less)
+            freq = self.position.rotary_frequencies(self.hs, x.device)
+            if freq is not NOT_ROTARY:
+                y = attn_ops.decode_attention_tma_fused(
+                    qkv, freq, cache.writable, cache.k, cache.v, ctx.positions, ctx.q_start,
+                    ctx.block_tables[cache.group], self.nh, self.g, self.hs, scale=self.scale,
+                    n_splits=min(8, attn_ops.decode_splits(ctx.n_requests, self.g)), error_flag=ctx.error_flag,
+                    early_fetch=bool(getattr(ctx, "settled", False)))
+                return linear_partial(y, self.w_o)
         q = self.position.encode_and_store(qkv, self.nh, self.g, self.hs, ctx, cache, dtype=x.dtype)
         y = attn_ops.paged_attention(q, cache.k, cache.v, ctx, cache.group, self.nh, self.g, self.hs,
                                      scale=self.scale, window=self.window)

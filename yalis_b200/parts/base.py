@@ -140,11 +140,21 @@ class Norm(Part):
         raise NotImplementedError
 
 
+NOT_ROTARY = object()     # answer of PositionEncoding.rotary_frequencies for encodings a mixer's kernel cannot apply itself
+
+
 class PositionEncoding(Part):
     category = "position"
 
     def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, ctx, cache: PagedKVCache, dtype=None):
         raise NotImplementedError
+
+    def rotary_frequencies(self, head_dim: int, device):
+        """For mixers whose kernel can encode positions itself (one launch less): the float32 inverse
+        frequencies [head_dim / 2] of a half-split rotary encoding with angle position * frequency, ``None``
+        for "store and use Q, K unrotated", or ``NOT_ROTARY`` (the default) for anything else - the mixer
+        then calls ``encode_and_store``."""
+        return NOT_ROTARY
 
 
 class Mixer(Part):

@@ -58,8 +58,19 @@ class RotaryEncoding(PositionEncoding):
                              head_dim, out_dtype=dtype, bad_flag=ctx.error_flag)
 
 
+    def rotary_frequencies(self, head_dim: int, device):
+        if head_dim != self.head_dim:
+            raise ValueError(f"rotary encoding built for head_dim {self.head_dim}, used with {head_dim}")
+        if self.inv_freq is None or self.inv_freq.device != torch.device(device):
+            self.to(device)
+        return self.inv_freq
+
+
 class NoPositionEncoding(PositionEncoding):
     """Stores K and V unrotated (a mixer that wants positions handled elsewhere)."""
+
+    def rotary_frequencies(self, head_dim: int, device):
+        return None
 
     def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, ctx, cache: PagedKVCache, dtype=None):
         store = cache.writable
