@@ -60,9 +60,11 @@ class PagedAttention(Mixer):
 
     def forward(self, x: torch.Tensor, ctx, cache: PagedKVCache) -> torch.Tensor:
         qkv = linear_partial(x, self.w_qkv)          # [N, width], or float32 partial sums [S, N, width]
-        if attn_ops.USE_FUSED_ROPE and attn_ops.decode_tma_applicable(x.dtype, ctx, self.hs, cache.k.shape[2],
-                                                                        self.nh // self.g, self.window):
-            # a decode step: the attention kernel rotates Q and the new K itself and stores K, V (one launch less)
+        if (attn_ops.USE_FUSED_ROPE and ctx.n_requests * self.g <= 2 * attn_ops.SM_COUNT
+                and attn_ops.decode_tma_applicable(x.dtype, ctx, self.hs, cache.k.shape[2], self.nh // self.g, self.window)):
+            # A decode step whose attention blocks fit the GPU at once: the attention kernel rotates Q and the new K
+            # itself and stores K, V (one launch less).  With more blocks than that the extra work at the start of
+            # every block costs more than the launch (measured at batch 64: 59.5 against 57 us per layer).
             freq = self.position.rotary_frequencies(self.hs, x.device)
             if freq is not NOT_ROTARY:
                 y = attn_ops.decode_attention_tma_fused(
