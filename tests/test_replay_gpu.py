@@ -32,7 +32,8 @@ def make_requests(cfg, lengths, seed):
 
 
 def lengths_for(which):
-    return [5, 17, 33, 70, 100, 128] if which == "A" else [1, 40, 100, 64, 203, 90]
+    return {"A": [5, 17, 33, 70, 100, 128], "B": [1, 40, 100, 64, 203, 90], "C": [3, 64, 65, 130, 200, 77],
+            "D": [16, 63, 129, 250, 34, 100]}[which]
 
 
 _oracle_cache = {}
@@ -77,7 +78,7 @@ def compare(got, want, tol, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["A", "B"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("cut", ["whole", "tail_decoded", "portions", "mixed"])
 def test_cuttings_match_plain(which, dtype, cut):
     std = STD[dtype]
@@ -186,3 +187,26 @@ def test_wanted_subset_and_skipped_logits():
                      (s1[2], ref("r0", 13))):
         assert np.abs(got - exp).max() <= 1e-4 * np.abs(exp).max()
     assert s0.shape[0] == 2 and s1.shape[0] == 3
+
+
+@pytest.mark.parametrize("which", ["C", "D"])
+def test_head_sizes_64_and_128_take_the_tma_and_tcgen05_kernels(which):
+    """With the head sizes they are built for, bfloat16 steps go to the tcgen05 prompt kernel and to the
+    TMA-fed decode kernel that also rotates and stores (and float32 steps to neither)."""
+    from yalis_b200.ops import attention as attn_ops
+    std = STD["bfloat16"]
+    d = tiny_model_dir(which, std)
+    cfg = plain.read_config(d)
+    requests = make_requests(cfg, lengths_for(which)[2:4], seed=5)
+    steps = traces.number(traces.tail_decoded(requests))
+    before = dict(attn_ops.LAUNCHED)
+    replay_in_process(d, "bfloat16", page_size_of(which), steps, traces.peak_tokens(steps))
+    took = {k: attn_ops.LAUNCHED[k] - before.get(k, 0) for k in attn_ops.LAUNCHED}
+    layers = cfg["num_hidden_layers"]
+    assert took.get("prefill_tcgen05", 0) == layers * len(requests)         # one prompt portion per request
+    assert took.get("decode_tma_fused", 0) == layers * 32 * len(requests)     # 32 decoded tokens each, one step each
+    assert took.get("generic", 0) == 0 and took.get("mma", 0) == 0
+    before = dict(attn_ops.LAUNCHED)
+    replay_in_process(d, "float32", page_size_of(which), steps, traces.peak_tokens(steps))
+    took = {k: attn_ops.LAUNCHED[k] - before.get(k, 0) for k in attn_ops.LAUNCHED}
+    assert took.get("generic", 0) > 0 and sum(v for k, v in took.items() if k != "generic") == 0

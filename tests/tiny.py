@@ -1,5 +1,6 @@
-"""Tiny model folders for the tests: two configurations of the architecture that
-differ in every size and option, written with seeded random weights into a
+"""Tiny model folders for the tests: configurations of the architecture that
+differ in every size and option (A and B; C and D have the head sizes 64 and 128 of the
+TMA- and tcgen05-based attention kernels), written with seeded random weights into a
 temporary folder (never committed)."""
 
 import functools
@@ -20,7 +21,7 @@ def _root():
 
 
 # name -> (preset, seed, page size used with it)
-TINY = {"A": ("tiny-A", 0, 16), "B": ("tiny-B", 1, 8)}
+TINY = {"A": ("tiny-A", 0, 16), "B": ("tiny-B", 1, 8), "C": ("tiny-C", 2, 16), "D": ("tiny-D", 3, 64)}
 
 
 @functools.lru_cache(maxsize=None)

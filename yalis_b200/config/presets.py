@@ -57,6 +57,16 @@ PRESETS["tiny-B"] = dict(
                 original_max_position_embeddings=32),
            tied=True, head_dim=32, vocab=512, theta=500000.0, eps=1e-6),
     torch_dtype="bfloat16", bos_token_id=None, eos_token_id=None)
+# Head sizes 64 and 128: the shapes that the TMA- and tcgen05-based attention kernels are built for.
+PRESETS["tiny-C"] = dict(
+    _llama(136, 2, 4, 2, 208, 512,
+           dict(rope_type="llama3", factor=4.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                original_max_position_embeddings=64),
+           tied=False, head_dim=64, vocab=320, theta=10000.0, eps=1e-5),
+    torch_dtype="bfloat16", bos_token_id=None, eos_token_id=None)
+PRESETS["tiny-D"] = dict(
+    _llama(192, 2, 2, 1, 320, 512, None, tied=True, head_dim=128, vocab=272, theta=500000.0, eps=1e-6),
+    torch_dtype="bfloat16", bos_token_id=None, eos_token_id=None)
 
 
 def preset(name: str) -> Dict[str, Any]:

@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+import collections
 import ctypes
 import math
 import os
@@ -39,6 +40,7 @@ def paged_attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch
     p - window < j <= p.  Returns [N, heads*head_dim] in q's dtype.
     """
     name = "paged_attention_generic"
+    LAUNCHED["generic"] += 1
     _check_common(name, q, k_pool, v_pool, positions, req_of_token, block_table, num_heads, num_kv_heads, head_dim)
     need(head_dim % 2 == 0 and head_dim <= 256, name, f"head_dim {head_dim} must be even and at most 256")
     n = q.shape[0]
@@ -56,6 +58,9 @@ def paged_attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch
 
 
 SM_COUNT = 148   # B200
+
+# How often each attention kernel was launched through these wrappers (tests read it to see which path a step took).
+LAUNCHED = collections.Counter()
 # YALIS_B200_NO_DECODE_TMA=1 keeps decode steps on the cp.async kernel (for comparisons).
 # YALIS_B200_NO_FUSED_ROPE=1 keeps the rotary / cache-write kernel apart from the decode attention.
 USE_FUSED_ROPE = os.environ.get("YALIS_B200_NO_FUSED_ROPE", "0") != "1"
@@ -102,6 +107,7 @@ def paged_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Ten
     a request among blocks (decode steps) and needs scratch memory for the partial results.
     """
     name = "paged_attention_mma"
+    LAUNCHED["mma"] += 1
     _check_common(name, q, k_pool, v_pool, positions, req_of_token, block_table, num_heads, num_kv_heads, head_dim)
     need(q.dtype == torch.bfloat16, name, "bfloat16 only (float32 goes to the generic kernel)")
     need(mma_supports(head_dim), name, f"head_dim {head_dim} is not built (multiples of 16 to 128, of 32 to 256)")
@@ -146,6 +152,7 @@ def decode_attention_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
     block table while the kernel before it on the stream is still running; pass it only when all of those
     were complete before that kernel began (inside a model step they are)."""
     name = "decode_attention_tma"
+    LAUNCHED["decode_tma"] += 1
     n, r = q.shape[0], q_start.numel() - 1
     req_dummy = positions      # only shapes and dtypes are checked through the common helper
     _check_common(name, q, k_pool, v_pool, positions, req_dummy, block_table, num_heads, num_kv_heads, head_dim)
@@ -185,6 +192,7 @@ def decode_attention_tma_fused(qkv: torch.Tensor, inv_freq: Optional[torch.Tenso
     the new key and value are written to the pools.  Same bits as ``rope_kv_write`` followed by
     ``decode_attention_tma``."""
     name = "decode_attention_tma_fused"
+    LAUNCHED["decode_tma_fused"] += 1
     width = (num_heads + 2 * num_kv_heads) * head_dim
     need_cuda(name, qkv, inv_freq, k_pool, v_pool, positions, q_start, block_table, error_flag)
     need(qkv.is_contiguous() and qkv.shape[-1] == width and qkv.dim() in (2, 3), name,
@@ -245,6 +253,7 @@ def prefill_attention_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
     """Causal paged attention of prompt portions on tcgen05 tensor cores (no window); the same
     semantics as ``paged_attention_generic``.  ``q`` is [N, >= heads*head_dim]."""
     name = "prefill_attention_tcgen05"
+    LAUNCHED["prefill_tcgen05"] += 1
     n, r = q.shape[0], q_start.numel() - 1
     _check_common(name, q, k_pool, v_pool, positions, positions, block_table, num_heads, num_kv_heads, head_dim)
     need(q.dtype == torch.bfloat16, name, "bfloat16 only")
