@@ -45,13 +45,15 @@ def test_greedy_generation_equals_plain_float32(which, lengths, new, chunk):
     assert all(eng.engine.manager.free_pages(g.name) == g.num_pages for g in eng.engine.groups)
 
 
-def test_greedy_generation_bfloat16_follows_the_oracle():
+@pytest.mark.parametrize("which", ["A", "C", "D"])
+def test_greedy_generation_bfloat16_follows_the_oracle(which):
     """In bfloat16 every generated token is the oracle's best or within rounding of it
-    (the reference's own criterion is top-5 containment: tests/basic_correctness/test_yalis_vs_hf.py:163-185)."""
-    d = tiny_model_dir("A", 0.02)
+    (the reference's own criterion is top-5 containment: tests/basic_correctness/test_yalis_vs_hf.py:163-185).
+    C and D have the head sizes of the TMA / tcgen05 kernels; decode steps run as captured graphs."""
+    d = tiny_model_dir(which, 0.02)
     cfg, w = plain.read_config(d), plain.read_weights(d)
     prompts = prompts_for(cfg, [5, 17, 33])
-    eng = engine_for(d, "bf16")
+    eng = engine_for(d, "bf16", page_size=page_size_of(which))
     tokens, _ = eng.generate(prompts, tokens_to_generate=16)
     for p, row in zip(prompts, tokens.tolist()):
         seq = list(p)
