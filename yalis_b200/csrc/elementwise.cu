@@ -561,19 +561,10 @@ __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, i
   out[idx] = from_f32<T>(act * up);
 }
 
-// bfloat16, halves layout, inter % 8 == 0: eight elements per thread with 16-byte accesses.
-__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
-                                       int inter, size_t total_vec) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (v >= total_vec) return;
-  const int vec_per_row = inter >> 3;
-  const size_t t = v / vec_per_row;
-  const int i = (int)(v - t * vec_per_row) << 3;
-  const __nv_bfloat16* row = in + t * 2 * (size_t)inter;
-  const uint4 g4 = *reinterpret_cast<const uint4*>(row + i);
-  const uint4 u4 = *reinterpret_cast<const uint4*>(row + inter + i);
+// bfloat16, halves layout, inter % 8 == 0: eight elements per 16-byte access, two such groups per thread
+// (both pairs of loads are issued before the first use).  The inputs are read once and the output is read
+// by another kernel: streaming loads and stores keep them from pushing the weights out of the L2.
+__device__ __forceinline__ uint4 silu_mul_8(const uint4 g4, const uint4 u4) {
   const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
   const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
   uint4 o4;
@@ -583,7 +574,34 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __n
     const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
     o2[k] = __floats2bfloat162_rn((g.x / (1.0f + expf(-g.x))) * u.x, (g.y / (1.0f + expf(-g.y))) * u.y);
   }
-  *reinterpret_cast<uint4*>(out + t * (size_t)inter + i) = o4;
+  return o4;
+}
+
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                       int inter, size_t total_vec) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int vec_per_row = inter >> 3;
+  const size_t v0 = ((size_t)blockIdx.x * blockDim.x) * 2 + threadIdx.x, v1 = v0 + blockDim.x;
+  uint4 g[2], u[2];
+  size_t at[2];
+  bool live[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const size_t v = j == 0 ? v0 : v1;
+    live[j] = v < total_vec;
+    if (live[j]) {
+      const size_t t = v / vec_per_row;
+      const int i = (int)(v - t * vec_per_row) << 3;
+      const __nv_bfloat16* row = in + t * 2 * (size_t)inter;
+      g[j] = __ldcs(reinterpret_cast<const uint4*>(row + i));
+      u[j] = __ldcs(reinterpret_cast<const uint4*>(row + inter + i));
+      at[j] = t * (size_t)inter + i;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+    if (live[j]) *reinterpret_cast<uint4*>(out + at[j]) = silu_mul_8(g[j], u[j]);
 }
 
 YALIS_API int yalis_silu_mul(const void* in, void* out, int dtype, int n_tokens, int inter, int interleaved,
@@ -593,7 +611,7 @@ YALIS_API int yalis_silu_mul(const void* in, void* out, int dtype, int n_tokens,
   const int threads = 256;
   if (dtype == YALIS_BF16 && !interleaved && inter % 8 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
     const size_t total_vec = total >> 3;
-    return yalis_launch(silu_mul_bf16x8_kernel, dim3((unsigned)((total_vec + threads - 1) / threads)), dim3(threads), 0,
+    return yalis_launch(silu_mul_bf16x8_kernel, dim3((unsigned)((total_vec + 2 * threads - 1) / (2 * threads))), dim3(threads), 0,
                         stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter, total_vec);
   }
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
