@@ -6,6 +6,11 @@ ones, without a change to any file of the package.
   count), so portions and single tokens must carry state across steps, slots must be
   zeroed on admission and reused slots must not leak.
 * a schedule that runs a layer twice, the second time reading the first run's cache.
+* ``top1_experts``: a toy feed-forward with routing (float32 router logits, one of three small
+  gated MLPs per token).
+* ``decay``: a toy position encoding that is no rotation (keys grow and queries shrink by a
+  factor per position, so a score decays with distance); the attention part then keeps its
+  separate encode-and-store step on every path.
 """
 
 import os
@@ -20,7 +25,8 @@ import traces
 from yalis_b200.config import registry
 from yalis_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from yalis_b200.ops.linear import linear
-from yalis_b200.parts.base import Mixer, ParamSpec, SlotState, register_part
+from yalis_b200.ops.elementwise import rope_kv_write
+from yalis_b200.parts.base import FeedForward, Mixer, ParamSpec, PositionEncoding, SlotState, register_part
 
 pytestmark = pytest.mark.gpu
 
@@ -55,6 +61,56 @@ class RunningMean(Mixer):
         return linear(out, self.w)
 
 
+class Top1Experts(FeedForward):
+    """Router logits in float32; every token goes to the expert with the largest one."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden, self.inner, self.n = spec.params["hidden_size"], spec.params["intermediate_size"], spec.params["experts"]
+
+    def param_specs(self):
+        specs = {"router": ParamSpec((self.n, self.hidden), keep_float32=True)}
+        for j in range(self.n):
+            specs[f"gate{j}"] = ParamSpec((self.inner, self.hidden))
+            specs[f"up{j}"] = ParamSpec((self.inner, self.hidden))
+            specs[f"down{j}"] = ParamSpec((self.hidden, self.inner))
+        return specs
+
+    def load(self, tensors):
+        self.t = tensors
+
+    def forward(self, x, ctx):
+        choice = (x.float() @ self.t["router"].float().T).argmax(dim=-1)
+        out = torch.zeros_like(x)
+        for j in range(self.n):
+            rows = (choice == j).nonzero().flatten()
+            if rows.numel():
+                h = x[rows]
+                a = torch.nn.functional.silu((h @ self.t[f"gate{j}"].T).float()) * (h @ self.t[f"up{j}"].T).float()
+                out[rows] = a.to(x.dtype) @ self.t[f"down{j}"].T
+        return out
+
+
+class Decay(PositionEncoding):
+    """q_t <- q_t * gamma^(-t), k_t <- k_t * gamma^t: the score of (t, s) is scaled by gamma^(s - t)."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.gamma = float(spec.params["gamma"])
+
+    def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, ctx, cache, dtype=None):
+        if qkv.dim() == 3:                       # partial sums of a split product
+            qkv = qkv.sum(0)
+        qkv = qkv.float()
+        nq, nk = num_heads * head_dim, num_kv_heads * head_dim
+        grow = torch.pow(torch.tensor(self.gamma, device=qkv.device), ctx.positions.float())[:, None]
+        scaled = torch.cat([qkv[:, :nq] / grow, qkv[:, nq:nq + nk] * grow, qkv[:, nq + nk:]], dim=1).to(dtype).contiguous()
+        store = cache.writable
+        return rope_kv_write(scaled, ctx.positions, ctx.req_of_token, None, cache.k if store else None,
+                             cache.v if store else None, ctx.block_tables[cache.group], num_heads, num_kv_heads, head_dim,
+                             out_dtype=dtype, bad_flag=ctx.error_flag)
+
+
 class ToyArchitecture:
     """hidden/heads from its own config.json keys; layer kinds chosen per layer by ``mixers``."""
 
@@ -78,6 +134,10 @@ class ToyArchitecture:
                       "mixer.o_proj": "attn.o.weight"}
         common = {"feed_forward.gate_proj": "ff.gate.weight", "feed_forward.up_proj": "ff.up.weight",
                   "feed_forward.down_proj": "ff.down.weight", "norm_1.weight": "n1.weight", "norm_2.weight": "n2.weight"}
+        routed = PartSpec("top1_experts", {"hidden_size": h, "intermediate_size": c["inner"], "experts": 3})
+        routed_names = dict({"feed_forward.router": "ff.router.weight"},
+                            **{f"feed_forward.{n}{j}": f"ff.{j}.{n}.weight" for j in range(3) for n in ("gate", "up", "down")})
+        decay = PartSpec("decay", {"gamma": 0.98})
         layers = []
         for i, kind in enumerate(c["mixers"]):
             if kind == "attention":
@@ -87,7 +147,13 @@ class ToyArchitecture:
                 names = dict(attn_names, **common)
             else:
                 mixer, names = PartSpec("running_mean", {"hidden_size": h}), dict({"mixer.mix": "mean.mix.weight"}, **common)
-            layers.append(LayerSpec(PartSpec("pre_norm_residual"), mixer, ffn, norm, norm, rot, f"toy.{i}.", names))
+            ff, pos = ffn, rot
+            if c.get("ffs") and c["ffs"][i] == "routed":
+                ff = routed
+                names = dict({k: v for k, v in names.items() if not k.startswith("feed_forward.")}, **routed_names)
+            if c.get("positions") and c["positions"][i] == "decay":
+                pos = decay
+            layers.append(LayerSpec(PartSpec("pre_norm_residual"), mixer, ff, norm, norm, pos, f"toy.{i}.", names))
         schedule = tuple(ScheduleEntry(l, c) for l, c in c["schedule"])
         return ModelSpec("ToyForCausalLM", h, c["vocab"], c["max_len"], tuple(layers), schedule, norm, "toy.embed.weight",
                          "toy.head.weight", {"weight": "toy.norm.weight"})
@@ -95,12 +161,15 @@ class ToyArchitecture:
 
 def setup_module(module):
     register_part("mixer", "running_mean", RunningMean, replace=True)
+    register_part("feed_forward", "top1_experts", Top1Experts, replace=True)
+    register_part("position", "decay", Decay, replace=True)
     registry.register_architecture("ToyForCausalLM", ToyArchitecture, replace=True)
 
 
-def toy_config(mixers, schedule, window=None, head_dim=8):
+def toy_config(mixers, schedule, window=None, head_dim=8, ffs=None, positions=None):
     return dict(architectures=["ToyForCausalLM"], width=40, heads=4, kv_heads=2, head_dim=head_dim, inner=56, vocab=97,
-                max_len=160, eps=1e-5, mixers=mixers, schedule=schedule, window=window, torch_dtype="bfloat16")
+                max_len=160, eps=1e-5, mixers=mixers, schedule=schedule, window=window, ffs=ffs, positions=positions,
+                torch_dtype="bfloat16")
 
 
 def plain_toy(tokens, w, c):
@@ -117,10 +186,15 @@ def plain_toy(tokens, w, c):
         if c["mixers"][layer] in ("attention", "window_attention"):
             window = c["window"] if c["mixers"][layer] == "window_attention" else None
             nh, g, hs = c["heads"], c["kv_heads"], c["head_dim"]
-            cos, sin = plain.rope_tables(pos, plain.rope_inverse_frequencies(hs, 10000.0, None))
-            q = plain.apply_rope((h @ w[p + "attn.q.weight"].T).view(t, nh, hs), cos, sin)
+            if c.get("positions") and c["positions"][layer] == "decay":
+                grow = torch.pow(torch.tensor(0.98), pos.float())[:, None, None]
+                encode_q, encode_k = (lambda z: z / grow), (lambda z: z * grow)
+            else:
+                cos, sin = plain.rope_tables(pos, plain.rope_inverse_frequencies(hs, 10000.0, None))
+                encode_q = encode_k = lambda z: plain.apply_rope(z, cos, sin)
+            q = encode_q((h @ w[p + "attn.q.weight"].T).view(t, nh, hs))
             if cache_of is None:
-                k = plain.apply_rope((h @ w[p + "attn.k.weight"].T).view(t, g, hs), cos, sin)
+                k = encode_k((h @ w[p + "attn.k.weight"].T).view(t, g, hs))
                 v = (h @ w[p + "attn.v.weight"].T).view(t, g, hs)
                 kept[idx] = (k, v)
             else:
@@ -131,7 +205,15 @@ def plain_toy(tokens, w, c):
             y = means @ w[p + "mean.mix.weight"].T
         x = x + y
         h = plain.rms_norm(x, w[p + "n2.weight"], c["eps"])
-        x = x + plain.swiglu(h, w[p + "ff.gate.weight"], w[p + "ff.up.weight"], w[p + "ff.down.weight"])
+        if c.get("ffs") and c["ffs"][layer] == "routed":
+            choice = (h @ w[p + "ff.router.weight"].T).argmax(dim=-1)
+            y = torch.zeros_like(h)
+            for j in range(3):
+                rows = (choice == j).nonzero().flatten()
+                y[rows] = plain.swiglu(h[rows], w[p + f"ff.{j}.gate.weight"], w[p + f"ff.{j}.up.weight"], w[p + f"ff.{j}.down.weight"])
+            x = x + y
+        else:
+            x = x + plain.swiglu(h, w[p + "ff.gate.weight"], w[p + "ff.up.weight"], w[p + "ff.down.weight"])
     return plain.rms_norm(x, w["toy.norm.weight"], c["eps"]) @ w["toy.head.weight"].T
 
 
@@ -208,3 +290,40 @@ def test_window_layers_have_pages_of_their_own(dtype):
                 err = np.abs(got[rid] - want[rid]).max() / np.abs(want[rid]).max()
                 assert err < tol, (build.__name__, rid, err)
             rep.engine.manager.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_routed_feed_forward_and_another_position_encoding(dtype):
+    """A layer with a routed feed-forward and a layer whose position encoding is no rotation (head size
+    64: in bfloat16 its decode steps go to the TMA kernel through the separate encode-and-store step),
+    cut every way, against the plain model."""
+    from yalis_b200.engine.replay import Replayer
+    from yalis_b200.ops import attention as attn_ops
+    from yalis_b200.weights.loader import write_random_model
+    c = toy_config(["attention", "attention"], [(0, None), (1, None)], head_dim=64, ffs=["routed", "dense"],
+                   positions=["rotary", "decay"])
+    std = 0.2 if dtype == "float32" else 0.05
+    with tempfile.TemporaryDirectory() as d:
+        write_random_model(c, d, seed=9, std=std)
+        w = plain.read_weights(d)
+        g = torch.Generator().manual_seed(3)
+        requests = {f"r{i}": torch.randint(0, c["vocab"], (n,), generator=g).tolist() for i, n in enumerate([70, 9, 120, 40])}
+        want = {rid: plain_toy(t, w, c).numpy() for rid, t in requests.items()}
+        before = dict(attn_ops.LAUNCHED)
+        for build in (traces.whole, traces.tail_decoded, traces.portions, traces.mixed):
+            steps = traces.number(build(requests))
+            rep = Replayer(d, dtype, traces.peak_tokens(steps), page_size=16, max_live=4)
+            out = {}
+            for s in steps:
+                r = rep.run_step(s)
+                if r is not None:
+                    out[s["step"]] = r
+            got = traces.collect(steps, out, c["vocab"])
+            tol = 1e-4 if dtype == "float32" else 3e-2
+            for rid in want:
+                err = np.abs(got[rid] - want[rid]).max() / np.abs(want[rid]).max()
+                assert err < tol, (build.__name__, rid, err)
+            rep.engine.manager.check()
+        if dtype == "bfloat16":
+            took = {k: attn_ops.LAUNCHED[k] - before.get(k, 0) for k in attn_ops.LAUNCHED}
+            assert took.get("decode_tma", 0) > 0 and took.get("decode_tma_fused", 0) > 0    # the decay layer, the rotary layer
