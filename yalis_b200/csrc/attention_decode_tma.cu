@@ -185,17 +185,26 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   }
 
   int armed = 0;
-  // One tile: wait for the stage to be free, then one box copy per page and 64-column half.
+  // One tile, issued by the whole producer warp: lane 0 waits for the stage to be free and arms its barrier,
+  // then every lane issues its share of the box copies (one per page, 64-column half and K or V: with small
+  // pages a single thread would spend longer issuing them than the copies take).
+  const int lane_p = threadIdx.x & 31;
   auto issue_tile = [&](int it, int tile_lo, int hi_key, const int32_t* bt) -> bool {
     const int pages_per_tile = BN / p.page_size;
     const uint32_t page_bytes = (uint32_t)p.page_size * HS * 2;
     const int s = it % STAGES;
     const uint32_t ph = (it / STAGES) & 1;
-    if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) return false;
     const int key0 = (tile_lo + it) * BN;
     const int n_pages = min(pages_per_tile, (hi_key - key0) / p.page_size + 1);
-    mbar_expect_tx(&full[s], 2u * page_bytes * (uint32_t)n_pages);
-    for (int i = 0; i < n_pages; ++i) {
+    int ok = 1;
+    if (lane_p == 0) {
+      ok = mbar_wait(&empty[s], ph ^ 1, abort_flag) ? 1 : 0;
+      if (ok) mbar_expect_tx(&full[s], 2u * page_bytes * (uint32_t)n_pages);
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) return false;
+    for (int c = lane_p; c < n_pages * 2 * H2; c += 32) {
+      const int i = c / (2 * H2), kv = (c / H2) & 1, h = c % H2;
       const int pi = key0 / p.page_size + i;
       int page = pi < p.table_width ? bt[pi] : -1;
       if (page < 0 || page >= p.num_pages) {   // a visible key without a page: a caller's bug
@@ -203,18 +212,15 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         page = 0;
       }
       const int y = (page * p.g + kvh) * p.page_size;
-#pragma unroll
-      for (int h = 0; h < H2; ++h) {
-        const int off = h * (BN * 128) + i * p.page_size * 128;
-        tma_load_2d(k_s + s * TILE_BYTES + off, &map_k, h * 64, y, &full[s]);
-        tma_load_2d(v_s + s * TILE_BYTES + off, &map_v, h * 64, y, &full[s]);
-      }
+      const int off = h * (BN * 128) + i * p.page_size * 128;
+      tma_load_2d((kv ? v_s : k_s) + s * TILE_BYTES + off, kv ? &map_v : &map_k, h * 64, y, &full[s]);
     }
+    __syncwarp();
     armed = it + 1;
     return true;
   };
 
-  if (p.early_fetch && is_producer) {
+  if (p.early_fetch && warp == CWARPS) {
     // Tiles that end below the query's position hold keys of earlier steps only, and the caller
     // promises that the step's index arrays were complete before the preceding kernel began:
     // fetch them while that kernel (which writes this step's key and value) is still running.
@@ -263,11 +269,9 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
   if (warp == CWARPS) {
     // ---- producer -------------------------------------------------------------------------
-    if (lane == 0) {
-      for (int it = armed; it < n_tiles; ++it)
-        if (!issue_tile(it, tile_lo, hi_key, bt)) break;
-      pdl_launch_dependents();     // the last tile is on its way: the next kernel's blocks may start filling their rings
-    }
+    for (int it = armed; it < n_tiles; ++it)
+      if (!issue_tile(it, tile_lo, hi_key, bt)) break;
+    if (lane == 0) pdl_launch_dependents();     // the last tile is on its way: the next kernel's blocks may start filling their rings
     __syncwarp();
   } else {
     // ---- consumers ---------------------------------------------------------------------------

@@ -229,43 +229,50 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   int k_armed = 0, v_armed = 0;
   if (warp == 4) {
     // ---------------------------------- TMA producer ------------------------------------------
+    // Lane 0 waits for free buffers and arms the barriers; all lanes issue the box copies of a tile (with
+    // small pages one thread would spend longer issuing them than they take).
     if (lane == 0) {
       mbar_expect_tx(q_full, (uint32_t)(p.tokens_per_tile * p.per) * HS * 2);
 #pragma unroll
       for (int h = 0; h < H2; ++h)
         tma_load_3d(q_s + h * (BM * 128), &map_q, h * 64, kvh * p.per, tok0 + t0, q_full);
-      // A tile is fetched in boxes of min(page, BN) keys: several pages, or a part of one.
-      const int box_rows = min(p.page_size, BN);
-      const int boxes_per_tile = BN / box_rows;
-      const uint32_t box_bytes = (uint32_t)box_rows * HS * 2;
-      bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const int key0 = j * BN;
-        const int n_boxes = min(boxes_per_tile, (hi_key - key0) / box_rows + 1);
-        for (int kv = 0; kv < 2 && ok; ++kv) {
-          uint64_t* full = kv == 0 ? &k_full[b] : &v_full[b];
-          uint64_t* empty = kv == 0 ? &k_empty[b] : &v_empty[b];
-          unsigned char* dst = (kv == 0 ? k_s : v_s) + b * KV_BYTES;
-          const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
-          if (!mbar_wait(empty, ph ^ 1, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(full, box_bytes * (uint32_t)n_boxes);
-          for (int i = 0; i < n_boxes; ++i) {
-            const int key = key0 + i * box_rows;
-            const int pi = key / p.page_size;
-            int page = pi < p.table_width ? bt[pi] : -1;
-            if (page < 0 || page >= p.num_pages) {
-              if (p.error) atomicExch(p.error, 1);
-              page = 0;
-            }
-            const int y = (page * p.g + kvh) * p.page_size + (key - pi * p.page_size);
-#pragma unroll
-            for (int h = 0; h < H2; ++h)
-              tma_load_2d(dst + h * (BN * 128) + i * box_rows * 128, map, h * 64, y, full);
-          }
-          if (kv == 0) k_armed = j + 1; else v_armed = j + 1;
+    }
+    // A tile is fetched in boxes of min(page, BN) keys: several pages, or a part of one.
+    const int box_rows = min(p.page_size, BN);
+    const int boxes_per_tile = BN / box_rows;
+    const uint32_t box_bytes = (uint32_t)box_rows * HS * 2;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int b = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      const int key0 = j * BN;
+      const int n_boxes = min(boxes_per_tile, (hi_key - key0) / box_rows + 1);
+      for (int kv = 0; kv < 2 && ok; ++kv) {
+        uint64_t* full = kv == 0 ? &k_full[b] : &v_full[b];
+        uint64_t* empty = kv == 0 ? &k_empty[b] : &v_empty[b];
+        unsigned char* dst = (kv == 0 ? k_s : v_s) + b * KV_BYTES;
+        const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
+        int go = 1;
+        if (lane == 0) {
+          go = mbar_wait(empty, ph ^ 1, abort_flag) ? 1 : 0;
+          if (go) mbar_expect_tx(full, box_bytes * (uint32_t)n_boxes);
         }
+        go = __shfl_sync(0xffffffffu, go, 0);
+        if (!go) { ok = false; break; }
+        for (int c = lane; c < n_boxes * H2; c += 32) {
+          const int i = c / H2, h = c - i * H2;
+          const int key = key0 + i * box_rows;
+          const int pi = key / p.page_size;
+          int page = pi < p.table_width ? bt[pi] : -1;
+          if (page < 0 || page >= p.num_pages) {
+            if (p.error) atomicExch(p.error, 1);
+            page = 0;
+          }
+          const int y = (page * p.g + kvh) * p.page_size + (key - pi * p.page_size);
+          tma_load_2d(dst + h * (BN * 128) + i * box_rows * 128, map, h * 64, y, full);
+        }
+        __syncwarp();
+        if (kv == 0) k_armed = j + 1; else v_armed = j + 1;
       }
     }
     __syncwarp();
