@@ -210,3 +210,24 @@ def test_head_sizes_64_and_128_take_the_tma_and_tcgen05_kernels(which):
     replay_in_process(d, "float32", page_size_of(which), steps, traces.peak_tokens(steps))
     took = {k: attn_ops.LAUNCHED[k] - before.get(k, 0) for k in attn_ops.LAUNCHED}
     assert took.get("generic", 0) > 0 and sum(v for k, v in took.items() if k != "generic") == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_layer_of_the_8b_shape(dtype):
+    """Layer sizes of Llama-3-8B (width 4096, 32 heads over 8 KV heads of 128, inner width 14336) with one
+    layer and a small vocabulary, whole and with the tail decoded token by token, against the plain model."""
+    from yalis_b200.config.presets import preset
+    from yalis_b200.weights.loader import write_random_model
+    cfg = preset("Llama-3-8B")
+    cfg.update(num_hidden_layers=1, vocab_size=2048, max_position_embeddings=512, bos_token_id=None, eos_token_id=None)
+    with tempfile.TemporaryDirectory() as d:
+        write_random_model(cfg, d, seed=4, std=0.02)
+        pcfg, w = plain.read_config(d), plain.read_weights(d)
+        requests = make_requests(pcfg, [150, 40], seed=2)
+        want = {rid: plain.forward_logits(t, w, pcfg).numpy() for rid, t in requests.items()}
+        del w
+        for build in (traces.whole, traces.tail_decoded, traces.mixed):
+            steps = traces.number(build(requests))
+            out, _ = replay_in_process(d, dtype, 16, steps, traces.peak_tokens(steps))
+            got = traces.collect(steps, out, pcfg["vocab_size"])
+            compare(got, want, TOL[dtype], f"8B layer/{dtype}/{build.__name__}")
