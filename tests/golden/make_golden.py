@@ -158,6 +158,8 @@ def run(which: str, n_tokens: int, prefix: int, std: float):
 
 
 if __name__ == "__main__":
-    install_stand_ins(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <checkout of the reference>")
+    install_stand_ins(sys.argv[1])
     run("A", n_tokens=24, prefix=17, std=0.1)
     run("B", n_tokens=40, prefix=33, std=0.1)
