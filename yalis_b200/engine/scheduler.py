@@ -45,7 +45,7 @@ from yalis_b200.sampling.sampler import SamplingParams
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
 
 
-@dataclass
+@dataclass(eq=False)          # a request is itself: membership tests must not compare token lists
 class Request:
     id: Hashable
     prompt: List[int]
