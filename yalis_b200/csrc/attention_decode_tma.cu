@@ -1,15 +1,25 @@
 // Decode attention with TMA-fed key/value tiles: one query token per request, the keys of a
 // (request, KV head) divided among `n_splits` blocks.
 //
-// It computes what paged_attention_mma_kernel<HS, true> computes (attention_mma.cu) and merges
-// splits the same way (tickets, last block merges in split order); what differs is how K and V
-// reach shared memory.  There every thread computes page addresses and issues 16-byte
-// cp.async copies, which made the kernel instruction-bound.  Here one producer thread walks the
-// block table and issues one TMA box copy per (page, 64-column half) for K and for V
-// (cp.async.bulk.tensor.2d over the pool seen as a matrix [pages*kv_heads*page_size, head_dim],
-// 128-byte swizzle), completion is counted by an mbarrier per stage, and the four consumer
-// warps only wait, run ldmatrix on the swizzled tiles and mma.sync.  The ring has two stages (two
-// blocks per SM keep four tiles in flight, and a block of the next kernel still fits beside them).
+// It computes what paged_attention_mma_kernel<HS, true> computes (attention_mma.cu); what differs
+// is how K and V reach shared memory and how the splits are merged.
+//   * There every thread computes page addresses and issues 16-byte cp.async copies, which made
+//     the kernel instruction-bound.  Here a producer warp walks the block table and issues one TMA
+//     box copy per (page, 64-column half) for K and for V (cp.async.bulk.tensor.2d over the pool
+//     seen as a matrix [pages*kv_heads*page_size, head_dim], 128-byte swizzle; the lanes share
+//     the copies of a tile), completion is counted by an mbarrier per stage, and the four consumer
+//     warps only wait, run ldmatrix on the swizzled tiles and mma.sync.  The ring has two stages
+//     (two blocks per SM keep four tiles in flight, and a block of the next kernel still fits
+//     beside them).
+//   * Up to 8 splits are launched as one thread-block cluster and merged through distributed
+//     shared memory: every block leaves its (max, sum, unnormalised output) in its own shared
+//     memory, and after a cluster barrier each block finishes a share of the outputs, summing in
+//     split order.  More splits go through global memory with a ticket per (request, KV head).
+//   * Tiles that lie wholly below the query's position can be fetched before the preceding
+//     kernel has finished (early_fetch; see the entry point for what the caller promises).
+//   * Fused mode: the kernel takes the step's QKV projection instead of rotated queries, rotates
+//     the queries of its KV head itself and, in the block that owns the query's own position,
+//     the new key; that block writes the new key and value to the pools and into its tile.
 //
 // Limits (the launcher refuses anything else, the caller then uses the cp.async kernel):
 // bfloat16, head_dim a multiple of 64 up to 256, page_size 8, 16, 32 or 64, no window, at most
@@ -18,7 +28,7 @@
 // Keys beyond the query's position share the last page with visible ones and may hold anything:
 // their scores are masked by index and their V rows are zeroed in shared memory before use.
 // Every mbarrier wait is bounded; on a timeout the block raises the error word, drains its
-// outstanding copies and returns.
+// outstanding copies and returns (it still meets its cluster at both barriers).
 #include <cuda.h>
 
 #include "common.cuh"
