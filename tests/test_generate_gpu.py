@@ -124,3 +124,23 @@ def test_generate_shortcut_and_command_line():
     assert proc.returncode == 0, proc.stderr[-2000:]
     lines = [l for l in proc.stdout.splitlines() if l.startswith("output = ")]
     assert [eval(l[len("output = "):]) for l in lines] == out
+
+
+def test_long_context_kind_of_decode_steps(monkeypatch):
+    """Decode steps beyond the long-context mark are captured as a kind of their own, with more key
+    splits merged through global memory; with the mark lowered to 48 tokens a tiny model crosses it."""
+    from yalis_b200.ops import attention as attn_ops
+    monkeypatch.setattr(attn_ops, "LONG_CONTEXT", 48)
+    d = tiny_model_dir("C", 0.02)
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    prompts = prompts_for(cfg, [30, 44, 17])
+    eng = engine_for(d, "bf16", page_size=page_size_of("C"))
+    tokens, _ = eng.generate(prompts, tokens_to_generate=24)
+    kinds = {k[3] for k in eng.engine.decoder._buckets}
+    assert kinds == {False, True}                       # the batch crossed the mark while it decoded
+    for p, row in zip(prompts, tokens.tolist()):
+        seq = list(p)
+        for tok in row:
+            ref = plain.forward_logits(seq, w, cfg)[-1]
+            assert float(ref.max() - ref[tok]) <= 2e-2 * float(ref.abs().max())
+            seq.append(tok)

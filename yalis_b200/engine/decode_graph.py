@@ -40,8 +40,9 @@ def bucket_for(n: int) -> int:
 class _Bucket:
     """Static buffers and the captured graph for one batch size."""
 
-    def __init__(self, engine, size: int, greedy: bool, keep_logits: bool):
+    def __init__(self, engine, size: int, greedy: bool, keep_logits: bool, long_context: bool = False):
         self.engine, self.size, self.greedy, self.keep_logits = engine, size, greedy, keep_logits
+        self.long_context = long_context
         dev = engine.device
         self.widths = [g.max_pages_per_request for g in engine.groups]
         r = size
@@ -90,7 +91,9 @@ class _Bucket:
         self.ctx = StepContext(
             n_tokens=r, n_requests=r, token_ids=self.tokens, positions=d_pos, req_of_token=d_req, q_start=d_qs,
             kv_len=d_kv, slots=d_slots, logit_rows=d_rows, block_tables=d_tables,
-            host=HostStep(slots=[], q_start=list(range(r + 1)), ctx_before=[], max_q_len=1, max_kv_len=0),
+            # lengths are not part of a captured step; only whether it is of the long-context kind (more key splits)
+            host=HostStep(slots=[], q_start=list(range(r + 1)), ctx_before=[], max_q_len=1,
+                          max_kv_len=engine.max_context if long_context else 0),
             error_flag=engine._error_flag, decode_only=True, settled=True)
 
     def fill(self, slots: Sequence[int], lengths: Sequence[int], params: Optional[Sequence[SamplingParams]],
@@ -167,12 +170,14 @@ class GraphedDecoder:
         eng = self.engine
         n = len(slots)
         greedy = params is None or all(p.greedy for p in params)
-        key = (bucket_for(n), greedy, keep_logits)
-        b = self._buckets.get(key)
-        if b is None:
-            b = self._buckets[key] = _Bucket(eng, key[0], greedy, keep_logits)
         mgr = eng.manager
         lengths = [mgr.length(s) for s in slots]
+        from yalis_b200.ops.attention import LONG_CONTEXT
+        long_context = max(lengths) + 1 > LONG_CONTEXT
+        key = (bucket_for(n), greedy, keep_logits, long_context)
+        b = self._buckets.get(key)
+        if b is None:
+            b = self._buckets[key] = _Bucket(eng, key[0], greedy, keep_logits, long_context)
         for s, l in zip(slots, lengths):
             if l + 1 > eng.max_context or not mgr.fits(l + 1):
                 from yalis_b200.engine.engine import StepError
@@ -182,6 +187,10 @@ class GraphedDecoder:
                 raise OutOfPages(f"no pages left for a decode step (free: {eng.free_pages()})")
         if b.copy_done is not None:
             b.copy_done.synchronize()           # the last copies out of the pinned buffers have finished
+        if tokens is None and self.last_bucket is not None and self.last_bucket is not b:
+            # the same requests moved to another kind of step (e.g. past the long-context mark): their last
+            # tokens are in the buffer of the bucket that chose them
+            b.tokens[:n].copy_(self.last_bucket.tokens[:n], non_blocking=True)
         if tokens is not None:
             if min(tokens) < 0 or max(tokens) >= eng.vocab_size:
                 from yalis_b200.engine.engine import StepError

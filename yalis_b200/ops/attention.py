@@ -83,6 +83,17 @@ def decode_splits(n_requests: int, num_kv_heads: int) -> int:
     return max(1, min(32, (2 * SM_COUNT) // blocks))
 
 
+LONG_CONTEXT = 8192     # beyond this many cached tokens a few requests cannot keep HBM busy with 8 splits each
+
+
+def decode_tma_splits(ctx, num_kv_heads: int) -> int:
+    """Splits of a (request, KV head) for the TMA-fed decode kernel: up to 8 merge inside a thread-block
+    cluster (the cheaper merge); steps marked as long-context take up to 32 and merge through global memory,
+    so that a single long request still spreads over the whole GPU."""
+    n = decode_splits(ctx.n_requests, num_kv_heads)
+    return n if ctx.host.max_kv_len > LONG_CONTEXT else min(8, n)
+
+
 _ticket_cache = {}
 
 
@@ -284,7 +295,7 @@ def paged_attention(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     per = num_heads // num_kv_heads
     if decode_tma_applicable(qkv.dtype, ctx, head_dim, k_pool.shape[2], per, window):
         return decode_attention_tma(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, num_heads, num_kv_heads,
-                                    head_dim, scale=scale, n_splits=min(8, decode_splits(ctx.n_requests, num_kv_heads)),
+                                    head_dim, scale=scale, n_splits=decode_tma_splits(ctx, num_kv_heads),
                                     error_flag=ctx.error_flag, early_fetch=bool(getattr(ctx, "settled", False)))
     if (qkv.dtype == torch.bfloat16 and USE_PREFILL_TCGEN05 and window is None and ctx.host.max_q_len >= 16
             and prefill_tcgen05_supports(head_dim, k_pool.shape[2], per)):

@@ -70,7 +70,7 @@ class PagedAttention(Mixer):
                 y = attn_ops.decode_attention_tma_fused(
                     qkv, freq, cache.writable, cache.k, cache.v, ctx.positions, ctx.q_start,
                     ctx.block_tables[cache.group], self.nh, self.g, self.hs, scale=self.scale,
-                    n_splits=min(8, attn_ops.decode_splits(ctx.n_requests, self.g)), error_flag=ctx.error_flag,
+                    n_splits=attn_ops.decode_tma_splits(ctx, self.g), error_flag=ctx.error_flag,
                     early_fetch=bool(getattr(ctx, "settled", False)))
                 return linear_partial(y, self.w_o)
         q = self.position.encode_and_store(qkv, self.nh, self.g, self.hs, ctx, cache, dtype=x.dtype)
