@@ -78,6 +78,25 @@ def test_more_prompts_than_slots_and_few_pages():
     eng.engine.manager.check()
 
 
+def test_waiting_and_preemption_in_bfloat16_with_the_native_kernels():
+    """The same pressure in bfloat16 with head size 64 (tcgen05 / TMA kernels, captured decode steps that
+    run ahead of the host): every token is the oracle's best on the row's own prefix, or within rounding."""
+    d = tiny_model_dir("C", 0.02)
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    prompts = prompts_for(cfg, [30, 3, 61, 12, 45, 8, 70, 22, 5], seed=4)
+    eng = engine_for(d, "bf16", max_batch_size=3, page_size=16, cache_tokens=112, prefill_chunk=16, max_tokens_per_step=40)
+    tokens, metrics = eng.generate(prompts, tokens_to_generate=10)
+    assert metrics["Preemptions"] > 0
+    for p, row in zip(prompts, tokens.tolist()):
+        seq = list(p)
+        for tok in row:
+            ref = plain.forward_logits(seq, w, cfg)[-1]
+            assert float(ref.max() - ref[tok]) <= 2e-2 * float(ref.abs().max())
+            seq.append(tok)
+    eng.engine.manager.check()
+    assert all(eng.engine.manager.free_pages(g.name) == g.num_pages for g in eng.engine.groups)
+
+
 def test_eos_stops_a_row_and_pads_it():
     d = tiny_model_dir("A", 0.3)
     cfg, w = plain.read_config(d), plain.read_weights(d)
