@@ -163,3 +163,23 @@ def test_long_context_kind_of_decode_steps(monkeypatch):
             ref = plain.forward_logits(seq, w, cfg)[-1]
             assert float(ref.max() - ref[tok]) <= 2e-2 * float(ref.abs().max())
             seq.append(tok)
+
+
+def test_sampling_with_block_tables_used_to_their_last_entry():
+    """Requests that grow into the last page their block-table row can name, decoded with sampling in
+    captured steps: the per-row sampling parameters and the tables lie in one buffer and must not overlap
+    (a fuzzing run found the last table entries overwritten by the temperatures)."""
+    d = tiny_model_dir("B", 0.3)
+    cfg = plain.read_config(d)
+    prompts = prompts_for(cfg, [18, 7, 2, 43, 52], seed=9)
+    new = 19
+    longest = max(len(p) for p in prompts) + new
+    kw = dict(temperature=0.8, top_p=0.9, seed=5, max_batch_size=4, page_size=8,
+              max_length_of_generated_sequences=-(-longest // 8) * 8, cache_tokens=400)
+    a, _ = engine_for(d, "fp32", **kw).generate(prompts, tokens_to_generate=new)
+    os.environ["YALIS_DISABLE_DECODE_CUDAGRAPHS"] = "1"
+    try:
+        b, _ = engine_for(d, "fp32", **kw).generate(prompts, tokens_to_generate=new)
+    finally:
+        del os.environ["YALIS_DISABLE_DECODE_CUDAGRAPHS"]
+    assert torch.equal(a, b)            # captured steps draw what step-by-step launches draw

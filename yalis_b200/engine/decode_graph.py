@@ -48,7 +48,7 @@ class _Bucket:
         r = size
         # int32 layout: positions | req_of_token | q_start | kv_len | slots | logit_rows | top_k | tables... ;
         # then float32 temperature, top_p; then int64 seed, draw (kept 8-byte aligned at the end)
-        self.n_i32 = 3 * r + (r + 1) + 2 * r + sum(r * w for w in self.widths)
+        self.n_i32 = 6 * r + (r + 1) + sum(r * w for w in self.widths)      # six arrays of r, q_start, the tables
         self.n_i32 += (-self.n_i32) % 2
         total = self.n_i32 + 2 * r + 4 * r
         self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
@@ -62,8 +62,12 @@ class _Bucket:
         h, d = self.host.numpy(), self.dev
         o = 0
 
+        limit = [self.n_i32]
+
         def take(n):
             nonlocal o
+            if o + n > limit[0]:
+                raise AssertionError("the step buffer's regions overlap")
             a, b = h[o:o + n], d[o:o + n]
             o += n
             return a, b
@@ -79,7 +83,7 @@ class _Bucket:
         for g, w in zip(engine.groups, self.widths):
             a, b = take(r * w)
             self.h_tables[g.name], d_tables[g.name] = a.reshape(r, w), b.view(r, w)
-        o = self.n_i32
+        o, limit[0] = self.n_i32, total
         a, b = take(r)
         self.h_temp, self.d_temp = a.view(np.float32), b.view(torch.float32)
         a, b = take(r)
