@@ -183,3 +183,16 @@ def test_sampling_with_block_tables_used_to_their_last_entry():
     finally:
         del os.environ["YALIS_DISABLE_DECODE_CUDAGRAPHS"]
     assert torch.equal(a, b)            # captured steps draw what step-by-step launches draw
+
+
+def test_a_one_token_prompt_that_takes_over_a_slot():
+    """One slot, requests one after the other, one of them with a single prompt token: its first step is
+    a step of one token like a decode step, but its input is its own prompt token (a fuzzing run found it fed
+    the token that the slot's last owner drew)."""
+    d = tiny_model_dir("A", 0.3)
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    prompts = prompts_for(cfg, [9, 1, 14, 1], seed=12)
+    eng = engine_for(d, "fp32", max_batch_size=1)
+    tokens, _ = eng.generate(prompts, tokens_to_generate=6)
+    for p, row in zip(prompts, tokens.tolist()):
+        assert row == plain.greedy_generate(p, 6, w, cfg)

@@ -191,7 +191,10 @@ class LLMEngine:
         reqs = [e.request for e in plan.entries]
         slots = [r.slot for r in reqs]
         n = len(reqs)
-        same_batch = bool(pending) and pending[-1].slots == slots
+        # the same requests as the step before (not merely the same slots: a request that takes over a slot
+        # with a one-token prompt starts with that token, not with what the slot's last owner drew)
+        same_batch = bool(pending) and len(pending[-1].requests) == n and all(
+            a is b for a, b in zip(pending[-1].requests, reqs))
         if pending and not same_batch:
             self._resolve(pending)
         bucket = self.engine.decoder.step(
