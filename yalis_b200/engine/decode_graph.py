@@ -19,6 +19,7 @@ tables are uploaded at the full row width.
 
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -149,8 +150,16 @@ class _Bucket:
             torch.cuda.synchronize()
             l0 = _lib.LAUNCHES[0]
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, pool=self.engine.graph_pool()):
-                self._body()
+            # No garbage collection while the stream is capturing: a collected tensor or graph of an engine
+            # that is no longer used frees device memory, which is not allowed then and invalidates the capture.
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, pool=self.engine.graph_pool()):
+                    self._body()
+            finally:
+                if gc_was_on:
+                    gc.enable()
             self.launches = _lib.LAUNCHES[0] - l0
             self.graph = graph
         self.graph.replay()
