@@ -63,6 +63,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// The same with an L2 eviction policy (weights are read once: evict first; the x tile is read by every block: keep).
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -178,20 +196,21 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (lane == 0) {
       // Weights do not depend on the kernel before this one: fill the ring with W tiles at once,
       // and only then wait for that kernel before the first read of x.
+      const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
       const int n_pre = min(n_kt, STAGES);
       for (int kt = 0; kt < n_pre; ++kt) {
         mbar_expect_tx(&full[kt], A_BYTES + B_BYTES);
         if constexpr (SILU) {
-          tma_load_2d(a_s + kt * A_BYTES, &map_w, (kt_begin + kt) * TILE_K, n0, &full[kt]);
-          tma_load_2d(a_s + kt * A_BYTES + A_BYTES / 2, &map_w, (kt_begin + kt) * TILE_K, p.silu_inter + n0, &full[kt]);
+          tma_load_2d_hint(a_s + kt * A_BYTES, &map_w, (kt_begin + kt) * TILE_K, n0, &full[kt], pol_w);
+          tma_load_2d_hint(a_s + kt * A_BYTES + A_BYTES / 2, &map_w, (kt_begin + kt) * TILE_K, p.silu_inter + n0, &full[kt], pol_w);
         } else {
-          tma_load_2d(a_s + kt * A_BYTES, &map_w, (kt_begin + kt) * TILE_K, n0, &full[kt]);
+          tma_load_2d_hint(a_s + kt * A_BYTES, &map_w, (kt_begin + kt) * TILE_K, n0, &full[kt], pol_w);
         }
       }
       armed = n_pre;
       pdl_wait();
       for (int kt = 0; kt < n_pre; ++kt)
-        tma_load_2d(b_s + kt * B_BYTES, &map_x, (kt_begin + kt) * TILE_K, 0, &full[kt]);
+        tma_load_2d_hint(b_s + kt * B_BYTES, &map_x, (kt_begin + kt) * TILE_K, 0, &full[kt], pol_x);
       // When this block is about to ask for its last tiles, the next kernel's blocks may be scheduled and fill
       // their own rings: earlier they would take bandwidth from tiles this kernel still waits for (and
       // registers and shared memory from its later blocks); later the hand-over shows.  Measured on a decode
@@ -205,12 +224,12 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
         const int k = (kt_begin + kt) * TILE_K;
         if constexpr (SILU) {
-          tma_load_2d(a_s + s * A_BYTES, &map_w, k, n0, &full[s]);
-          tma_load_2d(a_s + s * A_BYTES + A_BYTES / 2, &map_w, k, p.silu_inter + n0, &full[s]);
+          tma_load_2d_hint(a_s + s * A_BYTES, &map_w, k, n0, &full[s], pol_w);
+          tma_load_2d_hint(a_s + s * A_BYTES + A_BYTES / 2, &map_w, k, p.silu_inter + n0, &full[s], pol_w);
         } else {
-          tma_load_2d(a_s + s * A_BYTES, &map_w, k, n0, &full[s]);
+          tma_load_2d_hint(a_s + s * A_BYTES, &map_w, k, n0, &full[s], pol_w);
         }
-        tma_load_2d(b_s + s * B_BYTES, &map_x, k, 0, &full[s]);
+        tma_load_2d_hint(b_s + s * B_BYTES, &map_x, k, 0, &full[s], pol_x);
         armed = kt + 1;
         if (kt == n_kt - 1 - kTriggerAhead) {
           pdl_launch_dependents();
