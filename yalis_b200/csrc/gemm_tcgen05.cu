@@ -127,7 +127,7 @@ struct GemmParams {
   long long ldo;        // row stride of out in elements
   int M, N, K;
   int splits;
-  int kt_per_split;     // K tiles of 64 per split
+  int kt_per_split;     // stage steps (of 64 or 128 columns of K) per split
   int silu_inter;       // 0, or I: w is [gate (I rows); up (I rows)] and out[m, i] = silu(gate_i) * up_i, [M, I] bfloat16
   int32_t* error;       // set to 1 if a wait ran out
 };
@@ -136,9 +136,12 @@ struct GemmParams {
 // grids between one and two blocks per SM run as one wave.  (A ring of a whole SM for grids of at most one block
 // per SM is faster for a product alone, but slower inside a decode step: the next kernel's blocks then find no
 // room beside it and cannot fetch ahead.  Measured 3.28 against 3.33 ms for a batch-8 step of Llama-3-8B.)
+// K blocks of 64 per stage: two for up to 16 tokens (32 KB of W per stage and barrier round trip), else one.
+template <int NTOK>
+__host__ __device__ constexpr int kblocks_for() { return NTOK <= 16 ? 2 : 1; }
 template <int NTOK>
 __host__ __device__ constexpr int stages_for() {
-  return NTOK <= 32 ? 5 : NTOK <= 64 ? 4 : NTOK <= 128 ? 3 : 4;
+  return NTOK <= 16 ? 3 : NTOK <= 32 ? 5 : NTOK <= 64 ? 4 : NTOK <= 128 ? 3 : 4;
 }
 
 // SILU: the gated-activation epilogue (p.silu_inter > 0).  A variant of its own: its extra registers would also
@@ -148,8 +151,10 @@ __global__ void __launch_bounds__(kThreads, NTOK > 128 ? 1 : 2)
 gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const GemmParams p) {
   constexpr int STAGES = stages_for<NTOK>();
-  constexpr int A_BYTES = TILE_N * TILE_K * 2;
-  constexpr int B_BYTES = NTOK * TILE_K * 2;
+  constexpr int KB = kblocks_for<NTOK>();
+  constexpr int A_SUB = TILE_N * TILE_K * 2, B_SUB = NTOK * TILE_K * 2;     // one K block of 64
+  constexpr int A_BYTES = KB * A_SUB;
+  constexpr int B_BYTES = KB * B_SUB;
   constexpr int TMEM_COLS = NTOK < 32 ? 32 : NTOK;
   extern __shared__ __align__(1024) unsigned char smem[];
   // The dynamic window is only guaranteed 16-byte aligned: round up to 1024 for the swizzled tiles.
@@ -167,7 +172,7 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   // up rows of the same outputs, I further down (lanes 64-127); the map's box is 64 rows then.
   const int n0 = blockIdx.x * (SILU ? TILE_N / 2 : TILE_N);
   const int split = blockIdx.y;
-  const int kt_total = (p.K + TILE_K - 1) / TILE_K;
+  const int kt_total = (p.K + KB * TILE_K - 1) / (KB * TILE_K);      // stage steps of KB * 64 columns
   const int kt_begin = split * p.kt_per_split;
   const int kt_end = min(kt_total, kt_begin + p.kt_per_split);
   const int n_kt = max(0, kt_end - kt_begin);
@@ -197,39 +202,46 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       // Weights do not depend on the kernel before this one: fill the ring with W tiles at once,
       // and only then wait for that kernel before the first read of x.
       const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
+      // K blocks past the end of K are filled with zeros by the copy (and still count their bytes).
+      auto load_w = [&](int s, int kt) {
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+          const int k = ((kt_begin + kt) * KB + kb) * TILE_K;
+          unsigned char* dst = a_s + s * A_BYTES + kb * A_SUB;
+          if constexpr (SILU) {
+            tma_load_2d_hint(dst, &map_w, k, n0, &full[s], pol_w);
+            tma_load_2d_hint(dst + A_SUB / 2, &map_w, k, p.silu_inter + n0, &full[s], pol_w);
+          } else {
+            tma_load_2d_hint(dst, &map_w, k, n0, &full[s], pol_w);
+          }
+        }
+      };
+      auto load_x = [&](int s, int kt) {
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_2d_hint(b_s + s * B_BYTES + kb * B_SUB, &map_x, ((kt_begin + kt) * KB + kb) * TILE_K, 0, &full[s], pol_x);
+      };
       const int n_pre = min(n_kt, STAGES);
       for (int kt = 0; kt < n_pre; ++kt) {
         mbar_expect_tx(&full[kt], A_BYTES + B_BYTES);
-        if constexpr (SILU) {
-          tma_load_2d_hint(a_s + kt * A_BYTES, &map_w, (kt_begin + kt) * TILE_K, n0, &full[kt], pol_w);
-          tma_load_2d_hint(a_s + kt * A_BYTES + A_BYTES / 2, &map_w, (kt_begin + kt) * TILE_K, p.silu_inter + n0, &full[kt], pol_w);
-        } else {
-          tma_load_2d_hint(a_s + kt * A_BYTES, &map_w, (kt_begin + kt) * TILE_K, n0, &full[kt], pol_w);
-        }
+        load_w(kt, kt);
       }
       armed = n_pre;
       pdl_wait();
-      for (int kt = 0; kt < n_pre; ++kt)
-        tma_load_2d_hint(b_s + kt * B_BYTES, &map_x, (kt_begin + kt) * TILE_K, 0, &full[kt], pol_x);
+      for (int kt = 0; kt < n_pre; ++kt) load_x(kt, kt);
       // When this block is about to ask for its last tiles, the next kernel's blocks may be scheduled and fill
       // their own rings: earlier they would take bandwidth from tiles this kernel still waits for (and
       // registers and shared memory from its later blocks); later the hand-over shows.  Measured on a decode
       // step of the Llama-3-8B shape: 4 tiles ahead is best with 8 tokens, 0 to 2 with 64.
-      constexpr int kTriggerAhead = NTOK <= 32 ? 4 : 1;
+      constexpr int kTriggerAhead = NTOK <= 32 ? 4 / KB : 1;      // in stage steps
       bool released = false;
       for (int kt = n_pre; kt < n_kt; ++kt) {
         const int s = kt % STAGES;
         const uint32_t ph = (kt / STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
         mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-        const int k = (kt_begin + kt) * TILE_K;
-        if constexpr (SILU) {
-          tma_load_2d_hint(a_s + s * A_BYTES, &map_w, k, n0, &full[s], pol_w);
-          tma_load_2d_hint(a_s + s * A_BYTES + A_BYTES / 2, &map_w, k, p.silu_inter + n0, &full[s], pol_w);
-        } else {
-          tma_load_2d_hint(a_s + s * A_BYTES, &map_w, k, n0, &full[s], pol_w);
-        }
-        tma_load_2d_hint(b_s + s * B_BYTES, &map_x, k, 0, &full[s], pol_x);
+        load_w(s, kt);
+        load_x(s, kt);
         armed = kt + 1;
         if (kt == n_kt - 1 - kTriggerAhead) {
           pdl_launch_dependents();
@@ -250,12 +262,15 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const uint32_t ph = (kt / STAGES) & 1;
         if (!mbar_wait(&full[s], ph, abort_flag)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t da = umma_desc_sw128(a_s + s * A_BYTES);
-        const uint64_t db = umma_desc_sw128(b_s + s * B_BYTES);
 #pragma unroll
-        for (int j = 0; j < TILE_K / UMMA_K; ++j) {
-          // 16 bfloat16 = 32 bytes further along K inside the swizzled row: +2 in the address field
-          umma(tmem_d, da + 2 * j, db + 2 * j, idesc, (kt > 0 || j > 0) ? 1u : 0u);
+        for (int kb = 0; kb < KB; ++kb) {
+          const uint64_t da = umma_desc_sw128(a_s + s * A_BYTES + kb * A_SUB);
+          const uint64_t db = umma_desc_sw128(b_s + s * B_BYTES + kb * B_SUB);
+#pragma unroll
+          for (int j = 0; j < TILE_K / UMMA_K; ++j) {
+            // 16 bfloat16 = 32 bytes further along K inside the swizzled row: +2 in the address field
+            umma(tmem_d, da + 2 * j, db + 2 * j, idesc, (kt > 0 || kb > 0 || j > 0) ? 1u : 0u);
+          }
         }
         umma_commit(&empty[s]);
       }
@@ -398,7 +413,8 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, lo
 template <int NTOK, bool SILU>
 int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t stream) {
   constexpr int STAGES = stages_for<NTOK>();
-  const size_t smem = 1024 + (size_t)STAGES * (TILE_N * TILE_K * 2 + NTOK * TILE_K * 2) + (2 * STAGES + 1) * 8 + 16;
+  const size_t smem = 1024 + (size_t)STAGES * kblocks_for<NTOK>() * (TILE_N * TILE_K * 2 + NTOK * TILE_K * 2) +
+                      (2 * STAGES + 1) * 8 + 16;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_wstream_kernel<NTOK, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -467,7 +483,8 @@ int gemm_wstream_impl(const void* x, long long ldx, const void* w, long long ldw
     return YALIS_ERR_LAUNCH;
   GemmParams p;
   p.out = out; p.out_dtype = out_dtype; p.ldo = ldo; p.M = M; p.N = N; p.K = K; p.splits = splits;
-  const int kt = (K + TILE_K - 1) / TILE_K;
+  const int step_k = (ntok <= 16 ? 2 : 1) * TILE_K;            // kblocks_for<ntok>() columns per stage step
+  const int kt = (K + step_k - 1) / step_k;
   p.kt_per_split = (kt + splits - 1) / splits;
   p.silu_inter = silu_inter;
   p.error = error;
