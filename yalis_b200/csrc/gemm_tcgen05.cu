@@ -235,6 +235,10 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       // step of the Llama-3-8B shape: 4 tiles ahead is best with 8 tokens, 0 to 2 with 64.
       constexpr int kTriggerAhead = NTOK <= 32 ? 4 / KB : 1;      // in stage steps
       bool released = false;
+      if (n_kt - 1 - kTriggerAhead < n_pre) {        // a short K range: the steps that are left are already on their way
+        pdl_launch_dependents();
+        released = true;
+      }
       for (int kt = n_pre; kt < n_kt; ++kt) {
         const int s = kt % STAGES;
         const uint32_t ph = (kt / STAGES) & 1;
