@@ -109,6 +109,20 @@ __device__ __forceinline__ float sum_parts(const TS* __restrict__ p, int n, size
   return acc;
 }
 
+// silu(g) = g / (1 + exp(-g)).  The float32 path uses the accurate functions; on the bfloat16 path the result is
+// rounded to 8 bits of mantissa at once, so the fast exponential and division (relative error about 1e-6) do not
+// show, and they make the activation kernel memory-bound instead of arithmetic-bound (34 -> ~10 instructions an
+// element).  One function for every bfloat16 place (activation kernels, the product's fused epilogue), so that
+// they agree to the bit.
+__device__ __forceinline__ float silu_exact(float g) { return g / (1.0f + expf(-g)); }
+__device__ __forceinline__ float silu_bf16_path(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+template <typename T>
+__device__ __forceinline__ float silu_for(float g);
+template <>
+__device__ __forceinline__ float silu_for<float>(float g) { return silu_exact(g); }
+template <>
+__device__ __forceinline__ float silu_for<__nv_bfloat16>(float g) { return silu_bf16_path(g); }
+
 // (x1, x2) turned by the angle with cosine cs and sine sn.  One pinned instruction sequence, so that every
 // kernel that rotates (the rotary kernels, the decode attention that rotates its own queries) agrees to the bit.
 __device__ __forceinline__ void rotate_pair(float x1, float x2, float cs, float sn, float& o1, float& o2) {

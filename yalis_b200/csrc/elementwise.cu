@@ -557,7 +557,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, i
   const T* row = in + t * 2 * (size_t)inter;
   const float gate = to_f32<T>(interleaved ? row[2 * i] : row[i]);
   const float up = to_f32<T>(interleaved ? row[2 * i + 1] : row[inter + i]);
-  const float act = gate / (1.0f + expf(-gate));
+  const float act = silu_for<T>(gate);
   out[idx] = from_f32<T>(act * up);
 }
 
@@ -572,7 +572,7 @@ __device__ __forceinline__ uint4 silu_mul_8(const uint4 g4, const uint4 u4) {
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-    o2[k] = __floats2bfloat162_rn((g.x / (1.0f + expf(-g.x))) * u.x, (g.y / (1.0f + expf(-g.y))) * u.y);
+    o2[k] = __floats2bfloat162_rn(silu_bf16_path(g.x) * u.x, silu_bf16_path(g.y) * u.y);
   }
   return o4;
 }

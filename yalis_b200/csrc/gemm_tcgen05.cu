@@ -119,7 +119,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr));
 }
 
-__device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }   // as the activation kernel
 
 struct GemmParams {
   void* out;            // splits == 1: [M, N] of out_dtype; splits > 1: float32 [splits, M, N]
@@ -323,7 +322,7 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
               // activation kernel
               const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));
               const float u = __bfloat162float(__float2bfloat16_rn(buf[i * 64 + col]));
-              reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(silu_f32(g) * u);
+              reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(silu_bf16_path(g) * u);
             }
           }
         }

@@ -118,6 +118,58 @@ def gemm_wstream(args) -> None:
           f"{us:.1f} us per launch, {n * k * 2 / us / 1e6:.2f} TB/s of weights")
 
 
+def elementwise(args) -> None:
+    """The memory-bound kernels between the products at prefill size: residual add + RMSNorm, SiLU-mul and
+    rotary + cache write for ``--tokens`` tokens of the Llama-3-8B shape."""
+    from yalis_b200.ops.elementwise import add_rmsnorm, rope_kv_write, silu_mul
+    from yalis_b200.parts.rotary import inverse_frequencies
+    dev = "cuda:0"
+    n, hidden, inter, nh, g, hs, page = args.tokens, 4096, 14336, 32, 8, 128, 64
+    bf = torch.bfloat16
+    copies = 4                                                  # rotate buffers: more than the L2 holds
+    xs = [torch.randn(n, hidden, device=dev) for _ in range(copies)]
+    deltas = [torch.randn(n, hidden, device=dev).to(bf) for _ in range(copies)]
+    w = torch.ones(hidden, device=dev)
+    gus = [torch.randn(n, 2 * inter, device=dev).to(bf) for _ in range(copies)]
+    qkvs = [torch.randn(n, (nh + 2 * g) * hs, device=dev).to(bf) for _ in range(copies)]
+    pages = -(-n // page)
+    k_pool = torch.zeros(pages, g, page, hs, dtype=bf, device=dev)
+    v_pool = torch.zeros_like(k_pool)
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages)
+    pos = torch.arange(n, dtype=torch.int32, device=dev)
+    req = torch.zeros(n, dtype=torch.int32, device=dev)
+    inv = inverse_frequencies(hs, 500000.0, None).to(dev)
+    st = {"i": 0}
+
+    def nxt():
+        st["i"] += 1
+        return st["i"] % copies
+
+    us = _time(lambda: add_rmsnorm(xs[nxt()], deltas[st["i"] % copies], w, 1e-5, bf), args.launches, graph=not args.eager)
+    print(f"add_rmsnorm {n} x {hidden}: {us:.1f} us, {n * hidden * (4 + 4 + 2 + 2) / us / 1e6:.2f} TB/s")
+    us = _time(lambda: silu_mul(gus[nxt()]), args.launches, graph=not args.eager)
+    print(f"silu_mul {n} x {inter}: {us:.1f} us, {n * inter * 6 / us / 1e6:.2f} TB/s")
+    us = _time(lambda: rope_kv_write(qkvs[nxt()], pos, req, inv, k_pool, v_pool, table, nh, g, hs), args.launches,
+               graph=not args.eager)
+    print(f"rope_kv_write {n} tokens: {us:.1f} us, {n * (nh + 2 * g) * hs * 4 / us / 1e6:.2f} TB/s")
+
+
+def sampling(args) -> None:
+    """Token selection over ``--rows`` rows of 128,256 logits: argmax, and the sampling kernels with top-k / top-p."""
+    from yalis_b200.ops.sampling import argmax, sample
+    dev = "cuda:0"
+    rows, vocab = args.rows, 128256
+    logits = torch.randn(rows, vocab, device=dev) * 3.0
+    i64 = lambda v: torch.full((rows,), v, dtype=torch.int64, device=dev)
+    f32 = lambda v: torch.full((rows,), v, dtype=torch.float32, device=dev)
+    k32 = lambda v: torch.full((rows,), v, dtype=torch.int32, device=dev)
+    print(f"argmax {rows} rows: {_time(lambda: argmax(logits), args.launches, graph=not args.eager):.1f} us")
+    for name, t, k, p in (("temperature only", 1.0, 0, 1.0), ("top-p 0.8", 1.0, 0, 0.8), ("top-k 50", 1.0, 50, 1.0),
+                          ("top-k 50, top-p 0.9, T 0.7", 0.7, 50, 0.9)):
+        us = _time(lambda: sample(logits, f32(t), k32(k), f32(p), i64(1), i64(2)), args.launches, graph=not args.eager)
+        print(f"sample {rows} rows, {name}: {us:.1f} us")
+
+
 def prefill(args) -> None:
     """One prompt of ``--tokens`` tokens through the whole engine (Llama-3-8B shape, ``--layers`` layers)."""
     from yalis_b200.bench_support import prefill_bench
@@ -164,6 +216,14 @@ def main() -> None:
     ap_.add_argument("--kernel", default="tcgen05", choices=["tcgen05", "mma"])
     ap_.add_argument("--launches", type=int, default=4)
     ap_.set_defaults(fn=attention_prefill)
+    ew = sub.add_parser("elementwise")
+    ew.add_argument("--tokens", type=int, default=2048)
+    ew.add_argument("--launches", type=int, default=4)
+    ew.set_defaults(fn=elementwise)
+    sm = sub.add_parser("sampling")
+    sm.add_argument("--rows", type=int, default=8)
+    sm.add_argument("--launches", type=int, default=4)
+    sm.set_defaults(fn=sampling)
     pf = sub.add_parser("prefill")
     pf.add_argument("--preset", default="Llama-3-8B")
     pf.add_argument("--layers", type=int, default=4)
