@@ -231,7 +231,10 @@ int launch_add_rmsnorm(float* x, const void* delta, int n_delta, size_t delta_st
   const uintptr_t ptrs = (uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)y;
   if (width % 4 == 0 && width <= 16384 && (ptrs & 15) == 0 && delta_stride % 4 == 0) {
     const int n4 = width / 4;
-    const int vthreads = n4 >= 1024 ? 1024 : (n4 + 31) / 32 * 32;
+    // Few rows (decode): as many threads per row as it has groups of four, every load in flight at once.
+    // Many rows (prefill): 256 threads per row, so that eight rows are in flight per SM instead of two.
+    const int cap = n_out_rows >= 256 ? 256 : 1024;
+    const int vthreads = n4 >= cap ? cap : (n4 + 31) / 32 * 32;
     const int nv = (n4 + vthreads - 1) / vthreads;
 #define YALIS_NORM_VEC(V)                                                                                          \
   return yalis_launch(add_rmsnorm_vec_kernel<T, TD, V>, dim3(n_out_rows), dim3(vthreads), 0, stream, x,            \
