@@ -280,14 +280,17 @@ def test_argmax_ties_go_to_the_lowest_index(rows, vocab):
     assert got[0] == vocab // 2 and all(g == 0 for g in got[1:])
 
 
-def draws(logits_row, temperature, top_k, top_p, n, seed=77):
+def draws(logits_row, temperature, top_k, top_p, n, seed=77, rows_per_call=None):
+    """n draws (draw numbers 0..n-1) from one row; in calls of rows_per_call rows each, since the
+    number of rows decides how many blocks walk a wide row."""
     from yalis_b200.ops.sampling import sample
     vocab = logits_row.numel()
-    logits = logits_row.view(1, vocab).repeat(n, 1).contiguous().to(DEV)
-    f = lambda v, dt: torch.full((n,), v, dtype=dt, device=DEV)
-    out = sample(logits, f(temperature, torch.float32), f(top_k or 0, torch.int32), f(top_p, torch.float32),
-                 f(seed, torch.int64), torch.arange(n, dtype=torch.int64, device=DEV))
-    return out.cpu()
+    per = rows_per_call or n
+    logits = logits_row.view(1, vocab).repeat(per, 1).contiguous().to(DEV)
+    f = lambda v, dt: torch.full((per,), v, dtype=dt, device=DEV)
+    args = (f(temperature, torch.float32), f(top_k or 0, torch.int32), f(top_p, torch.float32), f(seed, torch.int64))
+    out = [sample(logits, *args, torch.arange(at, at + per, dtype=torch.int64, device=DEV)) for at in range(0, n, per)]
+    return torch.cat(out)[:n].cpu()
 
 
 @pytest.mark.parametrize("temperature, top_k, top_p", [(1.0, None, 1.0), (0.7, None, 1.0), (1.0, 5, 1.0), (1.3, None, 0.8),
@@ -337,6 +340,42 @@ def test_top_k_and_top_p_cuts_on_clear_gaps():
         p = plain.sampling_distribution(logits, temperature, top_k, top_p)
         seen = set(draws(logits, temperature, top_k, top_p, 4000).tolist())
         assert seen == {i for i in range(8) if p[i] > 1e-4}, (temperature, top_k, top_p, seen)
+
+
+def test_cuts_of_a_wide_row_whose_blocks_each_see_a_slice():
+    """A row of 50,001 entries is walked by eight blocks: the entries that matter lie at the first
+    and last index, on both sides of slice edges and in the ragged tail; the rest carry no mass."""
+    vocab = 50001
+    per = ((vocab + 7) // 8 + 3) & ~3
+    at = [0, per - 1, per, 3 * per + 1, 4 * per - 1, 7 * per, vocab - 2, vocab - 1]
+    values = [5.0, 4.0, 3.0, -2.0, -3.0, 1.0, 0.0, -9.0]
+    logits = torch.randn(vocab, generator=torch.Generator().manual_seed(9)) * 0.5 - 40.0
+    logits[at] = torch.tensor(values)
+    for temperature, top_k, top_p in ((1.0, 3, 1.0), (1.0, None, 0.7), (1.0, None, 0.95), (2.0, 4, 0.9), (1.0, None, 0.2),
+                                      (3.0, 7, 1.0)):
+        p = plain.sampling_distribution(logits, temperature, top_k, top_p)
+        one_block = draws(logits, temperature, top_k, top_p, 3000)
+        seen = set(one_block.tolist())
+        assert seen <= set(at), (temperature, top_k, top_p, seen - set(at))
+        assert seen == {i for i in at if p[i] > 1e-4}, (temperature, top_k, top_p, seen)
+        for rows in (16, 32, 64):                                           # eight, four and two blocks per row
+            assert torch.equal(draws(logits, temperature, top_k, top_p, 3000, rows_per_call=rows), one_block), rows
+
+
+@pytest.mark.parametrize("vocab, top_k, top_p, temperature", [(128256, 50, 0.9, 0.8), (16384, None, 0.6, 1.0),
+                                                             (100003, 200, 1.0, 1.5)])
+def test_wide_rows_draw_only_what_the_reference_keeps(vocab, top_k, top_p, temperature):
+    logits = torch.randn(vocab, generator=torch.Generator().manual_seed(vocab)) * 3.0
+    p = plain.sampling_distribution(logits, temperature, top_k, top_p)
+    out = draws(logits, temperature, top_k, top_p, 1500)
+    assert bool((p[out] > 0).all())
+    likely = {int(i) for i in torch.nonzero(p > 0.02).flatten()}
+    assert likely <= set(out.tolist())
+    counts = torch.bincount(out, minlength=vocab).double() / out.numel()
+    top = torch.topk(p, 5).indices
+    assert float((counts[top] - p[top].double()).abs().max()) < 0.05
+    for rows in (8, 24, 48):                                                # eight, four and two blocks per row
+        assert torch.equal(draws(logits, temperature, top_k, top_p, 1500, rows_per_call=rows), out), rows
 
 
 @pytest.mark.parametrize("nh, g, hs, page, window", [

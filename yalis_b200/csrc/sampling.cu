@@ -13,15 +13,18 @@
 // own draw count and its own logits, not on the batch it sits in.
 //
 // No sort: the k-th largest logit and the top-p cut are found by a radix
-// descent over order-preserving 32-bit keys (digits of 12, 12 and 8 bits, one
-// block per row; the wide first digit spreads the entries over enough bins that
-// shared-memory atomics rarely collide).  Bin masses are accumulated as 64-bit fixed point, so
+// descent over order-preserving 32-bit keys (digits of 12, 12 and 8 bits; one
+// block per row, or a cluster of eight blocks for a wide row, whose histograms
+// the leading block adds through distributed shared memory; the wide first digit
+// spreads the entries over enough bins that shared-memory atomics rarely collide).  Bin masses are accumulated as 64-bit fixed point, so
 // every sum is exact in its order and the result is deterministic.  Entries
 // tied with the k-th value are all kept; entries tied with the top-p boundary
 // value are all dropped (unless that value is the maximum).  The draw itself is
 // an argmax of perturbed logits and runs on 32 blocks per row with a merge, as
 // the plain argmax does for wide rows.
 #include "common.cuh"
+
+#include <type_traits>
 
 namespace {
 
@@ -218,31 +221,133 @@ __device__ void find_crossing(const unsigned long long* hist, int nb, unsigned l
   __syncthreads();
 }
 
-// One block per row: the top-k and top-p cuts of the rows that ask for one.
+// ---- thread-block cluster helpers: the blocks of one row read each other's shared memory ----
+__device__ __forceinline__ uint32_t smem_addr_of(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t map_to_block(uint32_t saddr, int rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ uint32_t ld_cluster_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_cluster_u64(uint32_t addr, unsigned long long v) {
+  asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_cluster_u64(uint32_t addr) {
+  unsigned long long v;
+  asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(addr) : "memory");
+  return v;
+}
+// Barrier over the CL blocks of a row (release/acquire: shared-memory writes before it are visible
+// to the other blocks after it); over the block alone when CL is 1.
+template <int CL>
+__device__ __forceinline__ void row_sync() {
+  if constexpr (CL > 1)
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  else
+    __syncthreads();
+}
+
+// What the leading block found in a pass, read by the other blocks of the row.
+struct Found {
+  int chosen;
+  int pad;
+  unsigned long long above;
+};
+
+// The top-k and top-p cuts of the rows that ask for one.  A row is walked by CL blocks (one
+// thread-block cluster, CL == 1: one block): each builds the histogram of its slice in its own
+// shared memory, the leading block adds the slices' bins through distributed shared memory, finds
+// the crossing and publishes it.  Integer bins make the result independent of CL; the softmax
+// normaliser is summed block by block in rank order.
+template <int CL>
 __global__ void __launch_bounds__(kThreads)
 sample_cut_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
                   const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
                   const float* __restrict__ top_p, Cut* __restrict__ cuts) {
-  extern __shared__ unsigned long long hist[];          // [kBins] 64-bit bins, then [3][kBins] 32-bit pieces
+  extern __shared__ unsigned long long hist[];          // [kBins] 64-bit bins (leading block), then [3][kBins] 32-bit pieces
   __shared__ float fscratch[32];
   __shared__ unsigned long long warp_totals[32];
   __shared__ int sh_pick;
   __shared__ unsigned long long sh_above_pick;
+  __shared__ float exchange[2];                          // this block's maximum and sum
+  __shared__ Found found;
   pdl_launch_dependents();
   pdl_wait();
 
-  const int r = blockIdx.x;
-  const float* row = logits + (size_t)r * row_stride;
+  const int r = blockIdx.y;
+  const int rank = CL > 1 ? (int)blockIdx.x : 0;        // clusters are (CL, 1, 1) and the grid is (CL, rows)
   const float temp = temperature[r];
   const float tp = top_p[r];
   const int tk = top_k[r];
   const bool greedy = !(temp > 0.f) && !(tp > 0.f);
   const bool want_k = tk > 0 && tk < vocab, want_p = tp < 1.0f;
-  if (greedy || (!want_k && !want_p)) {
-    if (threadIdx.x == 0) cuts[r] = Cut{0u, 0u, 1u, 0u};
+  if (greedy || (!want_k && !want_p)) {                  // the same decision in every block of the row
+    if (rank == 0 && threadIdx.x == 0) cuts[r] = Cut{0u, 0u, 1u, 0u};
     return;
   }
+  // This block's slice of the row; a multiple of four entries keeps the 16-byte loads.
+  const int per = (((vocab + CL - 1) / CL) + 3) & ~3;
+  const int lo = min(vocab, rank * per);
+  const int n = min(vocab, lo + per) - lo;
+  const float* row = logits + (size_t)r * row_stride + lo;
+  unsigned int* pieces = reinterpret_cast<unsigned int*>(hist + kBins);   // [3][kBins], piece 0 doubles as counts
+  const uint32_t pieces_addr = smem_addr_of(pieces);
 
+  // hist[b] of the leading block = sum over the row's blocks of their pieces (13 bits apart).  Each
+  // block adds its share of the bins, all loads of a bin in flight at once, and stores the sums
+  // into the leading block's shared memory.
+  const uint32_t hist_addr = smem_addr_of(hist);
+  auto gather = [&](int nb, auto n_pieces) {
+    constexpr int NP = decltype(n_pieces)::value;
+    row_sync<CL>();                                      // every block's pieces are complete
+    if constexpr (CL == 1) {
+      for (int b = threadIdx.x; b < nb; b += blockDim.x) {
+        unsigned long long s = 0;
+#pragma unroll
+        for (int p = 0; p < NP; ++p) s += (unsigned long long)pieces[p * kBins + b] << (13 * p);
+        hist[b] = s;
+      }
+      __syncthreads();
+    } else {
+      const int share = nb / CL;                         // nb is 4096 or 256, CL a power of two up to 8
+      for (int j = threadIdx.x; j < share; j += blockDim.x) {
+        const int b = rank * share + j;
+        unsigned int v[CL][NP];
+#pragma unroll
+        for (int c = 0; c < CL; ++c)
+#pragma unroll
+          for (int p = 0; p < NP; ++p) v[c][p] = ld_cluster_u32(map_to_block(pieces_addr + 4u * (uint32_t)(p * kBins + b), c));
+        unsigned long long s = 0;
+#pragma unroll
+        for (int c = 0; c < CL; ++c)
+#pragma unroll
+          for (int p = 0; p < NP; ++p) s += (unsigned long long)v[c][p] << (13 * p);
+        st_cluster_u64(map_to_block(hist_addr + 8u * (uint32_t)b, 0), s);
+      }
+      row_sync<CL>();                                    // the leading block's bins are complete
+    }
+  };
+  // The crossing of the gathered bins, known to every thread of every block of the row afterwards.
+  auto crossing = [&](int nb, unsigned long long above_in, unsigned long long limit, int* chosen,
+                      unsigned long long* above_out) {
+    if (rank == 0) {
+      find_crossing(hist, nb, above_in, limit, warp_totals, &sh_pick, &sh_above_pick, chosen, above_out);
+      if (CL > 1 && threadIdx.x == 0) {
+        found.chosen = *chosen;
+        found.above = *above_out;
+      }
+    }
+    if constexpr (CL > 1) {
+      row_sync<CL>();
+      const uint32_t at = map_to_block(smem_addr_of(&found), 0);
+      *chosen = (int)ld_cluster_u32(at);
+      *above_out = ld_cluster_u64(at + 8);
+    }
+  };
   // ---- top-k: key of the k-th largest logit ---------------------------------------
   uint32_t k_key = 0;
   if (want_k) {
@@ -251,35 +356,18 @@ sample_cut_kernel(const float* __restrict__ logits, long long row_stride, int vo
     int done_bits = 0;
     for (int pass = 0; pass < 3; ++pass) {
       const int nb = 1 << digit_bits(pass), shift = digit_shift(pass);
-      // counts fit 32 bits: count in the upper half of the buffer (kBins * 4 bytes) with native 32-bit atomics, then widen
-      unsigned int* counts = reinterpret_cast<unsigned int*>(hist + kBins / 2);   // [kBins] 32-bit: the upper half
+      unsigned int* counts = pieces;                     // a count fits 32 bits: native shared atomics
       for (int b = threadIdx.x; b < nb; b += blockDim.x) counts[b] = 0;
       __syncthreads();
-      for_each_entry(row, vocab, [&](float v, int) {
+      for_each_entry(row, n, [&](float v, int) {
         const uint32_t key = order_key(v);
         if (done_bits == 0 || (key >> (32 - done_bits)) == (prefix >> (32 - done_bits)))
           atomicAdd(&counts[(key >> shift) & (nb - 1)], 1u);
       });
-      __syncthreads();
-      {   // widen to the 64-bit bins the scan reads, staged through registers (the arrays overlap)
-        constexpr int kPer = kBins / kThreads;
-        unsigned int c[kPer];
-#pragma unroll
-        for (int j = 0; j < kPer; ++j) {
-          const int b = threadIdx.x + j * kThreads;
-          c[j] = b < nb ? counts[b] : 0u;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int j = 0; j < kPer; ++j) {
-          const int b = threadIdx.x + j * kThreads;
-          if (b < nb) hist[b] = c[j];
-        }
-        __syncthreads();
-      }
+      gather(nb, std::integral_constant<int, 1>{});
       int chosen;
       unsigned long long above;
-      find_crossing(hist, nb, 0ull, remaining - 1, warp_totals, &sh_pick, &sh_above_pick, &chosen, &above);
+      crossing(nb, 0ull, remaining - 1, &chosen, &above);
       if (chosen < 0) chosen = 0;                        // cannot happen: k < vocab entries exist
       remaining -= above;
       prefix |= (uint32_t)chosen << shift;
@@ -293,16 +381,42 @@ sample_cut_kernel(const float* __restrict__ logits, long long row_stride, int vo
   if (want_p) {
     // ---- scale, max and normaliser over the entries that survive top-k ---------------
     const float inv_t = temp > 0.f ? 1.0f / temp : 1.0f;
-    float mx = -INFINITY;
-    for_each_entry(row, vocab, [&](float v, int) {
-      if (order_key(v) >= k_key && v == v) mx = fmaxf(mx, v);
+    // One walk: every thread keeps a running maximum and the sum of exponentials relative to it.
+    float mx = -INFINITY, z = 0.f;
+    for_each_entry(row, n, [&](float v, int) {
+      if (order_key(v) >= k_key && v == v) {
+        if (v > mx) {
+          z = z * expf((mx - v) * inv_t) + 1.0f;         // mx == -inf: z is 0 and stays finite
+          mx = v;
+        } else {
+          z += expf((v - mx) * inv_t);
+        }
+      }
     });
+    const float mine = mx;
     mx = block_max(mx, fscratch);
-    float z = 0.f;
-    for_each_entry(row, vocab, [&](float v, int) {
-      if (order_key(v) >= k_key && v == v) z += expf((v - mx) * inv_t);
-    });
-    z = block_sum(z, fscratch);
+    z = block_sum(mine == -INFINITY ? 0.f : z * expf((mine - mx) * inv_t), fscratch);
+    if constexpr (CL > 1) {
+      // The blocks' (maximum, sum) pairs, combined in rank order by every thread alike.
+      if (threadIdx.x == 0) {
+        exchange[0] = mx;
+        exchange[1] = z;
+      }
+      row_sync<CL>();
+      const uint32_t at = smem_addr_of(exchange);
+      float m_c[CL], z_c[CL];
+#pragma unroll
+      for (int c = 0; c < CL; ++c) {
+        m_c[c] = __uint_as_float(ld_cluster_u32(map_to_block(at, c)));
+        z_c[c] = __uint_as_float(ld_cluster_u32(map_to_block(at + 4, c)));
+      }
+      mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < CL; ++c) mx = fmaxf(mx, m_c[c]);
+      z = 0.f;
+#pragma unroll
+      for (int c = 0; c < CL; ++c) z += m_c[c] == -INFINITY ? 0.f : z_c[c] * expf((m_c[c] - mx) * inv_t);
+    }
     const float inv_z = 1.0f / z;
     // ---- top-p: the key at which the cumulative probability passes top_p ---------------
     const unsigned long long limit = (unsigned long long)((double)tp * kFixedOne);
@@ -315,10 +429,9 @@ sample_cut_kernel(const float* __restrict__ logits, long long row_stride, int vo
       // A probability is a 39-bit fixed-point mass; it is added as three 13-bit pieces with native
       // 32-bit shared atomics (64-bit ones are compare-and-swap loops, slow where bins are hot).
       // A piece sum stays under 2^32 for rows of up to 2^19 entries.
-      unsigned int* pieces = reinterpret_cast<unsigned int*>(hist + kBins);   // [3][kBins]
-      for (int b = threadIdx.x; b < 3 * kBins; b += blockDim.x) pieces[b] = 0;
+      for (int b = threadIdx.x; b < nb; b += blockDim.x) pieces[b] = pieces[kBins + b] = pieces[2 * kBins + b] = 0;
       __syncthreads();
-      for_each_entry(row, vocab, [&](float v, int) {
+      for_each_entry(row, n, [&](float v, int) {
         const uint32_t key = order_key(v);
         if (key < k_key || v != v) return;
         if (done_bits == 0 || (key >> (32 - done_bits)) == (prefix >> (32 - done_bits))) {
@@ -329,14 +442,10 @@ sample_cut_kernel(const float* __restrict__ logits, long long row_stride, int vo
           if (mass >> 26) atomicAdd(&pieces[2 * kBins + b], (unsigned int)(mass >> 26));
         }
       });
-      __syncthreads();
-      for (int b = threadIdx.x; b < nb; b += blockDim.x)
-        hist[b] = (unsigned long long)pieces[b] + ((unsigned long long)pieces[kBins + b] << 13) +
-                  ((unsigned long long)pieces[2 * kBins + b] << 26);
-      __syncthreads();
+      gather(nb, std::integral_constant<int, 3>{});
       int chosen;
       unsigned long long new_above;
-      find_crossing(hist, nb, above, limit, warp_totals, &sh_pick, &sh_above_pick, &chosen, &new_above);
+      crossing(nb, above, limit, &chosen, &new_above);
       if (chosen < 0) {
         // Only possible in the first pass (later passes split a bin whose mass is already known
         // to cross the limit, and the fixed-point masses add up exactly): the whole row fits
@@ -355,7 +464,9 @@ sample_cut_kernel(const float* __restrict__ logits, long long row_stride, int vo
     // entry is always kept).
     keep_equal = all_fit ? 1u : (above == 0 ? 1u : 0u);
   }
-  if (threadIdx.x == 0) cuts[r] = Cut{k_key, p_key, keep_equal, want_p ? 1u : 0u};
+  if (rank == 0 && threadIdx.x == 0) cuts[r] = Cut{k_key, p_key, keep_equal, want_p ? 1u : 0u};
+  // No block leaves while another may still read its shared memory.
+  if constexpr (CL > 1) row_sync<CL>();
 }
 
 // The draw, spread over kChunks blocks per row: each finds the best perturbed logit of its slice
@@ -411,6 +522,8 @@ sample_draw_partial_kernel(const float* __restrict__ logits, long long row_strid
 }  // namespace
 
 constexpr int kArgmaxChunks = 32;   // blocks per row in the first phase for wide rows
+constexpr int kCutBlocks = 8;       // most blocks per row of the cut search (one portable cluster)
+constexpr int kCutClusterVocab = 16384;
 
 // Phase 1 of the wide argmax: block (row, chunk) finds the best entry of its slice.
 __global__ void __launch_bounds__(kThreads) argmax_partial_kernel(const float* __restrict__ logits, long long row_stride,
@@ -485,14 +598,38 @@ YALIS_API int yalis_sample(const float* logits, long long row_stride, int n_rows
   int32_t* part_i = reinterpret_cast<int32_t*>(scratch + (size_t)n_rows * kDrawChunks);
   Cut* cuts = reinterpret_cast<Cut*>(scratch + (size_t)n_rows * 2 * kDrawChunks);
   const size_t smem = (size_t)kBins * (sizeof(unsigned long long) + 3 * sizeof(unsigned int));
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(sample_cut_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0, sms = 0;
+    const int bytes = (int)smem;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0 ||
+        cudaFuncSetAttribute(sample_cut_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess ||
+        cudaFuncSetAttribute(sample_cut_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess ||
+        cudaFuncSetAttribute(sample_cut_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess ||
+        cudaFuncSetAttribute(sample_cut_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
       return YALIS_ERR_LAUNCH;
-    configured = true;
+    sm_count = sms;
   }
-  int st = yalis_launch(sample_cut_kernel, dim3(n_rows), dim3(kThreads), smem, stream, logits, row_stride, vocab,
-                        temperature, top_k, top_p, cuts);
+  // A wide row is walked by a cluster of blocks, the more the fewer rows there are: one block per
+  // multiprocessor at most, since every pass ends in barriers over the cluster.
+  int blocks = 1;
+  if (vocab >= kCutClusterVocab)
+    while (blocks < kCutBlocks && (long long)n_rows * (2 * blocks) <= sm_count) blocks *= 2;
+  const dim3 grid(blocks, n_rows), block(kThreads), cluster(blocks, 1, 1);
+  int st;
+  if (blocks == 8)
+    st = yalis_launch_cluster(sample_cut_kernel<8>, grid, block, cluster, smem, stream, logits, row_stride, vocab, temperature,
+                              top_k, top_p, cuts);
+  else if (blocks == 4)
+    st = yalis_launch_cluster(sample_cut_kernel<4>, grid, block, cluster, smem, stream, logits, row_stride, vocab, temperature,
+                              top_k, top_p, cuts);
+  else if (blocks == 2)
+    st = yalis_launch_cluster(sample_cut_kernel<2>, grid, block, cluster, smem, stream, logits, row_stride, vocab, temperature,
+                              top_k, top_p, cuts);
+  else
+    st = yalis_launch(sample_cut_kernel<1>, grid, block, smem, stream, logits, row_stride, vocab, temperature, top_k, top_p,
+                      cuts);
   if (st != YALIS_OK) return st;
   st = yalis_launch(sample_draw_partial_kernel, dim3(n_rows, kDrawChunks), dim3(kThreads), 0, stream, logits, row_stride,
                     vocab, temperature, top_p, seed, draw_index, (const Cut*)cuts, part_v, part_i);
