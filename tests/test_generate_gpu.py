@@ -165,6 +165,27 @@ def test_long_context_kind_of_decode_steps(monkeypatch):
             seq.append(tok)
 
 
+def test_decode_steps_with_more_pairs_than_resident_blocks(monkeypatch):
+    """A batch with more (request, KV head) pairs than blocks fit the GPU at once goes to the decode kernel that
+    deals tiles to a fixed grid; with the GPU taken for two SMs, five requests of a tiny model are such a batch
+    (4 blocks for 10 pairs, so block borders cut pairs), through captured steps, lengths growing across tiles."""
+    from yalis_b200.ops import attention as attn_ops
+    monkeypatch.setattr(attn_ops, "SM_COUNT", 2)
+    d = tiny_model_dir("C", 0.02)
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    prompts = prompts_for(cfg, [30, 61, 3, 100, 17])
+    eng = engine_for(d, "bf16", page_size=page_size_of("C"), max_batch_size=5, max_length_of_generated_sequences=192)
+    before = attn_ops.LAUNCHED["decode_lean"]
+    tokens, _ = eng.generate(prompts, tokens_to_generate=40)
+    assert attn_ops.LAUNCHED["decode_lean"] > before
+    for p, row in zip(prompts, tokens.tolist()):
+        seq = list(p)
+        for tok in row:
+            ref = plain.forward_logits(seq, w, cfg)[-1]
+            assert float(ref.max() - ref[tok]) <= 2e-2 * float(ref.abs().max())
+            seq.append(tok)
+
+
 def test_sampling_with_block_tables_used_to_their_last_entry():
     """Requests that grow into the last page their block-table row can name, decoded with sampling in
     captured steps: the per-row sampling parameters and the tables lie in one buffer and must not overlap

@@ -508,6 +508,81 @@ def test_decode_attention_tma_against_plain_and_generic(nh, g, hs, page, splits,
         torch.testing.assert_close(out[r].float().cpu().view(1, nh, hs), ref, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("nh, g, hs, page", [(32, 8, 128, 16), (8, 2, 64, 8), (4, 4, 64, 32), (16, 1, 128, 64), (6, 2, 192, 16),
+                                             (2, 1, 256, 16), (5, 5, 128, 16)])
+@pytest.mark.parametrize("n_blocks", [1, 2, 5, 13, 64, 296, 5000])
+def test_decode_attention_lean_against_plain_and_generic(nh, g, hs, page, n_blocks):
+    """The decode kernel that deals the tiles of all (request, KV head) pairs to a fixed grid: one block that
+    walks everything, a few blocks whose borders cut pairs (a long request spans several), about as many
+    blocks as tiles, and more blocks than tiles; a request without a token in the middle; twice in a row
+    (the tickets must come back to zero)."""
+    from yalis_b200.ops.attention import decode_attention_lean, paged_attention_generic
+    dtype = torch.bfloat16
+    lens = [1, 15, 16, 17, 63, 64, 65, 130, 517, 1200, 2, 64]
+    ks, vs, k_pool, v_pool, table = paged_setup(len(lens), lens, g, hs, page, dtype, seed=hs + nh + page)
+    gen = torch.Generator().manual_seed(3)
+    q = torch.randn(len(lens), nh, hs, generator=gen).to(dtype)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    positions, req = i32([l - 1 for l in lens]), i32(list(range(len(lens))))
+    q_start = i32(list(range(len(lens) + 1)))
+    qd = q.view(-1, nh * hs).to(DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ref_gen = paged_attention_generic(qd, k_pool, v_pool, positions, req, table, nh, g, hs)
+    early = n_blocks % 2 == 1     # fetching before the preceding kernel has finished wants everything complete: it is
+    torch.cuda.synchronize()
+    for _ in range(2):
+        out = decode_attention_lean(qd, k_pool, v_pool, positions, q_start, table, nh, g, hs, n_blocks=n_blocks,
+                                    error_flag=flag, early_fetch=early)
+        assert int(flag) == 0 and not torch.isnan(out.float()).any()
+        torch.testing.assert_close(out.float(), ref_gen.float(), rtol=2e-2, atol=2e-2)
+    for r, l in enumerate(lens):
+        ref = plain.causal_attention(q[r:r + 1].float(), ks[r].to(dtype).float(), vs[r].to(dtype).float(),
+                                     torch.tensor([l - 1]), torch.arange(l))
+        torch.testing.assert_close(out[r].float().cpu().view(1, nh, hs), ref, rtol=2e-2, atol=2e-2)
+    # Requests 3 and 7 bring no token (padding of a captured batch): the others' results do not move.
+    keep = [r for r in range(len(lens)) if r not in (3, 7)]
+    starts, at = [], 0
+    for r in range(len(lens)):
+        starts.append(at)
+        at += 1 if r in keep else 0
+    starts.append(at)
+    out2 = decode_attention_lean(qd[keep].contiguous(), k_pool, v_pool, positions[keep].contiguous(), i32(starts), table,
+                                 nh, g, hs, n_blocks=n_blocks, error_flag=flag)
+    assert int(flag) == 0
+    if n_blocks in (1, 5000):       # every pair whole in both runs: the same bits
+        assert torch.equal(out2, out[keep])
+    torch.testing.assert_close(out2.float(), ref_gen[keep].float(), rtol=2e-2, atol=2e-2)
+
+
+def test_decode_attention_lean_many_requests_and_a_far_key():
+    """600 requests of mixed lengths on the engine's grid; in some, one far key is made to carry all the weight
+    (a tile dropped or read from the wrong pair would show)."""
+    from yalis_b200.ops.attention import decode_attention_lean, decode_lean_blocks, paged_attention_generic
+    nh, g, hs, page, dtype = 8, 4, 128, 16, torch.bfloat16
+    gen = torch.Generator().manual_seed(11)
+    lens = [int(x) for x in torch.randint(1, 400, (600,), generator=gen)]
+    ks, vs, k_pool, v_pool, table = paged_setup(len(lens), lens, g, hs, page, dtype, seed=5)
+    q = torch.randn(len(lens), nh, hs, generator=gen).to(dtype)
+    marked = {}
+    for r in range(0, len(lens), 37):
+        target = int(torch.randint(0, lens[r], (1,), generator=gen))
+        marked[r] = target
+        for h in range(nh):
+            q[r, h] = (ks[r][target, h // (nh // g)] * 6.0).to(dtype)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    positions, req, q_start = i32([l - 1 for l in lens]), i32(list(range(len(lens)))), i32(list(range(len(lens) + 1)))
+    qd = q.view(-1, nh * hs).to(DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = decode_attention_lean(qd, k_pool, v_pool, positions, q_start, table, nh, g, hs, error_flag=flag)
+    assert int(flag) == 0 and decode_lean_blocks(hs) < len(lens) * g
+    ref = paged_attention_generic(qd, k_pool, v_pool, positions, req, table, nh, g, hs)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+    for r, target in marked.items():
+        got = out[r].float().cpu().view(nh, hs)
+        for h in range(nh):
+            assert torch.allclose(got[h], vs[r][target, h // (nh // g)].to(dtype).float(), atol=8e-2), (r, h)
+
+
 @pytest.mark.parametrize("nh, g, hs, page", [(32, 8, 128, 64), (8, 2, 64, 8), (6, 2, 192, 16), (2, 1, 256, 32), (5, 5, 128, 16)])
 @pytest.mark.parametrize("parts, splits, rotate", [(1, 1, True), (3, 4, True), (2, 8, False), (0, 3, True), (3, 11, True)])
 def test_decode_attention_tma_fused_has_the_bits_of_rotary_kernel_then_attention(nh, g, hs, page, parts, splits, rotate):

@@ -29,17 +29,9 @@
 // their scores are masked by index and their V rows are zeroed in shared memory before use.
 // Every mbarrier wait is bounded; on a timeout the block raises the error word, drains its
 // outstanding copies and returns (it still meets its cluster at both barriers).
-#include <cuda.h>
-
-#include "common.cuh"
+#include "decode_tiles.cuh"
 
 namespace {
-
-constexpr int BN = 64;            // keys per tile
-constexpr int CWARPS = 4;         // consumer warps; warp CWARPS is the producer
-constexpr int kThreads = (CWARPS + 1) * 32;
-constexpr int STAGES = 2;         // the per-warp results reuse the K ring after the tiles: it must hold CWARPS*16*HS floats
-constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct DecParams {
   const __nv_bfloat16* q;      // [N, q_stride]; null when the kernel rotates the queries itself (fused mode)
@@ -71,56 +63,6 @@ struct DecParams {
   int32_t* error;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], uint32_t saddr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], uint32_t saddr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<unsigned*>(&v);
-}
 constexpr int kMaxCluster = 8;    // portable cluster size: the most splits merged through shared memory
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, int rank) {
   uint32_t r;
@@ -140,21 +82,6 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Four results scaled and rounded to bfloat16, one 8-byte store.
-__device__ __forceinline__ void store_bf16x4(__nv_bfloat16* dst, float4 v, float scale) {
-  uint2 w;
-  w.x = pack_bf16(v.x * scale, v.y * scale);
-  w.y = pack_bf16(v.z * scale, v.w * scale);
-  *reinterpret_cast<uint2*>(dst) = w;
-}
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CWARPS * 32) : "memory"); }
-
-// Byte offset of element (row, dim) inside a swizzled tile [HS/64 halves][BN rows][128 bytes].
-__device__ __forceinline__ uint32_t tile_off(int row, int dim) {
-  const int half = dim >> 6, chunk = (dim & 63) >> 3;
-  return (uint32_t)(half * (BN * 128) + row * 128 + (((chunk ^ (row & 7)) << 4)));
-}
-
 template <int HS>
 __global__ void __launch_bounds__(kThreads)
 decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -485,6 +412,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int r = gid + i * 8;
+      if (r >= n_rows) continue;                            // padding rows of the 16-row MMA tile are never read
 #pragma unroll
       for (int d = 0; d < DT; ++d)
         *reinterpret_cast<float2*>(mo + ((size_t)warp * 16 + r) * HS + d * 8 + tig * 2) = make_float2(o[d][i * 2], o[d][i * 2 + 1]);
@@ -637,36 +565,6 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
   }
   __syncthreads();
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-        qres != cudaDriverEntryPointSuccess)
-      return nullptr;
-    fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-// The pool [pages, g, page_size, hs] as a matrix [pages*g*page_size, hs]; boxes of [page_size rows, 64 columns].
-bool make_pool_map(CUtensorMap* map, const void* pool, long long rows, int hs, int page_size) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)hs, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)hs * 2};
-  cuuint32_t box[2] = {64u, (cuuint32_t)page_size};
-  cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int HS>

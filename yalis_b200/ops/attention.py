@@ -65,6 +65,8 @@ LAUNCHED = collections.Counter()
 # YALIS_B200_NO_FUSED_ROPE=1 keeps the rotary / cache-write kernel apart from the decode attention.
 USE_FUSED_ROPE = os.environ.get("YALIS_B200_NO_FUSED_ROPE", "0") != "1"
 USE_DECODE_TMA = os.environ.get("YALIS_B200_NO_DECODE_TMA", "0") != "1"
+# YALIS_B200_NO_DECODE_LEAN=1 keeps large decode batches on one block per (request, KV head).
+USE_DECODE_LEAN = os.environ.get("YALIS_B200_NO_DECODE_LEAN", "0") != "1"
 # YALIS_B200_NO_PREFILL_TCGEN05=1 keeps prompt portions on the mma.sync kernel.
 USE_PREFILL_TCGEN05 = os.environ.get("YALIS_B200_NO_PREFILL_TCGEN05", "0") != "1"
 
@@ -192,6 +194,56 @@ def decode_attention_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
     return out
 
 
+def decode_lean_blocks(head_dim: int) -> int:
+    """Blocks of the evenly dealt decode kernel that are resident at once (its grid)."""
+    return (2 if head_dim <= 128 else 1) * SM_COUNT
+
+
+def decode_lean_preferred(n_requests: int, num_kv_heads: int, head_dim: int) -> bool:
+    """Whether a decode step has more (request, KV head) pairs than blocks fit the GPU at once: a block per pair
+    would then run in waves, the last one mostly empty, and the tiles of all pairs are dealt out evenly instead."""
+    return USE_DECODE_LEAN and n_requests <= 4096 and n_requests * num_kv_heads > decode_lean_blocks(head_dim)
+
+
+def decode_attention_lean(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, positions: torch.Tensor,
+                          q_start: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int,
+                          head_dim: int, scale: Optional[float] = None, n_blocks: Optional[int] = None,
+                          error_flag: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                          early_fetch: bool = False) -> torch.Tensor:
+    """Decode attention (one token per request, no window) by a fixed grid of blocks that share the key/value
+    tiles of all (request, KV head) pairs evenly; same result as ``decode_attention_tma`` up to the order in which
+    the pieces of a pair cut between blocks are added.  ``q`` is [R, heads*head_dim] (one row per request);
+    ``early_fetch`` as for ``decode_attention_tma``."""
+    name = "decode_attention_lean"
+    LAUNCHED["decode_lean"] += 1
+    n, r = q.shape[0], q_start.numel() - 1
+    _check_common(name, q, k_pool, v_pool, positions, positions, block_table, num_heads, num_kv_heads, head_dim)
+    need(q.dtype == torch.bfloat16, name, "bfloat16 only")
+    need(decode_tma_supports(head_dim, k_pool.shape[2], num_heads // num_kv_heads), name,
+         "needs head_dim 64/128/192/256, page_size 8/16/32/64 and at most 16 heads per KV head")
+    need(q_start.dtype == torch.int32 and q_start.is_contiguous() and q_start.is_cuda, name, "q_start must be int32 [R+1]")
+    need(block_table.shape[0] >= r, name, "block_table has fewer rows than requests")
+    need(r <= 4096, name, "at most 4096 requests")
+    if out is None:
+        out = torch.empty((n, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    need(out.shape == (n, num_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous(), name, "bad out tensor")
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    if n_blocks is None:
+        n_blocks = decode_lean_blocks(head_dim)
+    need(n_blocks >= 1, name, "n_blocks must be positive")
+    floats = lib().yalis_decode_attention_lean_scratch_floats
+    floats.restype = ctypes.c_longlong
+    scratch = torch.empty(int(floats(i32(n_blocks), i32(head_dim))), dtype=torch.float32, device=q.device)
+    tickets = _tickets(q.device, r * num_kv_heads)
+    check(lib().yalis_decode_attention_lean(
+        ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(k_pool), ptr(v_pool), ptr(positions), ptr(q_start),
+        ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]), i32(k_pool.shape[0]), i32(n), i32(r),
+        i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), i32(n_blocks), i32(1 if early_fetch else 0),
+        ptr(scratch), ptr(tickets), ptr(error_flag), stream()), name)
+    return out
+
+
 def decode_attention_tma_fused(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], store: bool, k_pool: torch.Tensor,
                                v_pool: torch.Tensor, positions: torch.Tensor, q_start: torch.Tensor,
                                block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
@@ -294,6 +346,10 @@ def paged_attention(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     table = ctx.block_tables[group]
     per = num_heads // num_kv_heads
     if decode_tma_applicable(qkv.dtype, ctx, head_dim, k_pool.shape[2], per, window):
+        if decode_lean_preferred(ctx.n_requests, num_kv_heads, head_dim):
+            return decode_attention_lean(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, num_heads, num_kv_heads,
+                                         head_dim, scale=scale, error_flag=ctx.error_flag,
+                                         early_fetch=bool(getattr(ctx, "settled", False)))
         return decode_attention_tma(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, num_heads, num_kv_heads,
                                     head_dim, scale=scale, n_splits=decode_tma_splits(ctx, num_kv_heads),
                                     error_flag=ctx.error_flag, early_fetch=bool(getattr(ctx, "settled", False)))

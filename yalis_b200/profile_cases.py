@@ -43,7 +43,7 @@ def _time(fn, launches: int, graph: bool = True) -> float:
 
 
 def attention_decode(args) -> None:
-    from yalis_b200.ops.attention import decode_attention_tma, decode_splits, paged_attention_mma
+    from yalis_b200.ops.attention import decode_attention_lean, decode_attention_tma, decode_splits, paged_attention_mma
     dev = "cuda:0"
     nh, g, hs, page, b, ctx = args.heads, args.kv_heads, args.head_dim, args.page_size, args.batch, args.ctx
     pages_per = -(-ctx // page)
@@ -64,6 +64,8 @@ def attention_decode(args) -> None:
         state["i"] += 1
         if args.kernel == "tma":
             decode_attention_tma(q, k, v, pos, q_start, table, nh, g, hs, n_splits=splits)
+        elif args.kernel == "lean":
+            decode_attention_lean(q, k, v, pos, q_start, table, nh, g, hs, n_blocks=args.blocks or None)
         else:
             paged_attention_mma(q, k, v, pos, q_start, req, table, 1, nh, g, hs, n_splits=splits)
 
@@ -197,7 +199,9 @@ def main() -> None:
     a.add_argument("--head-dim", type=int, default=128)
     a.add_argument("--page-size", type=int, default=64)
     a.add_argument("--splits", type=int, default=0)
-    a.add_argument("--kernel", default="tma", choices=["tma", "mma"], help="TMA-fed decode kernel or the cp.async one")
+    a.add_argument("--kernel", default="tma", choices=["tma", "lean", "mma"],
+                   help="TMA-fed decode kernel (a block per pair and split), the one that deals tiles to a fixed grid, or the cp.async one")
+    a.add_argument("--blocks", type=int, default=0, help="grid of the lean kernel (0: as the engine chooses)")
     a.add_argument("--launches", type=int, default=8)
     a.set_defaults(fn=attention_decode)
     gm = sub.add_parser("gemm_wstream")
