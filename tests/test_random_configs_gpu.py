@@ -31,9 +31,14 @@ def random_config(rng, head_sizes):
     return dict(cfg, bos_token_id=None, eos_token_id=None)
 
 
-@pytest.mark.parametrize("seed", [1, 2])
-def test_replay_of_random_configurations(seed):
+@pytest.mark.parametrize("seed, sms", [(1, None), (2, None), (5, 1)])
+def test_replay_of_random_configurations(seed, sms, monkeypatch):
+    """``sms``: the number of SMs the attention wrappers plan for; with 1, decode steps of two requests already
+    count as large batches and go to the kernel that deals key tiles to a fixed grid (two blocks, or one)."""
     from yalis_b200.engine.replay import Replayer
+    from yalis_b200.ops import attention as attn_ops
+    if sms is not None:
+        monkeypatch.setattr(attn_ops, "SM_COUNT", sms)
     rng = random.Random(seed)
     for trial in range(6):
         cfg = random_config(rng, [16, 32, 48, 64, 80, 96, 112, 128, 160, 192, 224, 256, 24, 40])
@@ -59,9 +64,12 @@ def test_replay_of_random_configurations(seed):
                     assert err < tol, (seed, trial, dtype, build.__name__, err, cfg, page, lengths)
 
 
-@pytest.mark.parametrize("seed", [2, 3])
-def test_generation_with_random_settings(seed):
+@pytest.mark.parametrize("seed, sms", [(2, None), (3, None), (4, 1)])
+def test_generation_with_random_settings(seed, sms, monkeypatch):
     from yalis_b200 import InferenceConfig, LLMEngine, ModelConfig
+    from yalis_b200.ops import attention as attn_ops
+    if sms is not None:
+        monkeypatch.setattr(attn_ops, "SM_COUNT", sms)           # see test_replay_of_random_configurations
     rng = random.Random(seed)
     for trial in range(12):
         cfg = random_config(rng, [16, 32, 64, 128, 64, 128, 192, 256, 48])
