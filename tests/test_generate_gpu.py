@@ -145,24 +145,56 @@ def test_generate_shortcut_and_command_line():
     assert [eval(l[len("output = "):]) for l in lines] == out
 
 
-def test_long_context_kind_of_decode_steps(monkeypatch):
-    """Decode steps beyond the long-context mark are captured as a kind of their own, with more key
-    splits merged through global memory; with the mark lowered to 48 tokens a tiny model crosses it."""
-    from yalis_b200.ops import attention as attn_ops
-    monkeypatch.setattr(attn_ops, "LONG_CONTEXT", 48)
-    d = tiny_model_dir("C", 0.02)
-    cfg, w = plain.read_config(d), plain.read_weights(d)
-    prompts = prompts_for(cfg, [30, 44, 17])
-    eng = engine_for(d, "bf16", page_size=page_size_of("C"))
-    tokens, _ = eng.generate(prompts, tokens_to_generate=24)
-    kinds = {k[3] for k in eng.engine.decoder._buckets}
-    assert kinds == {False, True}                       # the batch crossed the mark while it decoded
+def follows_the_oracle(prompts, tokens, w, cfg):
     for p, row in zip(prompts, tokens.tolist()):
         seq = list(p)
         for tok in row:
             ref = plain.forward_logits(seq, w, cfg)[-1]
             assert float(ref.max() - ref[tok]) <= 2e-2 * float(ref.abs().max())
             seq.append(tok)
+
+
+def test_long_context_kind_of_decode_steps(monkeypatch):
+    """Decode steps of one request beyond the long-context mark are captured as a kind of their own, with more
+    key splits merged through global memory; with the mark lowered to 48 tokens a tiny model crosses it."""
+    from yalis_b200.ops import attention as attn_ops
+    monkeypatch.setattr(attn_ops, "LONG_CONTEXT", 48)
+    d = tiny_model_dir("C", 0.02)
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    prompts = prompts_for(cfg, [30])
+    eng = engine_for(d, "bf16", page_size=page_size_of("C"))
+    tokens, _ = eng.generate(prompts, tokens_to_generate=40)
+    assert {(k[3], k[4]) for k in eng.engine.decoder._buckets} == {(False, False), (True, False)}   # it crossed the mark
+    follows_the_oracle(prompts, tokens, w, cfg)
+
+
+def test_long_or_uneven_batches_have_their_key_tiles_dealt_out(monkeypatch):
+    """Two or more requests of which one is long (beyond the long-context mark), or much longer than the others,
+    make a kind of decode step of their own, in which the attention kernel deals the key tiles of all requests
+    to a fixed grid.  With the marks lowered a tiny model gets there: first by the long-context mark while it
+    decodes, then (mark out of reach) by one prompt of 100 tokens beside short ones."""
+    from yalis_b200.ops import attention as attn_ops
+    d = tiny_model_dir("C", 0.02)
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    monkeypatch.setattr(attn_ops, "LONG_CONTEXT", 48)
+    prompts = prompts_for(cfg, [30, 44, 17])
+    eng = engine_for(d, "bf16", page_size=page_size_of("C"))
+    before = attn_ops.LAUNCHED["decode_lean"]
+    tokens, _ = eng.generate(prompts, tokens_to_generate=24)
+    assert {(k[3], k[4]) for k in eng.engine.decoder._buckets} == {(False, False), (False, True)}
+    assert attn_ops.LAUNCHED["decode_lean"] > before
+    follows_the_oracle(prompts, tokens, w, cfg)
+    monkeypatch.setattr(attn_ops, "LONG_CONTEXT", 8192)
+    monkeypatch.setattr(attn_ops, "DEAL_MIN_LONGEST", 64)
+    assert attn_ops.deal_tiles_hint([101, 6, 8]) and not attn_ops.deal_tiles_hint([101, 90, 80]) \
+        and not attn_ops.deal_tiles_hint([40, 2, 2]) and not attn_ops.deal_tiles_hint([5000])
+    prompts = prompts_for(cfg, [100, 5, 7], seed=3)
+    eng = engine_for(d, "bf16", page_size=page_size_of("C"), max_length_of_generated_sequences=192)
+    before = attn_ops.LAUNCHED["decode_lean"]
+    tokens, _ = eng.generate(prompts, tokens_to_generate=24)
+    assert {(k[3], k[4]) for k in eng.engine.decoder._buckets} == {(False, True)}
+    assert attn_ops.LAUNCHED["decode_lean"] > before
+    follows_the_oracle(prompts, tokens, w, cfg)
 
 
 def test_decode_steps_with_more_pairs_than_resident_blocks(monkeypatch):

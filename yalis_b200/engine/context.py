@@ -27,6 +27,9 @@ class HostStep:
     ctx_before: List[int]     # tokens each request held before the step
     max_q_len: int
     max_kv_len: int
+    # A decode step whose requests are long or differ much in length (see ops.attention.deal_tiles_hint): attention
+    # kernels should share the cached keys out evenly among their blocks instead of giving each request its own.
+    deal_tiles: bool = False
 
 
 @dataclass

@@ -41,9 +41,10 @@ def bucket_for(n: int) -> int:
 class _Bucket:
     """Static buffers and the captured graph for one batch size."""
 
-    def __init__(self, engine, size: int, greedy: bool, keep_logits: bool, long_context: bool = False):
+    def __init__(self, engine, size: int, greedy: bool, keep_logits: bool, long_context: bool = False,
+                 deal_tiles: bool = False):
         self.engine, self.size, self.greedy, self.keep_logits = engine, size, greedy, keep_logits
-        self.long_context = long_context
+        self.long_context, self.deal_tiles = long_context, deal_tiles
         dev = engine.device
         self.widths = [g.max_pages_per_request for g in engine.groups]
         r = size
@@ -98,7 +99,7 @@ class _Bucket:
             kv_len=d_kv, slots=d_slots, logit_rows=d_rows, block_tables=d_tables,
             # lengths are not part of a captured step; only whether it is of the long-context kind (more key splits)
             host=HostStep(slots=[], q_start=list(range(r + 1)), ctx_before=[], max_q_len=1,
-                          max_kv_len=engine.max_context if long_context else 0),
+                          max_kv_len=engine.max_context if long_context else 0, deal_tiles=deal_tiles),
             error_flag=engine._error_flag, decode_only=True, settled=True)
 
     def fill(self, slots: Sequence[int], lengths: Sequence[int], params: Optional[Sequence[SamplingParams]],
@@ -185,12 +186,15 @@ class GraphedDecoder:
         greedy = params is None or all(p.greedy for p in params)
         mgr = eng.manager
         lengths = [mgr.length(s) for s in slots]
-        from yalis_b200.ops.attention import LONG_CONTEXT
-        long_context = max(lengths) + 1 > LONG_CONTEXT
-        key = (bucket_for(n), greedy, keep_logits, long_context)
+        from yalis_b200.ops import attention as attn_ops
+        # The kind of step decides how attention kernels divide their work (they cannot look at lengths when a
+        # captured step is replayed): dealt tiles for long or uneven batches, more key splits for one long request.
+        deal_tiles = attn_ops.deal_tiles_hint([l + 1 for l in lengths])
+        long_context = not deal_tiles and max(lengths) + 1 > attn_ops.LONG_CONTEXT
+        key = (bucket_for(n), greedy, keep_logits, long_context, deal_tiles)
         b = self._buckets.get(key)
         if b is None:
-            b = self._buckets[key] = _Bucket(eng, key[0], greedy, keep_logits, long_context)
+            b = self._buckets[key] = _Bucket(eng, key[0], greedy, keep_logits, long_context, deal_tiles)
         for s, l in zip(slots, lengths):
             if l + 1 > eng.max_context or not mgr.fits(l + 1):
                 from yalis_b200.engine.engine import StepError

@@ -25,6 +25,7 @@ from yalis_b200.cache.storage import CacheStorage, plan_groups
 from yalis_b200.config.registry import load_config, parse_config
 from yalis_b200.engine.context import HostStep, StepContext
 from yalis_b200.engine.model import Model
+from yalis_b200.ops.attention import deal_tiles_hint
 from yalis_b200.weights.loader import init_random, load_weights
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -249,7 +250,8 @@ class Engine:
             n_tokens=n, n_requests=r, token_ids=d_tok, positions=d_pos, req_of_token=d_req, q_start=d_qs, kv_len=d_kv,
             slots=d_sl, logit_rows=d_rows, block_tables=tables,
             host=HostStep(slots=slots, q_start=[int(x) for x in qs], ctx_before=before, max_q_len=max(q_lens),
-                          max_kv_len=max_kv),
+                          max_kv_len=max_kv,
+                          deal_tiles=all(q == 1 for q in q_lens) and deal_tiles_hint([b + 1 for b in before])),
             error_flag=self._error_flag, decode_only=all(q == 1 for q in q_lens), settled=True)
 
     def _validate(self, slots: Sequence[int], entries: Sequence[StepEntry]) -> None:

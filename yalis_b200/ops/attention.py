@@ -199,10 +199,30 @@ def decode_lean_blocks(head_dim: int) -> int:
     return (2 if head_dim <= 128 else 1) * SM_COUNT
 
 
-def decode_lean_preferred(n_requests: int, num_kv_heads: int, head_dim: int) -> bool:
-    """Whether a decode step has more (request, KV head) pairs than blocks fit the GPU at once: a block per pair
-    would then run in waves, the last one mostly empty, and the tiles of all pairs are dealt out evenly instead."""
-    return USE_DECODE_LEAN and n_requests <= 4096 and n_requests * num_kv_heads > decode_lean_blocks(head_dim)
+DEAL_MIN_LONGEST = 2048   # below this many cached tokens even a lone long request costs less than dealing tiles out
+
+
+def deal_tiles_hint(lengths) -> bool:
+    """Host-side choice for a decode step of requests holding ``lengths`` cached tokens: True when a block per
+    (request, KV head) - or a fixed number of them - would leave the GPU waiting for the longest request, i.e.
+    with two or more requests of which one is beyond the long-context mark, or is at least ``DEAL_MIN_LONGEST``
+    long and twice the mean.  Depends on lengths only; the engine keys its captured steps by it."""
+    n = len(lengths)
+    if n < 2:
+        return False
+    longest = max(lengths)
+    return longest > LONG_CONTEXT or (longest >= DEAL_MIN_LONGEST and longest * n >= 2 * sum(lengths))
+
+
+def decode_lean_preferred(n_requests: int, num_kv_heads: int, head_dim: int, host=None) -> bool:
+    """Whether a decode step goes to the kernel that deals the key tiles of all (request, KV head) pairs to a fixed
+    grid: with more pairs than blocks fit the GPU at once (a block per pair would run in waves, the last one
+    mostly empty), or when the step's host facts say that the requests are long or uneven (``deal_tiles``)."""
+    if not USE_DECODE_LEAN or n_requests > 4096:
+        return False
+    if host is not None and getattr(host, "deal_tiles", False) and n_requests >= 2:
+        return True
+    return n_requests * num_kv_heads > decode_lean_blocks(head_dim)
 
 
 def decode_attention_lean(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, positions: torch.Tensor,
@@ -346,7 +366,7 @@ def paged_attention(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     table = ctx.block_tables[group]
     per = num_heads // num_kv_heads
     if decode_tma_applicable(qkv.dtype, ctx, head_dim, k_pool.shape[2], per, window):
-        if decode_lean_preferred(ctx.n_requests, num_kv_heads, head_dim):
+        if decode_lean_preferred(ctx.n_requests, num_kv_heads, head_dim, ctx.host):
             return decode_attention_lean(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, num_heads, num_kv_heads,
                                          head_dim, scale=scale, error_flag=ctx.error_flag,
                                          early_fetch=bool(getattr(ctx, "settled", False)))

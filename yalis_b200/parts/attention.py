@@ -61,6 +61,7 @@ class PagedAttention(Mixer):
     def forward(self, x: torch.Tensor, ctx, cache: PagedKVCache) -> torch.Tensor:
         qkv = linear_partial(x, self.w_qkv)          # [N, width], or float32 partial sums [S, N, width]
         if (attn_ops.USE_FUSED_ROPE and ctx.n_requests * self.g <= 2 * attn_ops.SM_COUNT
+                and not attn_ops.decode_lean_preferred(ctx.n_requests, self.g, self.hs, ctx.host)
                 and attn_ops.decode_tma_applicable(x.dtype, ctx, self.hs, cache.k.shape[2], self.nh // self.g, self.window)):
             # A decode step whose attention blocks fit the GPU at once: the attention kernel rotates Q and the new K
             # itself and stores K, V (one launch less).  With more blocks than that the extra work at the start of
