@@ -218,6 +218,31 @@ def test_decode_steps_with_more_pairs_than_resident_blocks(monkeypatch):
             seq.append(tok)
 
 
+def test_prompt_portions_with_their_keys_divided_among_blocks(monkeypatch):
+    """The policy that divides the keys of a tile of queries among several blocks of the tcgen05 prompt kernel
+    only does so for long contexts; here it is made to (up to three shares of one key tile or more) for the
+    portions of a tiny model's prompts, and says what it should for shapes measured on the GPU."""
+    from types import SimpleNamespace
+    from yalis_b200.ops import attention as attn_ops
+    choice = lambda q_start, before, per: attn_ops.prefill_kv_splits(SimpleNamespace(q_start=q_start, ctx_before=before), per, 8, 128)
+    assert choice([0, 2048], [12000], 3)[0] > 1         # 392 blocks: 1.3 waves
+    assert choice([0, 512], [3584], 4)[0] > 1           # 128 blocks: less than half the GPU
+    assert choice([0, 2048], [12000], 4)[0] == 1        # 512 blocks of two to an SM are even enough
+    assert choice([0, 2048], [0], 4)[0] == 1 and choice([0, 8192], [0], 4)[0] == 1 and choice([0, 300, 301], [0, 500], 4)[0] == 1
+    splits, limit = choice([0, 1, 2048], [14012, 816], 3)    # a decoding request with a long context beside a fresh prompt
+    assert splits > 2 and limit * splits >= 14012 // 64 + 1 and limit >= 24
+    monkeypatch.setattr(attn_ops, "prefill_kv_splits", lambda host, per, g, hs: (3, 1))
+    d = tiny_model_dir("C", 0.02)
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    prompts = prompts_for(cfg, [150, 61, 100])
+    eng = engine_for(d, "bf16", page_size=page_size_of("C"), prefill_chunk=48, max_tokens_per_step=64,
+                     max_length_of_generated_sequences=192)
+    before = attn_ops.LAUNCHED["prefill_tcgen05"]
+    tokens, _ = eng.generate(prompts, tokens_to_generate=6)
+    assert attn_ops.LAUNCHED["prefill_tcgen05"] > before
+    follows_the_oracle(prompts, tokens, w, cfg)
+
+
 def test_sampling_with_block_tables_used_to_their_last_entry():
     """Requests that grow into the last page their block-table row can name, decoded with sampling in
     captured steps: the per-row sampling parameters and the tables lie in one buffer and must not overlap

@@ -688,10 +688,13 @@ def test_rope_kv_write_many_tokens(dtype, hs):
 
 @pytest.mark.parametrize("nh, g, hs, page", [(8, 2, 128, 16), (4, 4, 64, 8), (6, 2, 128, 32), (3, 1, 64, 64), (32, 8, 128, 16),
                                              (5, 1, 128, 128)])
-def test_prefill_attention_tcgen05_against_plain_and_generic(nh, g, hs, page):
+@pytest.mark.parametrize("kv_splits, tiles_per_split", [(1, 1), (2, 1), (3, 2), (5, 1), (16, 1), (4, 3), (2, 5)])
+def test_prefill_attention_tcgen05_against_plain_and_generic(nh, g, hs, page, kv_splits, tiles_per_split):
     """The tcgen05 prompt kernel: a whole prompt, a portion at an offset that ends inside a page,
     a short portion and a decode token in one launch; pools poisoned with NaN where nothing was
-    written; against the plain float32 attention and the exact kernel."""
+    written; against the plain float32 attention and the exact kernel.  With key splits: shares that end at
+    causal edges, shares of a single tile, more room for shares than a request has tiles, and limits (3 or 5 key
+    tiles per share) under which some tiles of queries are divided and others finished by one block."""
     from yalis_b200.ops.attention import paged_attention_generic, prefill_attention_tcgen05
     dtype = torch.bfloat16
     lens, q_lens = [300, 517, 40, 130, 1], [300, 67, 33, 128, 1]
@@ -708,7 +711,8 @@ def test_prefill_attention_tcgen05_against_plain_and_generic(nh, g, hs, page):
     positions, req_of_token, q_start_d = i32(pos), i32(req), i32(q_start)
     qd = q.view(-1, nh * hs).to(DEV)
     flag = torch.zeros(1, dtype=torch.int32, device=DEV)
-    out = prefill_attention_tcgen05(qd, k_pool, v_pool, positions, q_start_d, table, max(q_lens), nh, g, hs, error_flag=flag)
+    out = prefill_attention_tcgen05(qd, k_pool, v_pool, positions, q_start_d, table, max(q_lens), nh, g, hs, error_flag=flag,
+                                    kv_splits=kv_splits, tiles_per_split=tiles_per_split)
     torch.cuda.synchronize()
     assert int(flag) == 0
     assert not torch.isnan(out.float()).any()
@@ -729,11 +733,11 @@ def test_prefill_attention_tcgen05_far_key_and_causal_edge():
     nh, g, hs, page, l = 4, 1, 128, 16, 700
     ks, vs, k_pool, v_pool, table = paged_setup(1, [l], g, hs, page, torch.bfloat16, seed=21)
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    for target in (0, 127, 128, 300, 555):
+    for target, kv_splits in ((0, 1), (127, 1), (128, 1), (300, 1), (555, 1), (0, 3), (128, 4), (555, 3), (300, 2)):
         q_len = 200                                          # queries at positions 500..699
         q = (ks[0][target, 0] * 4.0).repeat(q_len * nh).view(q_len, nh * hs).to(torch.bfloat16).to(DEV)
         out = prefill_attention_tcgen05(q, k_pool, v_pool, i32(list(range(l - q_len, l))), i32([0, q_len]), table, q_len,
-                                        nh, g, hs)
+                                        nh, g, hs, kv_splits=kv_splits, tiles_per_split=2)
         got = out.float().cpu().view(q_len, nh, hs)
         want = vs[0][target, 0].to(torch.bfloat16).float()
         for t in (0, 54, 55, 56, 199):

@@ -51,6 +51,13 @@ struct PrefillParams {
   int nh, g, per;
   int tokens_per_tile;         // 128 / per
   float scale_log2;
+  // With key splits (gridDim.z > 1) a tile of queries whose visible keys fill more than tiles_per_split key tiles
+  // is shared by several blocks (at most gridDim.z): block z takes its share of the keys and leaves the
+  // unnormalised output with its (max, sum) here; a second kernel adds the shares.  Tiles of queries with fewer
+  // keys are finished by block 0 alone, which marks their rows (max = +inf in share 0) for the second kernel.
+  int tiles_per_split;
+  float* part_o;               // [N, nh, n_splits, HS]
+  float* part_ml;              // [N, nh, n_splits, 2]
   int32_t* error;
 };
 
@@ -200,7 +207,22 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int n_rows = n_tok * p.per;
   const int pos_first = p.positions[tok0 + t0];
   const int hi_key = p.positions[tok0 + t0 + n_tok - 1];
-  const int n_tiles = hi_key / BN + 1;
+  // This block's share of the key tiles (all of them without splits).
+  const int all_tiles = hi_key / BN + 1;
+  const int slots = gridDim.z, split = blockIdx.z;          // slots: shares that the scratch memory has room for
+  const int wanted = slots > 1 ? min(slots, (all_tiles + p.tiles_per_split - 1) / p.tiles_per_split) : 1;
+  const int per_split = (all_tiles + wanted - 1) / wanted;
+  const int n_splits = (all_tiles + per_split - 1) / per_split;     // shares that get a tile (7 tiles in 5 shares: 4 of 2)
+  if (split >= n_splits) {                                  // uniform for the block
+    if (n_splits > 1 && (int)threadIdx.x < n_rows) {        // an unused share of a divided tile: nothing to add
+      const int t_in = threadIdx.x / p.per, head = threadIdx.x - t_in * p.per;
+      const size_t slot = ((size_t)(tok0 + t0 + t_in) * p.nh + kvh * p.per + head) * slots + split;
+      *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(-INFINITY, 0.f);
+    }
+    return;
+  }
+  const int tile_base = split * per_split;
+  const int n_tiles = min(all_tiles, tile_base + per_split) - tile_base;     // >= 1
   const int32_t* bt = p.block_table + (size_t)req * p.table_width;
 
   if (threadIdx.x == 0) {
@@ -245,7 +267,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int b = j & 1;
       const uint32_t ph = (j >> 1) & 1;
-      const int key0 = j * BN;
+      const int key0 = (tile_base + j) * BN;
       const int n_boxes = min(boxes_per_tile, (hi_key - key0) / box_rows + 1);
       for (int kv = 0; kv < 2 && ok; ++kv) {
         uint64_t* full = kv == 0 ? &k_full[b] : &v_full[b];
@@ -333,7 +355,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int b = j & 1;
       const uint32_t ph = (j >> 1) & 1;
-      const int key0 = j * BN;
+      const int key0 = (tile_base + j) * BN;
       if (!warp_wait(&s_full[b], ph, abort_flag, lane)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float sv[BN];
@@ -419,7 +441,27 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // ---- O / l -> global --------------------------------------------------------------------
     if (ok) ok = warp_wait(o_done, 0, abort_flag, lane);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
+    if (ok && n_splits > 1) {
+      // a share: unnormalised, with the maximum it is relative to and its sum
+      const size_t slot = ((size_t)(tok0 + t0 + (valid ? t_in : 0)) * p.nh + kvh * p.per + (valid ? head : 0)) * slots + split;
+      float* dst = p.part_o + slot * HS;
+      if (valid) *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(m_run, l_run);
+#pragma unroll 1
+      for (int c0 = 0; c0 < HS; c0 += 16) {
+        uint32_t o[16];
+        tmem_ld16(lane_base + COL_O + c0, o);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (valid) {
+#pragma unroll
+          for (int c = 0; c < 16; c += 4)
+            *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+        }
+      }
+    } else if (ok) {
+      if (slots > 1 && valid) {                             // finished here: the second kernel leaves these rows alone
+        const size_t slot = ((size_t)(tok0 + t0 + t_in) * p.nh + kvh * p.per + head) * slots;
+        *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(INFINITY, 0.f);
+      }
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
       __nv_bfloat16* dst = p.out + (size_t)(tok0 + t0 + (valid ? t_in : 0)) * p.out_stride +
                            (size_t)(kvh * p.per + (valid ? head : 0)) * HS;
@@ -512,9 +554,40 @@ bool make_q_map(CUtensorMap* map, const void* q, long long n_tokens, int q_strid
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Adds the shares of every (token, head) that was divided: one block per token, a thread per four output columns.
+__global__ void prefill_merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                            __nv_bfloat16* __restrict__ out, int out_stride, int nh, int hs, int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tok = blockIdx.x, vec = hs / 4;
+  for (int e = threadIdx.x; e < nh * vec; e += blockDim.x) {
+    const int head = e / vec, d = (e - head * vec) * 4;
+    const size_t slot0 = ((size_t)tok * nh + head) * n_splits;
+    if (part_ml[slot0 * 2] == INFINITY) continue;        // written by the first kernel itself
+    float mm = -INFINITY;
+    for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, part_ml[(slot0 + sp) * 2]);
+    float ll = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sp = 0; sp < n_splits; ++sp) {              // in split order
+      const float2 ml = *reinterpret_cast<const float2*>(part_ml + (slot0 + sp) * 2);
+      if (ml.x == -INFINITY) continue;                   // a split without visible keys wrote no output
+      const float f = exp2f(ml.x - mm);
+      const float4 v = *reinterpret_cast<const float4*>(part_o + (slot0 + sp) * hs + d);
+      ll += ml.y * f;
+      acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+    }
+    const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    uint2 w;
+    w.x = *reinterpret_cast<unsigned*>(&lo);
+    w.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(out + (size_t)tok * out_stride + (size_t)head * hs + d) = w;
+  }
+}
+
 template <int HS>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, int n_requests,
-           int max_q_len, cudaStream_t stream) {
+           int max_q_len, int n_splits, int n_tokens, cudaStream_t stream) {
   const size_t smem = 1024 + (size_t)BM * HS * 2 + (size_t)4 * BN * HS * 2 + 17 * 8 + 16;
   static bool configured = false;
   if (!configured) {
@@ -523,9 +596,12 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
       return YALIS_ERR_LAUNCH;
     configured = true;
   }
-  dim3 grid((max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile, n_requests * p.g);
+  dim3 grid((max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile, n_requests * p.g, n_splits);
   if (grid.y > 65535) return YALIS_ERR_SHAPE;
-  return yalis_launch(prefill_attention_tcgen05_kernel<HS>, grid, dim3(kThreads), smem, stream, mq, mk, mv, p);
+  int st = yalis_launch(prefill_attention_tcgen05_kernel<HS>, grid, dim3(kThreads), smem, stream, mq, mk, mv, p);
+  if (st != YALIS_OK || n_splits == 1) return st;
+  return yalis_launch(prefill_merge_splits_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)p.part_o,
+                      (const float*)p.part_ml, p.out, p.out_stride, p.nh, HS, n_splits);
 }
 
 }  // namespace
@@ -535,15 +611,27 @@ YALIS_API int yalis_prefill_attention_tcgen05_supports(int hs, int page_size, in
   return ((hs == 64 || hs == 128) && page_ok && per >= 1 && per <= 128) ? 1 : 0;
 }
 
+// Floats of scratch memory for n_splits > 1.
+YALIS_API long long yalis_prefill_attention_tcgen05_scratch_floats(int n_tokens, int nh, int hs, int n_splits) {
+  return (long long)n_tokens * nh * n_splits * (hs + 2);
+}
+
 // q: [N, q_stride] (head h at column h*hs); out [N, out_stride].  error: device int32 raised on a timed-out
-// wait or an unmapped page.  No window.
+// wait or an unmapped page.  No window.  With n_splits > 1 a tile of queries that sees more than tiles_per_split
+// tiles of 64 keys has them divided among ceil(tiles / tiles_per_split) blocks, at most n_splits (long contexts:
+// too few tiles of queries to fill the GPU evenly, or a few of them with far more keys than the rest); it needs
+// scratch: yalis_prefill_attention_tcgen05_scratch_floats floats, and every token row of [0, n_tokens) must then
+// belong to a request.
 YALIS_API int yalis_prefill_attention_tcgen05(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
                                               const void* v_pool, const int32_t* positions, const int32_t* q_start,
                                               const int32_t* block_table, int table_width, int page_size,
                                               int num_pages, int n_tokens, int n_requests, int max_q_len, int nh,
-                                              int g, int hs, float scale, int32_t* error, cudaStream_t stream) {
+                                              int g, int hs, float scale, int n_splits, int tiles_per_split, float* scratch,
+                                              int32_t* error, cudaStream_t stream) {
   if (n_tokens <= 0 || n_requests <= 0) return YALIS_OK;
-  if (g <= 0 || nh % g != 0 || max_q_len < 1) return YALIS_ERR_SHAPE;
+  if (g <= 0 || nh % g != 0 || max_q_len < 1 || n_splits < 1 || n_splits > 64) return YALIS_ERR_SHAPE;
+  if (n_splits > 1 && (scratch == nullptr || ((uintptr_t)scratch & 15))) return YALIS_ERR_ALIGN;
+  if (n_splits > 1 && tiles_per_split < 1) return YALIS_ERR_SHAPE;
   if (!yalis_prefill_attention_tcgen05_supports(hs, page_size, nh / g)) return YALIS_ERR_SHAPE;
   if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) return YALIS_ERR_ALIGN;
   if ((q_stride % 8) || (out_stride % 8)) return YALIS_ERR_ALIGN;
@@ -554,12 +642,15 @@ YALIS_API int yalis_prefill_attention_tcgen05(const void* q, int q_stride, void*
   p.nh = nh; p.g = g; p.per = nh / g;
   p.tokens_per_tile = BM / p.per;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.tiles_per_split = tiles_per_split > 0 ? tiles_per_split : 1;
+  p.part_o = scratch;
+  p.part_ml = scratch ? scratch + (size_t)n_tokens * nh * n_splits * hs : nullptr;
   p.error = error;
   CUtensorMap mq, mk, mv;
   const long long rows = (long long)num_pages * g * page_size;
   if (!make_q_map(&mq, q, n_tokens, q_stride, nh, hs, p.per, p.tokens_per_tile) ||
       !make_pool_map(&mk, k_pool, rows, hs, page_size) || !make_pool_map(&mv, v_pool, rows, hs, page_size))
     return YALIS_ERR_LAUNCH;
-  return hs == 64 ? launch<64>(mq, mk, mv, p, n_requests, max_q_len, stream)
-                  : launch<128>(mq, mk, mv, p, n_requests, max_q_len, stream);
+  return hs == 64 ? launch<64>(mq, mk, mv, p, n_requests, max_q_len, n_splits, n_tokens, stream)
+                  : launch<128>(mq, mk, mv, p, n_requests, max_q_len, n_splits, n_tokens, stream);
 }

@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import collections
 import ctypes
+import heapq
 import math
 import os
 from typing import Optional
@@ -332,9 +333,13 @@ def prefill_attention_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
                               q_start: torch.Tensor, block_table: torch.Tensor, max_q_len: int, num_heads: int,
                               num_kv_heads: int, head_dim: int, scale: Optional[float] = None,
                               error_flag: Optional[torch.Tensor] = None,
-                              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                              out: Optional[torch.Tensor] = None, kv_splits: int = 1,
+                              tiles_per_split: int = 1) -> torch.Tensor:
     """Causal paged attention of prompt portions on tcgen05 tensor cores (no window); the same
-    semantics as ``paged_attention_generic``.  ``q`` is [N, >= heads*head_dim]."""
+    semantics as ``paged_attention_generic``.  ``q`` is [N, >= heads*head_dim].  With ``kv_splits`` > 1 a tile of
+    queries that sees more than ``tiles_per_split`` tiles of 64 keys has them divided among up to ``kv_splits``
+    blocks, whose shares a second kernel adds (see ``prefill_kv_splits``); every row of ``q`` must then belong
+    to a request."""
     name = "prefill_attention_tcgen05"
     LAUNCHED["prefill_tcgen05"] += 1
     n, r = q.shape[0], q_start.numel() - 1
@@ -349,11 +354,90 @@ def prefill_attention_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
     need(out.shape == (n, num_heads * head_dim) and out.dtype == q.dtype and out.is_contiguous(), name, "bad out tensor")
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
+    need(1 <= kv_splits <= 64 and tiles_per_split >= 1, name, "kv_splits must be 1..64, tiles_per_split positive")
+    scratch = None
+    if kv_splits > 1:
+        floats = lib().yalis_prefill_attention_tcgen05_scratch_floats
+        floats.restype = ctypes.c_longlong
+        scratch = torch.empty(int(floats(i32(n), i32(num_heads), i32(head_dim), i32(kv_splits))), dtype=torch.float32,
+                              device=q.device)
     check(lib().yalis_prefill_attention_tcgen05(
         ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(k_pool), ptr(v_pool), ptr(positions), ptr(q_start),
         ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]), i32(k_pool.shape[0]), i32(n), i32(r),
-        i32(max_q_len), i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), ptr(error_flag), stream()), name)
+        i32(max_q_len), i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), i32(kv_splits), i32(tiles_per_split),
+        ptr(scratch), ptr(error_flag), stream()), name)
     return out
+
+
+PREFILL_SPLIT_MIN_TILES = 16     # a share of a divided tile of queries is at least this many key tiles long
+PREFILL_SPLIT_START_UP = 20.0    # what one more block costs (fill and drain, its share's outputs), in key tiles
+PREFILL_SPLIT_UNSHARED = 1.4     # pace of a block whose keys no other block reads at the time (they come from HBM)
+
+
+def _prefill_step_length(items, slots: int, splits: int, limit: int) -> float:
+    """Length of the tcgen05 prompt kernel, in key tiles of a block, for ``items`` = (key tiles, pace) of the
+    tiles of queries of one KV head: the blocks in launch order (share after share) each go to the first of
+    ``slots`` places to come free."""
+    lengths = []
+    for z in range(splits):
+        for tiles, pace in items:
+            wanted = min(splits, -(-tiles // limit)) if splits > 1 else 1
+            per_share = -(-tiles // wanted)
+            if z * per_share < tiles:
+                lengths.append((min(tiles, (z + 1) * per_share) - z * per_share) * pace + PREFILL_SPLIT_START_UP)
+    free = [0.0] * slots
+    end = 0.0
+    for length in lengths:
+        done = heapq.heappop(free) + length
+        heapq.heappush(free, done)
+        end = max(end, done)
+    return end
+
+
+def prefill_kv_splits(host, heads_per_group: int, num_kv_heads: int, head_dim: int):
+    """(kv_splits, tiles_per_split) for the tcgen05 prompt kernel in a step with the host facts ``host``.
+
+    The kernel runs one block per (tile of 128 // heads_per_group queries, KV head), two to an SM, and a block's
+    time grows with the keys its queries see.  Two things leave the GPU idle.  A few blocks with far more keys
+    than the rest: one decoding request with 14,000 cached tokens beside a fresh prompt keeps its 8 blocks busy
+    for 0.47 ms, everything else is done after 0.1 ms (with its keys in four shares the step takes 0.17 ms).  And
+    a number of long blocks just above a multiple of the 296 that run at once, or well below it: a 2,048-token
+    portion behind 12,000 tokens with 24 heads in 8 groups is 392 blocks, two rounds of which the second is a
+    third full (0.59 ms; in halves 0.51 ms); a 512-token portion is 128 blocks (89 us; in halves 73 us).
+    The choice is the best of 1, 2, 3, 4, 6 or 8 shares for the longest tile of queries (shorter ones get fewer)
+    under a model of the launch (``_prefill_step_length``) whose three constants are fitted to 26 measured steps
+    (portions of 512 to 2,048 tokens behind up to 14,000 cached ones, alone and beside decoding requests, 24 and
+    32 heads in 8 groups: the choices cost 1.4 % over the best measured ones, the model's times are 10 % off)."""
+    q_lens = [b - a for a, b in zip(host.q_start[:-1], host.q_start[1:])]
+    if not host.ctx_before or sum(q_lens) == 0:
+        return 1, 1
+    per_tile = 128 // heads_per_group
+    items = []                                              # (key tiles, pace) of every tile of queries of one KV head
+    for q, before in zip(q_lens, host.ctx_before):
+        # few tiles of queries on the same keys: nobody else brings them into the L2 cache
+        pace = PREFILL_SPLIT_UNSHARED if q <= 3 * per_tile else 1.0
+        for first in range(0, q, per_tile):
+            items.append(((before + min(q, first + per_tile) - 1) // 64 + 1, pace))
+    longest = max(t for t, _ in items)
+    if longest < 3 * PREFILL_SPLIT_MIN_TILES:
+        return 1, 1
+    slots = max(1, 2 * SM_COUNT // num_kv_heads)
+    best, best_length = (1, 1), 0.92 * _prefill_step_length(items, slots, 1, 1)    # dividing has to bring 8 %
+    for shares in (2, 3, 4, 6, 8):
+        limit = max(PREFILL_SPLIT_MIN_TILES, -(-longest // shares))
+        length = _prefill_step_length(items, slots, shares, limit)
+        if length < best_length:
+            best, best_length = (min(64, -(-longest // limit)), limit), length
+    return best
+
+
+def _prefill_split_choice(ctx, per: int, num_kv_heads: int, head_dim: int) -> dict:
+    """``prefill_kv_splits`` once per step and shape (every layer asks)."""
+    key = ("prefill_kv_splits", per, num_kv_heads, head_dim)
+    choice = ctx.extras.get(key)
+    if choice is None:
+        choice = ctx.extras[key] = prefill_kv_splits(ctx.host, per, num_kv_heads, head_dim)
+    return dict(kv_splits=choice[0], tiles_per_split=choice[1])
 
 
 def paged_attention(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: str, num_heads: int,
@@ -376,7 +460,8 @@ def paged_attention(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     if (qkv.dtype == torch.bfloat16 and USE_PREFILL_TCGEN05 and window is None and ctx.host.max_q_len >= 16
             and prefill_tcgen05_supports(head_dim, k_pool.shape[2], per)):
         return prefill_attention_tcgen05(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, ctx.host.max_q_len,
-                                         num_heads, num_kv_heads, head_dim, scale=scale, error_flag=ctx.error_flag)
+                                         num_heads, num_kv_heads, head_dim, scale=scale, error_flag=ctx.error_flag,
+                                         **_prefill_split_choice(ctx, per, num_kv_heads, head_dim))
     if qkv.dtype == torch.bfloat16 and mma_supports(head_dim):
         splits = decode_splits(ctx.n_requests, num_kv_heads) if ctx.host.max_q_len * per <= 16 else 1
         return paged_attention_mma(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, ctx.req_of_token, table,

@@ -76,29 +76,30 @@ def attention_decode(args) -> None:
 
 
 def attention_prefill(args) -> None:
-    """One prompt of ``--tokens`` tokens attending to itself (causal), one layer's worth of heads."""
+    """A portion of ``--tokens`` tokens of one prompt, ``--before`` tokens of which are cached already (causal),
+    one layer's worth of heads."""
     from yalis_b200.ops.attention import paged_attention_mma, prefill_attention_tcgen05
     dev = "cuda:0"
-    nh, g, hs, page, n = args.heads, args.kv_heads, args.head_dim, args.page_size, args.tokens
-    pages = -(-n // page)
+    nh, g, hs, page, n, before = args.heads, args.kv_heads, args.head_dim, args.page_size, args.tokens, args.before
+    pages = -(-(before + n) // page)
     k_pool = torch.randn(pages, g, page, hs, device=dev).to(torch.bfloat16)
     v_pool = torch.randn(pages, g, page, hs, device=dev).to(torch.bfloat16)
     table = torch.randperm(pages, device=dev).to(torch.int32).view(1, pages).contiguous()
     q = torch.randn(n, nh * hs, device=dev).to(torch.bfloat16)
-    pos = torch.arange(n, dtype=torch.int32, device=dev)
+    pos = before + torch.arange(n, dtype=torch.int32, device=dev)
     q_start = torch.tensor([0, n], dtype=torch.int32, device=dev)
     req = torch.zeros(n, dtype=torch.int32, device=dev)
 
     def fn():
         if args.kernel == "tcgen05":
-            prefill_attention_tcgen05(q, k_pool, v_pool, pos, q_start, table, n, nh, g, hs)
+            prefill_attention_tcgen05(q, k_pool, v_pool, pos, q_start, table, n, nh, g, hs, kv_splits=args.splits)
         else:
             paged_attention_mma(q, k_pool, v_pool, pos, q_start, req, table, n, nh, g, hs)
 
     us = _time(fn, args.launches, graph=not args.eager)
-    flops = 4.0 * nh * hs * n * (n + 1) / 2
-    print(f"attention_prefill ({args.kernel}) tokens {n} heads {nh}/{g} head_dim {hs}: {us:.1f} us per launch, "
-          f"{flops / us / 1e6:.1f} TFLOP/s (causal flops)")
+    flops = 4.0 * nh * hs * (n * before + n * (n + 1) / 2)
+    print(f"attention_prefill ({args.kernel}) tokens {n} after {before} heads {nh}/{g} head_dim {hs} key splits {args.splits}: "
+          f"{us:.1f} us per launch, {flops / us / 1e6:.1f} TFLOP/s (causal flops)")
 
 
 def gemm_wstream(args) -> None:
@@ -213,6 +214,8 @@ def main() -> None:
     gm.set_defaults(fn=gemm_wstream)
     ap_ = sub.add_parser("attention_prefill")
     ap_.add_argument("--tokens", type=int, default=2048)
+    ap_.add_argument("--before", type=int, default=0, help="tokens of the prompt that are cached already")
+    ap_.add_argument("--splits", type=int, default=1, help="key splits of the tcgen05 kernel")
     ap_.add_argument("--heads", type=int, default=32)
     ap_.add_argument("--kv-heads", type=int, default=8)
     ap_.add_argument("--head-dim", type=int, default=128)
