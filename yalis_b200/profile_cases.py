@@ -76,30 +76,49 @@ def attention_decode(args) -> None:
 
 
 def attention_prefill(args) -> None:
-    """A portion of ``--tokens`` tokens of one prompt, ``--before`` tokens of which are cached already (causal),
-    one layer's worth of heads."""
-    from yalis_b200.ops.attention import paged_attention_mma, prefill_attention_tcgen05
+    """The prompt attention of one step, one layer's worth of heads: requests that bring ``--tokens`` tokens each
+    (a list: portions of prompts, 1 for a decoding request) behind ``--before`` cached ones (causal).
+    ``--splits 0`` lets the engine's policy choose the key splits."""
+    from types import SimpleNamespace
+    from yalis_b200.ops.attention import paged_attention_mma, prefill_attention_tcgen05, prefill_kv_splits
     dev = "cuda:0"
-    nh, g, hs, page, n, before = args.heads, args.kv_heads, args.head_dim, args.page_size, args.tokens, args.before
-    pages = -(-(before + n) // page)
+    nh, g, hs, page = args.heads, args.kv_heads, args.head_dim, args.page_size
+    q_lens = [int(x) for x in str(args.tokens).split(",")]
+    before = [int(x) for x in str(args.before).split(",")]
+    assert len(q_lens) == len(before), "--tokens and --before list one number per request"
+    pages_per = [-(-(b + q) // page) for q, b in zip(q_lens, before)]
+    pages = sum(pages_per)
     k_pool = torch.randn(pages, g, page, hs, device=dev).to(torch.bfloat16)
     v_pool = torch.randn(pages, g, page, hs, device=dev).to(torch.bfloat16)
-    table = torch.randperm(pages, device=dev).to(torch.int32).view(1, pages).contiguous()
+    table = torch.zeros(len(q_lens), max(pages_per), dtype=torch.int32)
+    perm, at = torch.randperm(pages).to(torch.int32), 0
+    for r, n_pages in enumerate(pages_per):
+        table[r, :n_pages] = perm[at:at + n_pages]
+        at += n_pages
+    table = table.to(dev)
+    n = sum(q_lens)
     q = torch.randn(n, nh * hs, device=dev).to(torch.bfloat16)
-    pos = before + torch.arange(n, dtype=torch.int32, device=dev)
-    q_start = torch.tensor([0, n], dtype=torch.int32, device=dev)
-    req = torch.zeros(n, dtype=torch.int32, device=dev)
+    pos = torch.cat([torch.arange(b, b + ql, dtype=torch.int32) for ql, b in zip(q_lens, before)]).to(dev)
+    starts = [0]
+    for ql in q_lens:
+        starts.append(starts[-1] + ql)
+    q_start = torch.tensor(starts, dtype=torch.int32, device=dev)
+    req = torch.cat([torch.full((ql,), r, dtype=torch.int32) for r, ql in enumerate(q_lens)]).to(dev)
+    splits, limit = args.splits, args.tiles_per_split
+    if splits == 0:
+        splits, limit = prefill_kv_splits(SimpleNamespace(q_start=starts, ctx_before=before), nh // g, g, hs)
 
     def fn():
         if args.kernel == "tcgen05":
-            prefill_attention_tcgen05(q, k_pool, v_pool, pos, q_start, table, n, nh, g, hs, kv_splits=args.splits)
+            prefill_attention_tcgen05(q, k_pool, v_pool, pos, q_start, table, max(q_lens), nh, g, hs, kv_splits=splits,
+                                      tiles_per_split=limit)
         else:
-            paged_attention_mma(q, k_pool, v_pool, pos, q_start, req, table, n, nh, g, hs)
+            paged_attention_mma(q, k_pool, v_pool, pos, q_start, req, table, max(q_lens), nh, g, hs)
 
     us = _time(fn, args.launches, graph=not args.eager)
-    flops = 4.0 * nh * hs * (n * before + n * (n + 1) / 2)
-    print(f"attention_prefill ({args.kernel}) tokens {n} after {before} heads {nh}/{g} head_dim {hs} key splits {args.splits}: "
-          f"{us:.1f} us per launch, {flops / us / 1e6:.1f} TFLOP/s (causal flops)")
+    flops = 4.0 * nh * hs * sum(ql * b + ql * (ql + 1) / 2 for ql, b in zip(q_lens, before))
+    print(f"attention_prefill ({args.kernel}) tokens {q_lens} after {before} heads {nh}/{g} head_dim {hs} key splits "
+          f"{splits} of at least {limit} tiles: {us:.1f} us per launch, {flops / us / 1e6:.1f} TFLOP/s (causal flops)")
 
 
 def gemm_wstream(args) -> None:
@@ -213,9 +232,10 @@ def main() -> None:
     gm.add_argument("--launches", type=int, default=8)
     gm.set_defaults(fn=gemm_wstream)
     ap_ = sub.add_parser("attention_prefill")
-    ap_.add_argument("--tokens", type=int, default=2048)
-    ap_.add_argument("--before", type=int, default=0, help="tokens of the prompt that are cached already")
-    ap_.add_argument("--splits", type=int, default=1, help="key splits of the tcgen05 kernel")
+    ap_.add_argument("--tokens", default="2048", help="tokens each request brings, comma-separated")
+    ap_.add_argument("--before", default="0", help="tokens each request has cached already, comma-separated")
+    ap_.add_argument("--splits", type=int, default=1, help="most key splits of a tile of queries (0: the engine's choice)")
+    ap_.add_argument("--tiles-per-split", type=int, default=1, help="key tiles from which a tile of queries is divided")
     ap_.add_argument("--heads", type=int, default=32)
     ap_.add_argument("--kv-heads", type=int, default=8)
     ap_.add_argument("--head-dim", type=int, default=128)
