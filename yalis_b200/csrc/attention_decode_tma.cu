@@ -8,9 +8,8 @@
 //     box copy per (page, 64-column half) for K and for V (cp.async.bulk.tensor.2d over the pool
 //     seen as a matrix [pages*kv_heads*page_size, head_dim], 128-byte swizzle; the lanes share
 //     the copies of a tile), completion is counted by an mbarrier per stage, and the four consumer
-//     warps only wait, run ldmatrix on the swizzled tiles and mma.sync.  The ring has two stages
-//     (two blocks per SM keep four tiles in flight, and a block of the next kernel still fits
-//     beside them).
+//     warps only wait, run ldmatrix on the swizzled tiles and mma.sync.  The ring has three stages
+//     (two blocks per SM keep six tiles in flight).
 //   * Up to 8 splits are launched as one thread-block cluster and merged through distributed
 //     shared memory: every block leaves its (max, sum, unnormalised output) in its own shared
 //     memory, and after a cluster barrier each block finishes a share of the outputs, summing in
