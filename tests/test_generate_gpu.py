@@ -231,7 +231,7 @@ def test_prompt_portions_with_their_keys_divided_among_blocks(monkeypatch):
     assert choice([0, 2048], [0], 4)[0] == 1 and choice([0, 8192], [0], 4)[0] == 1 and choice([0, 300, 301], [0, 500], 4)[0] == 1
     splits, limit = choice([0, 1, 2048], [14012, 816], 3)    # a decoding request with a long context beside a fresh prompt
     assert splits > 2 and limit * splits >= 14012 // 64 + 1 and limit >= 24
-    monkeypatch.setattr(attn_ops, "prefill_kv_splits", lambda host, per, g, hs: (3, 1))
+    monkeypatch.setattr(attn_ops, "prefill_kv_splits", lambda host, per, g, hs, skip_single=False: (3, 1))
     d = tiny_model_dir("C", 0.02)
     cfg, w = plain.read_config(d), plain.read_weights(d)
     prompts = prompts_for(cfg, [150, 61, 100])
@@ -241,6 +241,27 @@ def test_prompt_portions_with_their_keys_divided_among_blocks(monkeypatch):
     tokens, _ = eng.generate(prompts, tokens_to_generate=6)
     assert attn_ops.LAUNCHED["prefill_tcgen05"] > before
     follows_the_oracle(prompts, tokens, w, cfg)
+
+
+def test_steps_of_portions_and_decoding_requests_use_two_attention_kernels(monkeypatch):
+    """While long prompts are still read in portions, requests with short prompts already decode: in such steps the
+    decoding requests go to the decode kernel once they hold enough tokens (here: any), the portions to the
+    prompt kernel."""
+    from yalis_b200.ops import attention as attn_ops
+    monkeypatch.setattr(attn_ops, "MIXED_DECODE_MIN_KEYS", 0)
+    d = tiny_model_dir("C", 0.02)
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    prompts = prompts_for(cfg, [150, 20, 90, 7])
+    eng = engine_for(d, "bf16", page_size=page_size_of("C"), prefill_chunk=32, max_tokens_per_step=40,
+                     max_length_of_generated_sequences=192)
+    before = attn_ops.LAUNCHED["decode_lean"], attn_ops.LAUNCHED["prefill_tcgen05"]
+    tokens, _ = eng.generate(prompts, tokens_to_generate=12)
+    assert attn_ops.LAUNCHED["decode_lean"] > before[0] and attn_ops.LAUNCHED["prefill_tcgen05"] > before[1]
+    follows_the_oracle(prompts, tokens, w, cfg)
+    assert attn_ops.mixed_step_splits_off_decodes(type("H", (), dict(q_start=[0, 1, 2, 50], ctx_before=[5, 9, 100]))()) is True
+    monkeypatch.setattr(attn_ops, "MIXED_DECODE_MIN_KEYS", 4096)
+    assert not attn_ops.mixed_step_splits_off_decodes(type("H", (), dict(q_start=[0, 1, 2, 50], ctx_before=[5, 9, 100]))())
+    assert attn_ops.mixed_step_splits_off_decodes(type("H", (), dict(q_start=[0, 1, 2, 50], ctx_before=[3000, 2000, 100]))())
 
 
 def test_sampling_with_block_tables_used_to_their_last_entry():

@@ -726,6 +726,41 @@ def test_prefill_attention_tcgen05_against_plain_and_generic(nh, g, hs, page, kv
         o += ql
 
 
+@pytest.mark.parametrize("nh, g, hs, page", [(8, 2, 128, 16), (6, 2, 64, 8), (32, 8, 128, 64)])
+@pytest.mark.parametrize("kv_splits, tiles_per_split", [(1, 1), (3, 2)])
+def test_mixed_step_with_its_decoding_requests_in_the_decode_kernel(nh, g, hs, page, kv_splits, tiles_per_split):
+    """A step of prompt portions and decoding requests: the decode kernel that deals tiles to a fixed grid takes
+    the requests that bring one token, the tcgen05 prompt kernel the others, both into one output; neither
+    touches the other's rows (the output starts as NaN and ends without)."""
+    from yalis_b200.ops.attention import decode_attention_lean, paged_attention_generic, prefill_attention_tcgen05
+    dtype = torch.bfloat16
+    lens, q_lens = [300, 517, 40, 700, 1, 90, 200], [300, 67, 33, 1, 1, 1, 2]
+    ks, vs, k_pool, v_pool, table = paged_setup(len(lens), lens, g, hs, page, dtype, seed=hs + nh)
+    gen = torch.Generator().manual_seed(1)
+    qs, pos, req, q_start = [], [], [], [0]
+    for r, (l, ql) in enumerate(zip(lens, q_lens)):
+        qs.append(torch.randn(ql, nh, hs, generator=gen))
+        pos += list(range(l - ql, l))
+        req += [r] * ql
+        q_start.append(q_start[-1] + ql)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    positions, req_of_token, q_start_d = i32(pos), i32(req), i32(q_start)
+    qd = torch.cat(qs).to(dtype).view(-1, nh * hs).to(DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((qd.shape[0], nh * hs), float("nan"), dtype=dtype, device=DEV)
+    decode_attention_lean(qd, k_pool, v_pool, positions, q_start_d, table, nh, g, hs, n_blocks=5, error_flag=flag, out=out,
+                          only_single=True)
+    single_rows = [q_start[r] for r, ql in enumerate(q_lens) if ql == 1]
+    written = ~torch.isnan(out.float()).any(dim=1).cpu()
+    assert sorted(torch.nonzero(written).flatten().tolist()) == single_rows
+    prefill_attention_tcgen05(qd, k_pool, v_pool, positions, q_start_d, table, max(q_lens), nh, g, hs, error_flag=flag, out=out,
+                              kv_splits=kv_splits, tiles_per_split=tiles_per_split, skip_single=True)
+    torch.cuda.synchronize()
+    assert int(flag) == 0 and not torch.isnan(out.float()).any()
+    ref = paged_attention_generic(qd, k_pool, v_pool, positions, req_of_token, table, nh, g, hs)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
 def test_prefill_attention_tcgen05_far_key_and_causal_edge():
     """One key takes nearly all the weight: each query row must return that key's value if it
     can see the key, and must not if the key lies after it (causal edge inside a tile)."""

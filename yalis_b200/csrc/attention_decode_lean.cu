@@ -39,6 +39,7 @@ struct LeanParams {
   int n_requests, nh, g, per;
   float scale_log2;
   int early_fetch;             // 1: index arrays and keys below the queries' positions are settled (see the kernel)
+  int only_single;             // 1: requests that bring more than one token are left to another kernel
   float* part_o;               // [blocks, 2, 16, HS]
   float* part_ml;              // [blocks, 2, 16, 2]
   int32_t* tickets;            // [R * g], zero before and after
@@ -139,7 +140,8 @@ decode_attention_lean_kernel(const __grid_constant__ CUtensorMap map_k, const __
   // ---- the schedule: tiles per request, their prefix sum, this block's range ---------------------
   for (int r = threadIdx.x; r < p.n_requests; r += kThreads) {
     const int tok = p.q_start[r];
-    cum[r + 1] = (p.q_start[r + 1] - tok > 0) ? p.positions[tok] / BN + 1 : 0;
+    const int n_tok = p.q_start[r + 1] - tok;
+    cum[r + 1] = (p.only_single ? n_tok == 1 : n_tok > 0) ? p.positions[tok] / BN + 1 : 0;
   }
   if (threadIdx.x == 0) cum[0] = 0;
   __syncthreads();
@@ -508,12 +510,15 @@ YALIS_API long long yalis_decode_attention_lean_scratch_floats(int n_blocks, int
 // pieces of a cut (request, KV head) are added.  n_blocks: the grid (the number of blocks resident at once is
 // the intended value; any positive number is correct).  scratch: yalis_decode_attention_lean_scratch_floats
 // floats; tickets: n_requests * g int32, zero before the call and left zero.  error: device int32 raised on a
-// timed-out wait or an unmapped page.  early_fetch as for yalis_decode_attention_tma.
+// timed-out wait or an unmapped page.  early_fetch as for yalis_decode_attention_tma.  A request's token is the
+// first of its range in q_start; with only_single = 1 requests that bring more than one token are skipped (their
+// rows of out are not written: a step that mixes prompt portions and decoding requests gives those to the
+// prompt kernel).
 YALIS_API int yalis_decode_attention_lean(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
                                           const void* v_pool, const int32_t* positions, const int32_t* q_start,
                                           const int32_t* block_table, int table_width, int page_size, int num_pages,
                                           int n_tokens, int n_requests, int nh, int g, int hs, float scale, int n_blocks,
-                                          int early_fetch, float* scratch, int32_t* tickets, int32_t* error, cudaStream_t stream) {
+                                          int early_fetch, int only_single, float* scratch, int32_t* tickets, int32_t* error, cudaStream_t stream) {
   if (n_tokens <= 0 || n_requests <= 0) return YALIS_OK;
   if (g <= 0 || nh % g != 0 || n_blocks < 1 || n_requests > kMaxRequests) return YALIS_ERR_SHAPE;
   const bool hs_ok = hs == 64 || hs == 128 || hs == 192 || hs == 256;
@@ -534,6 +539,7 @@ YALIS_API int yalis_decode_attention_lean(const void* q, int q_stride, void* out
   p.n_requests = n_requests; p.nh = nh; p.g = g; p.per = nh / g;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.early_fetch = early_fetch ? 1 : 0;
+  p.only_single = only_single ? 1 : 0;
   p.part_o = scratch;
   p.part_ml = scratch + (size_t)n_blocks * 2 * 16 * hs;
   p.tickets = tickets;

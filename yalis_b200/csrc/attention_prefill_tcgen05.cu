@@ -56,6 +56,7 @@ struct PrefillParams {
   // unnormalised output with its (max, sum) here; a second kernel adds the shares.  Tiles of queries with fewer
   // keys are finished by block 0 alone, which marks their rows (max = +inf in share 0) for the second kernel.
   int tiles_per_split;
+  int skip_single;             // 1: requests that bring one token are left to another kernel
   float* part_o;               // [N, nh, n_splits, HS]
   float* part_ml;              // [N, nh, n_splits, 2]
   int32_t* error;
@@ -203,6 +204,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   // Later query tiles see more keys: they are given to the first blocks, so the light ones fill the tail.
   const int t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * p.tokens_per_tile;   // first token of this block within the request
   if (t0 >= q_len) return;                                  // uniform: nothing allocated yet
+  if (p.skip_single && q_len == 1) {
+    // Another kernel writes this request's row; with key splits the second kernel must leave it alone.
+    if (gridDim.z > 1 && blockIdx.z == 0 && (int)threadIdx.x < p.per)
+      *reinterpret_cast<float2*>(p.part_ml + (((size_t)tok0 * p.nh + kvh * p.per + threadIdx.x) * gridDim.z) * 2) =
+          make_float2(INFINITY, 0.f);
+    return;
+  }
   const int n_tok = min(p.tokens_per_tile, q_len - t0);
   const int n_rows = n_tok * p.per;
   const int pos_first = p.positions[tok0 + t0];
@@ -621,13 +629,14 @@ YALIS_API long long yalis_prefill_attention_tcgen05_scratch_floats(int n_tokens,
 // tiles of 64 keys has them divided among ceil(tiles / tiles_per_split) blocks, at most n_splits (long contexts:
 // too few tiles of queries to fill the GPU evenly, or a few of them with far more keys than the rest); it needs
 // scratch: yalis_prefill_attention_tcgen05_scratch_floats floats, and every token row of [0, n_tokens) must then
-// belong to a request.
+// belong to a request.  skip_single = 1 leaves the rows of requests that bring one token unwritten (a decode
+// kernel takes them).
 YALIS_API int yalis_prefill_attention_tcgen05(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
                                               const void* v_pool, const int32_t* positions, const int32_t* q_start,
                                               const int32_t* block_table, int table_width, int page_size,
                                               int num_pages, int n_tokens, int n_requests, int max_q_len, int nh,
-                                              int g, int hs, float scale, int n_splits, int tiles_per_split, float* scratch,
-                                              int32_t* error, cudaStream_t stream) {
+                                              int g, int hs, float scale, int n_splits, int tiles_per_split, int skip_single,
+                                              float* scratch, int32_t* error, cudaStream_t stream) {
   if (n_tokens <= 0 || n_requests <= 0) return YALIS_OK;
   if (g <= 0 || nh % g != 0 || max_q_len < 1 || n_splits < 1 || n_splits > 64) return YALIS_ERR_SHAPE;
   if (n_splits > 1 && (scratch == nullptr || ((uintptr_t)scratch & 15))) return YALIS_ERR_ALIGN;
@@ -643,6 +652,7 @@ YALIS_API int yalis_prefill_attention_tcgen05(const void* q, int q_stride, void*
   p.tokens_per_tile = BM / p.per;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.tiles_per_split = tiles_per_split > 0 ? tiles_per_split : 1;
+  p.skip_single = skip_single ? 1 : 0;
   p.part_o = scratch;
   p.part_ml = scratch ? scratch + (size_t)n_tokens * nh * n_splits * hs : nullptr;
   p.error = error;

@@ -230,11 +230,13 @@ def decode_attention_lean(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.T
                           q_start: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int,
                           head_dim: int, scale: Optional[float] = None, n_blocks: Optional[int] = None,
                           error_flag: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                          early_fetch: bool = False) -> torch.Tensor:
+                          early_fetch: bool = False, only_single: bool = False) -> torch.Tensor:
     """Decode attention (one token per request, no window) by a fixed grid of blocks that share the key/value
     tiles of all (request, KV head) pairs evenly; same result as ``decode_attention_tma`` up to the order in which
-    the pieces of a pair cut between blocks are added.  ``q`` is [R, heads*head_dim] (one row per request);
-    ``early_fetch`` as for ``decode_attention_tma``."""
+    the pieces of a pair cut between blocks are added.  ``q`` is [N, >= heads*head_dim]; a request's token is the
+    first of its range in ``q_start``.  ``early_fetch`` as for ``decode_attention_tma``.  With ``only_single``
+    requests that bring more than one token are skipped and their rows of ``out`` left as they are (the decoding
+    requests of a step that also holds prompt portions)."""
     name = "decode_attention_lean"
     LAUNCHED["decode_lean"] += 1
     n, r = q.shape[0], q_start.numel() - 1
@@ -261,7 +263,7 @@ def decode_attention_lean(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.T
         ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(k_pool), ptr(v_pool), ptr(positions), ptr(q_start),
         ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]), i32(k_pool.shape[0]), i32(n), i32(r),
         i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), i32(n_blocks), i32(1 if early_fetch else 0),
-        ptr(scratch), ptr(tickets), ptr(error_flag), stream()), name)
+        i32(1 if only_single else 0), ptr(scratch), ptr(tickets), ptr(error_flag), stream()), name)
     return out
 
 
@@ -334,12 +336,12 @@ def prefill_attention_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
                               num_kv_heads: int, head_dim: int, scale: Optional[float] = None,
                               error_flag: Optional[torch.Tensor] = None,
                               out: Optional[torch.Tensor] = None, kv_splits: int = 1,
-                              tiles_per_split: int = 1) -> torch.Tensor:
+                              tiles_per_split: int = 1, skip_single: bool = False) -> torch.Tensor:
     """Causal paged attention of prompt portions on tcgen05 tensor cores (no window); the same
     semantics as ``paged_attention_generic``.  ``q`` is [N, >= heads*head_dim].  With ``kv_splits`` > 1 a tile of
     queries that sees more than ``tiles_per_split`` tiles of 64 keys has them divided among up to ``kv_splits``
     blocks, whose shares a second kernel adds (see ``prefill_kv_splits``); every row of ``q`` must then belong
-    to a request."""
+    to a request.  ``skip_single`` leaves the rows of requests that bring one token as they are."""
     name = "prefill_attention_tcgen05"
     LAUNCHED["prefill_tcgen05"] += 1
     n, r = q.shape[0], q_start.numel() - 1
@@ -365,7 +367,7 @@ def prefill_attention_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
         ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(k_pool), ptr(v_pool), ptr(positions), ptr(q_start),
         ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]), i32(k_pool.shape[0]), i32(n), i32(r),
         i32(max_q_len), i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), i32(kv_splits), i32(tiles_per_split),
-        ptr(scratch), ptr(error_flag), stream()), name)
+        i32(1 if skip_single else 0), ptr(scratch), ptr(error_flag), stream()), name)
     return out
 
 
@@ -394,7 +396,7 @@ def _prefill_step_length(items, slots: int, splits: int, limit: int) -> float:
     return end
 
 
-def prefill_kv_splits(host, heads_per_group: int, num_kv_heads: int, head_dim: int):
+def prefill_kv_splits(host, heads_per_group: int, num_kv_heads: int, head_dim: int, skip_single: bool = False):
     """(kv_splits, tiles_per_split) for the tcgen05 prompt kernel in a step with the host facts ``host``.
 
     The kernel runs one block per (tile of 128 // heads_per_group queries, KV head), two to an SM, and a block's
@@ -414,11 +416,13 @@ def prefill_kv_splits(host, heads_per_group: int, num_kv_heads: int, head_dim: i
     per_tile = 128 // heads_per_group
     items = []                                              # (key tiles, pace) of every tile of queries of one KV head
     for q, before in zip(q_lens, host.ctx_before):
+        if q == 0 or (skip_single and q == 1):              # decoding requests go to another kernel
+            continue
         # few tiles of queries on the same keys: nobody else brings them into the L2 cache
         pace = PREFILL_SPLIT_UNSHARED if q <= 3 * per_tile else 1.0
         for first in range(0, q, per_tile):
             items.append(((before + min(q, first + per_tile) - 1) // 64 + 1, pace))
-    longest = max(t for t, _ in items)
+    longest = max((t for t, _ in items), default=0)
     if longest < 3 * PREFILL_SPLIT_MIN_TILES:
         return 1, 1
     slots = max(1, 2 * SM_COUNT // num_kv_heads)
@@ -431,12 +435,26 @@ def prefill_kv_splits(host, heads_per_group: int, num_kv_heads: int, head_dim: i
     return best
 
 
-def _prefill_split_choice(ctx, per: int, num_kv_heads: int, head_dim: int) -> dict:
+MIXED_DECODE_MIN_KEYS = 4096     # cached tokens of a step's decoding requests from which they get a kernel of their own
+
+
+def mixed_step_splits_off_decodes(host) -> bool:
+    """Whether, in a step that holds prompt portions and decoding requests, the decoding requests go to the decode
+    kernel (which streams their keys at HBM speed) and only the portions to the prompt kernel (where a request's
+    single token would occupy a 128-row tile of its own per KV head and be fed two key tiles at a time): when
+    the decoding requests hold enough cached tokens for that to outweigh one more launch."""
+    q_lens = [b - a for a, b in zip(host.q_start[:-1], host.q_start[1:])]
+    if not host.ctx_before:
+        return False
+    return sum(before for q, before in zip(q_lens, host.ctx_before) if q == 1) >= MIXED_DECODE_MIN_KEYS
+
+
+def _prefill_split_choice(ctx, per: int, num_kv_heads: int, head_dim: int, skip_single: bool = False) -> dict:
     """``prefill_kv_splits`` once per step and shape (every layer asks)."""
-    key = ("prefill_kv_splits", per, num_kv_heads, head_dim)
+    key = ("prefill_kv_splits", per, num_kv_heads, head_dim, skip_single)
     choice = ctx.extras.get(key)
     if choice is None:
-        choice = ctx.extras[key] = prefill_kv_splits(ctx.host, per, num_kv_heads, head_dim)
+        choice = ctx.extras[key] = prefill_kv_splits(ctx.host, per, num_kv_heads, head_dim, skip_single)
     return dict(kv_splits=choice[0], tiles_per_split=choice[1])
 
 
@@ -459,9 +477,19 @@ def paged_attention(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
                                     error_flag=ctx.error_flag, early_fetch=bool(getattr(ctx, "settled", False)))
     if (qkv.dtype == torch.bfloat16 and USE_PREFILL_TCGEN05 and window is None and ctx.host.max_q_len >= 16
             and prefill_tcgen05_supports(head_dim, k_pool.shape[2], per)):
+        out = None
+        split_off = ctx.extras.get("mixed_step_splits_off_decodes")
+        if split_off is None:
+            split_off = ctx.extras["mixed_step_splits_off_decodes"] = mixed_step_splits_off_decodes(ctx.host)
+        split_off = split_off and USE_DECODE_LEAN and ctx.n_requests <= 4096 and decode_tma_supports(head_dim, k_pool.shape[2], per)
+        if split_off:
+            out = decode_attention_lean(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, num_heads, num_kv_heads,
+                                        head_dim, scale=scale, error_flag=ctx.error_flag,
+                                        early_fetch=bool(getattr(ctx, "settled", False)), only_single=True)
         return prefill_attention_tcgen05(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, ctx.host.max_q_len,
                                          num_heads, num_kv_heads, head_dim, scale=scale, error_flag=ctx.error_flag,
-                                         **_prefill_split_choice(ctx, per, num_kv_heads, head_dim))
+                                         out=out, skip_single=split_off,
+                                         **_prefill_split_choice(ctx, per, num_kv_heads, head_dim, split_off))
     if qkv.dtype == torch.bfloat16 and mma_supports(head_dim):
         splits = decode_splits(ctx.n_requests, num_kv_heads) if ctx.host.max_q_len * per <= 16 else 1
         return paged_attention_mma(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, ctx.req_of_token, table,
