@@ -31,14 +31,26 @@ def random_config(rng, head_sizes):
     return dict(cfg, bos_token_id=None, eos_token_id=None)
 
 
-@pytest.mark.parametrize("seed, sms", [(1, None), (2, None), (5, 1)])
-def test_replay_of_random_configurations(seed, sms, monkeypatch):
+def force_rare_paths(monkeypatch, attn_ops, seed):
+    """Choices that the attention wrappers only make for long contexts, made for every step: decoding requests of
+    mixed steps in the decode kernel, and the keys of prompt tiles divided among blocks in changing ways."""
+    rng = random.Random(seed)
+    monkeypatch.setattr(attn_ops, "MIXED_DECODE_MIN_KEYS", 0)
+    monkeypatch.setattr(attn_ops, "prefill_kv_splits",
+                        lambda host, per, g, hs, skip_single=False: rng.choice([(1, 1), (2, 1), (3, 1), (4, 2), (2, 3)]))
+
+
+@pytest.mark.parametrize("seed, sms, rare", [(1, None, False), (2, None, False), (5, 1, False), (6, None, True), (7, 1, True)])
+def test_replay_of_random_configurations(seed, sms, rare, monkeypatch):
     """``sms``: the number of SMs the attention wrappers plan for; with 1, decode steps of two requests already
-    count as large batches and go to the kernel that deals key tiles to a fixed grid (two blocks, or one)."""
+    count as large batches and go to the kernel that deals key tiles to a fixed grid (two blocks, or one).
+    ``rare``: see ``force_rare_paths``."""
     from yalis_b200.engine.replay import Replayer
     from yalis_b200.ops import attention as attn_ops
     if sms is not None:
         monkeypatch.setattr(attn_ops, "SM_COUNT", sms)
+    if rare:
+        force_rare_paths(monkeypatch, attn_ops, seed)
     rng = random.Random(seed)
     for trial in range(6):
         cfg = random_config(rng, [16, 32, 48, 64, 80, 96, 112, 128, 160, 192, 224, 256, 24, 40])
@@ -64,12 +76,14 @@ def test_replay_of_random_configurations(seed, sms, monkeypatch):
                     assert err < tol, (seed, trial, dtype, build.__name__, err, cfg, page, lengths)
 
 
-@pytest.mark.parametrize("seed, sms", [(2, None), (3, None), (4, 1)])
-def test_generation_with_random_settings(seed, sms, monkeypatch):
+@pytest.mark.parametrize("seed, sms, rare", [(2, None, False), (3, None, False), (4, 1, False), (8, None, True), (9, 1, True)])
+def test_generation_with_random_settings(seed, sms, rare, monkeypatch):
     from yalis_b200 import InferenceConfig, LLMEngine, ModelConfig
     from yalis_b200.ops import attention as attn_ops
     if sms is not None:
         monkeypatch.setattr(attn_ops, "SM_COUNT", sms)           # see test_replay_of_random_configurations
+    if rare:
+        force_rare_paths(monkeypatch, attn_ops, seed)
     rng = random.Random(seed)
     for trial in range(12):
         cfg = random_config(rng, [16, 32, 64, 128, 64, 128, 192, 256, 48])
