@@ -17,6 +17,14 @@
 //     requests' tile counts in shared memory), so a captured launch can be replayed with other
 //     lengths.
 //
+//   * The next pair's queries are fetched into registers while the current pair is computed; the
+//     ring has three stages where two blocks of them still share an SM, else two.
+//   * With early_fetch the schedule and the first tiles (those that lie wholly below a query's
+//     position) do not wait for the preceding kernel (see the entry point for what the caller
+//     promises).
+//   * The same kernel takes batches that are long or uneven in length at any size (the host
+//     decides), and the decoding requests of a step that also holds prompt portions (only_single).
+//
 // Tile handling, masking and the arithmetic are those of decode_attention_tma_kernel; limits are
 // the same (bfloat16, head_dim 64/128/192/256, pages of 8..64 tokens, no window, at most 16 query
 // heads per KV head, one token per request), and at most 4096 requests.  Every mbarrier wait is
