@@ -38,6 +38,10 @@ def test_which_decode_kernel_takes_a_step():
     assert attn.decode_lean_preferred(19, 8, 256, plain_step)       # one block per SM at head size 256: 152 pairs > 148
     assert not attn.decode_lean_preferred(5000, 8, 128, dealt)      # the kernel's schedule holds 4096 requests
     assert attn.decode_splits(8, 8) == 4 and attn.decode_splits(1, 8) == 32 and attn.decode_splits(64, 8) == 1
+    step = lambda r, longest=0: SimpleNamespace(n_requests=r, host=SimpleNamespace(max_kv_len=longest))
+    # clusters of up to 8 splits, of more than 4 only while they leave room; beyond the long-context mark up to 32
+    assert [attn.decode_tma_splits(step(r), 8) for r in (1, 2, 4, 8, 16, 32, 64)] == [8, 8, 6, 4, 2, 1, 1]
+    assert [attn.decode_tma_splits(step(r, 100000), 8) for r in (1, 2, 4, 8)] == [32, 18, 9, 4]
 
 
 def test_decoding_requests_of_a_mixed_step():

@@ -43,7 +43,9 @@ def _time(fn, launches: int, graph: bool = True) -> float:
 
 
 def attention_decode(args) -> None:
-    from yalis_b200.ops.attention import decode_attention_lean, decode_attention_tma, decode_splits, paged_attention_mma
+    from types import SimpleNamespace
+    from yalis_b200.ops.attention import (decode_attention_lean, decode_attention_tma, decode_splits, decode_tma_splits,
+                                          paged_attention_mma)
     dev = "cuda:0"
     nh, g, hs, page, b, ctx = args.heads, args.kv_heads, args.head_dim, args.page_size, args.batch, args.ctx
     pages_per = -(-ctx // page)
@@ -56,7 +58,8 @@ def attention_decode(args) -> None:
     pos = torch.full((b,), ctx - 1, dtype=torch.int32, device=dev)
     q_start = torch.arange(b + 1, dtype=torch.int32, device=dev)
     req = torch.arange(b, dtype=torch.int32, device=dev)
-    splits = args.splits or (min(8, decode_splits(b, g)) if args.kernel == "tma" else decode_splits(b, g))   # as the engine chooses
+    step = SimpleNamespace(n_requests=b, host=SimpleNamespace(max_kv_len=0))
+    splits = args.splits or (decode_tma_splits(step, g) if args.kernel == "tma" else decode_splits(b, g))   # as the engine chooses
     state = {"i": 0}
 
     def fn():
