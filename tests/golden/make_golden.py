@@ -16,8 +16,10 @@ For each tiny configuration it writes the same seeded random weights the tests u
 re-lays them out the way the reference stores them (QKV grouped per KV group,
 gate/up rows interleaved: yalis/external/convert_hf_checkpoint.py:791-796, 833-835),
 runs (1) one whole prompt as PREFILL and (2) a prefix as PREFILL followed by
-DECODE_SINGLE tokens, and stores the logits with a checksum of the weights.
-tests/test_plain.py compares the plain implementation with these files.
+DECODE_SINGLE tokens, and stores the logits together with the weights themselves
+(under ``w/<tensor name>``, as the 16 bits of their bfloat16 values, which is what the
+model file holds), so that the comparison never depends on how a torch build draws
+random numbers.  tests/test_plain.py compares the plain implementation with these files.
 """
 
 import hashlib
@@ -150,9 +152,14 @@ def run(which: str, n_tokens: int, prefix: int, std: float):
             steps.append(out)
         decoded = torch.stack(steps)
     out = os.path.join(HERE, f"tiny_{which}.npz")
+    stored = {}
+    for wname, t in weights.items():
+        as_bf16 = t.to(torch.bfloat16)
+        assert torch.equal(as_bf16.float(), t.float()), f"{wname} is not representable in bfloat16"
+        stored["w/" + wname] = as_bf16.view(torch.int16).numpy().view(np.uint16)
     np.savez_compressed(out, tokens=tokens.numpy(), whole=whole.numpy().astype(np.float32),
                         decoded=decoded.numpy().astype(np.float32), prefix=np.int64(prefix), std=np.float64(std),
-                        weights_sha256=np.array(weights_checksum(weights)))
+                        weights_sha256=np.array(weights_checksum(weights)), **stored)
     print(f"{out}: whole {tuple(whole.shape)}, decoded {tuple(decoded.shape)}, "
           f"whole-vs-decoded max abs {float((whole[prefix:] - decoded).abs().max()):.3e}")
 

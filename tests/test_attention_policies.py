@@ -27,9 +27,14 @@ def test_long_or_uneven_decode_batches_are_marked():
     assert not attn.deal_tiles_hint([1040] * 8)
 
 
+@pytest.fixture(autouse=True)
+def a_gpu_of_148_multiprocessors(monkeypatch):
+    """The policies ask the device for its size; without one, these tests state the B200's."""
+    monkeypatch.setattr(attn, "SM_COUNT", 148)
+
+
 def test_which_decode_kernel_takes_a_step():
-    plain_step = SimpleNamespace(deal_tiles=False)
-    dealt = SimpleNamespace(deal_tiles=True)
+    plain_step, dealt = False, True
     assert not attn.decode_lean_preferred(8, 8, 128, plain_step)    # 64 pairs: a block (or four) each
     assert not attn.decode_lean_preferred(37, 8, 128, plain_step)   # 296 pairs still fit at once
     assert attn.decode_lean_preferred(38, 8, 128, plain_step)
@@ -38,10 +43,12 @@ def test_which_decode_kernel_takes_a_step():
     assert attn.decode_lean_preferred(19, 8, 256, plain_step)       # one block per SM at head size 256: 152 pairs > 148
     assert not attn.decode_lean_preferred(5000, 8, 128, dealt)      # the kernel's schedule holds 4096 requests
     assert attn.decode_splits(8, 8) == 4 and attn.decode_splits(1, 8) == 32 and attn.decode_splits(64, 8) == 1
-    step = lambda r, longest=0: SimpleNamespace(n_requests=r, host=SimpleNamespace(max_kv_len=longest))
-    # clusters of up to 8 splits, of more than 4 only while they leave room; beyond the long-context mark up to 32
-    assert [attn.decode_tma_splits(step(r), 8) for r in (1, 2, 4, 8, 16, 32, 64)] == [8, 8, 6, 4, 2, 1, 1]
-    assert [attn.decode_tma_splits(step(r, 100000), 8) for r in (1, 2, 4, 8)] == [32, 18, 9, 4]
+    # clusters of up to 8 splits, of more than 4 only while they leave room; steps of the long-context kind up to 32
+    assert [attn.decode_tma_splits(r, 8, False) for r in (1, 2, 4, 8, 16, 32, 64)] == [8, 8, 6, 4, 2, 1, 1]
+    assert [attn.decode_tma_splits(r, 8, True) for r in (1, 2, 4, 8)] == [32, 18, 9, 4]
+    # what a recorded decode step is keyed by: (tiles dealt out, long context)
+    assert attn.decode_step_kind([1040] * 8) == (False, False) and attn.decode_step_kind([20000]) == (False, True)
+    assert attn.decode_step_kind([20000, 100]) == (True, False) and attn.decode_step_kind([]) == (False, False)
 
 
 def test_decoding_requests_of_a_mixed_step():

@@ -95,6 +95,41 @@ def test_shortage_changes_nothing():
     m.check()
 
 
+def test_a_refused_step_leaves_every_page_where_it_was():
+    """``reserve_many`` is for all requests of a step or for none: a step that does not fit takes no page from
+    the requests named first, so a caller that retries with a smaller batch finds the pool unchanged."""
+    m = two_groups(pages=6, page=4, window=10)
+    a, b, c = m.acquire(), m.acquire(), m.acquire()
+    assert m.reserve_many([a, b], [8, 4]) and m.free_pages("kv_all") == 3
+    m.commit(a, 8); m.commit(b, 4)
+    before = (m.free_pages("kv_all"), m.free_pages("kv_window_10"), m.table("kv_all").copy())
+    assert not m.reserve_many([a, b, c], [12, 8, 8])          # needs 1 + 1 + 2 pages, 3 are free
+    assert (m.free_pages("kv_all"), m.free_pages("kv_window_10")) == before[:2]
+    assert np.array_equal(m.table("kv_all"), before[2])
+    m.check()
+    assert m.reserve_many([a, b], [12, 8]) and m.free_pages("kv_all") == 1      # the smaller step fits
+    assert m.reserve_many([], [])
+    with pytest.raises(CacheError):
+        m.reserve_many([a, a], [13, 13])
+    with pytest.raises(CacheError):
+        m.reserve_many([a], [13, 14])
+    with pytest.raises(CacheError):
+        m.reserve_many([a], [4])                               # below what it holds
+    m.check()
+
+
+def test_groups_with_a_window_get_no_more_pages_than_they_can_use():
+    from yalis_b200.cache.storage import group_page_bytes, plan_groups, window_group_pages
+    from yalis_b200.parts.base import PagedKV, SlotState
+    requests = [PagedKV(2, 16), PagedKV(2, 16, window=20), None, SlotState((5,)), PagedKV(4, 32)]
+    groups = {g.name: g for g in plan_groups(requests, page_size=8, num_pages=1000, max_context=4096, max_slots=4, step_tokens=64)}
+    assert groups["kv_all"].num_pages == 1000
+    assert groups["kv_window_20"].num_pages == window_group_pages(20, 8, 4, 64) == 4 * (11 + 2)
+    assert {g.name: g.num_pages for g in plan_groups(requests, 8, 1000, 4096)} == {"kv_all": 1000, "kv_window_20": 1000}
+    assert group_page_bytes(requests, [None, None, None, None, 0], 8, 2) == {"kv_all": 2 * 2 * 8 * 16 * 2, "kv_window_20": 2 * 2 * 8 * 16 * 2}
+    assert group_page_bytes(requests, [None] * 5, 8, 2)["kv_all"] == 2 * 2 * 8 * 16 * 2 + 2 * 4 * 8 * 32 * 2
+
+
 def test_misuse_raises():
     m = two_groups()
     with pytest.raises(CacheError):

@@ -132,7 +132,38 @@ def test_model_and_inference_config_rules(tmp_path):
     ic = InferenceConfig(max_batch_size=3, max_length_of_generated_sequences=77, top_k=5, top_p=0.5, temperature=0.0)
     assert (ic.max_batch_size, ic.max_length, ic.top_k, ic.top_p, ic.temperature) == (3, 77, 5, 0.5, 0.0)
     for bad in (dict(max_batch_size=0), dict(max_length_of_generated_sequences=0), dict(temperature=-1.0),
-                dict(top_k=0), dict(top_p=1.5), dict(tp_dims=(2, 1, 1)), dict(attention_backend="nope"),
-                dict(use_paged_kv_caching=False), dict(page_size=0), dict(symmetric_allreduce_strategy="one-shot")):
+                dict(top_k=0), dict(top_p=1.5), dict(attention_backend="flash"), dict(attention_backend="sdpa"),
+                dict(use_paged_kv_caching=False), dict(page_size=0), dict(num_pages=4, cache_tokens=64),
+                dict(memory_fraction=1.5), dict(prefill_chunk=0)):
         with pytest.raises(ValueError):
             InferenceConfig(**bad)
+    for gone in (dict(tp_dims=(1, 1, 1)), dict(symmetric_allreduce_strategy=None), dict(prestore_kv_cache=True),
+                 dict(use_intra_head_parallelism=False)):
+        with pytest.raises(TypeError):          # options for several GPUs do not exist here
+            InferenceConfig(**gone)
+    assert InferenceConfig(attention_backend="paged").page_size == 64
+
+
+def test_engine_config_is_typed_and_sizes_the_pool():
+    from yalis_b200 import EngineConfig
+    ec = EngineConfig(dtype="bf16", page_size=16, max_slots=8, max_context=1000)
+    assert ec.dtype == "bfloat16"
+    with pytest.raises(Exception):
+        ec.page_size = 32                                            # frozen
+    assert ec.with_(page_size=32).page_size == 32 and ec.page_size == 16
+    assert ec.pool_pages(4096) == 8 * 63                            # every slot at its longest
+    assert EngineConfig(page_size=16, num_pages=11).pool_pages(4096) == 11
+    assert EngineConfig(page_size=16, cache_tokens=100).pool_pages(4096) == 7
+    by_memory = EngineConfig(page_size=16, max_slots=4, max_context=4096, memory_fraction=0.5)
+    assert by_memory.pool_pages(8192, free_bytes=1 << 20, bytes_per_page=4096) == 128
+    assert by_memory.pool_pages(8192, free_bytes=1 << 40, bytes_per_page=4096) == 4 * 256     # never more than can be mapped
+    with pytest.raises(ValueError):
+        by_memory.pool_pages(8192, free_bytes=1000, bytes_per_page=4096)
+    for bad in (dict(dtype="fp16"), dict(dtype="int8"), dict(page_size=0), dict(max_slots=-1), dict(num_pages=0),
+                dict(num_pages=3, memory_fraction=0.5), dict(memory_fraction=0.0), dict(max_tokens_per_step=True)):
+        with pytest.raises(ValueError):
+            EngineConfig(**bad)
+    ic = InferenceConfig(max_batch_size=3, max_length_of_generated_sequences=77, page_size=8, prefill_chunk=24)
+    got = ic.engine_config("fp32")
+    assert (got.dtype, got.max_slots, got.max_context, got.cache_tokens, got.page_size, got.prefill_chunk) == \
+        ("float32", 3, 77, 3 * 77, 8, 24)

@@ -35,6 +35,32 @@ def test_embedding(dtype, vocab, width):
     assert int(flag) == 0
     embedding(table, torch.tensor([vocab], dtype=torch.int32, device=DEV), bad_flag=flag)
     assert int(flag) == 1                                   # an id out of range is flagged, not read
+    # a scale; and ids taken from the per-slot array of chosen tokens where a token names a slot
+    assert torch.equal(embedding(table, ids, scale=2.5), table[ids.long()].float() * 2.5)
+    chosen = torch.tensor([9, 3, 30, 1], dtype=torch.int32, device=DEV)
+    from_slot = torch.tensor([-1, 2, -1, 0, 3], dtype=torch.int32, device=DEV)
+    want = torch.tensor([0, 30, 5, 9, 1], device=DEV)
+    assert torch.equal(embedding(table, ids, from_slot=from_slot, chosen=chosen), table[want].float())
+
+
+def test_softcap_and_chosen_tokens_per_slot():
+    from yalis_b200.ops.elementwise import softcap_
+    from yalis_b200.ops.sampling import argmax, sample
+    x = rnd(7, 1000, seed=3, scale=20.0)
+    torch.testing.assert_close(softcap_(x.clone(), 8.0), 8.0 * torch.tanh(x / 8.0), rtol=1e-5, atol=1e-5)
+    for vocab in (1000, 40000):                            # one block per row; 32 blocks per row and a merge
+        logits = rnd(5, vocab, seed=4)
+        where = torch.tensor([3, -1, 0, 6, -1], dtype=torch.int32, device=DEV)
+        kept = torch.full((8,), -7, dtype=torch.int32, device=DEV)
+        got = argmax(logits, scatter_index=where, scatter=kept)
+        best = logits.argmax(dim=-1).tolist()
+        assert got.tolist() == best
+        assert kept.tolist() == [best[2], -7, -7, best[0], -7, -7, best[3], -7]
+        kept.fill_(-7)
+        zeros = torch.zeros(5, device=DEV)
+        got = sample(logits, zeros, torch.zeros(5, dtype=torch.int32, device=DEV), zeros, torch.zeros(5, dtype=torch.int64, device=DEV),
+                     torch.zeros(5, dtype=torch.int64, device=DEV), scatter_index=where, scatter=kept)
+        assert got.tolist() == best and kept.tolist() == [best[2], -7, -7, best[0], -7, -7, best[3], -7]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -114,7 +114,8 @@ def test_block_part_matches_plain_block():
                                                             "head_dim": hs}), position=position)
     ff = make_part("feed_forward", PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": inter}))
     n1, n2 = make_part("norm", norm), make_part("norm", norm)
-    block = make_part("block", PartSpec("pre_norm_residual"), mixer=mixer, feed_forward=ff, norm_1=n1, norm_2=n2)
+    block = make_part("block", PartSpec("pre_norm_residual"),
+                      parts={"position": position, "norm_1": n1, "mixer": mixer, "norm_2": n2, "feed_forward": ff})
     names = {"q_proj": "self_attn.q_proj.weight", "k_proj": "self_attn.k_proj.weight", "v_proj": "self_attn.v_proj.weight",
              "o_proj": "self_attn.o_proj.weight", "gate_proj": "mlp.gate_proj.weight", "up_proj": "mlp.up_proj.weight",
              "down_proj": "mlp.down_proj.weight"}

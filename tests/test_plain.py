@@ -28,13 +28,18 @@ def _checksum(weights):
 
 @pytest.mark.parametrize("which", ["A", "B"])
 def test_plain_matches_reference_model(which):
+    """The golden file holds the weights the reference's model ran with, so nothing here depends on how this
+    torch build draws random numbers."""
     g = np.load(os.path.join(GOLDEN, f"tiny_{which}.npz"))
     name, seed, _ = TINY[which]
-    with tempfile.TemporaryDirectory() as d:
+    cfg = plain.normalise_config(preset(name))
+    weights = {k[2:]: torch.from_numpy(g[k].view(np.int16).copy()).view(torch.bfloat16).float()
+               for k in g.files if k.startswith("w/")}
+    assert weights and _checksum(weights) == str(g["weights_sha256"])
+    with tempfile.TemporaryDirectory() as d:             # and the loader's view of the same model folder agrees
         write_random_model(preset(name), d, seed=seed, std=float(g["std"]))
-        cfg, weights = plain.read_config(d), plain.read_weights(d)
-    if _checksum(weights) != str(g["weights_sha256"]):
-        pytest.skip("this torch build draws other random weights than the one that made the golden file")
+        fresh = plain.read_weights(d)
+    assert set(fresh) == set(weights) and all(fresh[k].shape == weights[k].shape for k in weights)
     tokens = g["tokens"].tolist()
     ours = plain.forward_logits(tokens, weights, cfg).numpy()
     scale = np.abs(g["whole"]).max()

@@ -48,9 +48,9 @@ def oracle(which, std, requests):
     return _oracle_cache[key]
 
 
-def replay_in_process(model_dir, dtype, page_size, steps, max_tokens):
+def replay_in_process(model_dir, dtype, page_size, steps, max_tokens, graphs=False):
     from yalis_b200.engine.replay import Replayer
-    rep = Replayer(model_dir, dtype, max_tokens, page_size=page_size)
+    rep = Replayer(model_dir, dtype, max_tokens, page_size=page_size, graphs=graphs)
     out = {}
     for s in steps:
         r = rep.run_step(s)
@@ -79,8 +79,9 @@ def compare(got, want, tol, what):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("which", ["A", "B", "C", "D"])
-@pytest.mark.parametrize("cut", ["whole", "tail_decoded", "portions", "mixed"])
+@pytest.mark.parametrize("cut", ["whole", "tail_decoded", "portions", "mixed", "tail_decoded/recorded", "mixed/recorded"])
 def test_cuttings_match_plain(which, dtype, cut):
+    cut, _, recorded = cut.partition("/")
     std = STD[dtype]
     d = tiny_model_dir(which, std)
     cfg = plain.read_config(d)
@@ -90,9 +91,12 @@ def test_cuttings_match_plain(which, dtype, cut):
              "mixed": traces.mixed}[cut]
     steps = traces.number(build(requests))
     peak = traces.peak_tokens(steps)
-    out, rep = replay_in_process(d, dtype, page_size_of(which), steps, peak)
+    out, rep = replay_in_process(d, dtype, page_size_of(which), steps, peak, graphs=bool(recorded))
     got = traces.collect(steps, out, cfg["vocab_size"])
-    compare(got, want, TOL[dtype], f"{which}/{dtype}/{cut}")
+    compare(got, want, TOL[dtype], f"{which}/{dtype}/{cut}{'/recorded' if recorded else ''}")
+    if recorded:
+        single = sum(all(len(e["tokens"]) == 1 for e in s["entries"]) for s in steps)
+        assert rep.steps_replayed == single > 0
     if cut == "mixed":
         # the pool was smaller than the sum of all requests: pages were used again
         assert peak < sum(traces.round_up(len(t)) for t in requests.values())
@@ -107,9 +111,11 @@ def test_cuttings_agree_with_each_other(dtype):
     cfg = plain.read_config(d)
     requests = make_requests(cfg, [3, 61, 130, 77, 18], seed=5)
     results = []
-    for build in (traces.whole, traces.tail_decoded, traces.portions, traces.mixed):
+    for build, graphs in ((traces.whole, False), (traces.tail_decoded, False), (traces.portions, False), (traces.mixed, False),
+                          (traces.tail_decoded, True), (traces.mixed, True)):
         steps = traces.number(build(requests))
-        out, _ = replay_in_process(d, dtype, page_size_of(which), steps, traces.peak_tokens(steps))
+        out, rep = replay_in_process(d, dtype, page_size_of(which), steps, traces.peak_tokens(steps), graphs=graphs)
+        assert (rep.steps_replayed > 0) == graphs
         results.append(traces.collect(steps, out, cfg["vocab_size"]))
     tol = 1e-6 if dtype == "float32" else 2e-2
     for other in results[1:]:
@@ -166,6 +172,127 @@ def test_long_decoding_and_first_tokens(dtype):
     out, _ = replay_in_process(d, dtype, page_size_of(which), first, 64)
     got = traces.collect(first, out, cfg["vocab_size"])
     compare(got, {"f": want["r0"][:3]}, TOL[dtype], f"first tokens {dtype}")
+
+
+def decoding_together(requests, heads, leave_after):
+    """A trace in which the requests are fed whole up to ``heads[i]`` tokens and then decode together, one
+    token each per step; request i ends (and leaves the batch) ``leave_after[i]`` steps after the decoding began,
+    or when its tokens run out."""
+    ids = list(requests)
+    steps = [{"entries": [{"id": rid, "tokens": requests[rid][:h], "want": list(range(h))} for rid, h in zip(ids, heads)],
+              "end": []}]
+    at = dict(zip(ids, heads))
+    live, k = list(ids), 0
+    while live:
+        k += 1
+        entries, end = [], []
+        for i, rid in enumerate(ids):
+            if rid not in live:
+                continue
+            entries.append({"id": rid, "tokens": [requests[rid][at[rid]]], "want": [0]})
+            at[rid] += 1
+            if at[rid] == len(requests[rid]) or k == leave_after[i]:
+                end.append(rid)
+        live = [rid for rid in live if rid not in end]
+        steps.append({"entries": entries, "end": end})
+    return steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["B", "C"])
+def test_recorded_steps_with_padding_and_changes_of_kind(which, dtype, monkeypatch):
+    """Steps replayed from recordings, where they differ from launched ones: three live requests in a recording
+    made for four (a padding row), a request that leaves so that the others move to a smaller recording, and
+    requests that grow past the marks by which the attention part keys its recordings (lowered here so that a
+    tiny model crosses them): from the plain kind to dealt tiles while three decode, to the long-context kind
+    when one is left.  Every logit against the plain model, as for launched steps."""
+    from yalis_b200.ops import attention as attn_ops
+    monkeypatch.setattr(attn_ops, "LONG_CONTEXT", 60)
+    std = STD[dtype]
+    d = tiny_model_dir(which, std)
+    cfg = plain.read_config(d)
+    requests = make_requests(cfg, [70, 30, 52], seed=21)
+    want = oracle(which, std, requests)
+    steps = traces.number(decoding_together(requests, heads=[40, 6, 20], leave_after=[99, 14, 25]))
+    out, rep = replay_in_process(d, dtype, page_size_of(which), steps, traces.peak_tokens(steps), graphs=True)
+    got = traces.collect(steps, out, cfg["vocab_size"])
+    want = {rid: want[rid][:got[rid].shape[0]] for rid in got}
+    compare(got, want, TOL[dtype], f"recorded steps {which}/{dtype}")
+    assert rep.steps_replayed == len(steps) - 1
+    sizes = {key[0] for key in rep.engine._recordings}
+    assert sizes == {4, 2, 1}                                     # 3 live in a recording of 4, then 2, then 1
+    if which == "C" and dtype == "bfloat16":                      # the kernels that look at the kind of step
+        kinds = set()
+        for key in rep.engine._recordings:
+            kinds |= {k for block in key[3] if isinstance(block, tuple) for k in block if isinstance(k, tuple)}
+        assert kinds == {(False, False), (True, False), (False, True)}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_steps_that_take_their_tokens_from_the_device(dtype, graphs):
+    """A step may name "the token chosen for this request last" instead of a token id: the choice stays on the
+    device and the host need not have read it.  Greedy decoding that way gives the logits of the plain model on
+    the sequence it produces, and the same tokens as decoding with the ids passed through the host."""
+    from yalis_b200.engine.engine import Engine, StepEntry
+    from yalis_b200.sampling.sampler import GREEDY
+    which, std = "C", STD[dtype]
+    d = tiny_model_dir(which, std)
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    prompts = make_requests(cfg, [23, 5, 40], seed=9)
+    eng = Engine(d, dtype=dtype, page_size=page_size_of(which), cache_tokens=512, max_slots=4)
+    for rid in prompts:
+        eng.add_request(rid)
+    ids = list(prompts)
+    out = eng.run([StepEntry(rid, prompts[rid], [len(prompts[rid]) - 1]) for rid in ids], sampling=[GREEDY] * 3, draws=[0] * 3)
+    seqs = {rid: list(prompts[rid]) for rid in ids}
+    logits = {rid: [out.logits[i].cpu()] for i, rid in enumerate(ids)}
+    reports = [eng.fetch_chosen()]
+    for k in range(1, 12):
+        if k == 6:
+            eng.finish_request(ids.pop(1))               # the batch shrinks: another recording, same slots
+        out = eng.run([StepEntry(rid, None, [0]) for rid in ids], sampling=[GREEDY] * len(ids), draws=[k] * len(ids),
+                      graphs=graphs)
+        assert out.captured == graphs
+        for i, rid in enumerate(ids):
+            logits[rid].append(out.logits[i].cpu())
+        reports.append(eng.fetch_chosen())                # read only after the loop: the host runs ahead
+    slot = {rid: eng.slot_of(rid) for rid in ids}
+    for rid in prompts:
+        s = slot.get(rid, 1)                              # the request that left held slot 1
+        for k, rep in enumerate(reports):
+            if rid in ids or k < 6:
+                seqs[rid].append(int(rep.wait()[s]))
+    for rid in prompts:
+        ref = plain.forward_logits(seqs[rid][:-1], w, cfg)[len(prompts[rid]) - 1:]
+        got = torch.stack(logits[rid])
+        assert got.shape == ref.shape
+        err = float((got - ref).abs().max() / ref.abs().max())
+        assert err <= TOL[dtype], (rid, err)
+        if dtype == "float32":
+            assert seqs[rid][len(prompts[rid]):] == plain.greedy_generate(prompts[rid], len(seqs[rid]) - len(prompts[rid]), w, cfg)
+    with pytest.raises(Exception, match="no token was chosen"):
+        eng.add_request("new")
+        eng.run([StepEntry("new", None, [0])])
+    for rid in ids + ["new"]:
+        eng.finish_request(rid)
+    eng.manager.check()
+
+
+def test_a_refused_step_reserves_nothing():
+    """A step that needs more pages than are free raises before anything runs and keeps no page, whoever calls it."""
+    from yalis_b200.engine.engine import Engine, OutOfPages, StepEntry
+    d = tiny_model_dir("A", 0.2)
+    eng = Engine(d, dtype="float32", page_size=16, num_pages=4, max_slots=3)
+    for rid in "abc":
+        eng.add_request(rid)
+    eng.step([StepEntry("a", [1] * 20, [19])])
+    free = eng.free_pages()
+    with pytest.raises(OutOfPages):
+        eng.step([StepEntry("a", [2] * 10, []), StepEntry("b", [3] * 16, []), StepEntry("c", [4] * 17, [])])
+    assert eng.free_pages() == free and eng.length("b") == 0 and eng.length("a") == 20
+    assert eng.step([StepEntry("a", [2] * 10, []), StepEntry("b", [3] * 16, [15])]).shape[0] == 1
+    eng.manager.check()
 
 
 def test_wanted_subset_and_skipped_logits():
@@ -226,8 +353,54 @@ def test_one_layer_of_the_8b_shape(dtype):
         requests = make_requests(pcfg, [150, 40], seed=2)
         want = {rid: plain.forward_logits(t, w, pcfg).numpy() for rid, t in requests.items()}
         del w
-        for build in (traces.whole, traces.tail_decoded, traces.mixed):
+        for build, graphs in ((traces.whole, False), (traces.tail_decoded, False), (traces.portions, False), (traces.mixed, False),
+                              (traces.tail_decoded, True)):
             steps = traces.number(build(requests))
-            out, _ = replay_in_process(d, dtype, 16, steps, traces.peak_tokens(steps))
+            out, _ = replay_in_process(d, dtype, 16, steps, traces.peak_tokens(steps), graphs=graphs)
             got = traces.collect(steps, out, pcfg["vocab_size"])
-            compare(got, want, TOL[dtype], f"8B layer/{dtype}/{build.__name__}")
+            compare(got, want, TOL[dtype], f"8B layer/{dtype}/{build.__name__}{'/recorded' if graphs else ''}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_two_layers_of_the_8b_shape_with_its_vocabulary(dtype):
+    """Two layers at the full sizes of Llama-3-8B including the vocabulary of 128,256: the output product, the
+    two-phase argmax and the sampler at that width run on the engine's path, in both precisions.  A short request
+    cut three ways against the plain model, then greedy and sampled tokens through the entry point."""
+    from yalis_b200 import InferenceConfig, LLMEngine, ModelConfig, SamplingParams
+    from yalis_b200.config.presets import preset
+    from yalis_b200.sampling.sampler import GREEDY
+    from yalis_b200.weights.loader import write_random_model
+    cfg = preset("Llama-3-8B")
+    cfg.update(num_hidden_layers=2, max_position_embeddings=256, bos_token_id=None, eos_token_id=None)
+    with tempfile.TemporaryDirectory() as d:
+        write_random_model(cfg, d, seed=6, std=0.02)
+        pcfg, w = plain.read_config(d), plain.read_weights(d)
+        assert pcfg["vocab_size"] == 128256
+        requests = make_requests(pcfg, [21, 9], seed=3)
+        want = {rid: plain.forward_logits(t, w, pcfg).numpy() for rid, t in requests.items()}
+        for build, graphs in ((traces.whole, False), (lambda r: traces.tail_decoded(r, tail=6), True),
+                              (lambda r: traces.mixed(r, tail=4), False)):
+            steps = traces.number(build(requests))
+            out, _ = replay_in_process(d, dtype, 16, steps, traces.peak_tokens(steps), graphs=graphs)
+            got = traces.collect(steps, out, pcfg["vocab_size"])
+            compare(got, want, TOL[dtype], f"8B two layers/{dtype}")
+        eng = LLMEngine(ModelConfig(model_name="two", model_path=d, precision="fp32" if dtype == "float32" else "bf16"),
+                        InferenceConfig(max_batch_size=2, max_length_of_generated_sequences=64, page_size=16))
+        prompts = list(requests.values())
+        hot = SamplingParams(temperature=0.7, top_k=40, top_p=0.9, seed=11)
+        results, _ = eng.run(prompts, 5, sampling=[GREEDY, hot], return_logits=True)
+        again, _ = eng.run(prompts, 5, sampling=[GREEDY, hot])
+        assert [g.tokens for g in results] == [g.tokens for g in again]
+        seq = list(prompts[0])
+        for k, tok in enumerate(results[0].tokens):          # the greedy row: the plain model's best, or within rounding
+            ref = plain.forward_logits(seq, w, pcfg)[-1]
+            assert float(ref.max() - ref[tok]) <= (1e-5 if dtype == "float32" else 2e-2) * float(ref.abs().max())
+            got = results[0].logits[k].cpu()
+            assert float((got - ref).abs().max() / ref.abs().max()) <= TOL[dtype]
+            seq.append(tok)
+        seq = list(prompts[1])
+        near = 48 if dtype == "float32" else 400             # bfloat16 moves ranks among 128,256 close logits
+        for tok in results[1].tokens:                        # the sampled row: among the best of the plain model (top_k = 40)
+            ref = plain.forward_logits(seq, w, pcfg)[-1]
+            assert tok in torch.topk(ref, near).indices.tolist()
+            seq.append(tok)

@@ -11,6 +11,12 @@ ones, without a change to any file of the package.
 * ``decay``: a toy position encoding that is no rotation (keys grow and queries shrink by a
   factor per position, so a score decays with distance); the attention part then keeps its
   separate encode-and-store step on every path.
+* ``sandwich`` and ``mixer_only``: block arrangements with other places than the built-in one
+  (a norm after the mixer; no feed-forward at all), declared by the block kinds themselves.
+* ``running_mean_on_device``: the stateful mixer written so that a step of single tokens can
+  be recorded and replayed (it reads its slots from the device), run through the entry point
+  with recorded steps; the host-loop variant says nothing about recording and is launched.
+* an embedding scale and a soft cap on the logits, from the toy architecture's config.
 """
 
 import os
@@ -26,7 +32,7 @@ from yalis_b200.config import registry
 from yalis_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from yalis_b200.ops.linear import linear
 from yalis_b200.ops.elementwise import rope_kv_write
-from yalis_b200.parts.base import FeedForward, Mixer, ParamSpec, PositionEncoding, SlotState, register_part
+from yalis_b200.parts.base import Block, FeedForward, Mixer, ParamSpec, PositionEncoding, SlotState, register_part
 
 pytestmark = pytest.mark.gpu
 
@@ -59,6 +65,47 @@ class RunningMean(Mixer):
             st[:-1] = sums[-1]
             st[-1] = counts[-1]
         return linear(out, self.w)
+
+
+class RunningMeanOnDevice(RunningMean):
+    """The same mixer, with steps of single tokens done by index operations over the device's slot array,
+    so that such a step can be recorded: nothing in it depends on the host's lists."""
+
+    def forward(self, x, ctx, cache):
+        if not ctx.decode_only:
+            return super().forward(x, ctx, cache)
+        slots = ctx.slots.long()                          # padding rows point to the state row that is nobody's
+        st = cache.state.index_select(0, slots)
+        sums = st[:, :-1] + x.float()
+        counts = st[:, -1:] + 1.0
+        cache.state.index_copy_(0, slots, torch.cat([sums, counts], dim=1))
+        return linear((sums / counts).to(x.dtype), self.w)
+
+    def capture_key(self, host):
+        return None
+
+
+class Sandwich(Block):
+    """x += after(mixer(norm_1(x))); x += feed_forward(norm_2(x)): a norm on the mixer's output."""
+
+    slots = {"position": "position", "norm_1": "norm", "mixer": "mixer", "after": "norm", "norm_2": "norm",
+             "feed_forward": "feed_forward"}
+
+    def forward(self, stream, ctx, cache):
+        y = self.mixer.forward(self.norm_1.forward(stream), ctx, cache)
+        if y.dim() == 3:                                  # partial sums of a split product
+            y = y.sum(0).to(stream.dtype)
+        stream.add(self.after.normalize(y))
+        stream.add(self.feed_forward.forward(self.norm_2.forward(stream), ctx))
+
+
+class MixerOnly(Block):
+    """x += mixer(norm_1(x)) and nothing else."""
+
+    slots = {"position": "position", "norm_1": "norm", "mixer": "mixer"}
+
+    def forward(self, stream, ctx, cache):
+        stream.add(self.mixer.forward(self.norm_1.forward(stream), ctx, cache))
 
 
 class Top1Experts(FeedForward):
@@ -146,30 +193,43 @@ class ToyArchitecture:
                 mixer = PartSpec("paged_attention", dict(attn.params, window=c["window"]))
                 names = dict(attn_names, **common)
             else:
-                mixer, names = PartSpec("running_mean", {"hidden_size": h}), dict({"mixer.mix": "mean.mix.weight"}, **common)
+                mixer, names = PartSpec(kind, {"hidden_size": h}), dict({"mixer.mix": "mean.mix.weight"}, **common)
             ff, pos = ffn, rot
             if c.get("ffs") and c["ffs"][i] == "routed":
                 ff = routed
                 names = dict({k: v for k, v in names.items() if not k.startswith("feed_forward.")}, **routed_names)
             if c.get("positions") and c["positions"][i] == "decay":
                 pos = decay
-            layers.append(LayerSpec(PartSpec("pre_norm_residual"), mixer, ff, norm, norm, pos, f"toy.{i}.", names))
+            parts = {"position": pos, "norm_1": norm, "mixer": mixer, "norm_2": norm, "feed_forward": ff}
+            block = c["blocks"][i] if c.get("blocks") else "pre_norm_residual"
+            if block == "sandwich":
+                parts["after"] = norm
+                names = dict(names, **{"after.weight": "after.weight"})
+            elif block == "mixer_only":
+                parts = {k: parts[k] for k in ("position", "norm_1", "mixer")}
+                names = {k: v for k, v in names.items() if k.split(".")[0] in parts}
+            layers.append(LayerSpec(PartSpec(block), parts, f"toy.{i}.", names))
         schedule = tuple(ScheduleEntry(l, c) for l, c in c["schedule"])
         return ModelSpec("ToyForCausalLM", h, c["vocab"], c["max_len"], tuple(layers), schedule, norm, "toy.embed.weight",
-                         "toy.head.weight", {"weight": "toy.norm.weight"})
+                         "toy.head.weight", {"weight": "toy.norm.weight"}, embedding_scale=c.get("embed_scale"),
+                         logit_softcap=c.get("softcap"))
 
 
 def setup_module(module):
     register_part("mixer", "running_mean", RunningMean, replace=True)
+    register_part("mixer", "running_mean_on_device", RunningMeanOnDevice, replace=True)
+    register_part("block", "sandwich", Sandwich, replace=True)
+    register_part("block", "mixer_only", MixerOnly, replace=True)
     register_part("feed_forward", "top1_experts", Top1Experts, replace=True)
     register_part("position", "decay", Decay, replace=True)
     registry.register_architecture("ToyForCausalLM", ToyArchitecture, replace=True)
 
 
-def toy_config(mixers, schedule, window=None, head_dim=8, ffs=None, positions=None):
+def toy_config(mixers, schedule, window=None, head_dim=8, ffs=None, positions=None, blocks=None, embed_scale=None,
+               softcap=None):
     return dict(architectures=["ToyForCausalLM"], width=40, heads=4, kv_heads=2, head_dim=head_dim, inner=56, vocab=97,
                 max_len=160, eps=1e-5, mixers=mixers, schedule=schedule, window=window, ffs=ffs, positions=positions,
-                torch_dtype="bfloat16")
+                blocks=blocks, embed_scale=embed_scale, softcap=softcap, torch_dtype="bfloat16")
 
 
 def plain_toy(tokens, w, c):
@@ -179,6 +239,8 @@ def plain_toy(tokens, w, c):
     t = len(tokens)
     pos = torch.arange(t)
     x = w["toy.embed.weight"][torch.tensor(tokens)]
+    if c.get("embed_scale"):
+        x = x * c["embed_scale"]
     kept = {}
     for idx, (layer, cache_of) in enumerate(c["schedule"]):
         p = f"toy.{layer}."
@@ -203,7 +265,12 @@ def plain_toy(tokens, w, c):
         else:
             means = torch.cumsum(h, dim=0) / torch.arange(1, t + 1)[:, None]
             y = means @ w[p + "mean.mix.weight"].T
+        block = c["blocks"][layer] if c.get("blocks") else "pre_norm_residual"
+        if block == "sandwich":
+            y = plain.rms_norm(y, w[p + "after.weight"], c["eps"])
         x = x + y
+        if block == "mixer_only":
+            continue
         h = plain.rms_norm(x, w[p + "n2.weight"], c["eps"])
         if c.get("ffs") and c["ffs"][layer] == "routed":
             choice = (h @ w[p + "ff.router.weight"].T).argmax(dim=-1)
@@ -214,7 +281,39 @@ def plain_toy(tokens, w, c):
             x = x + y
         else:
             x = x + plain.swiglu(h, w[p + "ff.gate.weight"], w[p + "ff.up.weight"], w[p + "ff.down.weight"])
-    return plain.rms_norm(x, w["toy.norm.weight"], c["eps"]) @ w["toy.head.weight"].T
+    logits = plain.rms_norm(x, w["toy.norm.weight"], c["eps"]) @ w["toy.head.weight"].T
+    if c.get("softcap"):
+        logits = c["softcap"] * torch.tanh(logits / c["softcap"])
+    return logits
+
+
+def replay_all_cuttings(c, seed, lengths, std, dtype, page_size=16, builds=None, graphs=False):
+    """The toy model of config ``c`` cut every way against ``plain_toy``; returns the replayers."""
+    from yalis_b200.engine.replay import Replayer
+    from yalis_b200.weights.loader import write_random_model
+    reps = []
+    with tempfile.TemporaryDirectory() as d:
+        write_random_model(c, d, seed=seed, std=std)
+        w = plain.read_weights(d)
+        g = torch.Generator().manual_seed(seed + 1)
+        requests = {f"r{i}": torch.randint(0, c["vocab"], (n,), generator=g).tolist() for i, n in enumerate(lengths)}
+        want = {rid: plain_toy(t, w, c).numpy() for rid, t in requests.items()}
+        for build in builds or (traces.whole, traces.tail_decoded, traces.portions, traces.mixed):
+            steps = traces.number(build(requests))
+            rep = Replayer(d, dtype, traces.peak_tokens(steps), page_size=page_size, max_live=4, graphs=graphs)
+            out = {}
+            for s in steps:
+                r = rep.run_step(s)
+                if r is not None:
+                    out[s["step"]] = r
+            got = traces.collect(steps, out, c["vocab"])
+            tol = 1e-4 if dtype == "float32" else 3e-2
+            for rid in want:
+                err = np.abs(got[rid] - want[rid]).max() / np.abs(want[rid]).max()
+                assert err < tol, (build.__name__, rid, err)
+            rep.engine.manager.check()
+            reps.append(rep)
+    return reps
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -237,7 +336,7 @@ def test_toy_model_steps_like_a_builtin(dtype, mixers, schedule):
             steps = traces.number(build(requests))
             rep = Replayer(d, dtype, traces.peak_tokens(steps), page_size=16, max_live=4)
             state_entries = [e for e in rep.engine.storage.entries if hasattr(e, "state")]
-            assert state_entries and all(e.state.shape[0] == 4 for e in state_entries)     # one row per slot
+            assert state_entries and all(e.state.shape[0] == 4 + 1 for e in state_entries)   # a row per slot and nobody's
             out = {}
             for s in steps:
                 r = rep.run_step(s)
@@ -327,3 +426,51 @@ def test_routed_feed_forward_and_another_position_encoding(dtype):
         if dtype == "bfloat16":
             took = {k: attn_ops.LAUNCHED[k] - before.get(k, 0) for k in attn_ops.LAUNCHED}
             assert took.get("decode_tma", 0) > 0 and took.get("decode_tma_fused", 0) > 0    # the decay layer, the rotary layer
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_other_block_arrangements_and_model_hooks(dtype):
+    """A layer with a norm after its mixer, a layer without a feed-forward, an embedding scale and a soft cap on
+    the logits: block kinds and config keys of this file only, cut every way (the steps of single tokens
+    both launched and replayed from recordings), against the plain model."""
+    c = toy_config(["attention", "running_mean_on_device", "attention"], [(0, None), (1, None), (2, None)],
+                   blocks=["sandwich", "mixer_only", "pre_norm_residual"], embed_scale=3.0, softcap=5.0)
+    std = 0.2 if dtype == "float32" else 0.05
+    for graphs in (False, True):
+        reps = replay_all_cuttings(c, 4, [50, 7, 90, 33, 64], std, dtype, graphs=graphs)
+        assert (sum(r.steps_replayed for r in reps) > 0) == graphs
+    from yalis_b200.parts.base import build_block
+    spec = ToyArchitecture.model_spec(c)
+    assert sorted(build_block(spec.layers[1]).parts) == ["mixer", "norm_1", "position"]
+    with pytest.raises(ValueError, match="feed_forward"):
+        build_block(LayerSpec(PartSpec("pre_norm_residual"), spec.layers[1].parts, "x.", {}))       # a place left empty
+    with pytest.raises(ValueError, match="after"):
+        build_block(LayerSpec(PartSpec("pre_norm_residual"), spec.layers[0].parts, "x.", {}))       # a place the block lacks
+
+
+@pytest.mark.parametrize("mixer, recorded", [("running_mean_on_device", True), ("running_mean", False)])
+def test_a_stateful_mixer_through_the_entry_point(mixer, recorded):
+    """Greedy generation with the toy architecture through ``LLMEngine``: more prompts than slots, so slots are
+    reused and their state must start from zero.  The mixer that reads its slots from the device has its decode
+    steps recorded and replayed (the first step of a recording runs twice and must not advance the state twice;
+    padding rows must not touch a request's state); the one that loops on the host says nothing about recording
+    and is launched step by step.  Both must give the plain model's tokens."""
+    from yalis_b200 import InferenceConfig, LLMEngine, ModelConfig
+    from yalis_b200.weights.loader import write_random_model
+    c = toy_config(["attention", mixer], [(0, None), (1, None)])
+    with tempfile.TemporaryDirectory() as d:
+        write_random_model(c, d, seed=6, std=0.3)
+        w = plain.read_weights(d)
+        g = torch.Generator().manual_seed(5)
+        prompts = [torch.randint(0, c["vocab"], (n,), generator=g).tolist() for n in (9, 30, 4, 17, 1)]
+        eng = LLMEngine(ModelConfig(model_name="toy", model_path=d, precision="fp32"),
+                        InferenceConfig(max_batch_size=3, max_length_of_generated_sequences=64, temperature=0.0, top_p=0.0,
+                                        page_size=16))
+        tokens, _ = eng.generate(prompts, tokens_to_generate=12)
+        for p, row in zip(prompts, tokens.tolist()):
+            seq = list(p)
+            for tok in row:
+                assert tok == int(plain_toy(seq, w, c)[-1].argmax())
+                seq.append(tok)
+        replays = sum(r.replays for r in eng.engine._recordings.values())
+        assert (replays > 0) == recorded

@@ -6,13 +6,18 @@ token-ids-out shortcut.  Importing the package touches neither CUDA nor the
 compiler; the native libraries are built at first use.
 """
 
+from yalis_b200.config.engine_config import EngineConfig
 from yalis_b200.config.runtime import InferenceConfig, ModelConfig
 
-__all__ = ["ModelConfig", "InferenceConfig", "LLMEngine", "generate", "Engine"]
+__all__ = ["ModelConfig", "InferenceConfig", "EngineConfig", "LLMEngine", "generate", "Generation", "Engine",
+           "SamplingParams"]
 
 
 def __getattr__(name):
-    if name in ("LLMEngine", "generate"):
+    if name == "SamplingParams":
+        from yalis_b200.sampling.sampler import SamplingParams
+        return SamplingParams
+    if name in ("LLMEngine", "generate", "Generation"):
         from yalis_b200.engine import llm_engine
         return getattr(llm_engine, name)
     if name == "Engine":

@@ -9,8 +9,8 @@ from typing import Callable, Dict, List
 import torch
 
 from yalis_b200.engine.engine import Engine, StepEntry
-from yalis_b200.ops.sampling import argmax
 from yalis_b200.parts.base import PagedKV
+from yalis_b200.sampling.sampler import GREEDY
 
 
 def model_numbers(engine: Engine) -> Dict[str, object]:
@@ -26,31 +26,25 @@ def model_numbers(engine: Engine) -> Dict[str, object]:
     for req, cache in zip(m.cache_requests(), engine.storage.entries):
         if isinstance(req, PagedKV) and getattr(cache, "writable", False):
             kv_per_token += 2 * req.num_kv_heads * req.head_dim * elt
-    matrix_params = 0
-    attn_dims: List[tuple] = []
+    matrix_flops = 0.0
+    mixers = []
     for entry in engine.spec.schedule:
         b = m.blocks[entry.layer]
-        for part in (b.mixer, b.feed_forward):
-            for ps in part.param_specs().values():
-                if len(ps.shape) == 2:
-                    matrix_params += ps.shape[0] * ps.shape[1]
-        req = b.mixer.cache_request()
-        if isinstance(req, PagedKV):
-            attn_dims.append((b.mixer.nh, req.head_dim))
+        matrix_flops += sum(part.matrix_flops_per_token() for part in b.parts.values())
+        mixers += [part for part in b.parts.values() if hasattr(part, "mixing_flops")]
     head_params = m.head.shape[0] * m.head.shape[1]
 
     def flops_prefill(tokens: int, logit_rows: int = 1) -> float:
-        linear = 2.0 * tokens * matrix_params
-        attn = sum(4.0 * nh * hs * tokens * (tokens + 1) / 2 for nh, hs in attn_dims)    # causal QK^T and PV
-        return linear + attn + 2.0 * logit_rows * head_params
+        """One prompt of ``tokens`` tokens from an empty cache, logits at ``logit_rows`` places."""
+        return tokens * matrix_flops + sum(mx.mixing_flops(tokens, 0) for mx in mixers) + 2.0 * logit_rows * head_params
 
     return {"weight_bytes_per_step": weight_bytes, "kv_bytes_per_token": kv_per_token, "flops_prefill": flops_prefill,
-            "matrix_params": matrix_params}
+            "matrix_flops_per_token": matrix_flops}
 
 
 class DecodeBench:
-    """``batch`` requests with ``prompt_len`` cached tokens each, decoded step by step through
-    the captured decode graph with device-side feedback of the chosen tokens (greedy)."""
+    """``batch`` requests with ``prompt_len`` cached tokens each, decoded step by step through the engine's
+    step function (recorded steps, greedy choice) with the chosen tokens fed back on the device."""
 
     def __init__(self, engine: Engine, batch: int, prompt_len: int, seed: int = 0, prefill_tokens_per_step: int = 2048):
         self.engine, self.batch, self.prompt_len, self.seed = engine, batch, prompt_len, seed
@@ -59,11 +53,11 @@ class DecodeBench:
         self.slots: List[int] = []
         self.steps_done = 0
         self.launches_per_step = 0
+        self.h2d_bytes_per_step = 0
 
     def prepare(self) -> None:
         eng = self.engine
         gen = torch.Generator().manual_seed(self.seed)
-        first = []
         for rid in self.ids:
             slot = eng.add_request(rid)
             if slot is None:
@@ -75,8 +69,8 @@ class DecodeBench:
         def flush():
             nonlocal group, group_tokens
             if group:
-                logits = eng.step([StepEntry(rid, p, [len(p) - 1]) for rid, p in group])
-                first.append(argmax(logits))
+                eng.run([StepEntry(rid, p, [len(p) - 1]) for rid, p in group], sampling=[GREEDY] * len(group),
+                        draws=[0] * len(group), keep_logits=False)
                 group, group_tokens = [], 0
 
         for rid, p in zip(self.ids, prompts):
@@ -85,17 +79,19 @@ class DecodeBench:
             group.append((rid, p))
             group_tokens += len(p)
         flush()
-        self.first_tokens = torch.cat(first).tolist()
-        # first decode step takes its tokens from the host; later ones from the device
-        self.engine.decoder.step(self.slots, tokens=self.first_tokens)
-        self.steps_done = 1
+        self._entries = [StepEntry(rid, None, [0]) for rid in self.ids]
+        self._greedy = [GREEDY] * self.batch
+        self.run(1)
 
     def run(self, steps: int) -> None:
-        dec = self.engine.decoder
-        for _ in range(steps):
-            b = dec.step(self.slots)
+        eng = self.engine
+        for i in range(steps):
+            eng.run_step(self.slots, self._entries, sampling=self._greedy, draws=[self.steps_done + i] * self.batch,
+                         graphs=True, keep_logits=False)
         self.steps_done += steps
-        self.launches_per_step = b.launches if steps else self.launches_per_step
+        if steps and eng.last_captured is not None:
+            self.launches_per_step = eng.last_captured.launches
+            self.h2d_bytes_per_step = eng.last_h2d_bytes
 
     def run_timed(self, steps: int) -> float:
         """Milliseconds of ``steps`` decode steps on the device (CUDA events, synchronised on both sides)."""
@@ -106,6 +102,7 @@ class DecodeBench:
         self.run(steps)
         end.record()
         torch.cuda.synchronize()
+        self.engine.check_device_errors()
         return start.elapsed_time(end)
 
     def mean_context(self, steps: int) -> float:

@@ -9,7 +9,8 @@ It owns no device memory: the pools that the pages index live in
   state tensor;
 * before a step runs, ``reserve(slot, new_len)`` maps pages so the slot can
   hold ``new_len`` tokens in every group; it returns False, changing nothing,
-  when some group has too few free pages;
+  when some group has too few free pages (``reserve_many`` does the same for
+  all requests of a step together);
 * after the step, ``commit(slot, new_len)`` records the length; groups with a
   window give back the pages that no later query can see;
 * ``release(slot)`` gives back all pages and the slot at once.
@@ -63,6 +64,7 @@ def _bind(lib: ctypes.CDLL) -> None:
         "ycm_acquire_slot": (c_int, [vp]),
         "ycm_pages_needed": (c_int, [vp, c_int, c_int, c_int]),
         "ycm_reserve": (c_int, [vp, c_int, c_int]),
+        "ycm_reserve_many": (c_int, [vp, c_int, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]),
         "ycm_commit": (c_int, [vp, c_int, c_int]),
         "ycm_release_slot": (c_int, [vp, c_int]),
         "ycm_table": (ctypes.POINTER(ctypes.c_int32), [vp, c_int]),
@@ -146,6 +148,22 @@ class CacheManager:
 
     def reserve(self, slot: int, new_len: int) -> bool:
         r = self._lib.ycm_reserve(self._h, slot, new_len)
+        if r == 0:
+            return True
+        if r == 1:
+            return False
+        raise CacheError(self._err())
+
+    def reserve_many(self, slots: Sequence[int], new_lens: Sequence[int]) -> bool:
+        """``reserve`` for all requests of a step: True and every slot has its pages, or False and nothing
+        has changed (slots must be distinct)."""
+        n = len(slots)
+        if n != len(new_lens):
+            raise CacheError("reserve_many: one length per slot")
+        if len(set(slots)) != n:
+            raise CacheError("reserve_many: a slot is named twice")
+        arr = (ctypes.c_int32 * n)
+        r = self._lib.ycm_reserve_many(self._h, n, arr(*[int(s) for s in slots]), arr(*[int(l) for l in new_lens]))
         if r == 0:
             return True
         if r == 1:

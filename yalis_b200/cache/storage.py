@@ -24,19 +24,45 @@ from .manager import PageGroup
 
 
 def group_name(request: PagedKV) -> str:
+    """Paged entries with the same retention rule share block tables (a page id means the same token range
+    in each of their pools); the rule is all a group is known by."""
     return "kv_all" if request.window is None else f"kv_window_{request.window}"
 
 
-def plan_groups(requests: List[Optional[object]], page_size: int, num_pages: int,
-                max_context: int) -> List[PageGroup]:
-    """One page group per distinct retention rule among the paged requests."""
+def group_page_bytes(requests: List[Optional[object]], cache_of: List[Optional[int]], page_size: int,
+                     element_size: int) -> Dict[str, int]:
+    """Bytes that one page id of each group stands for: the K and V pages of every schedule entry of the group
+    that keeps a cache of its own."""
+    out: Dict[str, int] = {}
+    for req, src in zip(requests, cache_of):
+        if isinstance(req, PagedKV) and src is None:
+            name = group_name(req)
+            out[name] = out.get(name, 0) + 2 * req.num_kv_heads * page_size * req.head_dim * element_size
+    return out
+
+
+def window_group_pages(window: int, page_size: int, max_slots: int, step_tokens: int) -> int:
+    """Pages a group with a window can have in use at once: per request the window, the tokens of the step that
+    is running (their pages are mapped before the step and those behind the window returned after it) and the
+    two partly used pages at the ends."""
+    return max_slots * (-(-(window + step_tokens) // page_size) + 2)
+
+
+def plan_groups(requests: List[Optional[object]], page_size: int, num_pages: int, max_context: int,
+                max_slots: Optional[int] = None, step_tokens: Optional[int] = None) -> List[PageGroup]:
+    """One page group per distinct retention rule among the paged requests.  ``num_pages`` is the pool of a
+    group that keeps every key; a group with a window gets no more pages than it can ever use
+    (``window_group_pages``) when ``max_slots`` and ``step_tokens`` are known."""
     groups: Dict[str, PageGroup] = {}
     width = -(-max_context // page_size)
     for r in requests:
         if isinstance(r, PagedKV):
             name = group_name(r)
             if name not in groups:
-                groups[name] = PageGroup(name, page_size, num_pages, r.window, width)
+                pages = num_pages
+                if r.window is not None and max_slots is not None and step_tokens is not None:
+                    pages = min(pages, window_group_pages(r.window, page_size, max_slots, min(step_tokens, max_context)))
+                groups[name] = PageGroup(name, page_size, pages, r.window, width)
     return list(groups.values())
 
 
@@ -71,7 +97,8 @@ class CacheStorage:
                 self.bytes += 2 * k.numel() * k.element_size()
                 self.entries.append(PagedKVCache(k, v, g.name))
             elif isinstance(req, SlotState):
-                st = torch.zeros((max_slots,) + tuple(req.shape), dtype=req.dtype, device=device)
+                # one row more than there are slots: the row that padding rows of a recorded step point to
+                st = torch.zeros((max_slots + 1,) + tuple(req.shape), dtype=req.dtype, device=device)
                 self.bytes += st.numel() * st.element_size()
                 self.state_tensors.append(st)
                 self.entries.append(SlotStateCache(st))
@@ -82,3 +109,11 @@ class CacheStorage:
         """Zero the per-request state of a newly admitted request."""
         for st in self.state_tensors:
             st[slot].zero_()
+
+    def snapshot_state(self) -> List[torch.Tensor]:
+        """Copies of all per-request state (for a trial run whose effects must not stay)."""
+        return [st.clone() for st in self.state_tensors]
+
+    def restore_state(self, saved: List[torch.Tensor]) -> None:
+        for st, old in zip(self.state_tensors, saved):
+            st.copy_(old)

@@ -50,6 +50,10 @@ def build_parser() -> argparse.ArgumentParser:
     e = ap.add_argument_group("engine")
     e.add_argument("--page-size", type=int, default=64)
     e.add_argument("--cache-tokens", type=int, default=None, help="size of the page pool in tokens")
+    e.add_argument("--num-pages", type=int, default=None, help="size of the page pool in pages")
+    e.add_argument("--memory-fraction", type=float, default=None,
+                   help="size of the page pool as a share of the device memory free after loading")
+    e.add_argument("--no-graphs", action="store_true", help="launch every step kernel by kernel")
     e.add_argument("--max-tokens-per-step", type=int, default=2048)
     e.add_argument("--chunk", "--prefill-chunk", dest="prefill_chunk", type=int, default=None)
     p = ap.add_argument_group("prompts")
@@ -86,6 +90,7 @@ def main(argv=None) -> int:
     inference_config = InferenceConfig(
         max_batch_size=args.max_batch_size, max_length_of_generated_sequences=args.max_length, top_k=args.top_k,
         top_p=args.top_p, temperature=args.temperature, page_size=args.page_size, cache_tokens=args.cache_tokens,
+        num_pages=args.num_pages, memory_fraction=args.memory_fraction, use_graphs=not args.no_graphs,
         max_tokens_per_step=args.max_tokens_per_step, prefill_chunk=args.prefill_chunk, seed=args.sampling_seed)
     engine = LLMEngine(model_config=model_config, inference_config=inference_config)
 

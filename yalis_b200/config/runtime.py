@@ -1,137 +1,110 @@
-"""``ModelConfig`` and ``InferenceConfig``: the reference's two user-facing
-configuration classes (yalis/config.py:8-228), with the same option names and
-meanings where this engine has the option, and the engine's own knobs beside
-them.  Architectural numbers never live here: they come from config.json.
+"""``ModelConfig`` and ``InferenceConfig``: what a user of the reference passes to
+``LLMEngine`` (yalis/config.py:8-228), kept by name so that such code carries
+over, and turned into this engine's own ``EngineConfig`` before anything runs.
+
+Only options that mean something on one GPU with a paged cache exist here.  The
+reference's options for spreading a model over GPUs or choosing among its
+attention libraries are gone, not ignored: passing one is a ``TypeError`` like
+any unknown keyword.  ``attention_backend`` and ``use_paged_kv_caching`` are
+accepted at the one value that describes this engine, because the reference's
+examples pass them.
 """
 
 from __future__ import annotations
 
 import os
-from typing import Literal, Optional, Tuple
+from typing import Optional
 
+from .engine_config import EngineConfig
 from .presets import PRESETS
 
 
 class ModelConfig:
-    """Which model to run and in which precision.
+    """Which model, where it lies, in which precision.
 
-    ``model_name``: a name for messages, or a preset name (``Llama-3-8B`` ...)
-    when ``random_weights`` is set.  ``model_path``: folder with config.json
-    and model.safetensors; as in the reference it defaults to
-    ``$YALIS_CACHE/checkpoints/<model_name>`` (yalis/config.py:52-58) and must
-    exist.  ``precision``: ``bf16`` (default) or ``fp32`` (the true 32-bit
-    path); the reference's ``fp16`` is refused because weights are kept in
-    bfloat16.  ``random_weights``: build the named preset with seeded random
-    weights on the device instead of reading a folder.
+    ``model_path``: a folder with config.json and model.safetensors; without it the folder is
+    ``$YALIS_CACHE/checkpoints/<model_name>`` (``~/.cache/yalis`` when the variable is unset), the
+    reference's place (yalis/config.py:52-58).  ``precision``: ``bf16`` or ``fp32`` (the true 32-bit path).
+    ``random_weights``: no folder; ``model_name`` is a preset and the weights are drawn on the device from
+    ``seed``.
     """
 
-    def __init__(self, model_name: Optional[str] = None, model_path: Optional[str] = None,
-                 precision: Literal["fp32", "bf16"] = "bf16", disable_tp: bool = True,
+    def __init__(self, model_name: Optional[str] = None, model_path: Optional[str] = None, precision: str = "bf16",
                  random_weights: bool = False, seed: int = 0):
-        self.model_name = model_name
-        self.model_path = model_path
-        self.precision = precision
-        self.disable_tp = disable_tp
-        self.random_weights = random_weights
-        self.seed = seed
-        self._validate()
-        if not random_weights:
-            self.model_path = self._resolve_model_path(model_path)
-
-    def _resolve_model_path(self, model_path: Optional[str]) -> str:
-        if model_path is None:
-            cache_dir = os.getenv("YALIS_CACHE", "~/.cache/yalis/")
-            model_path = os.path.join(os.path.expanduser(cache_dir), "checkpoints", self.model_name)
-        if not os.path.exists(model_path):
-            raise ValueError(f"Model path does not exist: {model_path}")
-        return model_path
-
-    def _validate(self) -> None:
-        if self.model_path is None and self.model_name is None:
-            raise ValueError("Either 'model_name' or 'model_path' must be provided.")
-        if self.precision == "fp16":
-            raise ValueError("Invalid precision: fp16. This engine keeps weights in bfloat16; use 'bf16' or 'fp32'.")
-        if self.precision not in {"fp32", "bf16"}:
-            raise ValueError(f"Invalid precision: {self.precision}. Supported values are 'fp32', 'bf16'.")
-        if self.random_weights and self.model_name not in PRESETS:
-            raise ValueError(f"random_weights needs a preset name, one of: {', '.join(sorted(PRESETS))}")
+        if model_name is None and model_path is None:
+            raise ValueError("ModelConfig: name a model (model_name) or a folder (model_path)")
+        if precision == "fp16":
+            raise ValueError("ModelConfig: precision fp16 is not offered, weights are held in bfloat16; use bf16 or fp32")
+        if precision not in ("bf16", "fp32"):
+            raise ValueError(f"ModelConfig: precision {precision!r} is neither bf16 nor fp32")
+        if random_weights and model_name not in PRESETS:
+            raise ValueError(f"ModelConfig: random_weights wants a preset as model_name ({', '.join(sorted(PRESETS))})")
+        self.model_name, self.precision, self.random_weights, self.seed = model_name, precision, random_weights, seed
+        if random_weights:
+            self.model_path = None
+        else:
+            if model_path is None:
+                root = os.path.expanduser(os.getenv("YALIS_CACHE", "~/.cache/yalis/"))
+                model_path = os.path.join(root, "checkpoints", model_name)
+            if not os.path.isdir(model_path):
+                raise ValueError(f"ModelConfig: no model folder at {model_path}")
+            self.model_path = model_path
 
     def __repr__(self) -> str:
-        return (f"ModelConfig(model_name={self.model_name}, model_path={self.model_path}, "
-                f"precision={self.precision})")
+        where = "random weights" if self.random_weights else self.model_path
+        return f"ModelConfig({self.model_name or ''} at {where}, {self.precision})"
 
 
 class InferenceConfig:
-    """Generation limits, sampling options and the engine's memory and batching knobs.
+    """Limits and defaults of generation, and the engine's memory and batching knobs.
 
-    Options of the reference kept with their meaning (yalis/config.py:93-158):
-    ``max_batch_size`` (most requests alive at once), ``max_length_of_generated_sequences``
-    (most tokens a request may hold, prompt included; stored as ``max_length``),
-    ``top_k``, ``top_p``, ``temperature``, ``metrics``.  Options that choose among the
-    reference's backends or spread the model over GPUs are accepted only at the values
-    that describe this engine: one GPU, its own paged attention kernels.
-
-    Own options: ``page_size`` (tokens per cache page), ``cache_tokens`` (size of the page
-    pool; default ``max_batch_size * max_length``), ``max_tokens_per_step`` (token budget
-    of one step), ``prefill_chunk`` (largest portion of one prompt in a step), ``seed``.
+    From the reference, with its meaning (yalis/config.py:93-158): ``max_batch_size`` (most requests alive at
+    once), ``max_length_of_generated_sequences`` (most tokens a request may hold, prompt included; kept as
+    ``max_length``), ``top_k``, ``top_p``, ``temperature`` (defaults of requests that bring no sampling
+    parameters of their own), ``metrics``.  This engine's own: ``page_size``; the pool as one of ``num_pages``,
+    ``cache_tokens`` or ``memory_fraction`` (default: ``max_batch_size * max_length`` tokens);
+    ``max_tokens_per_step``; ``prefill_chunk``; ``seed`` (of the draws); ``use_graphs``.
     """
 
     def __init__(self, max_batch_size: int = 1, max_length_of_generated_sequences: int = 1024,
                  top_k: Optional[int] = None, top_p: Optional[float] = 1.0, temperature: Optional[float] = 1.0,
-                 metrics: bool = False, tp_dims: Optional[Tuple[int, int, int]] = None,
-                 attention_backend: str = "paged", use_intra_head_parallelism: bool = False,
-                 use_paged_kv_caching: bool = True, prestore_kv_cache: bool = True,
-                 symmetric_allreduce_strategy: Optional[str] = None,
-                 page_size: int = 64, cache_tokens: Optional[int] = None, max_tokens_per_step: int = 2048,
-                 prefill_chunk: Optional[int] = None, seed: int = 1234):
+                 metrics: bool = False, attention_backend: Optional[str] = None, use_paged_kv_caching: bool = True,
+                 page_size: int = 64, num_pages: Optional[int] = None, cache_tokens: Optional[int] = None,
+                 memory_fraction: Optional[float] = None, max_tokens_per_step: int = 2048,
+                 prefill_chunk: Optional[int] = None, seed: int = 1234, use_graphs: bool = True):
+        if attention_backend not in (None, "paged"):
+            raise ValueError(f"InferenceConfig: attention_backend {attention_backend!r} selects nothing here; the engine "
+                             "has one attention path, its own paged kernels (leave the option out or pass 'paged')")
+        if not use_paged_kv_caching:
+            raise ValueError("InferenceConfig: the cache is paged; use_paged_kv_caching cannot be switched off")
+        if isinstance(max_length_of_generated_sequences, bool) or not isinstance(max_length_of_generated_sequences, int) \
+                or max_length_of_generated_sequences < 1:
+            raise ValueError("InferenceConfig: max_length_of_generated_sequences counts tokens, at least 1")
         self.max_batch_size = max_batch_size
         self.max_length = max_length_of_generated_sequences
-        self.temperature = temperature
-        self.top_k = top_k
-        self.top_p = top_p
+        self.top_k, self.top_p, self.temperature = top_k, top_p, temperature
         self.metrics = metrics
-        self.tp_dims = tp_dims
-        self.attention_backend = attention_backend
-        self.use_intra_head_parallelism = use_intra_head_parallelism
-        self.use_paged_kv_caching = use_paged_kv_caching
-        self.prestore_kv_cache = prestore_kv_cache
-        self.symmetric_allreduce_strategy = symmetric_allreduce_strategy
-        self.page_size = page_size
-        self.cache_tokens = cache_tokens
-        self.max_tokens_per_step = max_tokens_per_step
-        self.prefill_chunk = prefill_chunk
-        self.seed = seed
-        self._validate()
+        self.page_size, self.num_pages, self.cache_tokens, self.memory_fraction = page_size, num_pages, cache_tokens, memory_fraction
+        self.max_tokens_per_step, self.prefill_chunk = max_tokens_per_step, prefill_chunk
+        self.seed, self.use_graphs = seed, use_graphs
+        self.default_sampling()          # validates the three sampling numbers
+        self.engine_config("bf16")       # validates the rest
 
-    def _validate(self) -> None:
-        if self.max_batch_size <= 0:
-            raise ValueError("max_batch_size must be a positive integer.")
-        if self.max_length <= 0:
-            raise ValueError("max_length must be a positive integer.")
-        if self.temperature is not None and self.temperature < 0.0:
-            raise ValueError("temperature must be >=0.0.")
-        if self.top_k is not None and self.top_k <= 0:
-            raise ValueError("top_k must be a positive integer.")
-        if self.top_p is not None and (self.top_p < 0.0 or self.top_p > 1.0):
-            raise ValueError("top_p must be in the range [0.0, 1.0].")
-        if self.tp_dims is not None and tuple(self.tp_dims) != (1, 1, 1):
-            raise ValueError("tp_dims: this engine runs on one GPU; leave it None or (1, 1, 1).")
-        if self.attention_backend not in ("paged", "flash", "sdpa", "flex"):
-            raise ValueError(f"Invalid attention backend: {self.attention_backend}.")
-        if self.use_intra_head_parallelism:
-            raise ValueError("use_intra_head_parallelism splits heads over GPUs; this engine runs on one GPU.")
-        if not self.use_paged_kv_caching:
-            raise ValueError("use_paged_kv_caching=False: this engine's cache is always paged.")
-        if self.symmetric_allreduce_strategy is not None:
-            raise ValueError("symmetric_allreduce_strategy applies to several GPUs; this engine runs on one GPU.")
-        if self.page_size <= 0 or self.max_tokens_per_step <= 0:
-            raise ValueError("page_size and max_tokens_per_step must be positive integers.")
-        if self.prefill_chunk is not None and self.prefill_chunk <= 0:
-            raise ValueError("prefill_chunk must be a positive integer.")
-        if self.cache_tokens is not None and self.cache_tokens <= 0:
-            raise ValueError("cache_tokens must be a positive integer.")
+    def default_sampling(self, seed: Optional[int] = None):
+        """The sampling parameters of a request that brings none."""
+        from yalis_b200.sampling.sampler import SamplingParams
+        return SamplingParams(temperature=1.0 if self.temperature is None else self.temperature, top_k=self.top_k,
+                              top_p=1.0 if self.top_p is None else self.top_p, seed=self.seed if seed is None else seed)
+
+    def engine_config(self, precision: str, max_context: Optional[int] = None, device: str = "cuda:0") -> EngineConfig:
+        pool = dict(num_pages=self.num_pages, cache_tokens=self.cache_tokens, memory_fraction=self.memory_fraction)
+        if all(v is None for v in pool.values()):
+            pool["cache_tokens"] = self.max_batch_size * self.max_length
+        return EngineConfig(dtype=precision, page_size=self.page_size, max_slots=self.max_batch_size,
+                            max_tokens_per_step=self.max_tokens_per_step, prefill_chunk=self.prefill_chunk,
+                            max_context=max_context or self.max_length, use_graphs=self.use_graphs, device=device, **pool)
 
     def __repr__(self) -> str:
-        keys = ("max_batch_size", "max_length", "top_k", "top_p", "temperature", "metrics", "page_size",
-                "cache_tokens", "max_tokens_per_step", "prefill_chunk", "seed")
-        return "InferenceConfig(\n" + "".join(f"  {k}={getattr(self, k)},\n" for k in keys) + ")"
+        shown = ("max_batch_size", "max_length", "top_k", "top_p", "temperature", "page_size", "num_pages", "cache_tokens",
+                 "memory_fraction", "max_tokens_per_step", "prefill_chunk", "seed", "use_graphs")
+        return "InferenceConfig(" + ", ".join(f"{k}={getattr(self, k)!r}" for k in shown) + ")"

@@ -2,8 +2,9 @@
 
 A model is data.  ``ModelSpec`` lists the layers; each ``LayerSpec`` names, by
 kind and parameters, the block arrangement and the parts inside it (mixer,
-feed-forward, norms, position encoding).  Kinds are looked up in the part
-registry (``yalis_b200.parts.registry``) when the model is built, so different
+feed-forward, norms, position encoding; which of them a layer has is decided
+by its block kind).  Kinds are looked up in the part
+registry (``yalis_b200.parts.base``) when the model is built, so different
 layers may use different mixers and feed-forwards, and a kind defined outside
 the package works like a built-in one.
 
@@ -37,20 +38,21 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: the block arrangement and its parts.
+    """One layer: the block arrangement and the parts it is made of.
+
+    ``parts`` maps the names of the block's places (for the pre-norm block:
+    ``norm_1``, ``mixer``, ``norm_2``, ``feed_forward``, ``position``) to the
+    part that fills each.  Which places exist is the block kind's business
+    (``Block.slots``): another arrangement may have a norm after the mixer, one
+    norm for both branches, or no feed-forward at all.
 
     ``weight_prefix`` is where this layer's tensors live in the checkpoint
-    (for instance ``model.layers.3.``); ``weight_names`` maps ``"<part>.<param>"``
-    (part in mixer / feed_forward / norm_1 / norm_2) to the tensor name under
-    that prefix.
+    (for instance ``model.layers.3.``); ``weight_names`` maps
+    ``"<place>.<param>"`` to the tensor name under that prefix.
     """
 
     block: PartSpec
-    mixer: PartSpec
-    feed_forward: PartSpec
-    norm_1: PartSpec
-    norm_2: PartSpec
-    position: PartSpec
+    parts: Mapping[str, PartSpec]
     weight_prefix: str
     weight_names: Mapping[str, str]
 
@@ -78,6 +80,8 @@ class ModelSpec:
     final_norm_names: Mapping[str, str]  # "<param>" -> tensor name
     eos_token_id: Optional[int] = None
     bos_token_id: Optional[int] = None
+    embedding_scale: Optional[float] = None   # token rows are multiplied by it as they enter the stream (None: not)
+    logit_softcap: Optional[float] = None     # logits become cap * tanh(logits / cap) (None: not)
 
     def __post_init__(self):
         for i, e in enumerate(self.schedule):

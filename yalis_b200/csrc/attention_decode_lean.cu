@@ -208,7 +208,7 @@ decode_attention_lean_kernel(const __grid_constant__ CUtensorMap map_k, const __
           const int pi = key0 / p.page_size + i;
           int page = pi < p.table_width ? bt[pi] : -1;
           if (page < 0 || page >= p.num_pages) {   // a visible key without a page: a caller's bug
-            if (p.error) atomicExch(p.error, 1);
+            if (p.error) atomicOr(p.error, YALIS_FLAG_BAD_PAGE);
             page = 0;
           }
           const int y = (page * p.g + sg.kvh) * p.page_size;
@@ -467,7 +467,7 @@ decode_attention_lean_kernel(const __grid_constant__ CUtensorMap map_k, const __
   // ---- exit: on an abort wait (bounded) for copies in flight so none lands after the block ---
   __syncthreads();
   if (*abort_flag && threadIdx.x == CWARPS * 32) {
-    if (p.error) atomicExch(p.error, 1);
+    if (p.error) atomicOr(p.error, YALIS_FLAG_WAIT_ATTENTION);
     for (int it = max(0, armed - NST); it < armed; ++it) {
       const int s = it % NST;
       const uint32_t ph = (it / NST) & 1;

@@ -144,7 +144,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       const int pi = key0 / p.page_size + i;
       int page = pi < p.table_width ? bt[pi] : -1;
       if (page < 0 || page >= p.num_pages) {   // a visible key without a page: a caller's bug
-        if (p.error) atomicExch(p.error, 1);
+        if (p.error) atomicOr(p.error, YALIS_FLAG_BAD_PAGE);
         page = 0;
       }
       const int y = (page * p.g + kvh) * p.page_size;
@@ -273,7 +273,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       const int pi = pos / p.page_size;
       int page = pi < p.table_width ? bt[pi] : -1;
       if (page < 0 || page >= p.num_pages) {
-        if (threadIdx.x == 0 && p.error) atomicExch(p.error, 1);
+        if (threadIdx.x == 0 && p.error) atomicOr(p.error, YALIS_FLAG_BAD_PAGE);
       } else {
         const size_t at = (((size_t)page * p.g + kvh) * p.page_size + (pos - pi * p.page_size)) * HS;
         for (int c = threadIdx.x; c < 2 * (HS / 8); c += CWARPS * 32) {
@@ -555,7 +555,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   // ---- exit: on an abort wait (bounded) for copies in flight so none lands after the block ---
   __syncthreads();
   if (*abort_flag && threadIdx.x == CWARPS * 32) {
-    if (p.error) atomicExch(p.error, 1);
+    if (p.error) atomicOr(p.error, YALIS_FLAG_WAIT_ATTENTION);
     for (int it = max(0, armed - STAGES); it < armed; ++it) {
       const int s = it % STAGES;
       const uint32_t ph = (it / STAGES) & 1;

@@ -295,7 +295,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
           const int pi = key / p.page_size;
           int page = pi < p.table_width ? bt[pi] : -1;
           if (page < 0 || page >= p.num_pages) {
-            if (p.error) atomicExch(p.error, 1);
+            if (p.error) atomicOr(p.error, YALIS_FLAG_BAD_PAGE);
             page = 0;
           }
           const int y = (page * p.g + kvh) * p.page_size + (key - pi * p.page_size);
@@ -500,7 +500,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   __syncthreads();
   if (*abort_flag) {
     if (threadIdx.x == 4 * 32) {
-      if (p.error) atomicExch(p.error, 1);
+      if (p.error) atomicOr(p.error, YALIS_FLAG_WAIT_ATTENTION);
       for (uint32_t i = 0; i < kSpinLimit; ++i)
         if (mbar_try_wait(q_full, 0)) break;
       for (int j = max(0, k_armed - 2); j < k_armed; ++j)

@@ -19,6 +19,15 @@ enum : int {
   YALIS_ERR_ALIGN = -4,      // a pointer or stride not aligned as the kernel needs
 };
 
+// Bits of the device error word (one int32 per engine).  Kernels never trap: what they cannot do they skip,
+// raise a bit here with atomicOr and return; the host reads the word where it synchronises anyway.
+enum : int {
+  YALIS_FLAG_BAD_ID = 1,          // a token id outside the vocabulary (its embedding row was zeroed)
+  YALIS_FLAG_BAD_PAGE = 2,        // a block-table entry outside the pool (the token was skipped)
+  YALIS_FLAG_WAIT_ATTENTION = 4,  // a bounded wait of an attention kernel ran out (its block gave up)
+  YALIS_FLAG_WAIT_PRODUCT = 8,    // a bounded wait of the weight-streaming product ran out
+};
+
 inline int yalis_launch_status() {
   return cudaGetLastError() == cudaSuccess ? YALIS_OK : YALIS_ERR_LAUNCH;
 }

@@ -14,32 +14,64 @@ YALIS_API void yalis_set_pdl(int enabled) { g_pdl_enabled = enabled != 0; }
 // --------------------------------------------------------------------------
 // Embedding: out[t, :] = float(table[ids[t], :])      (yalis/external/model.py:137)
 // The residual stream is float32 whatever the weight type.
-// A token id outside [0, vocab) yields a row of zeros and raises *bad_id.
+// A token id outside [0, vocab) yields a row of zeros and raises YALIS_FLAG_BAD_ID in *bad_id.
+// `scale` multiplies every value in float32 (1 for models that do not scale their embeddings).
+// With `from_slot`, a token whose entry there is not negative takes its id from chosen[from_slot[t]] instead of
+// ids[t]: the token that an earlier step chose for that request and left on the device.
 // --------------------------------------------------------------------------
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids,
-                                 float* __restrict__ out, int width, int vocab, int32_t* bad_id) {
+                                 const int32_t* __restrict__ from_slot, const int32_t* __restrict__ chosen,
+                                 float* __restrict__ out, int width, int vocab, float scale, int32_t* bad_id) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
-  const int id = ids[t];
+  int id = ids[t];
+  if (from_slot != nullptr) {
+    const int s = from_slot[t];
+    if (s >= 0) id = chosen[s];
+  }
   float* o = out + (size_t)t * width;
   if (id < 0 || id >= vocab) {
     for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = 0.f;
-    if (threadIdx.x == 0 && bad_id) atomicExch(bad_id, 1);
+    if (threadIdx.x == 0 && bad_id) atomicOr(bad_id, YALIS_FLAG_BAD_ID);
     return;
   }
   const T* row = table + (size_t)id * width;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = to_f32<T>(row[c]);
+  if (scale == 1.0f) {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = to_f32<T>(row[c]);
+  } else {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = to_f32<T>(row[c]) * scale;
+  }
 }
 
-YALIS_API int yalis_embedding(const void* table, int dtype, const int32_t* ids, float* out, int n_tokens,
-                              int width, int vocab, int32_t* bad_id, cudaStream_t stream) {
+YALIS_API int yalis_embedding(const void* table, int dtype, const int32_t* ids, const int32_t* from_slot,
+                              const int32_t* chosen, float* out, int n_tokens, int width, int vocab, float scale,
+                              int32_t* bad_id, cudaStream_t stream) {
   if (n_tokens <= 0) return YALIS_OK;
+  if ((from_slot == nullptr) != (chosen == nullptr)) return YALIS_ERR_SHAPE;
   YALIS_DISPATCH_DTYPE(dtype, T,
                        return yalis_launch(embedding_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)table,
-                                           ids, out, width, vocab, bad_id));
+                                           ids, from_slot, chosen, out, width, vocab, scale, bad_id));
   return YALIS_OK;
+}
+
+// --------------------------------------------------------------------------
+// Soft cap of float32 logits in place: v <- cap * tanh(v / cap).
+// --------------------------------------------------------------------------
+__global__ void softcap_kernel(float* __restrict__ v, size_t n, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const float inv = 1.0f / cap;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    v[i] = cap * tanhf(v[i] * inv);
+}
+
+YALIS_API int yalis_softcap_f32(float* v, long long n, float cap, cudaStream_t stream) {
+  if (n <= 0) return YALIS_OK;
+  if (!(cap > 0.f)) return YALIS_ERR_SHAPE;
+  const int blocks = (int)((n + 1023) / 1024 < 2048 ? (n + 1023) / 1024 : 2048);
+  return yalis_launch(softcap_kernel, dim3(blocks), dim3(256), 0, stream, v, (size_t)n, cap);
 }
 
 // --------------------------------------------------------------------------
@@ -342,7 +374,7 @@ __global__ void rope_kv_write_kernel(const TS* __restrict__ src, int src_stride,
     const int page_idx = pos / page_size;
     const int page = (page_idx < table_width) ? block_table[(size_t)req * table_width + page_idx] : -1;
     if (page < 0 || page >= num_pages) {
-      if (threadIdx.x == 0 && bad_page) atomicExch(bad_page, 1);
+      if (threadIdx.x == 0 && bad_page) atomicOr(bad_page, YALIS_FLAG_BAD_PAGE);
       return;
     }
     const int kvh = is_v ? head - nh - g : head - nh;
@@ -395,7 +427,7 @@ __global__ void rope_kv_write_token_kernel(const TS* __restrict__ src, int src_s
     off = pos - page_idx * page_size;
     page = (page_idx < table_width) ? block_table[(size_t)req * table_width + page_idx] : -1;
     if (page < 0 || page >= num_pages) {
-      if (threadIdx.x == 0 && bad_page) atomicExch(bad_page, 1);
+      if (threadIdx.x == 0 && bad_page) atomicOr(bad_page, YALIS_FLAG_BAD_PAGE);
       page = -1;
     }
   }
@@ -458,7 +490,7 @@ __global__ void rope_kv_write_token_vec_kernel(const TS* __restrict__ src, int s
     off = pos - page_idx * page_size;
     page = (page_idx < table_width) ? block_table[(size_t)req * table_width + page_idx] : -1;
     if (page < 0 || page >= num_pages) {
-      if (threadIdx.x == 0 && bad_page) atomicExch(bad_page, 1);
+      if (threadIdx.x == 0 && bad_page) atomicOr(bad_page, YALIS_FLAG_BAD_PAGE);
       page = -1;
     }
   }
@@ -638,4 +670,17 @@ YALIS_API int yalis_gather_rows_f32(const float* x, const int32_t* rows, float* 
                                     cudaStream_t stream) {
   if (n_rows <= 0) return YALIS_OK;
   return yalis_launch(gather_rows_kernel, dim3(n_rows), dim3(256), 0, stream, x, rows, out, width);
+}
+
+// --------------------------------------------------------------------------
+// rows x width_bytes from pinned host memory to the device, both with a row pitch: the columns in use of a
+// block table whose rows are wider (one strided copy instead of one per row).
+// --------------------------------------------------------------------------
+YALIS_API int yalis_copy_rows_h2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                                  size_t rows, cudaStream_t stream) {
+  if (rows == 0 || width_bytes == 0) return YALIS_OK;
+  if (width_bytes > dst_pitch || width_bytes > src_pitch) return YALIS_ERR_SHAPE;
+  return cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyHostToDevice, stream) == cudaSuccess
+             ? YALIS_OK
+             : YALIS_ERR_LAUNCH;
 }

@@ -25,6 +25,9 @@
 // tensor memory is freed and the block returns.
 #include <cuda.h>
 
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
 
 namespace {
@@ -34,7 +37,6 @@ constexpr int TILE_K = 64;       // bfloat16 elements per stage along K: one 128
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;    // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
 constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr int kSMs = 148;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -128,7 +130,7 @@ struct GemmParams {
   int splits;
   int kt_per_split;     // stage steps (of 64 or 128 columns of K) per split
   int silu_inter;       // 0, or I: w is [gate (I rows); up (I rows)] and out[m, i] = silu(gate_i) * up_i, [M, I] bfloat16
-  int32_t* error;       // set to 1 if a wait ran out
+  int32_t* error;       // YALIS_FLAG_WAIT_PRODUCT is raised in it if a wait ran out
 };
 
 // Ring depth. A stage is 16 KB of W plus NTOK * 128 bytes of x.  Two blocks fit an SM with ~95 KB each, so that
@@ -364,7 +366,7 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   __syncthreads();
   if (*abort_flag) {
     if (threadIdx.x == 0) {
-      atomicExch(p.error, 1);
+      atomicOr(p.error, YALIS_FLAG_WAIT_PRODUCT);
       // Wait (bounded) for every TMA transaction this block started, so none lands after exit.
       for (int kt = max(0, armed - STAGES); kt < armed; ++kt) {
         const int s = kt % STAGES;
@@ -381,6 +383,19 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 }
 
 // ---- host side ------------------------------------------------------------------------------
+
+// Streaming multiprocessors of the current device (asked of the driver once per device).
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -401,16 +416,52 @@ EncodeTiledFn encode_fn() {
 
 // A 2-D bfloat16 matrix [rows, K] with row stride ld (elements), boxes of [box_rows, 64], 128-byte swizzle,
 // out-of-range elements read as zero.
+// Encoded maps are kept by what they describe: a step asks for the same few hundred (matrix, box) pairs again and
+// again (weights never move, and the allocator hands activations the same addresses step after step), and one
+// encoding costs the host more than the launch it serves.  A map describes addresses and shapes only, never
+// contents, so a kept one stays valid while its key repeats.
+struct MapKey {
+  const void* ptr;
+  long long rows, K, ld;
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && K == o.K && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+    h ^= (size_t)k.rows * 0xC2B2AE3D27D4EB4Full + (size_t)k.K * 0x165667B19E3779F9ull + (size_t)k.ld * 31 + (size_t)k.box_rows;
+    return h;
+  }
+};
+
 bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, long long ld, int box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> kept;
+  const MapKey key{ptr, rows, K, ld, box_rows};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = kept.find(key);
+    if (it != kept.end()) {
+      *map = it->second;
+      return true;
+    }
+  }
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return false;
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (kept.size() >= 8192) kept.clear();
+  kept.emplace(key, *map);
+  return true;
 }
 
 template <int NTOK, bool SILU>
@@ -446,19 +497,20 @@ YALIS_API int yalis_gemm_wstream_splits(int N, int K) {
   const int kt = (K + TILE_K - 1) / TILE_K;
   int best = 1;
   double best_cost = 1e30;
+  const int sms = sm_count();
   for (int s = 1; s <= 16; ++s) {
     if (s > 1 && kt / s < 8) break;
     const int blocks = tiles * s;
     double cost;
-    if (blocks <= 2 * kSMs) {
+    if (blocks <= 2 * sms) {
       // A grid keeps HBM busy from about one and a half blocks per SM on (a block alone on an SM has only its own
       // five tiles in flight); measured on the decode shapes of Llama-3-8B, where 7 / 5 / 7 splits for the down, QKV
       // and attention-output products beat 5 / 3 / 5 by 2 % of a step.
-      const int full = kSMs + kSMs / 2;
+      const int full = sms + sms / 2;
       cost = blocks >= full ? 1.0 : (double)full / blocks;
     } else {
-      const int waves = (blocks + 2 * kSMs - 1) / (2 * kSMs);
-      cost = (double)waves * 2 * kSMs / blocks;
+      const int waves = (blocks + 2 * sms - 1) / (2 * sms);
+      cost = (double)waves * 2 * sms / blocks;
     }
     cost += 0.02 * s;
     if (cost < best_cost - 1e-9) {

@@ -163,6 +163,33 @@ YCM_API int ycm_reserve(void* h, int slot, int new_len) {
   return 0;
 }
 
+// The same for all requests of a step at once: either every slot gets its pages or nothing changes.
+// slots must be distinct.  Return values as ycm_reserve.
+YCM_API int ycm_reserve_many(void* h, int n, const int32_t* slots, const int32_t* new_lens) {
+  Manager* m = static_cast<Manager*>(h);
+  if (n < 0 || (n > 0 && (slots == nullptr || new_lens == nullptr))) return fail(m, -7, "reserve_many: bad arguments");
+  for (int i = 0; i < n; ++i) {
+    if (int e = check_slot(m, slots[i], "reserve_many")) return e;
+    if (new_lens[i] < m->ctx_len[slots[i]]) return fail(m, -5, "reserve_many: new length is below the committed length");
+  }
+  for (const Group& g : m->groups) {
+    long long need = 0;
+    for (int i = 0; i < n; ++i) {
+      int want_end = ceil_div(new_lens[i], g.page_size);
+      if (want_end > g.max_pages_per_slot)
+        return fail(m, 2, "reserve_many: " + std::to_string(new_lens[i]) + " tokens exceed the block-table width");
+      int have_end = g.end_mapped[slots[i]];
+      if (want_end > have_end) need += want_end - have_end;
+    }
+    if (need > static_cast<long long>(g.free_pages.size())) return fail(m, 1, "reserve_many: insufficient free pages");
+  }
+  for (int i = 0; i < n; ++i) {
+    int r = ycm_reserve(h, slots[i], new_lens[i]);
+    if (r != 0) return fail(m, -8, "reserve_many: a slot was named twice");   // the sums above were checked
+  }
+  return 0;
+}
+
 // The slot now holds `new_len` tokens.  Groups with a window give back the
 // pages no later query can see.  Returns the number of pages given back, < 0 on misuse.
 YCM_API int ycm_commit(void* h, int slot, int new_len) {

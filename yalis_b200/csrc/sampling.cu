@@ -128,8 +128,22 @@ __device__ ArgMax block_argmax(ArgMax a, ArgMax* scratch) {
   return t;
 }
 
+// A chosen token goes to out[row] and, when `scatter_index` is given and not negative for the row, also to
+// scatter[scatter_index[row]]: the engine keeps each request's last chosen token in a per-slot array on the
+// device, from which the next step can take its input without the host in between.
+__device__ __forceinline__ void put_choice(int row, int token, int32_t* __restrict__ out,
+                                           const int32_t* __restrict__ scatter_index, int32_t* __restrict__ scatter) {
+  out[row] = token;
+  if (scatter_index != nullptr) {
+    const int where = scatter_index[row];
+    if (where >= 0) scatter[where] = token;
+  }
+}
+
 __global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restrict__ logits, long long row_stride,
-                                                          int vocab, int32_t* __restrict__ out) {
+                                                          int vocab, int32_t* __restrict__ out,
+                                                          const int32_t* __restrict__ scatter_index,
+                                                          int32_t* __restrict__ scatter) {
   __shared__ ArgMax scratch[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -144,7 +158,7 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restric
     if (v == v) a = better(a, b);  // NaN never wins
   });
   a = block_argmax(a, scratch);
-  if (threadIdx.x == 0) out[blockIdx.x] = a.i < 0 ? 0 : a.i;
+  if (threadIdx.x == 0) put_choice(blockIdx.x, a.i < 0 ? 0 : a.i, out, scatter_index, scatter);
 }
 
 constexpr double kFixedOne = 549755813888.0;  // 2^39
@@ -553,7 +567,8 @@ __global__ void __launch_bounds__(kThreads) argmax_partial_kernel(const float* _
 
 // Phase 2: one warp per row merges the slices (ties still go to the lowest index).
 __global__ void argmax_merge_kernel(const float* __restrict__ part_v, const int32_t* __restrict__ part_i,
-                                    int32_t* __restrict__ out) {
+                                    int32_t* __restrict__ out, const int32_t* __restrict__ scatter_index,
+                                    int32_t* __restrict__ scatter) {
   pdl_launch_dependents();
   pdl_wait();
   ArgMax a;
@@ -566,31 +581,34 @@ __global__ void argmax_merge_kernel(const float* __restrict__ part_v, const int3
     b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
     a = better(a, b);
   }
-  if (threadIdx.x == 0) out[blockIdx.x] = a.i < 0 ? 0 : a.i;
+  if (threadIdx.x == 0) put_choice(blockIdx.x, a.i < 0 ? 0 : a.i, out, scatter_index, scatter);
 }
 
 // scratch: n_rows * 32 floats followed by n_rows * 32 int32 for rows wider than 16384 (may be null
 // for narrower rows, which one block per row handles).
+// scatter_index / scatter: see put_choice (both may be null).
 YALIS_API int yalis_argmax(const float* logits, long long row_stride, int n_rows, int vocab, int32_t* out,
-                           float* scratch, cudaStream_t stream) {
+                           float* scratch, const int32_t* scatter_index, int32_t* scatter, cudaStream_t stream) {
   static_assert(kArgmaxChunks == 32, "the merge kernel is one warp wide");
   if (n_rows <= 0) return YALIS_OK;
   if (vocab <= 0) return YALIS_ERR_SHAPE;
   if (vocab <= 16384 || scratch == nullptr)
-    return yalis_launch(argmax_kernel, dim3(n_rows), dim3(kThreads), 0, stream, logits, row_stride, vocab, out);
+    return yalis_launch(argmax_kernel, dim3(n_rows), dim3(kThreads), 0, stream, logits, row_stride, vocab, out,
+                        scatter_index, scatter);
   float* part_v = scratch;
   int32_t* part_i = reinterpret_cast<int32_t*>(scratch + (size_t)n_rows * kArgmaxChunks);
   int st = yalis_launch(argmax_partial_kernel, dim3(n_rows, kArgmaxChunks), dim3(kThreads), 0, stream, logits,
                         row_stride, vocab, part_v, part_i);
   if (st != YALIS_OK) return st;
   return yalis_launch(argmax_merge_kernel, dim3(n_rows), dim3(32), 0, stream, (const float*)part_v,
-                      (const int32_t*)part_i, out);
+                      (const int32_t*)part_i, out, scatter_index, scatter);
 }
 
 // scratch: n_rows * (64 + 4) 32-bit words (partial results of the draw, then the cuts).
 YALIS_API int yalis_sample(const float* logits, long long row_stride, int n_rows, int vocab, const float* temperature,
                            const int32_t* top_k, const float* top_p, const unsigned long long* seed,
-                           const unsigned long long* draw_index, int32_t* out, float* scratch, cudaStream_t stream) {
+                           const unsigned long long* draw_index, int32_t* out, float* scratch,
+                           const int32_t* scatter_index, int32_t* scatter, cudaStream_t stream) {
   static_assert(kDrawChunks == kArgmaxChunks, "the merge kernel is shared with argmax");
   if (n_rows <= 0) return YALIS_OK;
   if (vocab <= 0 || vocab > (1 << 19) || scratch == nullptr) return YALIS_ERR_SHAPE;   // see the piece sums of top-p
@@ -635,5 +653,5 @@ YALIS_API int yalis_sample(const float* logits, long long row_stride, int n_rows
                     vocab, temperature, top_p, seed, draw_index, (const Cut*)cuts, part_v, part_i);
   if (st != YALIS_OK) return st;
   return yalis_launch(argmax_merge_kernel, dim3(n_rows), dim3(32), 0, stream, (const float*)part_v,
-                      (const int32_t*)part_i, out);
+                      (const int32_t*)part_i, out, scatter_index, scatter);
 }

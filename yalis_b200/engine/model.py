@@ -13,21 +13,10 @@ from typing import Callable, Dict, List, Optional
 
 import torch
 
-from yalis_b200.config.spec import LayerSpec, ModelSpec
-from yalis_b200.ops.elementwise import embedding
+from yalis_b200.config.spec import ModelSpec
+from yalis_b200.ops.elementwise import embedding, softcap_
 from yalis_b200.ops.linear import linear
-from yalis_b200.parts.base import Block, ParamSpec, ResidualStream, make_part
-
-_PART_SLOTS = ("norm_1", "mixer", "norm_2", "feed_forward")
-
-
-def build_block(layer: LayerSpec) -> Block:
-    position = make_part("position", layer.position)
-    mixer = make_part("mixer", layer.mixer, position=position)
-    feed_forward = make_part("feed_forward", layer.feed_forward)
-    norm_1 = make_part("norm", layer.norm_1)
-    norm_2 = make_part("norm", layer.norm_2)
-    return make_part("block", layer.block, mixer=mixer, feed_forward=feed_forward, norm_1=norm_1, norm_2=norm_2)
+from yalis_b200.parts.base import NOT_CAPTURABLE, Block, ParamSpec, ResidualStream, build_block, make_part
 
 
 class Model:
@@ -44,8 +33,7 @@ class Model:
         """part slot -> {local parameter name -> tensor name in the checkpoint}."""
         layer, block = self.spec.layers[li], self.blocks[li]
         out: Dict[str, Dict[str, str]] = {}
-        for slot in _PART_SLOTS:
-            part = getattr(block, slot)
+        for slot, part in block.parts.items():
             names = {}
             for local in part.param_specs():
                 key = f"{slot}.{local}"
@@ -67,8 +55,8 @@ class Model:
 
         for li, block in enumerate(self.blocks):
             names = self._layer_tensor_names(li)
-            for slot in _PART_SLOTS:
-                for local, ps in getattr(block, slot).param_specs().items():
+            for slot, part in block.parts.items():
+                for local, ps in part.param_specs().items():
                     put(names[slot][local], ps)
         for local, ps in self.final_norm.param_specs().items():
             put(s.final_norm_names[local], ps)
@@ -83,21 +71,31 @@ class Model:
         self.embedding = fetch(s.embedding_name).contiguous()
         for li, block in enumerate(self.blocks):
             names = self._layer_tensor_names(li)
-            for slot in _PART_SLOTS:
-                part = getattr(block, slot)
+            for slot, part in block.parts.items():
                 part.load({local: fetch(name) for local, name in names[slot].items()})
         self.final_norm.load({local: fetch(s.final_norm_names[local]) for local in self.final_norm.param_specs()})
         self.head = self.embedding if s.head_name is None else fetch(s.head_name).contiguous()
 
     # ---- cache -------------------------------------------------------------------------
     def cache_requests(self) -> List[Optional[object]]:
-        """What the mixer of each schedule entry wants to keep (an entry that reads another
+        """What the block of each schedule entry wants to keep (an entry that reads another
         entry's cache still says what it expects to find there)."""
-        return [self.blocks[e.layer].mixer.cache_request() for e in self.spec.schedule]
+        return [self.blocks[e.layer].cache_request() for e in self.spec.schedule]
+
+    def capture_key(self, host):
+        """The keys of all parts that run in a step, or ``NOT_CAPTURABLE`` if one of them cannot be recorded."""
+        keys = []
+        for part in [self.blocks[i] for i in sorted({e.layer for e in self.spec.schedule})] + [self.final_norm]:
+            key = part.capture_key(host)
+            if key is NOT_CAPTURABLE:
+                return NOT_CAPTURABLE
+            keys.append(key)
+        return tuple(keys)
 
     # ---- forward -----------------------------------------------------------------------
     def forward(self, ctx, caches: List[Optional[object]]) -> ResidualStream:
-        x = embedding(self.embedding, ctx.token_ids, bad_flag=ctx.error_flag)
+        x = embedding(self.embedding, ctx.token_ids, bad_flag=ctx.error_flag, scale=self.spec.embedding_scale,
+                      from_slot=ctx.token_from_slot, chosen=ctx.chosen if ctx.token_from_slot is not None else None)
         stream = ResidualStream(x, self.dtype)
         for entry, cache in zip(self.spec.schedule, caches):
             self.blocks[entry.layer].forward(stream, ctx, cache)
@@ -106,7 +104,10 @@ class Model:
     def logits(self, stream: ResidualStream, rows: torch.Tensor) -> torch.Tensor:
         """float32 logits [len(rows), vocab] of the given token rows."""
         h = self.final_norm.forward(stream, rows=rows)
-        return linear(h, self.head, out_dtype=torch.float32)
+        out = linear(h, self.head, out_dtype=torch.float32)
+        if self.spec.logit_softcap is not None:
+            softcap_(out, self.spec.logit_softcap)
+        return out
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
@@ -120,8 +121,8 @@ class Model:
         add(self.embedding)
         add(self.head)
         for b in self.blocks:
-            for slot in _PART_SLOTS:
-                for v in vars(getattr(b, slot)).values():
+            for part in b.parts.values():
+                for v in vars(part).values():
                     if isinstance(v, torch.Tensor) and v.is_cuda:
                         add(v)
         add(getattr(self.final_norm, "weight", None))

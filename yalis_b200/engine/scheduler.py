@@ -80,6 +80,7 @@ class PlannedEntry:
     start: int        # index of the first token fed (== request.computed)
     count: int        # tokens fed
     samples: bool     # the portion reaches the request's last token: sample after it
+    slot: Optional[int] = None    # the request's slot when the step ran (it may finish and lose it in the update)
 
 
 @dataclass

@@ -190,8 +190,9 @@ class LlamaArchitecture:
             "norm_2.weight": "post_attention_layernorm.weight",
         }
         layers = tuple(
-            LayerSpec(block=PartSpec("pre_norm_residual"), mixer=mixer, feed_forward=ffn, norm_1=norm, norm_2=norm,
-                      position=position, weight_prefix=f"model.layers.{i}.", weight_names=names)
+            LayerSpec(block=PartSpec("pre_norm_residual"),
+                      parts={"position": position, "norm_1": norm, "mixer": mixer, "norm_2": norm, "feed_forward": ffn},
+                      weight_prefix=f"model.layers.{i}.", weight_names=names)
             for i in range(c.num_hidden_layers))
         return ModelSpec(
             architecture=ARCHITECTURE_NAME,

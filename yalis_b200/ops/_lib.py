@@ -68,6 +68,39 @@ def stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+# ---- the device error word -----------------------------------------------------------------------
+# One int32 per device that every kernel of the library may raise bits in (csrc/common.cuh) instead of trapping;
+# the host reads it where it synchronises anyway.
+FLAG_BAD_ID, FLAG_BAD_PAGE, FLAG_WAIT_ATTENTION, FLAG_WAIT_PRODUCT = 1, 2, 4, 8
+_FLAG_TEXT = {
+    FLAG_BAD_ID: "a token id outside the vocabulary",
+    FLAG_BAD_PAGE: "a block-table entry outside the page pool (a visible token without a page)",
+    FLAG_WAIT_ATTENTION: "a bounded wait inside an attention kernel ran out (its block gave up)",
+    FLAG_WAIT_PRODUCT: "a bounded wait inside the weight-streaming product ran out (its block gave up)",
+}
+_error_words = {}
+
+
+def error_word(device) -> torch.Tensor:
+    """int32 [1] on ``device``: the error word every kernel launched through these wrappers reports to."""
+    key = torch.device(device)
+    if key.index is None:
+        key = torch.device("cuda", torch.cuda.current_device())
+    word = _error_words.get(key)
+    if word is None:
+        word = _error_words[key] = torch.zeros(1, dtype=torch.int32, device=key)
+    return word
+
+
+def describe_error_word(value: int) -> str:
+    """What the bits of an error word mean, for messages."""
+    found = [text for bit, text in _FLAG_TEXT.items() if value & bit]
+    rest = value & ~sum(_FLAG_TEXT)
+    if rest:
+        found.append(f"unknown bits {rest:#x}")
+    return "; ".join(found) if found else "no error"
+
+
 LAUNCHES = [0]   # kernels of this library launched by this process (one per successful launcher call)
 
 

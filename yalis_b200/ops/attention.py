@@ -58,7 +58,22 @@ def paged_attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch
     return out
 
 
-SM_COUNT = 148   # B200
+SM_COUNT: Optional[int] = None    # set to override what the device reports (tests pretend a small GPU)
+_sm_counts = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device (asked of the driver once per device)."""
+    if SM_COUNT is not None:
+        return SM_COUNT
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    n = _sm_counts.get(index)
+    if n is None:
+        n = _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return n
+
 
 # How often each attention kernel was launched through these wrappers (tests read it to see which path a step took).
 LAUNCHED = collections.Counter()
@@ -83,26 +98,26 @@ def decode_splits(n_requests: int, num_kv_heads: int) -> int:
     nearly empty wave would double the kernel's time).  Depends on the batch shape only, never
     on lengths, so a captured step can be replayed."""
     blocks = max(1, n_requests * num_kv_heads)
-    return max(1, min(32, (2 * SM_COUNT) // blocks))
+    return max(1, min(32, (2 * sm_count()) // blocks))
 
 
 LONG_CONTEXT = 8192     # beyond this many cached tokens a few requests cannot keep HBM busy with 8 splits each
 
 
-def decode_tma_splits(ctx, num_kv_heads: int) -> int:
+def decode_tma_splits(n_requests: int, num_kv_heads: int, long_context: bool) -> int:
     """Splits of a (request, KV head) for the TMA-fed decode kernel: up to 8 merge inside a thread-block
-    cluster (the cheaper merge); steps marked as long-context take up to 32 and merge through global memory,
+    cluster (the cheaper merge); steps of the long-context kind take up to 32 and merge through global memory,
     so that a single long request still spreads over the whole GPU.  Clusters of more than four blocks are
     kept to 70 % of the places for blocks: a cluster starts only when all its blocks find room in one part of
     the GPU, and inside a step the kernel before still holds some (4 requests x 8 KV heads in 8 splits are 256
     blocks in 32 clusters: 5 % of a decode step slower than in 6 splits)."""
-    n = decode_splits(ctx.n_requests, num_kv_heads)
-    if ctx.host.max_kv_len > LONG_CONTEXT:
+    n = decode_splits(n_requests, num_kv_heads)
+    if long_context:
         return n
     n = min(8, n)
     if n > 4:
-        pairs = max(1, ctx.n_requests * num_kv_heads)
-        n = min(n, max(4, int(0.7 * 2 * SM_COUNT) // pairs))
+        pairs = max(1, n_requests * num_kv_heads)
+        n = min(n, max(4, int(0.7 * 2 * sm_count()) // pairs))
     return n
 
 
@@ -206,7 +221,7 @@ def decode_attention_tma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
 
 def decode_lean_blocks(head_dim: int) -> int:
     """Blocks of the evenly dealt decode kernel that are resident at once (its grid)."""
-    return (2 if head_dim <= 128 else 1) * SM_COUNT
+    return (2 if head_dim <= 128 else 1) * sm_count()
 
 
 DEAL_MIN_LONGEST = 2048   # below this many cached tokens even a lone long request costs less than dealing tiles out
@@ -216,7 +231,7 @@ def deal_tiles_hint(lengths) -> bool:
     """Host-side choice for a decode step of requests holding ``lengths`` cached tokens: True when a block per
     (request, KV head) - or a fixed number of them - would leave the GPU waiting for the longest request, i.e.
     with two or more requests of which one is beyond the long-context mark, or is at least ``DEAL_MIN_LONGEST``
-    long and twice the mean.  Depends on lengths only; the engine keys its captured steps by it."""
+    long and twice the mean.  Depends on lengths only."""
     n = len(lengths)
     if n < 2:
         return False
@@ -224,13 +239,33 @@ def deal_tiles_hint(lengths) -> bool:
     return longest > LONG_CONTEXT or (longest >= DEAL_MIN_LONGEST and longest * n >= 2 * sum(lengths))
 
 
-def decode_lean_preferred(n_requests: int, num_kv_heads: int, head_dim: int, host=None) -> bool:
+def decode_step_kind(lengths) -> tuple:
+    """(deal_tiles, long_context) of a decode step whose requests hold ``lengths`` tokens after it: everything
+    the decode kernels' launch depends on besides the shapes.  A recorded step is keyed by it, because a replay
+    cannot look at lengths: dealt tiles for long or uneven batches, more key splits for one long request."""
+    if not lengths:
+        return (False, False)
+    deal = deal_tiles_hint(lengths)
+    return (deal, not deal and max(lengths) > LONG_CONTEXT)
+
+
+def step_kind(ctx) -> tuple:
+    """``decode_step_kind`` of the step, computed once (every layer asks)."""
+    kind = ctx.extras.get("paged_attention.kind")
+    if kind is None:
+        host = ctx.host
+        lengths = [b + (q1 - q0) for b, q0, q1 in zip(host.ctx_before, host.q_start[:-1], host.q_start[1:])]
+        kind = ctx.extras["paged_attention.kind"] = decode_step_kind(lengths) if ctx.decode_only else (False, False)
+    return kind
+
+
+def decode_lean_preferred(n_requests: int, num_kv_heads: int, head_dim: int, deal_tiles: bool = False) -> bool:
     """Whether a decode step goes to the kernel that deals the key tiles of all (request, KV head) pairs to a fixed
     grid: with more pairs than blocks fit the GPU at once (a block per pair would run in waves, the last one
-    mostly empty), or when the step's host facts say that the requests are long or uneven (``deal_tiles``)."""
+    mostly empty), or when the requests are long or uneven (``deal_tiles``)."""
     if not USE_DECODE_LEAN or n_requests > 4096:
         return False
-    if host is not None and getattr(host, "deal_tiles", False) and n_requests >= 2:
+    if deal_tiles and n_requests >= 2:
         return True
     return n_requests * num_kv_heads > decode_lean_blocks(head_dim)
 
@@ -434,7 +469,7 @@ def prefill_kv_splits(host, heads_per_group: int, num_kv_heads: int, head_dim: i
     longest = max((t for t, _ in items), default=0)
     if longest < 3 * PREFILL_SPLIT_MIN_TILES:
         return 1, 1
-    slots = max(1, 2 * SM_COUNT // num_kv_heads)
+    slots = max(1, 2 * sm_count() // num_kv_heads)
     best, best_length = (1, 1), 0.92 * _prefill_step_length(items, slots, 1, 1)    # dividing has to bring 8 %
     for shares in (2, 3, 4, 6, 8):
         limit = max(PREFILL_SPLIT_MIN_TILES, -(-longest // shares))
@@ -477,12 +512,14 @@ def paged_attention(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     table = ctx.block_tables[group]
     per = num_heads // num_kv_heads
     if decode_tma_applicable(qkv.dtype, ctx, head_dim, k_pool.shape[2], per, window):
-        if decode_lean_preferred(ctx.n_requests, num_kv_heads, head_dim, ctx.host):
+        deal_tiles, long_context = step_kind(ctx)
+        if decode_lean_preferred(ctx.n_requests, num_kv_heads, head_dim, deal_tiles):
             return decode_attention_lean(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, num_heads, num_kv_heads,
                                          head_dim, scale=scale, error_flag=ctx.error_flag,
                                          early_fetch=bool(getattr(ctx, "settled", False)))
         return decode_attention_tma(qkv, k_pool, v_pool, ctx.positions, ctx.q_start, table, num_heads, num_kv_heads,
-                                    head_dim, scale=scale, n_splits=decode_tma_splits(ctx, num_kv_heads),
+                                    head_dim, scale=scale,
+                                    n_splits=decode_tma_splits(ctx.n_requests, num_kv_heads, long_context),
                                     error_flag=ctx.error_flag, early_fetch=bool(getattr(ctx, "settled", False)))
     if (qkv.dtype == torch.bfloat16 and USE_PREFILL_TCGEN05 and window is None and ctx.host.max_q_len >= 16
             and prefill_tcgen05_supports(head_dim, k_pool.shape[2], per)):

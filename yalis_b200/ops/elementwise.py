@@ -10,19 +10,38 @@ from ._lib import check, dtype_code, f32, i32, i64, lib, need, need_cuda, ptr, s
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None,
-              bad_flag: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t] = float32(table[ids[t]]).  ids int32 [N]; table [vocab, width]."""
+              bad_flag: Optional[torch.Tensor] = None, scale: Optional[float] = None,
+              from_slot: Optional[torch.Tensor] = None, chosen: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = float32(table[ids[t]]) (times ``scale`` if given).  ids int32 [N]; table [vocab, width].
+    With ``from_slot`` (int32 [N]) and ``chosen`` (int32 vector), token t takes its id from
+    ``chosen[from_slot[t]]`` where ``from_slot[t]`` is not negative."""
     name = "embedding"
-    need_cuda(name, table, ids, out, bad_flag)
+    need_cuda(name, table, ids, out, bad_flag, from_slot, chosen)
+    need((from_slot is None) == (chosen is None), name, "from_slot and chosen come together")
+    if from_slot is not None:
+        need(from_slot.dtype == torch.int32 and from_slot.shape == ids.shape and from_slot.is_contiguous()
+             and chosen.dtype == torch.int32 and chosen.dim() == 1 and chosen.is_contiguous(), name,
+             "from_slot must be int32 [N] and chosen a contiguous int32 vector")
     need(ids.dtype == torch.int32 and ids.dim() == 1 and ids.is_contiguous(), name, "ids must be contiguous int32 [N]")
     need(table.dim() == 2 and table.is_contiguous(), name, "table must be contiguous [vocab, width]")
     n, (vocab, width) = ids.numel(), table.shape
     if out is None:
         out = torch.empty((n, width), dtype=torch.float32, device=table.device)
     need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (n, width), name, "out must be float32 [N, width]")
-    check(lib().yalis_embedding(ptr(table), i32(dtype_code(table.dtype)), ptr(ids), ptr(out), i32(n), i32(width),
-                                i32(vocab), ptr(bad_flag), stream()), name)
+    check(lib().yalis_embedding(ptr(table), i32(dtype_code(table.dtype)), ptr(ids), ptr(from_slot), ptr(chosen),
+                                ptr(out), i32(n), i32(width),
+                                i32(vocab), f32(1.0 if scale is None else scale), ptr(bad_flag), stream()), name)
     return out
+
+
+def softcap_(values: torch.Tensor, cap: float) -> torch.Tensor:
+    """values <- cap * tanh(values / cap), in place (float32, contiguous)."""
+    name = "softcap"
+    need_cuda(name, values)
+    need(values.dtype == torch.float32 and values.is_contiguous(), name, "values must be contiguous float32")
+    need(cap > 0, name, "the cap must be positive")
+    check(lib().yalis_softcap_f32(ptr(values), i64(values.numel()), f32(cap), stream()), name)
+    return values
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,

@@ -20,7 +20,7 @@ import torch
 
 import os
 
-from ._lib import check, dtype_code, i32, i64, lib, need, need_cuda, ptr, stream
+from ._lib import check, dtype_code, error_word, i32, i64, lib, need, need_cuda, ptr, stream
 
 # YALIS_B200_NO_WSTREAM=1 sends every bfloat16 product to the library (for comparisons).
 USE_WSTREAM = os.environ.get("YALIS_B200_NO_WSTREAM", "0") != "1"
@@ -78,15 +78,11 @@ WSTREAM_MAX_TOKENS = 256        # what the kernel takes
 # Up to this many tokens the engine's own kernel is the faster one in a decode step (measured on the Llama-3-8B
 # shape: batch 32 4.20 ms against 4.36 ms with the library, batch 64 5.70 ms against 5.32 ms).
 WSTREAM_PREFERRED_TOKENS = int(os.environ.get("YALIS_B200_WSTREAM_TOKENS", "32"))
-_wstream_error = {}
 
 
 def wstream_error_flag(device) -> torch.Tensor:
-    """int32 [1] on the device; a kernel raises it if one of its bounded waits ran out."""
-    key = torch.device(device)
-    if key not in _wstream_error:
-        _wstream_error[key] = torch.zeros(1, dtype=torch.int32, device=key)
-    return _wstream_error[key]
+    """The device's error word: the kernel raises FLAG_WAIT_PRODUCT in it if one of its bounded waits ran out."""
+    return error_word(device)
 
 
 def wstream_splits(n: int, k: int) -> int:

@@ -58,11 +58,21 @@ class PagedAttention(Mixer):
     def cache_request(self) -> PagedKV:
         return PagedKV(self.g, self.hs, self.window)
 
+    def capture_key(self, host):
+        # which decode kernel runs, and in how many splits, depends on the lengths only through this
+        return attn_ops.decode_step_kind([b + 1 for b in host.ctx_before])
+
+    def mixing_flops(self, q_len: int, ctx_before: int) -> float:
+        # QK^T and PV over the keys each token sees (causal; a window bounds them)
+        keys = sum(min(ctx_before + t + 1, self.window or (ctx_before + t + 1)) for t in range(q_len)) if self.window \
+            else q_len * ctx_before + q_len * (q_len + 1) / 2
+        return 4.0 * self.nh * self.hs * keys
+
     def forward(self, x: torch.Tensor, ctx, cache: PagedKVCache) -> torch.Tensor:
         qkv = linear_partial(x, self.w_qkv)          # [N, width], or float32 partial sums [S, N, width]
-        if (attn_ops.USE_FUSED_ROPE and ctx.n_requests * self.g <= 2 * attn_ops.SM_COUNT
-                and not attn_ops.decode_lean_preferred(ctx.n_requests, self.g, self.hs, ctx.host)
-                and attn_ops.decode_tma_applicable(x.dtype, ctx, self.hs, cache.k.shape[2], self.nh // self.g, self.window)):
+        if (attn_ops.USE_FUSED_ROPE and ctx.n_requests * self.g <= 2 * attn_ops.sm_count(x.device)
+                and attn_ops.decode_tma_applicable(x.dtype, ctx, self.hs, cache.k.shape[2], self.nh // self.g, self.window)
+                and not attn_ops.decode_lean_preferred(ctx.n_requests, self.g, self.hs, attn_ops.step_kind(ctx)[0])):
             # A decode step whose attention blocks fit the GPU at once: the attention kernel rotates Q and the new K
             # itself and stores K, V (one launch less).  With more blocks than that the extra work at the start of
             # every block costs more than the launch (measured at batch 64: 59.5 against 57 us per layer).
@@ -71,7 +81,8 @@ class PagedAttention(Mixer):
                 y = attn_ops.decode_attention_tma_fused(
                     qkv, freq, cache.writable, cache.k, cache.v, ctx.positions, ctx.q_start,
                     ctx.block_tables[cache.group], self.nh, self.g, self.hs, scale=self.scale,
-                    n_splits=attn_ops.decode_tma_splits(ctx, self.g), error_flag=ctx.error_flag,
+                    n_splits=attn_ops.decode_tma_splits(ctx.n_requests, self.g, attn_ops.step_kind(ctx)[1]),
+                    error_flag=ctx.error_flag,
                     early_fetch=bool(getattr(ctx, "settled", False)))
                 return linear_partial(y, self.w_o)
         q = self.position.encode_and_store(qkv, self.nh, self.g, self.hs, ctx, cache, dtype=x.dtype)

@@ -12,19 +12,30 @@ Five categories, each with one small interface:
                   ``forward(x, ctx, cache) -> Tensor [N, hidden]``.
 ``feed_forward``  ``forward(x, ctx) -> Tensor [N, hidden]``.
 ``block``         ``forward(stream, ctx, cache) -> None``: the arrangement of the
-                  four above around the residual stream.
+                  four above around the residual stream.  A block kind declares the
+                  places it has (``slots``: place name -> category); a layer's
+                  ``LayerSpec.parts`` fills exactly those.
 
 Every part is constructed from a ``PartSpec`` (kind + parameters) alone, names
 its tensors with ``param_specs()`` and receives them in ``load()``.  A part
 never sees the model configuration, the architecture's name or another layer.
 New kinds are added with ``register_part(category, kind, cls)``; nothing else in
 the package has to change.
+
+Steps in which every request brings one token can be recorded once (a CUDA
+graph) and replayed.  A replay runs no Python, so whatever a part decides on the
+host from the step's facts has to be the same for every step that replays one
+recording: ``capture_key(host)`` returns a hashable that determines all such
+decisions (kernel choice, grid sizes), or ``NOT_CAPTURABLE`` (the default) for a
+part whose ``forward`` works on the host per request, synchronises or allocates
+by data.  The engine records one step per distinct tuple of keys and sends
+steps with a part that cannot be captured to the launched path.
 """
 
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Optional, Tuple
+from typing import Any, Callable, Dict, Hashable, Mapping, Optional, Tuple
 
 import torch
 
@@ -84,8 +95,10 @@ class PagedKVCache:
 
 
 class SlotStateCache:
-    """What a stateful mixer gets: ``state`` [max_slots, *shape]; rows are indexed
-    by the step context's ``slots``."""
+    """What a stateful mixer gets: ``state`` [max_slots + 1, *shape]; rows are indexed
+    by the step context's ``slots``.  The last row belongs to no request: the padding
+    rows of a recorded step point there, so a kernel may update ``state[ctx.slots]``
+    for every row of the step without a test."""
 
     def __init__(self, state: torch.Tensor, writable: bool = True):
         self.state, self.writable = state, writable
@@ -120,6 +133,14 @@ class ResidualStream:
 
 # ---- parts ---------------------------------------------------------------------------
 
+class _NotCapturable:
+    def __repr__(self) -> str:
+        return "NOT_CAPTURABLE"
+
+
+NOT_CAPTURABLE = _NotCapturable()   # answer of Part.capture_key: run this part's steps launch by launch
+
+
 class Part:
     category = ""
 
@@ -132,11 +153,26 @@ class Part:
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         """Receives the tensors named by param_specs(), on the device, in the engine's dtype."""
 
+    def capture_key(self, host) -> Hashable:
+        """What a recorded step of this part depends on beyond the shapes of its tensors (see the module
+        docstring).  ``host`` is the step's ``HostStep``.  Return None when ``forward`` launches the same
+        kernels whatever the requests' lengths are."""
+        return NOT_CAPTURABLE
+
+    def matrix_flops_per_token(self) -> float:
+        """Floating-point operations per token in this part's matrix products (2 per weight of every 2-D tensor)."""
+        return float(sum(2 * ps.shape[0] * ps.shape[1] for ps in self.param_specs().values() if len(ps.shape) == 2))
+
 
 class Norm(Part):
     category = "norm"
 
     def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+    def normalize(self, y: torch.Tensor) -> torch.Tensor:
+        """The norm of a plain tensor [N, width] in its own dtype (for arrangements that norm a sub-layer's
+        output rather than the stream)."""
         raise NotImplementedError
 
 
@@ -170,6 +206,11 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         raise NotImplementedError
 
+    def mixing_flops(self, q_len: int, ctx_before: int) -> float:
+        """Floating-point operations, beyond the matrix products, of ``q_len`` tokens fed after ``ctx_before``
+        cached ones (for rooflines; 0 when the mixer has none worth counting)."""
+        return 0.0
+
 
 class FeedForward(Part):
     category = "feed_forward"
@@ -179,14 +220,71 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    category = "block"
+    """An arrangement of parts around the residual stream.
 
-    def __init__(self, spec: PartSpec, mixer: Mixer, feed_forward: FeedForward, norm_1: Norm, norm_2: Norm):
+    ``slots`` names the places of the arrangement and the category of part each takes; the layer's
+    ``LayerSpec.parts`` must fill exactly these.  The built parts arrive as a dictionary and are also set as
+    attributes (``self.mixer`` ...).  A place of category ``position`` is built first and handed to the
+    block's mixers.  A block keeps at most one cache: what its ``cache_request`` returns (by default its
+    mixer's request, or nothing when it has no mixer).
+    """
+
+    category = "block"
+    slots: Mapping[str, str] = {}
+
+    def __init__(self, spec: PartSpec, parts: Dict[str, Part]):
         super().__init__(spec)
-        self.mixer, self.feed_forward, self.norm_1, self.norm_2 = mixer, feed_forward, norm_1, norm_2
+        self.parts = dict(parts)
+        for name, part in self.parts.items():
+            setattr(self, name, part)
 
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
         raise NotImplementedError
+
+    def cache_request(self):
+        mixers = [p for p in self.parts.values() if isinstance(p, Mixer)]
+        if len(mixers) > 1:
+            raise NotImplementedError("a block with several mixers must say itself what it caches")
+        return mixers[0].cache_request() if mixers else None
+
+    def capture_key(self, host) -> Hashable:
+        keys = []
+        for part in self.parts.values():
+            key = part.capture_key(host)
+            if key is NOT_CAPTURABLE:
+                return NOT_CAPTURABLE
+            keys.append(key)
+        return tuple(keys)
+
+
+def build_block(layer) -> Block:
+    """The block of a ``LayerSpec`` with all its parts."""
+    _ensure_builtin()
+    try:
+        factory = _REGISTRY["block"][layer.block.kind]
+    except KeyError:
+        known = ", ".join(sorted(_REGISTRY["block"])) or "none"
+        raise ValueError(f"no block of kind {layer.block.kind!r} is registered (known: {known})") from None
+    slots = dict(getattr(factory, "slots", {}))
+    missing = [n for n in slots if n not in layer.parts]
+    unknown = [n for n in layer.parts if n not in slots]
+    if missing or unknown:
+        raise ValueError(f"block kind {layer.block.kind!r} has the places {sorted(slots)}: "
+                         + (f"the layer fills none of {missing}" if missing else "")
+                         + ("; " if missing and unknown else "")
+                         + (f"the layer names {unknown}, which the block does not have" if unknown else ""))
+    built: Dict[str, Part] = {}
+    positions = [n for n, c in slots.items() if c == "position"]
+    for name in positions:
+        built[name] = make_part("position", layer.parts[name])
+    position = built[positions[0]] if len(positions) == 1 else None
+    for name, category in slots.items():
+        if category == "position":
+            continue
+        extra = {"position": position} if category == "mixer" else {}
+        built[name] = make_part(category, layer.parts[name], **extra)
+    ordered = {name: built[name] for name in slots}
+    return factory(layer.block, ordered)
 
 
 # ---- registry ---------------------------------------------------------------------------

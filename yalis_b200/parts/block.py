@@ -10,6 +10,9 @@ class PreNormResidualBlock(Block):
     (the non-parallel branch of yalis/external/model.py:414-438).
     Each addition is parked in the stream and performed by the next norm."""
 
+    slots = {"position": "position", "norm_1": "norm", "mixer": "mixer", "norm_2": "norm",
+             "feed_forward": "feed_forward"}
+
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
         h = self.norm_1.forward(stream)
         stream.add(self.mixer.forward(h, ctx, cache))

@@ -57,7 +57,6 @@ class RotaryEncoding(PositionEncoding):
                              cache.v if store else None, ctx.block_tables[cache.group], num_heads, num_kv_heads,
                              head_dim, out_dtype=dtype, bad_flag=ctx.error_flag)
 
-
     def rotary_frequencies(self, head_dim: int, device):
         if head_dim != self.head_dim:
             raise ValueError(f"rotary encoding built for head_dim {self.head_dim}, used with {head_dim}")
@@ -65,11 +64,17 @@ class RotaryEncoding(PositionEncoding):
             self.to(device)
         return self.inv_freq
 
+    def capture_key(self, host):
+        return None
+
 
 class NoPositionEncoding(PositionEncoding):
     """Stores K and V unrotated (a mixer that wants positions handled elsewhere)."""
 
     def rotary_frequencies(self, head_dim: int, device):
+        return None
+
+    def capture_key(self, host):
         return None
 
     def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, ctx, cache: PagedKVCache, dtype=None):

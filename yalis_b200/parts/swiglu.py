@@ -39,5 +39,8 @@ class SwiGLU(FeedForward):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         return linear_partial(linear_silu_mul(x, self.w_gate_up), self.w_down)
 
+    def capture_key(self, host):
+        return None
+
 
 register_part("feed_forward", "swiglu", SwiGLU)

@@ -59,7 +59,7 @@ def request_seed(base_seed: int, ordinal: int) -> int:
     return (int(base_seed) + (int(ordinal) + 1) * _MIX) & 0xFFFFFFFFFFFFFFFF
 
 
-def _as_int64(u: int) -> int:
+def as_int64(u: int) -> int:
     u &= 0xFFFFFFFFFFFFFFFF
     return u - (1 << 64) if u >= (1 << 63) else u
 
@@ -83,7 +83,7 @@ class Sampler:
             f[i, 0] = p.temperature
             host[i, 1] = p.top_k or 0
             f[i, 2] = p.top_p
-            q[i, 2] = _as_int64(p.seed)
+            q[i, 2] = as_int64(p.seed)
             q[i, 3] = int(d)
         dev = torch.from_numpy(host).to(self.device, non_blocking=False)
         temperature = dev[:, 0].contiguous().view(torch.float32)
