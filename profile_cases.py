@@ -1,7 +1,7 @@
 """Small, self-contained workloads of single kernels, for timing and for profiler captures.
 
-    python -m yalis_b200.profile_cases attention_decode --batch 64 --ctx 1040 --launches 8
-    python -m yalis_b200.profile_cases gemm_wstream --tokens 8 --n 28672 --k 4096 --launches 8
+    python profile_cases.py attention_decode --batch 64 --ctx 1040 --launches 8
+    python profile_cases.py gemm_wstream --tokens 8 --n 28672 --k 4096 --launches 8
 
 Each case allocates inputs larger than the L2 cache but at most a few GB, launches the
 kernel a few times, and prints the mean time per launch measured with CUDA events.
@@ -10,8 +10,12 @@ kernel a few times, and prints the mean time per launch measured with CUDA event
 from __future__ import annotations
 
 import argparse
+import os
+import sys
 
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
 def _time(fn, launches: int, graph: bool = True) -> float:
@@ -58,8 +62,7 @@ def attention_decode(args) -> None:
     pos = torch.full((b,), ctx - 1, dtype=torch.int32, device=dev)
     q_start = torch.arange(b + 1, dtype=torch.int32, device=dev)
     req = torch.arange(b, dtype=torch.int32, device=dev)
-    step = SimpleNamespace(n_requests=b, host=SimpleNamespace(max_kv_len=0))
-    splits = args.splits or (decode_tma_splits(step, g) if args.kernel == "tma" else decode_splits(b, g))   # as the engine chooses
+    splits = args.splits or (decode_tma_splits(b, g, False) if args.kernel == "tma" else decode_splits(b, g))   # as the engine chooses
     state = {"i": 0}
 
     def fn():

@@ -241,7 +241,7 @@ def test_rope_kv_write(dtype, nh, g, hs, page, scaled):
     # an unmapped page is flagged and skipped
     rope_kv_write(before.clone(), torch.tensor([9 * page], dtype=torch.int32, device=DEV).repeat(n)[:n], reqs * 0 + 1,
                   inv.to(DEV), k_pool, v_pool, table, nh, g, hs, bad_flag=flag)
-    assert int(flag) == 1
+    assert int(flag) == 2                                   # YALIS_FLAG_BAD_PAGE
 
 
 def test_rope_large_positions_match_float32_table():

@@ -94,12 +94,16 @@ class LLMEngine:
     # ---- generation ------------------------------------------------------------------------
     def run(self, prompts: Union[List[str], List[List[int]]], max_new_tokens: int = 50,
             sampling: Union[None, SamplingParams, Sequence[Optional[SamplingParams]]] = None,
-            eos_id: Optional[int] = None, return_logits: bool = False, enable_nvtx: bool = False):
+            eos_id: Optional[int] = None, return_logits: bool = False, enable_nvtx: bool = False,
+            step_log: Optional[list] = None):
         """Generate after each prompt; returns ``(results, metrics)`` with one ``Generation`` per prompt.
 
         ``sampling``: one ``SamplingParams`` for all prompts, or a list with one per prompt (None entries take
         the configuration's defaults with a seed of their own).  ``eos_id``: a request ends when it draws this
         token (None: only by length).  ``return_logits``: keep the float32 logits every token was drawn from.
+        ``step_log``: a list that receives, per step, a dictionary with its ``tokens``, ``requests``,
+        ``decoding`` (requests that brought one token), ``h2d_bytes``, ``captured`` and the CUDA events
+        ``start`` / ``end`` around it (for benchmarks).
         """
         t_tok = time.perf_counter()
         if len(prompts) == 0:
@@ -143,7 +147,16 @@ class LLMEngine:
                 if nvtx:
                     nvtx.range_push("Decode" if decode_only else "Prefill")
                 timers.start(name)
+                if step_log is not None:
+                    entry = {"tokens": plan.n_tokens, "requests": len(plan.entries),
+                             "decoding": sum(e.count == 1 for e in plan.entries), "start": torch.cuda.Event(enable_timing=True),
+                             "end": torch.cuda.Event(enable_timing=True)}
+                    entry["start"].record()
                 sampled = self._run_plan(plan, pending, logits_out)
+                if step_log is not None:
+                    entry["end"].record()
+                    entry["h2d_bytes"], entry["captured"] = eng.last_h2d_bytes, eng.last_captured is not None
+                    step_log.append(entry)
                 timers.stop(name)
                 if nvtx:
                     nvtx.range_pop()
