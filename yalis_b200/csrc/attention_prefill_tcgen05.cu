@@ -16,9 +16,15 @@
 //                  threads rescale O in place (tcgen05.ld / st); smaller growth is absorbed by
 //                  keeping the older maximum, which is exact as long as exp2 stays in range.
 //
-// One thread issues all TMA copies, one thread issues all MMAs, completion travels over
-// mbarriers (tcgen05.commit for the MMAs); QK^T of tile j+1 runs while the softmax of tile j is
-// computed.  Same semantics as paged_attention_generic (mask by absolute position,
+// One warp issues all TMA copies and one warp all MMAs; completion travels over mbarriers
+// (tcgen05.commit for the MMAs); QK^T of tile j+1 runs while the softmax of tile j is computed.
+// The MMA warp runs its loop converged, waits included, and an elected lane issues: the operands
+// of tcgen05.mma are warp-uniform values, and computing them in a branch that a single lane takes
+// made each issue cost about a hundred cycles (measured: 410 against 70 cycles for the four
+// products and two commits of a P V).  The copy warp looks the pages of a tile up one tile ahead
+// (a block-table entry is a global load whose latency would otherwise stand between a freed buffer
+// and the copy into it) and asks for K one tile ahead of V, the order in which their buffers come
+// free, so that a wait for one never holds up the other.  Same semantics as paged_attention_generic (mask by absolute position,
 // yalis/attention/backend_impl/sdpa_and_flex.py:15-19, 301-307) without a window.
 //
 // Limits (else the caller uses the mma.sync kernel): bfloat16, head_dim 64 or 128, page_size 8,
@@ -60,7 +66,19 @@ struct PrefillParams {
   float* part_o;               // [N, nh, n_splits, HS]
   float* part_ml;              // [N, nh, n_splits, 2]
   int32_t* error;
+#ifdef YALIS_TRACE_CLOCKS
+  long long* trace;            // [blocks][64 tiles][32 stamps] of clock64(), for timeline probes (compiled out by default)
+#endif
 };
+
+#ifdef YALIS_TRACE_CLOCKS
+#define STAMP(j, k)                                                                                             \
+  do {                                                                                                          \
+    if (p.trace && (j) < 64) p.trace[((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 64 + (j)) * 32 + (k)] = clock64(); \
+  } while (0)
+#else
+#define STAMP(j, k) do { } while (0)
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -81,11 +99,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
+#ifdef YALIS_TRACE_CLOCKS
+__device__ unsigned long long g_gave_up[8];      // the first wait that ran out: block, thread, barrier address, parity
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 1023u) == 1023u && *abort_flag) return false;
   }
+#ifdef YALIS_TRACE_CLOCKS
+  if (atomicCAS(&g_gave_up[0], 0ull, 1ull) == 0ull) {
+    g_gave_up[1] = blockIdx.x; g_gave_up[2] = blockIdx.y; g_gave_up[3] = threadIdx.x;
+    g_gave_up[4] = smem_u32(bar); g_gave_up[5] = parity;
+  }
+#endif
   *abort_flag = 1;
   return false;
 }
@@ -120,20 +147,30 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t lbo_by
 __device__ __forceinline__ uint32_t idesc_f16(int n, bool b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
-__device__ __forceinline__ void umma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+// 1 in one lane of a converged warp, 0 in the others.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred;
 }
-__device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+// The products and commits below are executed by every lane of the converged MMA warp and take effect in the
+// elected one: all lanes compute the (identical) operands, so these stay warp-uniform values.
+__device__ __forceinline__ void umma_ss(uint32_t elected, uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc) : "memory");
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc), "r"(elected) : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ void umma_ts(uint32_t elected, uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc), "r"(elected) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t elected, uint64_t* bar) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+               "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+               ::"r"(smem_u32(bar)), "r"(elected) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -157,6 +194,11 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
 }
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
@@ -189,56 +231,25 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   uint64_t* v_full = bars + 5;                     // 2
   uint64_t* v_empty = bars + 7;                    // 2
   uint64_t* s_full = bars + 9;                     // 2
-  uint64_t* s_empty = bars + 11;                   // 2
   uint64_t* p_full = bars + 13;                    // 2
   uint64_t* o_full = bars + 15;                    // 1
   uint64_t* o_done = bars + 16;                    // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  pdl_launch_dependents();
-  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int req = blockIdx.y / p.g, kvh = blockIdx.y - req * p.g;
-  const int tok0 = p.q_start[req], q_len = p.q_start[req + 1] - tok0;
-  // Later query tiles see more keys: they are given to the first blocks, so the light ones fill the tail.
-  const int t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * p.tokens_per_tile;   // first token of this block within the request
-  if (t0 >= q_len) return;                                  // uniform: nothing allocated yet
-  if (p.skip_single && q_len == 1) {
-    // Another kernel writes this request's row; with key splits the second kernel must leave it alone.
-    if (gridDim.z > 1 && blockIdx.z == 0 && (int)threadIdx.x < p.per)
-      *reinterpret_cast<float2*>(p.part_ml + (((size_t)tok0 * p.nh + kvh * p.per + threadIdx.x) * gridDim.z) * 2) =
-          make_float2(INFINITY, 0.f);
-    return;
-  }
-  const int n_tok = min(p.tokens_per_tile, q_len - t0);
-  const int n_rows = n_tok * p.per;
-  const int pos_first = p.positions[tok0 + t0];
-  const int hi_key = p.positions[tok0 + t0 + n_tok - 1];
-  // This block's share of the key tiles (all of them without splits).
-  const int all_tiles = hi_key / BN + 1;
-  const int slots = gridDim.z, split = blockIdx.z;          // slots: shares that the scratch memory has room for
-  const int wanted = slots > 1 ? min(slots, (all_tiles + p.tiles_per_split - 1) / p.tiles_per_split) : 1;
-  const int per_split = (all_tiles + wanted - 1) / wanted;
-  const int n_splits = (all_tiles + per_split - 1) / per_split;     // shares that get a tile (7 tiles in 5 shares: 4 of 2)
-  if (split >= n_splits) {                                  // uniform for the block
-    if (n_splits > 1 && (int)threadIdx.x < n_rows) {        // an unused share of a divided tile: nothing to add
-      const int t_in = threadIdx.x / p.per, head = threadIdx.x - t_in * p.per;
-      const size_t slot = ((size_t)(tok0 + t0 + t_in) * p.nh + kvh * p.per + head) * slots + split;
-      *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(-INFINITY, 0.f);
-    }
-    return;
-  }
-  const int tile_base = split * per_split;
-  const int n_tiles = min(all_tiles, tile_base + per_split) - tile_base;     // >= 1
-  const int32_t* bt = p.block_table + (size_t)req * p.table_width;
-
+  // Set-up that needs nothing of the step's data comes before the wait for the kernel in front: descriptors are
+  // asked for (the copy unit reads each from memory before its first copy), barriers initialised, tensor memory
+  // taken.  A block that then finds it has no work gives the tensor memory back on its way out.
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
     mbar_init(q_full, 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&k_full[b], 1); mbar_init(&k_empty[b], 1);
       mbar_init(&v_full[b], 1); mbar_init(&v_empty[b], 1);
-      mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 4);
+      mbar_init(&s_full[b], 1);
       mbar_init(&p_full[b], 4);
     }
     mbar_init(o_full, 1);
@@ -251,104 +262,184 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
+  if (threadIdx.x == 0) STAMP(63, 0);
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) STAMP(63, 1);
+  const int req = blockIdx.y / p.g, kvh = blockIdx.y - req * p.g;
+  const int32_t* bt = p.block_table + (size_t)req * p.table_width;
+  // The loads below are issued back to back: two round trips to memory (token range and first pages; then
+  // positions) stand between the start of a block and its first copy, not four.
+  const int page_shift = 31 - __clz(p.page_size);                   // pages are powers of two
+  const int box_shift = min(page_shift, 6);
+  const int my_box = lane / (HS / 64), my_half = lane - my_box * (HS / 64);
+  int early_page = -2;                                      // the copy warp's page of tile 0 (known before the positions are)
+  if (warp == 4 && gridDim.z == 1) {
+    const int pi = (my_box << box_shift) >> page_shift;
+    early_page = (my_box < (BN >> box_shift) && pi < p.table_width) ? bt[pi] : -1;
+  }
+  const int tok0 = p.q_start[req], q_len = p.q_start[req + 1] - tok0;
+  // Later query tiles see more keys: they are given to the first blocks, so the light ones fill the tail.
+  const int t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * p.tokens_per_tile;   // first token of this block within the request
+  bool active = t0 < q_len;                                 // uniform for the block, like everything up to the roles
+  if (active && p.skip_single && q_len == 1) {
+    // Another kernel writes this request's row; with key splits the second kernel must leave it alone.
+    if (gridDim.z > 1 && blockIdx.z == 0 && (int)threadIdx.x < p.per)
+      *reinterpret_cast<float2*>(p.part_ml + (((size_t)tok0 * p.nh + kvh * p.per + threadIdx.x) * gridDim.z) * 2) =
+          make_float2(INFINITY, 0.f);
+    active = false;
+  }
+  const int n_tok = active ? min(p.tokens_per_tile, q_len - t0) : 1;
+  const int n_rows = n_tok * p.per;
+  const int first_tok = active ? tok0 + t0 : 0;
+  const int pos_first = p.positions[first_tok];
+  const int hi_key = p.positions[first_tok + n_tok - 1];
+  // This block's share of the key tiles (all of them without splits).
+  const int all_tiles = hi_key / BN + 1;
+  const int slots = gridDim.z, split = blockIdx.z;          // slots: shares that the scratch memory has room for
+  const int wanted = slots > 1 ? min(slots, (all_tiles + p.tiles_per_split - 1) / p.tiles_per_split) : 1;
+  const int per_split = (all_tiles + wanted - 1) / wanted;
+  const int n_splits = (all_tiles + per_split - 1) / per_split;     // shares that get a tile (7 tiles in 5 shares: 4 of 2)
+  if (active && split >= n_splits) {
+    if (n_splits > 1 && (int)threadIdx.x < n_rows) {        // an unused share of a divided tile: nothing to add
+      const int t_in = threadIdx.x / p.per, head = threadIdx.x - t_in * p.per;
+      const size_t slot = ((size_t)(tok0 + t0 + t_in) * p.nh + kvh * p.per + head) * slots + split;
+      *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(-INFINITY, 0.f);
+    }
+    active = false;
+  }
+  const int tile_base = split * per_split;
+  const int n_tiles = min(all_tiles, tile_base + per_split) - tile_base;     // >= 1
+
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
+  if (threadIdx.x == 0) STAMP(63, 2);
+  if (!active) {                                            // nothing was started: give the tensor memory back and go
+    if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    return;
+  }
 
   int k_armed = 0, v_armed = 0;
   if (warp == 4) {
     // ---------------------------------- TMA producer ------------------------------------------
-    // Lane 0 waits for free buffers and arms the barriers; all lanes issue the box copies of a tile (with
-    // small pages one thread would spend longer issuing them than they take).
+    // Lane 0 waits for free buffers and arms the barriers; lane c issues box c of a tile (with small pages one
+    // thread would spend longer issuing them than they take).  A tile is fetched in boxes of min(page, BN) keys:
+    // several pages, or a part of one.
     if (lane == 0) {
       mbar_expect_tx(q_full, (uint32_t)(p.tokens_per_tile * p.per) * HS * 2);
 #pragma unroll
       for (int h = 0; h < H2; ++h)
         tma_load_3d(q_s + h * (BM * 128), &map_q, h * 64, kvh * p.per, tok0 + t0, q_full);
     }
-    // A tile is fetched in boxes of min(page, BN) keys: several pages, or a part of one.
-    const int box_rows = min(p.page_size, BN);
-    const int boxes_per_tile = BN / box_rows;
-    const uint32_t box_bytes = (uint32_t)box_rows * HS * 2;
+    const int box_rows = 1 << box_shift;
+    const int boxes_per_tile = BN >> box_shift;
+    const uint32_t box_bytes = (uint32_t)box_rows * HS * 2;         // my_box, my_half: boxes_per_tile * H2 <= 16 lanes have a box
+    // Row of this lane's box of tile j in the pool seen as a matrix (K and V pools are laid out alike), or -1.
+    auto box_row = [&](int j) -> int {
+      const int key = ((tile_base + j) << 6) + (my_box << box_shift);
+      if (j >= n_tiles || my_box >= boxes_per_tile || key > hi_key) return -1;
+      const int pi = key >> page_shift;
+      int page = (j == 0 && early_page != -2) ? early_page : (pi < p.table_width ? bt[pi] : -1);
+      if (page < 0 || page >= p.num_pages) {
+        if (p.error) atomicOr(p.error, YALIS_FLAG_BAD_PAGE);
+        page = 0;
+      }
+      return ((page * p.g + kvh) << page_shift) + (key & (p.page_size - 1));
+    };
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    auto fetch = [&](int j, int kv, int y) {
       const int b = j & 1;
       const uint32_t ph = (j >> 1) & 1;
-      const int key0 = (tile_base + j) * BN;
-      const int n_boxes = min(boxes_per_tile, (hi_key - key0) / box_rows + 1);
-      for (int kv = 0; kv < 2 && ok; ++kv) {
-        uint64_t* full = kv == 0 ? &k_full[b] : &v_full[b];
-        uint64_t* empty = kv == 0 ? &k_empty[b] : &v_empty[b];
-        unsigned char* dst = (kv == 0 ? k_s : v_s) + b * KV_BYTES;
-        const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
-        int go = 1;
-        if (lane == 0) {
-          go = mbar_wait(empty, ph ^ 1, abort_flag) ? 1 : 0;
-          if (go) mbar_expect_tx(full, box_bytes * (uint32_t)n_boxes);
-        }
-        go = __shfl_sync(0xffffffffu, go, 0);
-        if (!go) { ok = false; break; }
-        for (int c = lane; c < n_boxes * H2; c += 32) {
-          const int i = c / H2, h = c - i * H2;
-          const int key = key0 + i * box_rows;
-          const int pi = key / p.page_size;
-          int page = pi < p.table_width ? bt[pi] : -1;
-          if (page < 0 || page >= p.num_pages) {
-            if (p.error) atomicOr(p.error, YALIS_FLAG_BAD_PAGE);
-            page = 0;
-          }
-          const int y = (page * p.g + kvh) * p.page_size + (key - pi * p.page_size);
-          tma_load_2d(dst + h * (BN * 128) + i * box_rows * 128, map, h * 64, y, full);
-        }
-        __syncwarp();
-        if (kv == 0) k_armed = j + 1; else v_armed = j + 1;
+      const int n_boxes = min(boxes_per_tile, ((hi_key - ((tile_base + j) << 6)) >> box_shift) + 1);
+      uint64_t* full = kv == 0 ? &k_full[b] : &v_full[b];
+      uint64_t* empty = kv == 0 ? &k_empty[b] : &v_empty[b];
+      int go = 1;
+      if (lane == 0) {
+        go = mbar_wait(empty, ph ^ 1, abort_flag) ? 1 : 0;
+        if (go) mbar_expect_tx(full, box_bytes * (uint32_t)n_boxes);
       }
+      go = __shfl_sync(0xffffffffu, go, 0);
+      if (!go) { ok = false; return; }
+      if (lane == 0) STAMP(j, 30 + kv);
+      if (y >= 0)
+        tma_load_2d((kv == 0 ? k_s : v_s) + b * KV_BYTES + my_half * (BN * 128) + my_box * box_rows * 128,
+                    kv == 0 ? &map_k : &map_v, my_half * 64, y, full);
+      __syncwarp();
+      if (kv == 0) k_armed = j + 1; else v_armed = j + 1;
+    };
+    // K runs one tile ahead of V (their buffers come free in that order: QK(j-1), then PV(j-2)); the pages of
+    // a tile are looked up a tile before its K is asked for.
+    int y_v = box_row(0);
+    fetch(0, 0, y_v);                                       // the first keys are on their way before anything else is looked up
+    int y_k = box_row(1), y_ahead = box_row(2);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (j + 1 < n_tiles) fetch(j + 1, 0, y_k);
+      if (ok) fetch(j, 1, y_v);
+      y_v = y_k;
+      y_k = y_ahead;
+      y_ahead = box_row(j + 3);
     }
     __syncwarp();
   } else if (warp == 5) {
     // ---------------------------------- MMA issuer --------------------------------------------
-    if (lane == 0) {
+    // The whole warp runs the loop and every lane waits on the barriers itself; the elected lane issues.  (With
+    // one lane polling for the warp, blocks of four and more key tiles ran into their bounded waits.)
+    {
+      const uint32_t elected = elect_one();
       const uint32_t idesc_qk = idesc_f16(BN, false), idesc_pv = idesc_f16(HS, true);
-      const uint32_t q_addr = smem_u32(q_s);
+      const uint64_t q_desc = desc_kmajor(smem_u32(q_s));
+      const uint64_t k_desc0 = desc_kmajor(smem_u32(k_s));
+      const uint64_t v_desc0 = desc_mnmajor(smem_u32(v_s), BN * 128);
       bool ok = mbar_wait(q_full, 0, abort_flag);
+      if (lane == 0) STAMP(63, 3);
       auto issue_qk = [&](int j) -> bool {
         const int b = j & 1;
         const uint32_t ph = (j >> 1) & 1;
+        // The S buffer is free: the wait for P(j-2), which lay in it, came after every softmax thread had read
+        // S(j-2), and the product that read P(j-2) was issued before this one (products run in issue order).
         if (!mbar_wait(&k_full[b], ph, abort_flag)) return false;
-        if (!mbar_wait(&s_empty[b], ph ^ 1, abort_flag)) return false;
+        if (lane == 0 && j > 0) STAMP(j - 1, 11);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t k_addr = smem_u32(k_s + b * KV_BYTES);
+        const uint64_t k_desc = k_desc0 + (uint64_t)((b * KV_BYTES) >> 4);
 #pragma unroll
         for (int ks = 0; ks < HS / 16; ++ks) {
-          // 64-dim half (BM rows of Q, BN rows of K, 128 bytes each), then 32 bytes per 16 dims
+          // 64-dim half (BM rows of Q, BN rows of K, 128 bytes each), then 32 bytes per 16 dims; the address
+          // field of a descriptor counts 16-byte units
           const uint32_t q_off = (ks >> 2) * (BM * 128) + (ks & 3) * 32, k_off = (ks >> 2) * (BN * 128) + (ks & 3) * 32;
-          umma_ss(tmem + COL_S + b * BN, desc_kmajor(q_addr + q_off), desc_kmajor(k_addr + k_off), idesc_qk, ks > 0);
+          umma_ss(elected, tmem + COL_S + b * BN, q_desc + (q_off >> 4), k_desc + (k_off >> 4), idesc_qk, ks > 0);
         }
-        umma_commit(&s_full[b]);
-        umma_commit(&k_empty[b]);
+        umma_commit(elected, &s_full[b]);
+        umma_commit(elected, &k_empty[b]);
         return true;
       };
       if (ok) ok = issue_qk(0);
+      if (lane == 0) STAMP(63, 4);
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int b = j & 1;
         const uint32_t ph = (j >> 1) & 1;
+        if (lane == 0) STAMP(j, 6);
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);
         if (!ok) break;
+        if (lane == 0) STAMP(j, 7);
         if (!mbar_wait(&v_full[b], ph, abort_flag)) { ok = false; break; }
+        if (lane == 0) STAMP(j, 8);
         if (!mbar_wait(&p_full[b], ph, abort_flag)) { ok = false; break; }      // P(j) written, O rescaled if needed
+        if (lane == 0) STAMP(j, 9);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t v_addr = smem_u32(v_s + b * KV_BYTES);
+        const uint64_t v_desc = v_desc0 + (uint64_t)((b * KV_BYTES) >> 4);
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
           // 16 keys = two 8-key swizzle groups = 2048 bytes further; P: 16 bfloat16 = 8 columns further
-          umma_ts(tmem + COL_O, tmem + COL_S + b * BN + ks * 8, desc_mnmajor(v_addr + ks * 2048, BN * 128),
-                  idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          umma_ts(elected, tmem + COL_O, tmem + COL_S + b * BN + ks * 8, v_desc + ((ks * 2048) >> 4), idesc_pv,
+                  (j > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(o_full);
-        umma_commit(&v_empty[b]);
+        umma_commit(elected, o_full);
+        umma_commit(elected, &v_empty[b]);
+        if (lane == 0) STAMP(j, 10);
       }
-      if (ok) umma_commit(o_done);
+      if (ok) umma_commit(elected, o_done);
     }
     __syncwarp();
   } else {
@@ -364,8 +455,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       const int b = j & 1;
       const uint32_t ph = (j >> 1) & 1;
       const int key0 = (tile_base + j) * BN;
+      if (lane == 0) STAMP(j, 0 + (warp ? 6 + warp * 6 : 0));
       if (!warp_wait(&s_full[b], ph, abort_flag, lane)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (lane == 0) STAMP(j, 1 + (warp ? 6 + warp * 6 : 0));
       float sv[BN];
       {
         const uint32_t s_addr = lane_base + COL_S + b * BN;
@@ -373,10 +466,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         for (int c0 = 0; c0 < BN; c0 += 32) tmem_ld32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       }
-      // S is in registers: the buffer may be overwritten by the product after next
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[b]);
+      // S is in registers now; its buffer is written again only after P(j), which takes its place, has been used.
+      if (lane == 0) STAMP(j, 2 + (warp ? 6 + warp * 6 : 0));
       if (key0 + BN - 1 > pos_first || !valid) {           // some key of the tile is hidden from this row
 #pragma unroll
         for (int c = 0; c < BN; ++c)
@@ -384,12 +475,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       }
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < BN; c += 4) {
-        mx[0] = fmaxf(mx[0], sv[c]); mx[1] = fmaxf(mx[1], sv[c + 1]);
-        mx[2] = fmaxf(mx[2], sv[c + 2]); mx[3] = fmaxf(mx[3], sv[c + 3]);
+      for (int c = 0; c < BN; c += 8) {                    // four chains of three-input maxima
+        mx[0] = max3(mx[0], sv[c], sv[c + 1]); mx[1] = max3(mx[1], sv[c + 2], sv[c + 3]);
+        mx[2] = max3(mx[2], sv[c + 4], sv[c + 5]); mx[3] = max3(mx[3], sv[c + 6], sv[c + 7]);
       }
       const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
       const float m_new = fmaxf(m_run, m_tile);
+      if (lane == 0) STAMP(j, 3 + (warp ? 6 + warp * 6 : 0));
       // Keep the older maximum unless the new one is more than 2^8 larger: exp2 of at most 8 is
       // harmless in float32 and bfloat16, and O then needs no rescaling.
       const bool grow = (m_new - m_run > 8.0f) || (m_run == -INFINITY && m_new != -INFINITY);
@@ -412,6 +504,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         tmem_st16(p_addr + (c0 >> 1), pk);
       }
       l_run = l_run * corr + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
+      if (lane == 0) STAMP(j, 4 + (warp ? 6 + warp * 6 : 0));
       m_run = m_use;
       // Rescale O in place if some row of this warp moved its maximum (never for the first tile).
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
@@ -445,6 +538,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[b]);
+      if (lane == 0) STAMP(j, 5 + (warp ? 6 + warp * 6 : 0));
     }
     // ---- O / l -> global --------------------------------------------------------------------
     if (ok) ok = warp_wait(o_done, 0, abort_flag, lane);
@@ -614,6 +708,12 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 
 }  // namespace
 
+#ifdef YALIS_TRACE_CLOCKS
+YALIS_API int yalis_prefill_gave_up(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_gave_up, sizeof(g_gave_up)) == cudaSuccess ? 0 : -1;
+}
+#endif
+
 YALIS_API int yalis_prefill_attention_tcgen05_supports(int hs, int page_size, int per) {
   const bool page_ok = page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
   return ((hs == 64 || hs == 128) && page_ok && per >= 1 && per <= 128) ? 1 : 0;
@@ -636,7 +736,11 @@ YALIS_API int yalis_prefill_attention_tcgen05(const void* q, int q_stride, void*
                                               const int32_t* block_table, int table_width, int page_size,
                                               int num_pages, int n_tokens, int n_requests, int max_q_len, int nh,
                                               int g, int hs, float scale, int n_splits, int tiles_per_split, int skip_single,
-                                              float* scratch, int32_t* error, cudaStream_t stream) {
+                                              float* scratch, int32_t* error, cudaStream_t stream
+#ifdef YALIS_TRACE_CLOCKS
+                                              , long long* trace
+#endif
+) {
   if (n_tokens <= 0 || n_requests <= 0) return YALIS_OK;
   if (g <= 0 || nh % g != 0 || max_q_len < 1 || n_splits < 1 || n_splits > 64) return YALIS_ERR_SHAPE;
   if (n_splits > 1 && (scratch == nullptr || ((uintptr_t)scratch & 15))) return YALIS_ERR_ALIGN;
@@ -656,6 +760,9 @@ YALIS_API int yalis_prefill_attention_tcgen05(const void* q, int q_stride, void*
   p.part_o = scratch;
   p.part_ml = scratch ? scratch + (size_t)n_tokens * nh * n_splits * hs : nullptr;
   p.error = error;
+#ifdef YALIS_TRACE_CLOCKS
+  p.trace = trace;
+#endif
   CUtensorMap mq, mk, mv;
   const long long rows = (long long)num_pages * g * page_size;
   if (!make_q_map(&mq, q, n_tokens, q_stride, nh, hs, p.per, p.tokens_per_tile) ||
