@@ -43,49 +43,6 @@ def test_embedding(dtype, vocab, width):
     assert torch.equal(embedding(table, ids, from_slot=from_slot, chosen=chosen), table[want].float())
 
 
-@pytest.mark.parametrize("m, n, k, n2", [(8, 4096, 4096, 6144), (1, 512, 14336, 1024), (23, 1152, 2048, 384), (32, 4096, 1024, 2048)])
-def test_product_fused_with_the_residual_add_and_the_norm_around_it(m, n, k, n2):
-    """The weight-streaming product in its two fused forms: one that adds its result to the float32 residual
-    stream (partial sums in split order, by the last block of each tile to finish) and leaves the stream rounded
-    to bfloat16 with shares of the rows' sums of squares; and one that takes such a stream as its operand and
-    applies each row's norm factor in its epilogue (plain, with divided K, and with the gated activation)."""
-    from yalis_b200.ops.linear import (SummedStream, fused_residual_supported, gemm_wstream, gemm_wstream_silu,
-                                       linear_add_to_stream, wstream_splits)
-    eps = 1e-5
-    a = rnd(m, k, dtype=torch.bfloat16, seed=1)
-    w = rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
-    x0 = rnd(m, n, seed=3, scale=2.0)
-    if not fused_residual_supported(a, w):
-        assert wstream_splits(n, k) == 1
-        return
-    for repeat in range(2):                                   # the tickets are left as they were found
-        x = x0.clone()
-        s = linear_add_to_stream(a, w, x, eps)
-        want = x0 + a.float() @ w.float().T
-        torch.testing.assert_close(x, want, rtol=1e-4, atol=1e-3)
-        assert torch.equal(s.h, x.to(torch.bfloat16)) and s.x is x
-        torch.testing.assert_close(s.sumsq.sum(0), (x * x).sum(1), rtol=1e-4, atol=1e-3)
-    # the same twice gives the same bits (fixed order of addition)
-    x2 = x0.clone()
-    s2 = linear_add_to_stream(a, w, x2, eps)
-    assert torch.equal(x2, x) and torch.equal(s2.sumsq, s.sumsq)
-    # consumers
-    rstd = torch.rsqrt((x * x).mean(1) + eps)
-    normed = s.h.float() * rstd[:, None]
-    w2 = rnd(n2, n, dtype=torch.bfloat16, seed=4, scale=0.05)
-    want2 = normed @ w2.float().T
-    got = gemm_wstream(s.h, w2, out_dtype=torch.float32, row_scale=s)
-    torch.testing.assert_close(got, want2, rtol=2e-3, atol=2e-3 * float(want2.abs().max()))
-    parts = gemm_wstream(s.h, w2, split=True, row_scale=s)
-    torch.testing.assert_close(parts.sum(0), want2, rtol=2e-3, atol=2e-3 * float(want2.abs().max()))
-    inter = n2 // 2
-    act = gemm_wstream_silu(s.h, w2, row_scale=s)
-    gate, up = want2[:, :inter].to(torch.bfloat16).float(), want2[:, inter:].to(torch.bfloat16).float()
-    torch.testing.assert_close(act.float(), torch.nn.functional.silu(gate) * up, rtol=3e-2, atol=3e-2 * float(up.abs().max()))
-    torch.testing.assert_close(s.materialize().float(), normed, rtol=1e-2, atol=1e-2)
-    assert isinstance(s, SummedStream)
-
-
 def test_softcap_and_chosen_tokens_per_slot():
     from yalis_b200.ops.elementwise import softcap_
     from yalis_b200.ops.sampling import argmax, sample

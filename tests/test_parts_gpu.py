@@ -6,7 +6,7 @@ import torch
 import plain_llama as plain
 from ctx_helper import DEV, make_cache, make_context
 from yalis_b200.config.spec import PartSpec
-from yalis_b200.parts.base import as_tensor, ResidualStream, make_part, registered
+from yalis_b200.parts.base import ResidualStream, make_part, registered
 
 pytestmark = pytest.mark.gpu
 
@@ -59,7 +59,7 @@ def test_swiglu_part(dtype):
     ff.load({k: v.to(DEV) for k, v in w.items()})
     x = rnd(9, hidden, seed=7).to(dtype)
     ref = plain.swiglu(x.float(), w["gate_proj"].float(), w["up_proj"].float(), w["down_proj"].float())
-    torch.testing.assert_close(as_tensor(ff.forward(x.to(DEV), None)).float().cpu(), ref.to(dtype).float(), **tol(dtype))
+    torch.testing.assert_close(ff.forward(x.to(DEV), None).float().cpu(), ref.to(dtype).float(), **tol(dtype))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -97,8 +97,8 @@ def test_attention_part_in_two_steps(dtype, position_kind):
     cache = make_cache(n_pages, g, page, hs, dtype)
     # both steps must see the same pages for request a: reuse step 2's table for step 1
     ctx1.block_tables["kv_all"] = ctx2.block_tables["kv_all"][:1].contiguous()
-    y1 = as_tensor(mixer.forward(xa[:13].to(DEV), ctx1, cache))
-    y2 = as_tensor(mixer.forward(torch.cat([xa[13:], xb]).to(DEV), ctx2, cache))
+    y1 = mixer.forward(xa[:13].to(DEV), ctx1, cache)
+    y2 = mixer.forward(torch.cat([xa[13:], xb]).to(DEV), ctx2, cache)
     got_a = torch.cat([y1, y2[:8]]).float().cpu()
     torch.testing.assert_close(got_a, reference(xa).to(dtype).float(), **tol(dtype))
     torch.testing.assert_close(y2[8:].float().cpu(), reference(xb).to(dtype).float(), **tol(dtype))

@@ -32,7 +32,7 @@ from yalis_b200.config import registry
 from yalis_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from yalis_b200.ops.linear import linear
 from yalis_b200.ops.elementwise import rope_kv_write
-from yalis_b200.parts.base import Block, FeedForward, Mixer, ParamSpec, PositionEncoding, SlotState, as_tensor, register_part
+from yalis_b200.parts.base import Block, FeedForward, Mixer, ParamSpec, PositionEncoding, SlotState, register_part
 
 pytestmark = pytest.mark.gpu
 
@@ -92,8 +92,10 @@ class Sandwich(Block):
              "feed_forward": "feed_forward"}
 
     def forward(self, stream, ctx, cache):
-        y = as_tensor(self.mixer.forward(self.norm_1.forward(stream), ctx, cache))    # a deferred projection, partial sums
-        stream.add(self.after.normalize(y.to(stream.dtype)))
+        y = self.mixer.forward(self.norm_1.forward(stream), ctx, cache)
+        if y.dim() == 3:                                  # partial sums of a split product
+            y = y.sum(0).to(stream.dtype)
+        stream.add(self.after.normalize(y))
         stream.add(self.feed_forward.forward(self.norm_2.forward(stream), ctx))
 
 

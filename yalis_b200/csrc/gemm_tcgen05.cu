@@ -19,16 +19,6 @@
 // add + norm, or the rotary kernel) sums the partials in split order, which
 // keeps the result deterministic.
 //
-// Two fusions with the normalisation around a product (RMSNorm = h * rsqrt(mean(h^2) + eps) * weight, the weight
-// folded into the next product's matrix by the caller):
-//   * residual mode (splits > 1): the last block of an output tile to finish (a ticket per tile; nobody waits)
-//     adds the tile's partial sums in split order to the float32 residual stream, stores the new stream rounded
-//     to bfloat16 as the next product's operand, and leaves the tile's share of every row's sum of squares;
-//   * row scale: a product whose operand is such an un-normalised stream multiplies its accumulators by
-//     rsqrt(sum of the shares / width + eps) per row in the epilogue.
-// Together they replace the kernel that stood between two products (sum the partials, add, norm) and the two
-// kernel boundaries around it.
-//
 // Every wait on an mbarrier is bounded: after kSpinLimit failed polls a thread
 // raises the block's abort flag and the global error word, all roles leave
 // their loops, outstanding TMA transactions are waited for (bounded again),
@@ -141,15 +131,6 @@ struct GemmParams {
   int kt_per_split;     // stage steps (of 64 or 128 columns of K) per split
   int silu_inter;       // 0, or I: w is [gate (I rows); up (I rows)] and out[m, i] = silu(gate_i) * up_i, [M, I] bfloat16
   int32_t* error;       // YALIS_FLAG_WAIT_PRODUCT is raised in it if a wait ran out
-  // residual mode (resid != null; needs splits > 1, out = the partial sums)
-  float* resid;                 // [M, N] float32 residual stream, updated in place
-  __nv_bfloat16* h_out;         // [M, N] the updated stream rounded to bfloat16
-  float* sumsq_out;             // [tiles of 128 columns, M] each tile's share of the rows' sums of squares
-  int32_t* tile_tickets;        // [tiles], zero before and after
-  // row scale (rowsq != null): accumulator row m is multiplied by rsqrt(sum_t rowsq[t, m] * rowsq_inv_width + rowsq_eps)
-  const float* rowsq;
-  int rowsq_parts;
-  float rowsq_inv_width, rowsq_eps;
 };
 
 // Ring depth. A stage is 16 KB of W plus NTOK * 128 bytes of x.  Two blocks fit an SM with ~95 KB each, so that
@@ -162,17 +143,6 @@ __host__ __device__ constexpr int kblocks_for() { return NTOK <= 16 ? 2 : 1; }
 template <int NTOK>
 __host__ __device__ constexpr int stages_for() {
   return NTOK <= 16 ? 3 : NTOK <= 32 ? 5 : NTOK <= 64 ? 4 : NTOK <= 128 ? 3 : 4;
-}
-
-// The scale of every row of a product whose operand is an un-normalised stream: thread t of the 128 epilogue
-// threads computes rows t, t + 128 (shares added in tile order), all meet at named barrier 2.
-__device__ __forceinline__ void row_scales(const GemmParams& p, float* row_scale, int t) {
-  for (int m = t; m < p.M; m += 128) {
-    float sum = 0.f;
-    for (int part = 0; part < p.rowsq_parts; ++part) sum += p.rowsq[(size_t)part * p.M + m];
-    row_scale[m] = rsqrtf(sum * p.rowsq_inv_width + p.rowsq_eps);
-  }
-  asm volatile("bar.sync 2, 128;" ::: "memory");
 }
 
 // SILU: the gated-activation epilogue (p.silu_inter > 0).  A variant of its own: its extra registers would also
@@ -332,8 +302,6 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       // Warps 0 and 1 of the epilogue hold the gate rows, warps 2 and 3 the up rows of the same 64 outputs:
       // the up values cross through shared memory (the ring is free by now), 16 tokens at a time, two buffers.
       float* ex = reinterpret_cast<float*>(a_s);            // [2][16 tokens][64 outputs]
-      float* row_scale = ex + 2 * 16 * 64;                   // [256], behind the exchange buffers
-      if (p.rowsq != nullptr) row_scales(p, row_scale, (warp - 2) * 32 + lane);
       const int col = (q & 1) * 32 + lane;                   // output within the tile
       const int n = n0 + col;
 #pragma unroll
@@ -354,9 +322,8 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (m < p.M) {
               // both factors rounded to bfloat16 first: the same bits as the unfused product followed by the
               // activation kernel
-              const float rs = p.rowsq != nullptr ? row_scale[m] : 1.0f;
-              const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i]) * rs));
-              const float u = __bfloat162float(__float2bfloat16_rn(buf[i * 64 + col] * rs));
+              const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));
+              const float u = __bfloat162float(__float2bfloat16_rn(buf[i * 64 + col]));
               reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(silu_bf16_path(g) * u);
             }
           }
@@ -364,8 +331,6 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
     } else if (!SILU && ok) {
       const int n = n0 + q * 32 + lane;
-      float* row_scale = reinterpret_cast<float*>(a_s);        // [256]; the ring is free once the accumulator is complete
-      if (p.rowsq != nullptr) row_scales(p, row_scale, (warp - 2) * 32 + lane);
 #pragma unroll
       for (int c0 = 0; c0 < NTOK; c0 += 16) {
         uint32_t r[16];
@@ -381,8 +346,7 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           for (int i = 0; i < 16; ++i) {
             const int m = c0 + i;
             if (m < p.M) {
-              float v = __uint_as_float(r[i]);
-              if (p.rowsq != nullptr) v *= row_scale[m];
+              const float v = __uint_as_float(r[i]);
               if (p.splits > 1) {
                 reinterpret_cast<float*>(p.out)[((size_t)split * p.M + m) * (size_t)p.ldo + n] = v;
               } else if (p.out_dtype == YALIS_F32) {
@@ -392,35 +356,6 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
               }
             }
           }
-        }
-      }
-      if (p.resid != nullptr) {
-        // ---- residual mode: whoever finishes this tile last adds its partial sums to the stream ----
-        int32_t* ticket_s = reinterpret_cast<int32_t*>(a_s + 1024);
-        float* red = reinterpret_cast<float*>(a_s + 2048);     // [4 warps][M <= 256]
-        __threadfence();                                       // this block's partial sums before its ticket
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (warp == 2 && lane == 0) *ticket_s = atomicAdd(&p.tile_tickets[blockIdx.x], 1);
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (*ticket_s == p.splits - 1) {
-          __threadfence();                                     // the other blocks' partial sums after their tickets
-          const float* part = reinterpret_cast<const float*>(p.out);
-          for (int m = 0; m < p.M; ++m) {
-            float sq = 0.f;
-            if (n < p.N) {
-              const size_t at = (size_t)m * p.ldo + n;
-              const float h = p.resid[at] + sum_parts<float>(part + at, p.splits, (size_t)p.M * p.ldo);   // in split order
-              p.resid[at] = h;
-              p.h_out[at] = __float2bfloat16_rn(h);
-              sq = h * h;
-            }
-            sq = warp_sum(sq);
-            if (lane == 0) red[q * 256 + m] = sq;
-          }
-          asm volatile("bar.sync 2, 128;" ::: "memory");
-          for (int m = (warp - 2) * 32 + lane; m < p.M; m += 128)
-            p.sumsq_out[(size_t)blockIdx.x * p.M + m] = (red[m] + red[256 + m]) + (red[512 + m] + red[768 + m]);
-          if (warp == 2 && lane == 0) p.tile_tickets[blockIdx.x] = 0;      // as the next launch expects to find it
         }
       }
     }
@@ -589,19 +524,8 @@ YALIS_API int yalis_gemm_wstream_splits(int N, int K) {
 // out = x[M, K] . w[N, K]^T, bfloat16 operands.  splits must be yalis_gemm_wstream_splits(N, K) or 1;
 // with splits > 1, out is float32 [splits, M, N] (ldo = N).  error: device int32 raised on a timed-out wait.
 namespace {
-struct Fusion {
-  float* resid = nullptr;
-  __nv_bfloat16* h_out = nullptr;
-  float* sumsq_out = nullptr;
-  int32_t* tile_tickets = nullptr;
-  const float* rowsq = nullptr;
-  int rowsq_parts = 0;
-  float rowsq_inv_width = 0.f, rowsq_eps = 0.f;
-};
-
 int gemm_wstream_impl(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype, long long ldo,
-                      int M, int N, int K, int splits, int silu_inter, int32_t* error, cudaStream_t stream,
-                      const Fusion& f = Fusion()) {
+                      int M, int N, int K, int splits, int silu_inter, int32_t* error, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return YALIS_OK;
   if (M > 256 || K <= 0 || splits < 1) return YALIS_ERR_SHAPE;
   if ((K % 8) || (ldx % 8) || (ldw % 8)) return YALIS_ERR_ALIGN;          // TMA: 16-byte strides
@@ -619,12 +543,6 @@ int gemm_wstream_impl(const void* x, long long ldx, const void* w, long long ldw
   p.kt_per_split = (kt + splits - 1) / splits;
   p.silu_inter = silu_inter;
   p.error = error;
-  if (f.resid != nullptr && (splits < 2 || silu_inter || f.h_out == nullptr || f.sumsq_out == nullptr ||
-                             f.tile_tickets == nullptr || ldo != N))
-    return YALIS_ERR_SHAPE;
-  if (f.rowsq != nullptr && (f.rowsq_parts < 1 || !(f.rowsq_inv_width > 0.f))) return YALIS_ERR_SHAPE;
-  p.resid = f.resid; p.h_out = f.h_out; p.sumsq_out = f.sumsq_out; p.tile_tickets = f.tile_tickets;
-  p.rowsq = f.rowsq; p.rowsq_parts = f.rowsq_parts; p.rowsq_inv_width = f.rowsq_inv_width; p.rowsq_eps = f.rowsq_eps;
   switch (ntok) {
     case 16: return launch<16>(mw, mx, p, stream);
     case 32: return launch<32>(mw, mx, p, stream);
@@ -639,26 +557,6 @@ YALIS_API int yalis_gemm_wstream(const void* x, long long ldx, const void* w, lo
                                  long long ldo, int M, int N, int K, int splits, int32_t* error,
                                  cudaStream_t stream) {
   return gemm_wstream_impl(x, ldx, w, ldw, out, out_dtype, ldo, M, N, K, splits, 0, error, stream);
-}
-
-// Tiles of 128 output columns of a product with N outputs (the rows of a sum-of-squares buffer).
-YALIS_API int yalis_gemm_wstream_tiles(int N) { return (N + TILE_N - 1) / TILE_N; }
-
-// The product with the fusions described at the top of the file; any of the two groups of arguments may be null.
-//   resid, h_out, sumsq_out, tile_tickets: residual mode.  out must be the float32 partial sums [splits, M, N] with
-//     splits = yalis_gemm_wstream_splits(N, K) >= 2; resid [M, N] float32 is updated in place, h_out [M, N] bfloat16
-//     and sumsq_out [tiles, M] float32 are written, tile_tickets [tiles] int32 must be zero and is left zero.
-//   rowsq [rowsq_parts, M], rowsq_inv_width, rowsq_eps: the scale of row m of the result.
-// silu_inter > 0 selects the gated-activation epilogue (then N = 2 * silu_inter, splits = 1, out [M, silu_inter]).
-YALIS_API int yalis_gemm_wstream_fused(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
-                                       long long ldo, int M, int N, int K, int splits, int silu_inter, float* resid,
-                                       void* h_out, float* sumsq_out, int32_t* tile_tickets, const float* rowsq,
-                                       int rowsq_parts, float rowsq_inv_width, float rowsq_eps, int32_t* error,
-                                       cudaStream_t stream) {
-  Fusion f;
-  f.resid = resid; f.h_out = reinterpret_cast<__nv_bfloat16*>(h_out); f.sumsq_out = sumsq_out; f.tile_tickets = tile_tickets;
-  f.rowsq = rowsq; f.rowsq_parts = rowsq_parts; f.rowsq_inv_width = rowsq_inv_width; f.rowsq_eps = rowsq_eps;
-  return gemm_wstream_impl(x, ldx, w, ldw, out, out_dtype, ldo, M, N, K, splits, silu_inter, error, stream, f);
 }
 
 // The gated activation fused into the product: w is [2 * inter, K] with the gate rows first and the up rows

@@ -73,7 +73,6 @@ class Model:
             names = self._layer_tensor_names(li)
             for slot, part in block.parts.items():
                 part.load({local: fetch(name) for local, name in names[slot].items()})
-            block.after_load()
         self.final_norm.load({local: fetch(s.final_norm_names[local]) for local in self.final_norm.param_specs()})
         self.head = self.embedding if s.head_name is None else fetch(s.head_name).contiguous()
 

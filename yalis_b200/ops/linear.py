@@ -20,15 +20,13 @@ import torch
 
 import os
 
-from ._lib import check, dtype_code, error_word, f32, i32, i64, lib, need, need_cuda, ptr, stream
+from ._lib import check, dtype_code, error_word, i32, i64, lib, need, need_cuda, ptr, stream
 
 # YALIS_B200_NO_WSTREAM=1 sends every bfloat16 product to the library (for comparisons).
 USE_WSTREAM = os.environ.get("YALIS_B200_NO_WSTREAM", "0") != "1"
 # YALIS_B200_NO_FUSED_SILU=1 keeps the gated activation in its own kernel.
 USE_FUSED_SILU = os.environ.get("YALIS_B200_NO_FUSED_SILU", "0") != "1"
 FUSED_SILU_MAX_TOKENS = 16
-# YALIS_B200_NO_FUSED_NORM=1 keeps the residual add and the norm between two products in a kernel of their own.
-USE_FUSED_NORM = os.environ.get("YALIS_B200_NO_FUSED_NORM", "0") != "1"
 
 
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
@@ -51,63 +49,8 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype]
     return out
 
 
-class SummedStream:
-    """The residual stream after a product's output has been added to it, not yet normalised: what the next
-    product takes as its operand when the norm between them is folded into the two products.
-
-    ``h``: the stream rounded to bfloat16 [N, width]; ``sumsq``: float32 [parts, N], shares of each row's sum of
-    squares; the norm of row n is ``h[n] * rsqrt(sum(sumsq[:, n]) / width + eps)`` (the norm's weight sits in the
-    next product's matrix).  ``x`` is the float32 stream itself, for consumers that need the normed rows as a tensor.
-    """
-
-    def __init__(self, h: torch.Tensor, sumsq: torch.Tensor, eps: float, x: torch.Tensor):
-        self.h, self.sumsq, self.eps, self.x = h, sumsq, float(eps), x
-
-    dtype = property(lambda self: self.h.dtype)
-    device = property(lambda self: self.h.device)
-    shape = property(lambda self: self.h.shape)
-
-    def materialize(self) -> torch.Tensor:
-        """The normed rows (without the norm's weight, which the consumer's matrix holds) as a tensor."""
-        from .elementwise import add_rmsnorm
-        ones = _ones(self.x.shape[1], self.x.device)
-        return add_rmsnorm(self.x, None, ones, self.eps, self.h.dtype, rows=_all_rows(self.x.shape[0], self.x.device))
-
-
-_ones_cache, _rows_cache, _ticket_cache = {}, {}, {}
-
-
-def _ones(width: int, device) -> torch.Tensor:
-    key = (width, torch.device(device))
-    if key not in _ones_cache:
-        _ones_cache[key] = torch.ones(width, dtype=torch.float32, device=device)
-    return _ones_cache[key]
-
-
-def _all_rows(n: int, device) -> torch.Tensor:
-    key = (n, torch.device(device))
-    if key not in _rows_cache:
-        _rows_cache[key] = torch.arange(n, dtype=torch.int32, device=device)
-    return _rows_cache[key]
-
-
-def _tile_tickets(device, n: int) -> torch.Tensor:
-    """Zeroed int32 counters, one per output tile; every launch leaves them zero, so one buffer per device is
-    allocated once (outside any recording) and shared."""
-    key = torch.device(device)
-    t = _ticket_cache.get(key)
-    if t is None or t.numel() < n:
-        t = _ticket_cache[key] = torch.zeros(max(n, 2048), dtype=torch.int32, device=key)
-    return t
-
-
-def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """The projection used by the parts: picks the kernel by dtype and size (see module docstring).
-    ``x`` may be a ``SummedStream`` (the norm before this product is folded into it)."""
-    if isinstance(x, SummedStream):
-        if wstream_preferred(x.h, w):
-            return gemm_wstream(x.h, w, out_dtype=out_dtype or x.dtype, row_scale=x)
-        x = x.materialize()
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """The projection used by the parts: picks the kernel by dtype and size (see module docstring)."""
     need_cuda("linear", x, w)
     out_dtype = out_dtype or x.dtype
     if x.dtype == torch.float32:
@@ -121,51 +64,12 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch
     return torch.mm(x, w.t(), out_dtype=torch.float32)
 
 
-def linear_partial(x, w: torch.Tensor) -> torch.Tensor:
+def linear_partial(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """A projection whose consumer can add partial sums: returns [M, N] in x's dtype, or
     float32 partial sums [S, M, N] when the weight-streaming kernel divides K among blocks."""
-    h = x.h if isinstance(x, SummedStream) else x
-    if wstream_preferred(h, w) and wstream_splits(w.shape[0], w.shape[1]) > 1:
-        return gemm_wstream(h, w, split=True, row_scale=x if isinstance(x, SummedStream) else None)
+    if wstream_preferred(x, w) and wstream_splits(w.shape[0], w.shape[1]) > 1:
+        return gemm_wstream(x, w, split=True)
     return linear(x, w)
-
-
-class DeferredLinear:
-    """``x @ w.T`` that has not been computed yet: what a part hands to the residual stream as its output when
-    its last operation is a projection, so that whoever adds it to the stream may fuse the two."""
-
-    def __init__(self, x: torch.Tensor, w: torch.Tensor):
-        self.x, self.w = x, w
-
-    def compute(self) -> torch.Tensor:
-        return linear_partial(self.x, self.w)
-
-
-def fused_residual_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether ``linear_add_to_stream`` takes this product: the weight-streaming kernel with K divided among blocks."""
-    return (USE_FUSED_NORM and wstream_preferred(x, w) and wstream_splits(w.shape[0], w.shape[1]) > 1)
-
-
-def linear_add_to_stream(x: torch.Tensor, w: torch.Tensor, stream_x: torch.Tensor, eps: float) -> SummedStream:
-    """stream_x += x @ w.T (float32, partial sums added in split order by the last block of each output tile to
-    finish); returns the updated stream as a ``SummedStream`` for the next product."""
-    name = "linear_add_to_stream"
-    need_cuda(name, x, w, stream_x)
-    need(fused_residual_supported(x, w), name, "needs the weight-streaming kernel with divided K")
-    m, k = x.shape
-    n = w.shape[0]
-    need(stream_x.dtype == torch.float32 and stream_x.shape == (m, n) and stream_x.is_contiguous(), name,
-         "the stream must be contiguous float32 [tokens, outputs]")
-    splits = wstream_splits(n, k)
-    tiles = int(lib().yalis_gemm_wstream_tiles(i32(n)))
-    parts = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
-    h = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
-    sumsq = torch.empty((tiles, m), dtype=torch.float32, device=x.device)
-    check(lib().yalis_gemm_wstream_fused(
-        ptr(x), i64(x.stride(0)), ptr(w), i64(w.stride(0)), ptr(parts), i32(dtype_code(torch.float32)), i64(n), i32(m), i32(n),
-        i32(k), i32(splits), i32(0), ptr(stream_x), ptr(h), ptr(sumsq), ptr(_tile_tickets(x.device, tiles)), ptr(None), i32(0),
-        f32(0.0), f32(0.0), ptr(wstream_error_flag(x.device)), stream()), name)
-    return SummedStream(h, sumsq, eps, stream_x)
 
 
 # ---- the tcgen05 weight-streaming product (csrc/gemm_tcgen05.cu) -------------------------------
@@ -197,23 +101,13 @@ def wstream_preferred(x: torch.Tensor, w: torch.Tensor) -> bool:
     return USE_WSTREAM and x.dtype == torch.bfloat16 and x.shape[0] <= WSTREAM_PREFERRED_TOKENS and wstream_supports(x, w)
 
 
-def _row_scale_args(row_scale, m: int, k: int):
-    if row_scale is None:
-        return ptr(None), i32(0), f32(0.0), f32(0.0)
-    sq = row_scale.sumsq
-    need(sq.dtype == torch.float32 and sq.dim() == 2 and sq.shape[1] == m and sq.is_contiguous() and sq.is_cuda, "row_scale",
-         "sums of squares must be contiguous float32 [parts, rows]")
-    return ptr(sq), i32(sq.shape[0]), f32(1.0 / k), f32(row_scale.eps)
-
-
 def gemm_wstream(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-                 split: bool = False, row_scale: Optional[SummedStream] = None) -> torch.Tensor:
+                 split: bool = False) -> torch.Tensor:
     """x [M <= 256, K] . w [N, K]^T on tcgen05 tensor cores with TMA-streamed weights.
 
     ``split=False``: returns [M, N] in ``out_dtype``.  ``split=True``: the K range may be
     divided among blocks (decided by the shape); returns float32 partial sums [S, M, N]
-    that the consumer adds in order (S may be 1).  ``row_scale``: row m of the result is
-    multiplied by the norm factor of row m of that stream (x is then its ``h``)."""
+    that the consumer adds in order (S may be 1)."""
     name = "gemm_wstream"
     need_cuda(name, x, w)
     need(wstream_supports(x, w), name, "needs bfloat16, at most 256 tokens, K % 8 == 0, 16-byte aligned rows")
@@ -227,22 +121,15 @@ def gemm_wstream(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torc
     else:
         out = torch.empty((m, n), dtype=out_dtype, device=x.device)
         code = dtype_code(out_dtype)
-    if row_scale is None:
-        check(lib().yalis_gemm_wstream(ptr(x), i64(x.stride(0)), ptr(w), i64(w.stride(0)), ptr(out), i32(code), i64(n),
-                                       i32(m), i32(n), i32(k), i32(splits), ptr(wstream_error_flag(x.device)), stream()),
-              name)
-        return out
-    check(lib().yalis_gemm_wstream_fused(
-        ptr(x), i64(x.stride(0)), ptr(w), i64(w.stride(0)), ptr(out), i32(code), i64(n), i32(m), i32(n), i32(k), i32(splits),
-        i32(0), ptr(None), ptr(None), ptr(None), ptr(None), *_row_scale_args(row_scale, m, k),
-        ptr(wstream_error_flag(x.device)), stream()), name)
+    check(lib().yalis_gemm_wstream(ptr(x), i64(x.stride(0)), ptr(w), i64(w.stride(0)), ptr(out), i32(code), i64(n),
+                                   i32(m), i32(n), i32(k), i32(splits), ptr(wstream_error_flag(x.device)), stream()),
+          name)
     return out
 
 
-def gemm_wstream_silu(x: torch.Tensor, w_gate_up: torch.Tensor, row_scale: Optional[SummedStream] = None) -> torch.Tensor:
+def gemm_wstream_silu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x . Wgate^T) * (x . Wup^T) in one kernel: ``w_gate_up`` is [2 * inter, K] with the gate rows
-    first.  Returns [M, inter] bfloat16 with the same bits as ``silu_mul(gemm_wstream(x, w_gate_up))``.
-    ``row_scale`` as for ``gemm_wstream`` (applied to both products before the activation)."""
+    first.  Returns [M, inter] bfloat16 with the same bits as ``silu_mul(gemm_wstream(x, w_gate_up))``."""
     name = "gemm_wstream_silu"
     need_cuda(name, x, w_gate_up)
     need(wstream_supports(x, w_gate_up), name, "needs bfloat16, at most 256 tokens, K % 8 == 0, 16-byte aligned rows")
@@ -251,26 +138,19 @@ def gemm_wstream_silu(x: torch.Tensor, w_gate_up: torch.Tensor, row_scale: Optio
     m, k = x.shape
     inter = w_gate_up.shape[0] // 2
     out = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
-    if row_scale is None:
-        check(lib().yalis_gemm_wstream_silu(ptr(x), i64(x.stride(0)), ptr(w_gate_up), i64(w_gate_up.stride(0)), ptr(out),
-                                            i64(inter), i32(m), i32(inter), i32(k), ptr(wstream_error_flag(x.device)),
-                                            stream()), name)
-        return out
-    check(lib().yalis_gemm_wstream_fused(
-        ptr(x), i64(x.stride(0)), ptr(w_gate_up), i64(w_gate_up.stride(0)), ptr(out), i32(dtype_code(torch.bfloat16)), i64(inter),
-        i32(m), i32(2 * inter), i32(k), i32(1), i32(inter), ptr(None), ptr(None), ptr(None), ptr(None),
-        *_row_scale_args(row_scale, m, k), ptr(wstream_error_flag(x.device)), stream()), name)
+    check(lib().yalis_gemm_wstream_silu(ptr(x), i64(x.stride(0)), ptr(w_gate_up), i64(w_gate_up.stride(0)), ptr(out),
+                                        i64(inter), i32(m), i32(inter), i32(k), ptr(wstream_error_flag(x.device)),
+                                        stream()), name)
     return out
 
 
-def linear_silu_mul(x, w_gate_up: torch.Tensor) -> torch.Tensor:
+def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """The gated activation of a feed-forward: silu(gate) * up of the product with [Wgate; Wup];
-    fused into the product where the weight-streaming kernel takes the shape.  ``x`` may be a ``SummedStream``."""
+    fused into the product where the weight-streaming kernel takes the shape."""
     from .elementwise import silu_mul
     # Measured on the Llama-3-8B shape: the fused epilogue wins up to 16 tokens (one chunk of tensor-memory
     # columns); from 17 on its blocks, heavier in registers and TMA requests, slow the products around it by more
     # than the activation kernel costs.
-    h = x.h if isinstance(x, SummedStream) else x
-    if USE_FUSED_SILU and h.shape[0] <= FUSED_SILU_MAX_TOKENS and wstream_preferred(h, w_gate_up):
-        return gemm_wstream_silu(h, w_gate_up, row_scale=x if isinstance(x, SummedStream) else None)
+    if USE_FUSED_SILU and x.shape[0] <= FUSED_SILU_MAX_TOKENS and wstream_preferred(x, w_gate_up):
+        return gemm_wstream_silu(x, w_gate_up)
     return silu_mul(linear(x, w_gate_up))

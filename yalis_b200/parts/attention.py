@@ -17,7 +17,7 @@ import torch
 
 from yalis_b200.config.spec import PartSpec
 from yalis_b200.ops import attention as attn_ops
-from yalis_b200.ops.linear import DeferredLinear, linear_partial
+from yalis_b200.ops.linear import linear_partial
 from .base import NOT_ROTARY, Mixer, PagedKV, PagedKVCache, ParamSpec, PositionEncoding, register_part
 
 
@@ -55,12 +55,6 @@ class PagedAttention(Mixer):
         self.w_qkv = torch.cat([tensors["q_proj"], tensors["k_proj"], tensors["v_proj"]], dim=0).contiguous()
         self.w_o = tensors["o_proj"].contiguous()
 
-    def fold_input_scale(self, weight: torch.Tensor) -> bool:
-        if self.w_qkv is None or self.w_qkv.dtype != torch.bfloat16:
-            return False           # the float32 path keeps the reference's order of operations
-        self.w_qkv = (self.w_qkv.float() * weight.float()[None, :]).to(torch.bfloat16).contiguous()
-        return True
-
     def cache_request(self) -> PagedKV:
         return PagedKV(self.g, self.hs, self.window)
 
@@ -90,11 +84,11 @@ class PagedAttention(Mixer):
                     n_splits=attn_ops.decode_tma_splits(ctx.n_requests, self.g, attn_ops.step_kind(ctx)[1]),
                     error_flag=ctx.error_flag,
                     early_fetch=bool(getattr(ctx, "settled", False)))
-                return DeferredLinear(y, self.w_o)
+                return linear_partial(y, self.w_o)
         q = self.position.encode_and_store(qkv, self.nh, self.g, self.hs, ctx, cache, dtype=x.dtype)
         y = attn_ops.paged_attention(q, cache.k, cache.v, ctx, cache.group, self.nh, self.g, self.hs,
                                      scale=self.scale, window=self.window)
-        return DeferredLinear(y, self.w_o)             # the residual stream computes and adds it
+        return linear_partial(y, self.w_o)             # the residual stream adds the partial sums
 
 
 register_part("mixer", "paged_attention", PagedAttention)

@@ -106,41 +106,28 @@ class SlotStateCache:
 
 # ---- the residual stream ----------------------------------------------------------
 
-def as_tensor(y):
-    """A part's output as a tensor [N, width]: a projection that was left to the residual stream
-    (``ops.linear.DeferredLinear``) is computed, float32 partial sums [S, N, width] are added up."""
-    if hasattr(y, "compute"):
-        y = y.compute()
-    if y.dim() == 3:
-        y = y.sum(0)
-    return y
-
-
 class ResidualStream:
     """The float32 residual stream [N, hidden] with one pending delta.
 
     A sub-layer's output is not added at once: it is parked in ``pending`` and
     the next norm adds it while it reads the stream (one pass instead of two).
-    ``pending`` is [N, hidden] in the model dtype, float32 split partial sums
-    [S, N, hidden] that are added in order, or a projection that has not been
-    computed yet (``ops.linear.DeferredLinear``), which the next norm may fuse
-    with the addition.
+    ``pending`` is [N, hidden] in the model dtype, or float32 split partial sums
+    [S, N, hidden] that are added in order.
     """
 
     def __init__(self, x: torch.Tensor, dtype: torch.dtype):
         self.x = x
         self.dtype = dtype
-        self.pending = None
+        self.pending: Optional[torch.Tensor] = None
 
-    def add(self, delta) -> None:
+    def add(self, delta: torch.Tensor) -> None:
         self.flush()
         self.pending = delta
 
     def flush(self) -> None:
         if self.pending is not None:
             from yalis_b200.ops.elementwise import residual_add
-            delta = self.pending.compute() if hasattr(self.pending, "compute") else self.pending
-            residual_add(self.x, delta)
+            residual_add(self.x, self.pending)
             self.pending = None
 
 
@@ -172,12 +159,6 @@ class Part:
         kernels whatever the requests' lengths are."""
         return NOT_CAPTURABLE
 
-    def fold_input_scale(self, weight: torch.Tensor) -> bool:
-        """Offered by a block to the part that follows one of its norms: multiply the columns of the matrix
-        that the part's input first meets by ``weight`` (the norm's), so that the norm itself need not.
-        Return True if that was done; the default declines."""
-        return False
-
     def matrix_flops_per_token(self) -> float:
         """Floating-point operations per token in this part's matrix products (2 per weight of every 2-D tensor)."""
         return float(sum(2 * ps.shape[0] * ps.shape[1] for ps in self.param_specs().values() if len(ps.shape) == 2))
@@ -192,15 +173,6 @@ class Norm(Part):
     def normalize(self, y: torch.Tensor) -> torch.Tensor:
         """The norm of a plain tensor [N, width] in its own dtype (for arrangements that norm a sub-layer's
         output rather than the stream)."""
-        raise NotImplementedError
-
-    def foldable_weight(self) -> Optional[torch.Tensor]:
-        """The per-column scale that is this norm's last step, if the part after it may take it over
-        (``Part.fold_input_scale``); None for norms that end differently."""
-        return None
-
-    def weight_folded(self) -> None:
-        """Told by the block that the part after this norm has taken the scale over."""
         raise NotImplementedError
 
 
@@ -268,10 +240,6 @@ class Block(Part):
 
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
         raise NotImplementedError
-
-    def after_load(self) -> None:
-        """Called once when all parts of the block have their tensors (for arrangements that fold one part's
-        tensors into another's)."""
 
     def cache_request(self):
         mixers = [p for p in self.parts.values() if isinstance(p, Mixer)]

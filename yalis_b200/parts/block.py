@@ -19,13 +19,5 @@ class PreNormResidualBlock(Block):
         h = self.norm_2.forward(stream)
         stream.add(self.feed_forward.forward(h, ctx))
 
-    def after_load(self) -> None:
-        # A norm's scale may move into the matrix behind it: then the norm in front of a product can be fused
-        # with the products on both sides (see ops.linear.linear_add_to_stream).
-        for norm, part in ((self.norm_1, self.mixer), (self.norm_2, self.feed_forward)):
-            weight = norm.foldable_weight()
-            if weight is not None and part.fold_input_scale(weight):
-                norm.weight_folded()
-
 
 register_part("block", "pre_norm_residual", PreNormResidualBlock)

@@ -11,7 +11,7 @@ from typing import Dict, Optional
 import torch
 
 from yalis_b200.config.spec import PartSpec
-from yalis_b200.ops.linear import DeferredLinear, linear_silu_mul
+from yalis_b200.ops.linear import linear_partial, linear_silu_mul
 from .base import FeedForward, ParamSpec, register_part
 
 
@@ -36,14 +36,8 @@ class SwiGLU(FeedForward):
         self.w_gate_up = torch.cat([tensors["gate_proj"], tensors["up_proj"]], dim=0).contiguous()
         self.w_down = tensors["down_proj"].contiguous()
 
-    def fold_input_scale(self, weight: torch.Tensor) -> bool:
-        if self.w_gate_up is None or self.w_gate_up.dtype != torch.bfloat16:
-            return False
-        self.w_gate_up = (self.w_gate_up.float() * weight.float()[None, :]).to(torch.bfloat16).contiguous()
-        return True
-
-    def forward(self, x, ctx):
-        return DeferredLinear(linear_silu_mul(x, self.w_gate_up), self.w_down)
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        return linear_partial(linear_silu_mul(x, self.w_gate_up), self.w_down)
 
     def capture_key(self, host):
         return None
