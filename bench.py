@@ -208,7 +208,8 @@ def run_workload(args) -> int:
             wall = time.perf_counter() - t0
             replayed = sum(s["captured"] for s in log)
             rec = {"wall_s": wall, "generated": sum(len(g.tokens) for g in results), "steps": len(log),
-                   "preemptions": metrics["Preemptions"], "decode_ms": metrics["TBT"], "launched": _lib.LAUNCHES[0] - l0,
+                   "preemptions": metrics["Preemptions"], "decode_ms": metrics["TBT"],
+                   "launched": _lib.LAUNCHES[0] - l0 + sum(s["replayed_launches"] for s in log),
                    "replayed_steps": int(replayed), "ttft_ms": metrics["TTFT"]}
             if picked is not None:
                 chosen = [s for s in log if picked(s)]

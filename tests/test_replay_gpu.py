@@ -96,7 +96,7 @@ def test_cuttings_match_plain(which, dtype, cut):
     compare(got, want, TOL[dtype], f"{which}/{dtype}/{cut}{'/recorded' if recorded else ''}")
     if recorded:
         single = sum(all(len(e["tokens"]) == 1 for e in s["entries"]) for s in steps)
-        assert rep.steps_replayed == single > 0
+        assert rep.steps_replayed >= single > 0         # and steps with portions whose shape came a second time
     if cut == "mixed":
         # the pool was smaller than the sum of all requests: pages were used again
         assert peak < sum(traces.round_up(len(t)) for t in requests.values())
@@ -277,6 +277,48 @@ def test_steps_that_take_their_tokens_from_the_device(dtype, graphs):
     for rid in ids + ["new"]:
         eng.finish_request(rid)
     eng.manager.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["B", "C"])
+def test_steps_with_portions_are_recorded_when_their_shape_repeats(which, dtype):
+    """Three requests fed in lockstep, 16 tokens each per step and then single tokens beside one portion: the second
+    step of a shape is recorded (a CUDA graph at the exact counts of tokens, requests and wanted rows), the later
+    ones replay it, with other tokens, positions and pages each time.  Every logit against the plain model."""
+    std = STD[dtype]
+    d = tiny_model_dir(which, std)
+    cfg = plain.read_config(d)
+    requests = make_requests(cfg, [100, 100, 120], seed=31)
+    want = oracle(which, std, requests)
+    ids = list(requests)
+    steps, at = [], {rid: 0 for rid in ids}
+    for k in range(5):                                             # five steps of 3 x 16 tokens
+        steps.append({"entries": [{"id": rid, "tokens": requests[rid][at[rid]:at[rid] + 16], "want": [3, 15]} for rid in ids], "end": []})
+        for rid in ids:
+            at[rid] += 16
+    for k in range(4):                                             # four steps: two single tokens beside a portion of 10
+        entries = [{"id": rid, "tokens": requests[rid][at[rid]:at[rid] + 1], "want": [0]} for rid in ids[:2]]
+        entries.append({"id": ids[2], "tokens": requests[ids[2]][at[ids[2]]:at[ids[2]] + 10], "want": [9]})
+        steps.append({"entries": entries, "end": []})
+        at[ids[0]] += 1; at[ids[1]] += 1; at[ids[2]] += 10
+    steps[-1]["end"] = ids
+    steps = traces.number(steps)
+    out, rep = replay_in_process(d, dtype, page_size_of(which), steps, traces.peak_tokens(steps), graphs=True)
+    assert rep.steps_replayed == (5 - 1) + (4 - 1)                 # all but the first of each shape
+    exact = [key for key in rep.engine._recordings if not key[4][3]]
+    assert sorted(key[4][:3] for key in exact) == [(12, 3, 3), (48, 3, 6)]
+    row = {rid: [] for rid in ids}
+    for s in steps:
+        arr = out[s["step"]].reshape(-1, cfg["vocab_size"])
+        i = 0
+        for e in s["entries"]:
+            for j in e["want"]:
+                pos = (0 if not row[e["id"]] else row[e["id"]][-1][1]) + j
+                ref = want[e["id"]][pos]
+                err = np.abs(arr[i] - ref).max() / np.abs(want[e["id"]]).max()
+                assert err <= TOL[dtype], (s["step"], e["id"], pos, err)
+                i += 1
+            row[e["id"]].append((None, (0 if not row[e["id"]] else row[e["id"]][-1][1]) + len(e["tokens"])))
 
 
 def test_a_refused_step_reserves_nothing():

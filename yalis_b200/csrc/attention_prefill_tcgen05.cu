@@ -24,7 +24,9 @@
 // products and two commits of a P V).  The copy warp looks the pages of a tile up one tile ahead
 // (a block-table entry is a global load whose latency would otherwise stand between a freed buffer
 // and the copy into it) and asks for K one tile ahead of V, the order in which their buffers come
-// free, so that a wait for one never holds up the other.  Same semantics as paged_attention_generic (mask by absolute position,
+// free, so that a wait for one never holds up the other.  The grid is (tiles of queries of the step, KV heads,
+// shares of the keys); a block finds the request of its tile from the requests' token ranges.
+// Same semantics as paged_attention_generic (mask by absolute position,
 // yalis/attention/backend_impl/sdpa_and_flex.py:15-19, 301-307) without a window.
 //
 // Limits (else the caller uses the mma.sync kernel): bfloat16, head_dim 64 or 128, page_size 8,
@@ -32,6 +34,8 @@
 // Rows of V past a tile's last visible key may hold anything; they are zeroed in shared memory
 // before they are multiplied.  All mbarrier waits are bounded (error word, tensor memory freed).
 #include <cuda.h>
+
+#include <algorithm>
 
 #include "common.cuh"
 
@@ -55,6 +59,7 @@ struct PrefillParams {
   const int32_t* block_table;  // [R, table_width]
   int table_width, page_size, num_pages;
   int nh, g, per;
+  int n_requests;
   int tokens_per_tile;         // 128 / per
   float scale_log2;
   // With key splits (gridDim.z > 1) a tile of queries whose visible keys fill more than tiles_per_split key tiles
@@ -239,8 +244,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Set-up that needs nothing of the step's data comes before the wait for the kernel in front: descriptors are
-  // asked for (the copy unit reads each from memory before its first copy), barriers initialised, tensor memory
-  // taken.  A block that then finds it has no work gives the tensor memory back on its way out.
+  // asked for (the copy unit reads each from memory before its first copy) and the barriers initialised.  Tensor
+  // memory is taken only once a block knows that it has work: a step's grid is sized by its longest request, and
+  // beside a long portion most blocks of the other requests have none.
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
@@ -258,15 +264,41 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 5) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-  }
+  __syncthreads();
   if (threadIdx.x == 0) STAMP(63, 0);
   pdl_launch_dependents();
   pdl_wait();
   if (threadIdx.x == 0) STAMP(63, 1);
-  const int req = blockIdx.y / p.g, kvh = blockIdx.y - req * p.g;
+  // The grid's x counts tiles of queries of the whole step (an upper bound that the host can give without the
+  // requests' lengths); each warp finds the request of this block's tile by adding up the requests' tiles, 32
+  // requests at a time.  A step with one long portion beside many short requests launches no blocks for tiles
+  // that the short ones do not have.
+  const int kvh = blockIdx.y;
+  const int flat = (int)gridDim.x - 1 - (int)blockIdx.x;    // later tiles see more keys: they go first, light ones fill the tail
+  const bool count_single = !(p.skip_single && gridDim.z == 1);
+  int req = -1, tile_in_req = 0;
+  for (int c = 0, base = 0; c < p.n_requests; c += 32) {
+    int tiles = 0;
+    if (c + lane < p.n_requests) {
+      const int q = p.q_start[c + lane + 1] - p.q_start[c + lane];
+      tiles = (q == 1 && !count_single) ? 0 : (q + p.tokens_per_tile - 1) / p.tokens_per_tile;
+    }
+    int upto = tiles;                                       // tiles of requests c .. c + lane
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int below = __shfl_up_sync(0xffffffffu, upto, o);
+      if (lane >= o) upto += below;
+    }
+    const int total = __shfl_sync(0xffffffffu, upto, 31);
+    if (flat < base + total) {                              // uniform: flat, base and total are
+      const int owner = __ffs(__ballot_sync(0xffffffffu, base + upto > flat)) - 1;
+      req = c + owner;
+      tile_in_req = flat - base - __shfl_sync(0xffffffffu, upto - tiles, owner);
+      break;
+    }
+    base += total;
+  }
+  if (req < 0) return;                                      // uniform for the block, like everything up to the roles
   const int32_t* bt = p.block_table + (size_t)req * p.table_width;
   // The loads below are issued back to back: two round trips to memory (token range and first pages; then
   // positions) stand between the start of a block and its first copy, not four.
@@ -279,47 +311,48 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     early_page = (my_box < (BN >> box_shift) && pi < p.table_width) ? bt[pi] : -1;
   }
   const int tok0 = p.q_start[req], q_len = p.q_start[req + 1] - tok0;
-  // Later query tiles see more keys: they are given to the first blocks, so the light ones fill the tail.
-  const int t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * p.tokens_per_tile;   // first token of this block within the request
-  bool active = t0 < q_len;                                 // uniform for the block, like everything up to the roles
-  if (active && p.skip_single && q_len == 1) {
+  const int t0 = tile_in_req * p.tokens_per_tile;           // first token of this block within the request
+  if (p.skip_single && q_len == 1) {
     // Another kernel writes this request's row; with key splits the second kernel must leave it alone.
     if (gridDim.z > 1 && blockIdx.z == 0 && (int)threadIdx.x < p.per)
       *reinterpret_cast<float2*>(p.part_ml + (((size_t)tok0 * p.nh + kvh * p.per + threadIdx.x) * gridDim.z) * 2) =
           make_float2(INFINITY, 0.f);
-    active = false;
+    return;
   }
-  const int n_tok = active ? min(p.tokens_per_tile, q_len - t0) : 1;
+  const int n_tok = min(p.tokens_per_tile, q_len - t0);
   const int n_rows = n_tok * p.per;
-  const int first_tok = active ? tok0 + t0 : 0;
-  const int pos_first = p.positions[first_tok];
-  const int hi_key = p.positions[first_tok + n_tok - 1];
+  const int pos_first = p.positions[tok0 + t0];
+  const int hi_key = p.positions[tok0 + t0 + n_tok - 1];
   // This block's share of the key tiles (all of them without splits).
   const int all_tiles = hi_key / BN + 1;
   const int slots = gridDim.z, split = blockIdx.z;          // slots: shares that the scratch memory has room for
   const int wanted = slots > 1 ? min(slots, (all_tiles + p.tiles_per_split - 1) / p.tiles_per_split) : 1;
   const int per_split = (all_tiles + wanted - 1) / wanted;
   const int n_splits = (all_tiles + per_split - 1) / per_split;     // shares that get a tile (7 tiles in 5 shares: 4 of 2)
-  if (active && split >= n_splits) {
+  if (split >= n_splits) {
     if (n_splits > 1 && (int)threadIdx.x < n_rows) {        // an unused share of a divided tile: nothing to add
       const int t_in = threadIdx.x / p.per, head = threadIdx.x - t_in * p.per;
       const size_t slot = ((size_t)(tok0 + t0 + t_in) * p.nh + kvh * p.per + head) * slots + split;
       *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(-INFINITY, 0.f);
     }
-    active = false;
+    return;
   }
   const int tile_base = split * per_split;
   const int n_tiles = min(all_tiles, tile_base + per_split) - tile_base;     // >= 1
 
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem = *tmem_slot;
-  if (threadIdx.x == 0) STAMP(63, 2);
-  if (!active) {                                            // nothing was started: give the tensor memory back and go
-    if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
-    return;
+  // Tensor memory, for all but the copy warp, which starts its copies at once.
+  uint32_t tmem = 0;
+  if (warp != 4) {
+    if (warp == 5) {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    asm volatile("bar.sync 1, 160;" ::: "memory");
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    tmem = *tmem_slot;
   }
+  if (threadIdx.x == 0) STAMP(63, 2);
 
   int k_armed = 0, v_armed = 0;
   if (warp == 4) {
@@ -698,8 +731,13 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
       return YALIS_ERR_LAUNCH;
     configured = true;
   }
-  dim3 grid((max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile, n_requests * p.g, n_splits);
-  if (grid.y > 65535) return YALIS_ERR_SHAPE;
+  // Tiles of queries in the step: sum of ceil(q / tokens_per_tile) over the requests, bounded from their number,
+  // the step's tokens and the longest request.
+  const long long tpt = p.tokens_per_tile;
+  const long long tiles = std::min(((long long)n_tokens + (long long)n_requests * (tpt - 1)) / tpt,
+                                   (long long)n_requests * ((max_q_len + tpt - 1) / tpt));
+  if (tiles > 0x7fffffffLL || p.g > 65535) return YALIS_ERR_SHAPE;
+  dim3 grid((unsigned)tiles, p.g, n_splits);
   int st = yalis_launch(prefill_attention_tcgen05_kernel<HS>, grid, dim3(kThreads), smem, stream, mq, mk, mv, p);
   if (st != YALIS_OK || n_splits == 1) return st;
   return yalis_launch(prefill_merge_splits_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)p.part_o,
@@ -753,6 +791,7 @@ YALIS_API int yalis_prefill_attention_tcgen05(const void* q, int q_stride, void*
   p.positions = positions; p.q_start = q_start; p.block_table = block_table;
   p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages;
   p.nh = nh; p.g = g; p.per = nh / g;
+  p.n_requests = n_requests;
   p.tokens_per_tile = BM / p.per;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.tiles_per_split = tiles_per_split > 0 ? tiles_per_split : 1;

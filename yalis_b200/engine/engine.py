@@ -182,6 +182,7 @@ class Engine:
         self.last_captured = None           # the recording the last step replayed (None: it was launched)
         self._graph_pool = None
         self._recordings: Dict[tuple, object] = {}
+        self._seen_shapes: Dict[tuple, int] = {}
 
     # ---- requests ------------------------------------------------------------------------
     def has_request(self, request: Hashable) -> bool:
@@ -394,10 +395,10 @@ class Engine:
         mode = "none" if sampling is None else ("greedy" if all(p.greedy for p in sampling) else "sampled")
         keep = keep_logits or mode == "none"
         recording = None
-        if (self.engine_config.use_graphs if graphs is None else graphs) and host.max_q_len == 1 and n_want > 0:
+        if self.engine_config.use_graphs if graphs is None else graphs:
             key = self.model.capture_key(host)
             if key is not NOT_CAPTURABLE:
-                recording = self._recording(len(entries), mode, keep, key)
+                recording = self._recording(host, n_want, mode, keep, key)
         if recording is not None:
             out = recording.run(host, entries, q_lens, sampling, draws, n_want)
         else:
@@ -437,11 +438,36 @@ class Engine:
                 self.chosen[-1:].copy_(self._error_word)
         return StepOutput(logits if keep else None, tokens, False, 4 * layout.total)
 
-    def _recording(self, n_requests: int, mode: str, keep_logits: bool, capture_key):
+    MAX_EXACT_RECORDINGS = 48       # recordings of steps other than single tokens kept at a time
+
+    def _recording(self, host: HostStep, n_want: int, mode: str, keep_logits: bool, capture_key):
+        """The recording that replays a step with these facts, or None if the step is to be launched.
+
+        Steps of single tokens share a recording per bucket of requests (padded).  Any other step (prompt portions,
+        portions beside decoding requests) is recorded at its exact counts of tokens, requests and wanted rows,
+        and only when the same kind of step has been seen before: serving repeats shapes (a token budget filled
+        by the same number of decoding requests and one portion), one-off shapes are not worth a recording."""
         from yalis_b200.engine.recorded import RecordedStep, bucket_for
-        size = bucket_for(n_requests)
-        key = (size, mode, keep_logits, capture_key)
+        n, r = host.q_start[-1], len(host.slots)
+        if host.max_q_len == 1:
+            if n_want == 0:
+                return None
+            size = bucket_for(r)
+            shape = (size, size, size, True)
+        else:
+            shape = (n, r, n_want, False, host.max_q_len)
+        key = (shape[0], mode, keep_logits, capture_key, shape)
         rec = self._recordings.get(key)
         if rec is None:
-            rec = self._recordings[key] = RecordedStep(self, size, mode, keep_logits, key)
+            if not shape[3]:
+                seen = self._seen_shapes.get(key, 0)
+                self._seen_shapes[key] = seen + 1
+                if seen == 0:
+                    if len(self._seen_shapes) > 4096:
+                        self._seen_shapes.clear()
+                    return None
+                exact = [k for k in self._recordings if not k[4][3]]
+                if len(exact) >= self.MAX_EXACT_RECORDINGS:
+                    del self._recordings[exact[0]]              # the oldest
+            rec = self._recordings[key] = RecordedStep(self, shape[0], shape[1], shape[2], shape[3], mode, keep_logits, key)
         return rec

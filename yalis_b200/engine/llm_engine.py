@@ -102,8 +102,9 @@ class LLMEngine:
         the configuration's defaults with a seed of their own).  ``eos_id``: a request ends when it draws this
         token (None: only by length).  ``return_logits``: keep the float32 logits every token was drawn from.
         ``step_log``: a list that receives, per step, a dictionary with its ``tokens``, ``requests``,
-        ``decoding`` (requests that brought one token), ``h2d_bytes``, ``captured`` and the CUDA events
-        ``start`` / ``end`` around it (for benchmarks).
+        ``decoding`` (requests that brought one token), ``h2d_bytes``, ``captured``, ``replayed_launches``
+        (kernels in the recording, if the step replayed one) and the CUDA events ``start`` / ``end`` around it
+        (for benchmarks).
         """
         t_tok = time.perf_counter()
         if len(prompts) == 0:
@@ -156,6 +157,7 @@ class LLMEngine:
                 if step_log is not None:
                     entry["end"].record()
                     entry["h2d_bytes"], entry["captured"] = eng.last_h2d_bytes, eng.last_captured is not None
+                    entry["replayed_launches"] = eng.last_captured.launches if eng.last_captured is not None else 0
                     step_log.append(entry)
                 timers.stop(name)
                 if nvtx:
@@ -255,7 +257,7 @@ class LLMEngine:
                 params.append(r.sampling)
                 draws.append(len(r.output))
         if not params:
-            self.engine.run_step(slots, entries, graphs=False)
+            self.engine.run_step(slots, entries, graphs=self.use_graphs)
             return []
         out = self.engine.run_step(slots, entries, sampling=params, draws=draws, graphs=self.use_graphs,
                                    keep_logits=logits_out is not None)

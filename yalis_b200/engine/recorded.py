@@ -4,7 +4,10 @@ A step in which every request brings one token launches a few hundred small
 kernels; launched one by one from Python they cost more than they run.  The
 engine records such a step once per (batch bucket, kind of token choice, keys of
 the parts) and every later step of that kind is: fill one pinned buffer with
-the step's arrays, copy it, launch the graph.  The graph holds the whole step:
+the step's arrays, copy it, launch the graph.  Steps that hold prompt portions
+are recorded too, at their exact counts of tokens, requests and wanted rows,
+once the same kind of step has come a second time (a small model's step of a
+few hundred tokens is otherwise bound by the host's launches).  The graph holds the whole step:
 embedding, all blocks, final norm, output matrix, token choice and the copy of
 the error word beside the chosen tokens.
 
@@ -63,10 +66,12 @@ def _copy_rows_to_device(dst: torch.Tensor, src: torch.Tensor, rows: int, cols: 
 class RecordedStep:
     """Static buffers and the graph for one kind of step (see the module docstring)."""
 
-    def __init__(self, engine, size: int, mode: str, keep_logits: bool, key: tuple):
-        self.engine, self.size, self.mode, self.keep_logits, self.key = engine, size, mode, keep_logits, key
+    def __init__(self, engine, n_tokens: int, n_requests: int, n_rows: int, single_tokens: bool, mode: str,
+                 keep_logits: bool, key: tuple):
+        self.engine, self.mode, self.keep_logits, self.key = engine, mode, keep_logits, key
+        self.size, self.n_tokens, self.n_rows, self.single_tokens = n_requests, n_tokens, n_rows, single_tokens
         self.widths = [g.max_pages_per_request for g in engine.groups]
-        self.layout = StepLayout(size, size, size, self.widths, sampling=(mode == "sampled"))
+        self.layout = StepLayout(n_tokens, n_requests, n_rows, self.widths, sampling=(mode == "sampled"))
         self.host = torch.zeros(self.layout.total, dtype=torch.int32).pin_memory()
         self.dev = torch.zeros(self.layout.total, dtype=torch.int32, device=engine.device)
         self.h = self.layout.views(self.host, as_numpy=True)
@@ -75,7 +80,7 @@ class RecordedStep:
         for view in self.h["tables"]:
             view[:] = -1
         self.dev.copy_(self.host)
-        self.tokens = torch.zeros(size, dtype=torch.int32, device=engine.device) if mode != "none" else None
+        self.tokens = torch.zeros(max(1, n_rows), dtype=torch.int32, device=engine.device) if mode != "none" else None
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches = 0
@@ -87,6 +92,8 @@ class RecordedStep:
     def _body(self) -> None:
         eng = self.engine
         stream = eng.model.forward(self.ctx, eng.storage.entries)
+        if self.n_rows == 0:
+            return
         logits = eng.model.logits(stream, self.ctx.logit_rows)
         if self.keep_logits:
             if self.logits is None:
@@ -99,7 +106,7 @@ class RecordedStep:
     def _record(self, host: HostStep) -> None:
         eng = self.engine
         # The facts of this step stand for every step that will replay the recording (they share the parts' keys).
-        self.ctx, self.d = eng._context(self.layout, self.dev, host, decode_only=True)
+        self.ctx, self.d = eng._context(self.layout, self.dev, host, decode_only=self.single_tokens)
         saved_state = eng.storage.snapshot_state()
         saved_chosen = eng.chosen.clone()
         self._body()                                   # the trial: libraries initialise, buffers get their sizes
@@ -142,6 +149,6 @@ class RecordedStep:
             self._record(host)
         self.graph.replay()
         self.replays += 1
-        logits = self.logits[:n_want] if self.keep_logits else None
-        tokens = self.tokens[:n_want] if self.mode != "none" else None
+        logits = self.logits[:n_want] if self.keep_logits and n_want else None
+        tokens = self.tokens[:n_want] if self.mode != "none" and n_want else None
         return StepOutput(logits, tokens, True, 4 * copied)

@@ -1,6 +1,7 @@
 """Builds and loads the two native libraries of the package.
 
-* ``libyalis_host``: the page allocator of the cache manager (C++, no CUDA); it
+* ``libyalis_host``: the page allocator of the cache manager and the launch model of the prompt-attention
+  kernel (C++, no CUDA); it
   is what the CPU-only tests use.
 * ``libyalis_cuda``: every GPU kernel (CUDA C++ for sm_100a only).
 
@@ -41,7 +42,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo",
               "--expt-relaxed-constexpr"]
 GXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall"]
 
-HOST_SOURCES = ["host/page_allocator.cpp"]
+HOST_SOURCES = ["host/page_allocator.cpp", "host/attention_policy.cpp"]
 
 
 class NativeBuildError(RuntimeError):

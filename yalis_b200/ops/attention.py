@@ -4,12 +4,14 @@ from __future__ import annotations
 
 import collections
 import ctypes
-import heapq
 import math
 import os
 from typing import Optional
 
+import numpy as np
 import torch
+
+from yalis_b200 import native
 
 from ._lib import check, dtype_code, f32, i32, i64, lib, need, need_cuda, ptr, stream
 
@@ -420,24 +422,30 @@ PREFILL_SPLIT_START_UP = 20.0    # what one more block costs (fill and drain, it
 PREFILL_SPLIT_UNSHARED = 1.4     # pace of a block whose keys no other block reads at the time (they come from HBM)
 
 
+PREFILL_SPLIT_GAIN = 0.92        # dividing has to bring 8 %
+
+
+def _policy_lib():
+    host_lib = native.load("host")
+    if not getattr(host_lib, "_ypol_typed", False):
+        host_lib.ypol_step_length.restype = ctypes.c_double
+        host_lib.ypol_step_length.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 4 + [ctypes.c_double]
+        host_lib.ypol_kv_splits.restype = None
+        host_lib.ypol_kv_splits.argtypes = ([ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 5
+                                            + [ctypes.c_double] * 3 + [ctypes.c_void_p])
+        host_lib._ypol_typed = True
+    return host_lib
+
+
 def _prefill_step_length(items, slots: int, splits: int, limit: int) -> float:
     """Length of the tcgen05 prompt kernel, in key tiles of a block, for ``items`` = (key tiles, pace) of the
     tiles of queries of one KV head: the blocks in launch order (share after share) each go to the first of
-    ``slots`` places to come free."""
-    lengths = []
-    for z in range(splits):
-        for tiles, pace in items:
-            wanted = min(splits, -(-tiles // limit)) if splits > 1 else 1
-            per_share = -(-tiles // wanted)
-            if z * per_share < tiles:
-                lengths.append((min(tiles, (z + 1) * per_share) - z * per_share) * pace + PREFILL_SPLIT_START_UP)
-    free = [0.0] * slots
-    end = 0.0
-    for length in lengths:
-        done = heapq.heappop(free) + length
-        heapq.heappush(free, done)
-        end = max(end, done)
-    return end
+    ``slots`` places to come free.  (The model itself is native, csrc/host/attention_policy.cpp: it runs for
+    every step that is launched.)"""
+    tiles = np.asarray([t for t, _ in items], dtype=np.int32)
+    pace = np.asarray([p for _, p in items], dtype=np.float64)
+    return float(_policy_lib().ypol_step_length(tiles.ctypes.data, pace.ctypes.data, len(items), slots, splits, limit,
+                                                PREFILL_SPLIT_START_UP))
 
 
 def prefill_kv_splits(host, heads_per_group: int, num_kv_heads: int, head_dim: int, skip_single: bool = False):
@@ -453,30 +461,19 @@ def prefill_kv_splits(host, heads_per_group: int, num_kv_heads: int, head_dim: i
     The choice is the best of 1, 2, 3, 4, 6 or 8 shares for the longest tile of queries (shorter ones get fewer)
     under a model of the launch (``_prefill_step_length``) whose three constants are fitted to 26 measured steps
     (portions of 512 to 2,048 tokens behind up to 14,000 cached ones, alone and beside decoding requests, 24 and
-    32 heads in 8 groups: the choices cost 1.4 % over the best measured ones, the model's times are 10 % off)."""
-    q_lens = [b - a for a, b in zip(host.q_start[:-1], host.q_start[1:])]
-    if not host.ctx_before or sum(q_lens) == 0:
+    32 heads in 8 groups: the choices cost 1.4 % over the best measured ones, the model's times are 10 % off).
+    A tile of queries counts as reading its keys alone (a slower pace) when its request brings at most three
+    tiles; requests of one token are left out with ``skip_single`` (they go to another kernel)."""
+    if not host.ctx_before or host.q_start[-1] == host.q_start[0]:
         return 1, 1
-    per_tile = 128 // heads_per_group
-    items = []                                              # (key tiles, pace) of every tile of queries of one KV head
-    for q, before in zip(q_lens, host.ctx_before):
-        if q == 0 or (skip_single and q == 1):              # decoding requests go to another kernel
-            continue
-        # few tiles of queries on the same keys: nobody else brings them into the L2 cache
-        pace = PREFILL_SPLIT_UNSHARED if q <= 3 * per_tile else 1.0
-        for first in range(0, q, per_tile):
-            items.append(((before + min(q, first + per_tile) - 1) // 64 + 1, pace))
-    longest = max((t for t, _ in items), default=0)
-    if longest < 3 * PREFILL_SPLIT_MIN_TILES:
-        return 1, 1
-    slots = max(1, 2 * sm_count() // num_kv_heads)
-    best, best_length = (1, 1), 0.92 * _prefill_step_length(items, slots, 1, 1)    # dividing has to bring 8 %
-    for shares in (2, 3, 4, 6, 8):
-        limit = max(PREFILL_SPLIT_MIN_TILES, -(-longest // shares))
-        length = _prefill_step_length(items, slots, shares, limit)
-        if length < best_length:
-            best, best_length = (min(64, -(-longest // limit)), limit), length
-    return best
+    q_start = np.asarray(host.q_start, dtype=np.int32)
+    q_lens = np.ascontiguousarray(q_start[1:] - q_start[:-1])
+    before = np.asarray(host.ctx_before, dtype=np.int32)
+    out = np.ones(2, dtype=np.int32)
+    _policy_lib().ypol_kv_splits(q_lens.ctypes.data, before.ctypes.data, len(q_lens), 128 // heads_per_group,
+                                 max(1, 2 * sm_count() // num_kv_heads), 1 if skip_single else 0, PREFILL_SPLIT_MIN_TILES,
+                                 PREFILL_SPLIT_START_UP, PREFILL_SPLIT_UNSHARED, PREFILL_SPLIT_GAIN, out.ctypes.data)
+    return int(out[0]), int(out[1])
 
 
 MIXED_DECODE_MIN_KEYS = 4096     # cached tokens of a step's decoding requests from which they get a kernel of their own
@@ -491,6 +488,14 @@ def mixed_step_splits_off_decodes(host) -> bool:
     if not host.ctx_before:
         return False
     return sum(before for q, before in zip(q_lens, host.ctx_before) if q == 1) >= MIXED_DECODE_MIN_KEYS
+
+
+def portion_step_kind(host, heads_per_group: int, num_kv_heads: int, head_dim: int) -> tuple:
+    """What the attention of a step that holds prompt portions depends on besides the shapes of its tensors:
+    whether its decoding requests go to the decode kernel, and how the keys of long tiles of queries are divided
+    (a recorded step is keyed by it)."""
+    return (mixed_step_splits_off_decodes(host),) + tuple(prefill_kv_splits(host, heads_per_group, num_kv_heads, head_dim, True)) \
+        + tuple(prefill_kv_splits(host, heads_per_group, num_kv_heads, head_dim, False))
 
 
 def _prefill_split_choice(ctx, per: int, num_kv_heads: int, head_dim: int, skip_single: bool = False) -> dict:

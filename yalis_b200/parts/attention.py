@@ -59,8 +59,10 @@ class PagedAttention(Mixer):
         return PagedKV(self.g, self.hs, self.window)
 
     def capture_key(self, host):
-        # which decode kernel runs, and in how many splits, depends on the lengths only through this
-        return attn_ops.decode_step_kind([b + 1 for b in host.ctx_before])
+        # everything the choice of kernel and its launch depend on besides the shapes of the step's tensors
+        if host.max_q_len == 1:
+            return attn_ops.decode_step_kind([b + 1 for b in host.ctx_before])
+        return attn_ops.portion_step_kind(host, self.nh // self.g, self.g, self.hs)
 
     def mixing_flops(self, q_len: int, ctx_before: int) -> float:
         # QK^T and PV over the keys each token sees (causal; a window bounds them)
