@@ -139,10 +139,14 @@ def gemm_wstream(args) -> None:
     def fn():
         w = ws[state["i"] % copies]
         state["i"] += 1
-        gemm(x, w, split=args.split)
+        if args.library:
+            torch.matmul(x, w.t())
+        else:
+            gemm(x, w, split=args.split)
 
     us = _time(fn, args.launches, graph=not args.eager)
-    print(f"gemm_wstream tokens {m} n {n} k {k} splits {wstream_splits(n, k) if args.split else 1}: "
+    print(f"{'library product' if args.library else 'gemm_wstream'} tokens {m} n {n} k {k} splits "
+          f"{wstream_splits(n, k) if args.split and not args.library else 1}: "
           f"{us:.1f} us per launch, {n * k * 2 / us / 1e6:.2f} TB/s of weights")
 
 
@@ -235,6 +239,7 @@ def main() -> None:
     gm.add_argument("--n", type=int, default=28672)
     gm.add_argument("--k", type=int, default=4096)
     gm.add_argument("--split", action="store_true")
+    gm.add_argument("--library", action="store_true", help="time the library's product on the same operands instead")
     gm.add_argument("--launches", type=int, default=8)
     gm.set_defaults(fn=gemm_wstream)
     ap_ = sub.add_parser("attention_prefill")

@@ -1,6 +1,6 @@
 """The allocation-free entry point of the split-key decode attention, called through its
-exported C symbol as a host program without an allocator would call it, against the regular
-entry point.
+exported C symbol as a host program without an allocator would call it, against plain attention
+in float32 over the gathered keys and against the regular entry point.
 
 The caller of ``yalis_paged_attention_mma_noalloc`` owns inputs and output; the kernel's
 temporary memory comes from a fixed array inside the library (csrc/attention_noalloc.h), so
@@ -37,6 +37,19 @@ def _case(batch, lens, nh, g, hs, page, seed):
     return q, k_pool, v_pool, i32([l - 1 for l in lens]), i32(list(range(batch + 1))), i32(list(range(batch))), table.to(DEV)
 
 
+def _plain(q, k_pool, v_pool, lens, table, nh, g, hs):
+    """Every request's single query over its own keys, gathered page by page, in float32."""
+    page, rows = k_pool.shape[2], []
+    for r, n in enumerate(lens):
+        pages = table[r, :-(-n // page)].long()
+        keys = k_pool[pages].permute(1, 0, 2, 3).reshape(g, -1, hs)[:, :n].float()
+        values = v_pool[pages].permute(1, 0, 2, 3).reshape(g, -1, hs)[:, :n].float()
+        query = q[r].view(g, nh // g, hs).float()
+        weights = torch.softmax(torch.einsum("gpd,gkd->gpk", query, keys) / math.sqrt(hs), dim=-1)
+        rows.append(torch.einsum("gpk,gkd->gpd", weights, values).reshape(nh * hs))
+    return torch.stack(rows)
+
+
 def _call_noalloc(lib, q, k_pool, v_pool, positions, q_start, req, table, nh, g, hs, splits, out):
     vp = lambda t: ctypes.c_void_p(t.data_ptr())
     ci = ctypes.c_int
@@ -52,9 +65,10 @@ def test_noalloc_entry_matches_regular_entry_twice():
     from yalis_b200.ops.attention import paged_attention_mma
     lib = native.load("cuda")
     nh, g, hs, page, splits = 8, 2, 64, 16, 4
-    first = _case(5, [1, 70, 129, 300, 1000], nh, g, hs, page, seed=1)
-    second = _case(3, [513, 64, 2], nh, g, hs, page, seed=2)            # another shape: the array holds stale data
-    for q, k_pool, v_pool, positions, q_start, req, table in (first, second):
+    first_lens, second_lens = [1, 70, 129, 300, 1000], [513, 64, 2]
+    first = _case(5, first_lens, nh, g, hs, page, seed=1)
+    second = _case(3, second_lens, nh, g, hs, page, seed=2)             # another shape: the array holds stale data
+    for lens, (q, k_pool, v_pool, positions, q_start, req, table) in ((first_lens, first), (second_lens, second)):
         want = paged_attention_mma(q, k_pool, v_pool, positions, q_start, req, table, 1, nh, g, hs, n_splits=splits)
         out = torch.zeros_like(want)                                      # the caller's own output buffer
         torch.cuda.synchronize()
@@ -63,6 +77,7 @@ def test_noalloc_entry_matches_regular_entry_twice():
         torch.cuda.synchronize()
         assert status == 0
         assert torch.cuda.memory_allocated() == before                   # nothing went through torch's allocator
+        torch.testing.assert_close(out.float(), _plain(q, k_pool, v_pool, lens, table, nh, g, hs), rtol=2e-2, atol=2e-2)
         torch.testing.assert_close(out.float(), want.float(), rtol=2e-2, atol=2e-2)
         assert not torch.isnan(out.float()).any()
 

@@ -513,6 +513,8 @@ YALIS_API int yalis_paged_attention_mma(const void* q, int q_stride, void* out, 
 // The same kernel with its temporary memory in a fixed array of the library, for callers that
 // must not allocate (see attention_noalloc.h for who they are and for the rules).
 // ---------------------------------------------------------------------------------------
+#include <atomic>
+
 #include "attention_noalloc.h"
 
 namespace {
@@ -522,18 +524,20 @@ namespace {
 static __device__ __align__(256) unsigned char g_noalloc_scratch[YALIS_NOALLOC_SCRATCH_BYTES];
 
 constexpr int kMaxDevices = 64;
-void* g_noalloc_ptr[kMaxDevices] = {nullptr};   // device address of the array, per device
+// Device address of the array, per device.  Threads that make a device's first call at the same time all ask
+// the runtime and store the same address: the slots are atomic so that none of them reads a half-written one.
+std::atomic<void*> g_noalloc_ptr[kMaxDevices];
 
 // Device address of the array on the current device; looked up on the first call there.
 int noalloc_scratch(unsigned char** ptr) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return YALIS_ERR_LAUNCH;
-  if (g_noalloc_ptr[dev] == nullptr) {
-    void* p = nullptr;
+  void* p = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return YALIS_ERR_LAUNCH;
-    g_noalloc_ptr[dev] = p;
+    g_noalloc_ptr[dev].store(p, std::memory_order_release);
   }
-  *ptr = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
+  *ptr = static_cast<unsigned char*>(p);
   return YALIS_OK;
 }
 

@@ -24,7 +24,7 @@
 // products and two commits of a P V).  The copy warp looks the pages of a tile up one tile ahead
 // (a block-table entry is a global load whose latency would otherwise stand between a freed buffer
 // and the copy into it) and asks for K one tile ahead of V, the order in which their buffers come
-// free, so that a wait for one never holds up the other.  The grid is (tiles of queries of the step, KV heads,
+// free, so that a wait for one never holds up the other.  The grid is (tiles of queries of the step x KV heads, 1,
 // shares of the keys); a block finds the request of its tile from the requests' token ranges.
 // Same semantics as paged_attention_generic (mask by absolute position,
 // yalis/attention/backend_impl/sdpa_and_flex.py:15-19, 301-307) without a window.
@@ -79,10 +79,20 @@ struct PrefillParams {
 #ifdef YALIS_TRACE_CLOCKS
 #define STAMP(j, k)                                                                                             \
   do {                                                                                                          \
-    if (p.trace && (j) < 64) p.trace[((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 64 + (j)) * 32 + (k)] = clock64(); \
+    if (p.trace && (j) < 64) p.trace[((size_t)blockIdx.x * 64 + (j)) * 32 + (k)] = clock64(); \
+  } while (0)
+// Wall-clock stamps (nanoseconds, comparable between blocks) in row 62 of a block's record, and its SM.
+#define GSTAMP(k)                                                                                               \
+  do {                                                                                                          \
+    if (p.trace) {                                                                                              \
+      unsigned long long t_;                                                                                    \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                                    \
+      p.trace[((size_t)blockIdx.x * 64 + 62) * 32 + (k)] = (long long)t_;            \
+    }                                                                                                           \
   } while (0)
 #else
 #define STAMP(j, k) do { } while (0)
+#define GSTAMP(k) do { } while (0)
 #endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -248,9 +258,11 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   // memory is taken only once a block knows that it has work: a step's grid is sized by its longest request, and
   // beside a long portion most blocks of the other requests have none.
   if (threadIdx.x == 0) {
+    GSTAMP(3);
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
+    GSTAMP(4);
     mbar_init(q_full, 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&k_full[b], 1); mbar_init(&k_empty[b], 1);
@@ -261,11 +273,14 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     mbar_init(o_full, 1);
     mbar_init(o_done, 1);
     *abort_flag = 0;
+    GSTAMP(5);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    GSTAMP(6);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    GSTAMP(7);
   }
   __syncthreads();
-  if (threadIdx.x == 0) STAMP(63, 0);
+  if (threadIdx.x == 0) { STAMP(63, 0); GSTAMP(0); }
   pdl_launch_dependents();
   pdl_wait();
   if (threadIdx.x == 0) STAMP(63, 1);
@@ -273,8 +288,12 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   // requests' lengths); each warp finds the request of this block's tile by adding up the requests' tiles, 32
   // requests at a time.  A step with one long portion beside many short requests launches no blocks for tiles
   // that the short ones do not have.
-  const int kvh = blockIdx.y;
-  const int flat = (int)gridDim.x - 1 - (int)blockIdx.x;    // later tiles see more keys: they go first, light ones fill the tail
+  // Blocks are handed out in the order of blockIdx.x: the KV heads of a tile of queries are neighbours there, and
+  // later tiles, which see more keys, come first, so that the light ones fill the tail.  (With the tiles along x
+  // and the heads along y, the heavy tiles of the last heads started after the light tiles of the first: at
+  // 2,048 tokens and 8 heads the last block to end was a heaviest one that had started 33 us into the launch.)
+  const int kvh = (int)blockIdx.x % p.g;
+  const int flat = (int)gridDim.x / p.g - 1 - (int)blockIdx.x / p.g;
   const bool count_single = !(p.skip_single && gridDim.z == 1);
   int req = -1, tile_in_req = 0;
   for (int c = 0, base = 0; c < p.n_requests; c += 32) {
@@ -641,7 +660,16 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   }
   if (warp == 5) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    if (lane == 0) GSTAMP(8);
   }
+#ifdef YALIS_TRACE_CLOCKS
+  if (threadIdx.x == 0) {
+    GSTAMP(1);
+    unsigned sm_;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_));
+    if (p.trace) p.trace[((size_t)blockIdx.x * 64 + 62) * 32 + 2] = sm_ + 1;
+  }
+#endif
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -736,8 +764,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
   const long long tpt = p.tokens_per_tile;
   const long long tiles = std::min(((long long)n_tokens + (long long)n_requests * (tpt - 1)) / tpt,
                                    (long long)n_requests * ((max_q_len + tpt - 1) / tpt));
-  if (tiles > 0x7fffffffLL || p.g > 65535) return YALIS_ERR_SHAPE;
-  dim3 grid((unsigned)tiles, p.g, n_splits);
+  if (tiles * p.g > 0x7fffffffLL) return YALIS_ERR_SHAPE;
+  dim3 grid((unsigned)(tiles * p.g), 1, n_splits);
   int st = yalis_launch(prefill_attention_tcgen05_kernel<HS>, grid, dim3(kThreads), smem, stream, mq, mk, mv, p);
   if (st != YALIS_OK || n_splits == 1) return st;
   return yalis_launch(prefill_merge_splits_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)p.part_o,

@@ -34,6 +34,14 @@ class HostStep:
     ctx_before: List[int]     # tokens each request held before the step
     max_q_len: int
     max_kv_len: int
+    memo: Dict[tuple, object] = field(default_factory=dict)    # what parts work out from these facts once per step
+
+    def once(self, key: tuple, work):
+        """``work()``, computed the first time ``key`` is asked for in this step (every layer asks the same)."""
+        value = self.memo.get(key)
+        if value is None:
+            value = self.memo[key] = work()
+        return value
 
 
 @dataclass

@@ -490,20 +490,23 @@ def mixed_step_splits_off_decodes(host) -> bool:
     return sum(before for q, before in zip(q_lens, host.ctx_before) if q == 1) >= MIXED_DECODE_MIN_KEYS
 
 
+def _splits_once(host, heads_per_group: int, num_kv_heads: int, head_dim: int, skip_single: bool) -> tuple:
+    """``prefill_kv_splits`` once per step and shape (every layer asks, and so does the key of a recorded step)."""
+    work = lambda: tuple(prefill_kv_splits(host, heads_per_group, num_kv_heads, head_dim, skip_single))
+    once = getattr(host, "once", None)
+    return once(("prefill_kv_splits", heads_per_group, num_kv_heads, head_dim, skip_single), work) if once else work()
+
+
 def portion_step_kind(host, heads_per_group: int, num_kv_heads: int, head_dim: int) -> tuple:
     """What the attention of a step that holds prompt portions depends on besides the shapes of its tensors:
     whether its decoding requests go to the decode kernel, and how the keys of long tiles of queries are divided
     (a recorded step is keyed by it)."""
-    return (mixed_step_splits_off_decodes(host),) + tuple(prefill_kv_splits(host, heads_per_group, num_kv_heads, head_dim, True)) \
-        + tuple(prefill_kv_splits(host, heads_per_group, num_kv_heads, head_dim, False))
+    return ((mixed_step_splits_off_decodes(host),) + _splits_once(host, heads_per_group, num_kv_heads, head_dim, True)
+            + _splits_once(host, heads_per_group, num_kv_heads, head_dim, False))
 
 
 def _prefill_split_choice(ctx, per: int, num_kv_heads: int, head_dim: int, skip_single: bool = False) -> dict:
-    """``prefill_kv_splits`` once per step and shape (every layer asks)."""
-    key = ("prefill_kv_splits", per, num_kv_heads, head_dim, skip_single)
-    choice = ctx.extras.get(key)
-    if choice is None:
-        choice = ctx.extras[key] = prefill_kv_splits(ctx.host, per, num_kv_heads, head_dim, skip_single)
+    choice = _splits_once(ctx.host, per, num_kv_heads, head_dim, skip_single)
     return dict(kv_splits=choice[0], tiles_per_split=choice[1])
 
 

@@ -60,9 +60,11 @@ class PagedAttention(Mixer):
 
     def capture_key(self, host):
         # everything the choice of kernel and its launch depend on besides the shapes of the step's tensors
+        per = self.nh // self.g
         if host.max_q_len == 1:
-            return attn_ops.decode_step_kind([b + 1 for b in host.ctx_before])
-        return attn_ops.portion_step_kind(host, self.nh // self.g, self.g, self.hs)
+            return host.once(("decode_step_kind",), lambda: attn_ops.decode_step_kind([b + 1 for b in host.ctx_before]))
+        return host.once(("portion_step_kind", per, self.g, self.hs),
+                         lambda: attn_ops.portion_step_kind(host, per, self.g, self.hs))
 
     def mixing_flops(self, q_len: int, ctx_before: int) -> float:
         # QK^T and PV over the keys each token sees (causal; a window bounds them)
