@@ -45,6 +45,7 @@ constexpr int BM = 128;           // rows (tensor-memory lanes) per block
 constexpr int BN = 64;            // keys per tile
 constexpr int kThreads = 192;     // warps 0-3 softmax, warp 4 TMA, warp 5 MMA + tensor memory
 constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kBarriers = 21;     // mbarriers of a block (see the kernel)
 // Two blocks share an SM (one's softmax runs while the other's products do), so each takes half the tensor
 // memory: S0, S1 (BN columns each) and O (up to 128).  P(j) is written over the first half of S(j): by then S(j)
 // is in registers, and the product that next writes that buffer is issued after the one that reads P(j).
@@ -60,10 +61,14 @@ struct PrefillParams {
   int table_width, page_size, num_pages;
   int nh, g, per;
   int n_requests;
+  int n_items;                 // work items: items_per_share * n_z
+  int items_per_share;         // tiles of queries of the step (an upper bound) * KV heads
+  int n_z;                     // shares of the keys that a tile of queries may be divided into
+  int32_t* work;               // [2] zero between launches: the next item, blocks that are done
   int tokens_per_tile;         // 128 / per
   float scale_log2;
-  // With key splits (gridDim.z > 1) a tile of queries whose visible keys fill more than tiles_per_split key tiles
-  // is shared by several blocks (at most gridDim.z): block z takes its share of the keys and leaves the
+  // With key splits (n_z > 1) a tile of queries whose visible keys fill more than tiles_per_split key tiles
+  // is shared by several work items (at most n_z): item z takes its share of the keys and leaves the
   // unnormalised output with its (max, sum) here; a second kernel adds the shares.  Tiles of queries with fewer
   // keys are finished by block 0 alone, which marks their rows (max = +inf in share 0) for the second kernel.
   int tiles_per_split;
@@ -79,7 +84,7 @@ struct PrefillParams {
 #ifdef YALIS_TRACE_CLOCKS
 #define STAMP(j, k)                                                                                             \
   do {                                                                                                          \
-    if (p.trace && (j) < 64) p.trace[((size_t)blockIdx.x * 64 + (j)) * 32 + (k)] = clock64(); \
+    if (p.trace && (j) < 64) p.trace[((size_t)trace_row * 64 + (j)) * 32 + (k)] = clock64(); \
   } while (0)
 // Wall-clock stamps (nanoseconds, comparable between blocks) in row 62 of a block's record, and its SM.
 #define GSTAMP(k)                                                                                               \
@@ -87,7 +92,7 @@ struct PrefillParams {
     if (p.trace) {                                                                                              \
       unsigned long long t_;                                                                                    \
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                                    \
-      p.trace[((size_t)blockIdx.x * 64 + 62) * 32 + (k)] = (long long)t_;            \
+      p.trace[((size_t)trace_row * 64 + 62) * 32 + (k)] = (long long)t_;            \
     }                                                                                                           \
   } while (0)
 #else
@@ -227,6 +232,20 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
+// What a work item is, as the copy warp hands it to the others through shared memory.
+struct ItemDesc {
+  int n_tiles;      // key tiles of the item (> 0), or -1: no more items
+  int tile_base;    // its first key tile among the tiles its queries see
+  int n_splits;     // shares that the tile of queries is divided into (1: finished here)
+  int split;        // which of them this item is
+  int kvh;
+  int tok_first;    // row of the first query token in the step
+  int n_rows;       // rows of the tile in use: tokens * heads_per_group
+  int pos_first;    // absolute position of the first query token
+  int hi_key;       // absolute position of the last one = the last visible key
+  int trace_row;
+};
+
 template <int HS>
 __global__ void __launch_bounds__(kThreads, 2)
 prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -246,209 +265,258 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   uint64_t* v_full = bars + 5;                     // 2
   uint64_t* v_empty = bars + 7;                    // 2
   uint64_t* s_full = bars + 9;                     // 2
+  uint64_t* q_empty = bars + 11;                   // 1
   uint64_t* p_full = bars + 13;                    // 2
   uint64_t* o_full = bars + 15;                    // 1
   uint64_t* o_done = bars + 16;                    // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* desc_full = bars + 17;                 // 2
+  uint64_t* desc_empty = bars + 19;                // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kBarriers);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  ItemDesc* descs = reinterpret_cast<ItemDesc*>(tmem_slot + 2);     // [2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // Set-up that needs nothing of the step's data comes before the wait for the kernel in front: descriptors are
-  // asked for (the copy unit reads each from memory before its first copy) and the barriers initialised.  Tensor
-  // memory is taken only once a block knows that it has work: a step's grid is sized by its longest request, and
-  // beside a long portion most blocks of the other requests have none.
+  // The blocks stay for the whole launch, two to an SM, and draw work items (a tile of queries of one KV head,
+  // one share of its keys) from a counter.  The hardware would hand out a block per item as well, but not onto
+  // an SM where another block of this kernel is at work: while a resident block writes tensor memory
+  // (tcgen05.st: P, and O when it is rescaled), the SM is given no new block until that one has ended (measured
+  // with variants of this kernel that left out the copies, the products, the loads or the stores of tensor
+  // memory: only without the stores did a block start as soon as one of the two before it had ended).  With a
+  // block per item every pair of blocks therefore ran as long as its longer one.
+  //
+  // The copy warp draws the items, works out what each is (request, tokens, keys) and hands that to the other
+  // warps through a ring of two descriptors; since it runs up to two key tiles ahead of them, it draws the next
+  // item while the current one is at its last tiles, and has that item's queries and first keys in shared
+  // memory by the time the softmax warps have written the current one's output.  Barriers are initialised
+  // once: buffers and phases are counted on from item to item (every warp keeps the same counts).
+  //
+  // Set-up that needs nothing of the step's data comes before the wait for the kernel in front.
   if (threadIdx.x == 0) {
-    GSTAMP(3);
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
-    GSTAMP(4);
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&k_full[b], 1); mbar_init(&k_empty[b], 1);
       mbar_init(&v_full[b], 1); mbar_init(&v_empty[b], 1);
       mbar_init(&s_full[b], 1);
       mbar_init(&p_full[b], 4);
+      mbar_init(&desc_full[b], 1);
+      mbar_init(&desc_empty[b], 5);                 // the product warp and the four softmax warps
     }
     mbar_init(o_full, 1);
     mbar_init(o_done, 1);
     *abort_flag = 0;
-    GSTAMP(5);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    GSTAMP(6);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    GSTAMP(7);
   }
-  __syncthreads();
-  if (threadIdx.x == 0) { STAMP(63, 0); GSTAMP(0); }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
   pdl_launch_dependents();
-  pdl_wait();
-  if (threadIdx.x == 0) STAMP(63, 1);
-  // The grid's x counts tiles of queries of the whole step (an upper bound that the host can give without the
-  // requests' lengths); each warp finds the request of this block's tile by adding up the requests' tiles, 32
-  // requests at a time.  A step with one long portion beside many short requests launches no blocks for tiles
-  // that the short ones do not have.
-  // Blocks are handed out in the order of blockIdx.x: the KV heads of a tile of queries are neighbours there, and
-  // later tiles, which see more keys, come first, so that the light ones fill the tail.  (With the tiles along x
-  // and the heads along y, the heavy tiles of the last heads started after the light tiles of the first: at
-  // 2,048 tokens and 8 heads the last block to end was a heaviest one that had started 33 us into the launch.)
-  const int kvh = (int)blockIdx.x % p.g;
-  const int flat = (int)gridDim.x / p.g - 1 - (int)blockIdx.x / p.g;
-  const bool count_single = !(p.skip_single && gridDim.z == 1);
-  int req = -1, tile_in_req = 0;
-  for (int c = 0, base = 0; c < p.n_requests; c += 32) {
-    int tiles = 0;
-    if (c + lane < p.n_requests) {
-      const int q = p.q_start[c + lane + 1] - p.q_start[c + lane];
-      tiles = (q == 1 && !count_single) ? 0 : (q + p.tokens_per_tile - 1) / p.tokens_per_tile;
-    }
-    int upto = tiles;                                       // tiles of requests c .. c + lane
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int below = __shfl_up_sync(0xffffffffu, upto, o);
-      if (lane >= o) upto += below;
-    }
-    const int total = __shfl_sync(0xffffffffu, upto, 31);
-    if (flat < base + total) {                              // uniform: flat, base and total are
-      const int owner = __ffs(__ballot_sync(0xffffffffu, base + upto > flat)) - 1;
-      req = c + owner;
-      tile_in_req = flat - base - __shfl_sync(0xffffffffu, upto - tiles, owner);
-      break;
-    }
-    base += total;
-  }
-  if (req < 0) return;                                      // uniform for the block, like everything up to the roles
-  const int32_t* bt = p.block_table + (size_t)req * p.table_width;
-  // The loads below are issued back to back: two round trips to memory (token range and first pages; then
-  // positions) stand between the start of a block and its first copy, not four.
-  const int page_shift = 31 - __clz(p.page_size);                   // pages are powers of two
-  const int box_shift = min(page_shift, 6);
-  const int my_box = lane / (HS / 64), my_half = lane - my_box * (HS / 64);
-  int early_page = -2;                                      // the copy warp's page of tile 0 (known before the positions are)
-  if (warp == 4 && gridDim.z == 1) {
-    const int pi = (my_box << box_shift) >> page_shift;
-    early_page = (my_box < (BN >> box_shift) && pi < p.table_width) ? bt[pi] : -1;
-  }
-  const int tok0 = p.q_start[req], q_len = p.q_start[req + 1] - tok0;
-  const int t0 = tile_in_req * p.tokens_per_tile;           // first token of this block within the request
-  if (p.skip_single && q_len == 1) {
-    // Another kernel writes this request's row; with key splits the second kernel must leave it alone.
-    if (gridDim.z > 1 && blockIdx.z == 0 && (int)threadIdx.x < p.per)
-      *reinterpret_cast<float2*>(p.part_ml + (((size_t)tok0 * p.nh + kvh * p.per + threadIdx.x) * gridDim.z) * 2) =
-          make_float2(INFINITY, 0.f);
-    return;
-  }
-  const int n_tok = min(p.tokens_per_tile, q_len - t0);
-  const int n_rows = n_tok * p.per;
-  const int pos_first = p.positions[tok0 + t0];
-  const int hi_key = p.positions[tok0 + t0 + n_tok - 1];
-  // This block's share of the key tiles (all of them without splits).
-  const int all_tiles = hi_key / BN + 1;
-  const int slots = gridDim.z, split = blockIdx.z;          // slots: shares that the scratch memory has room for
-  const int wanted = slots > 1 ? min(slots, (all_tiles + p.tiles_per_split - 1) / p.tiles_per_split) : 1;
-  const int per_split = (all_tiles + wanted - 1) / wanted;
-  const int n_splits = (all_tiles + per_split - 1) / per_split;     // shares that get a tile (7 tiles in 5 shares: 4 of 2)
-  if (split >= n_splits) {
-    if (n_splits > 1 && (int)threadIdx.x < n_rows) {        // an unused share of a divided tile: nothing to add
-      const int t_in = threadIdx.x / p.per, head = threadIdx.x - t_in * p.per;
-      const size_t slot = ((size_t)(tok0 + t0 + t_in) * p.nh + kvh * p.per + head) * slots + split;
-      *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(-INFINITY, 0.f);
-    }
-    return;
-  }
-  const int tile_base = split * per_split;
-  const int n_tiles = min(all_tiles, tile_base + per_split) - tile_base;     // >= 1
+  pdl_wait();             // the counter is read only after this: the launch before this one has left it at zero
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+  const int slots = p.n_z;                                  // shares that the scratch memory has room for
 
-  // Tensor memory, for all but the copy warp, which starts its copies at once.
-  uint32_t tmem = 0;
-  if (warp != 4) {
-    if (warp == 5) {
-      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    asm volatile("bar.sync 1, 160;" ::: "memory");
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    tmem = *tmem_slot;
-  }
-  if (threadIdx.x == 0) STAMP(63, 2);
-
-  int k_armed = 0, v_armed = 0;
+  int q_armed = 0, k_armed = 0, v_armed = 0;                // copies the copy warp has asked for (for the drain)
   if (warp == 4) {
-    // ---------------------------------- TMA producer ------------------------------------------
+    // ---------------------------------- items and TMA copies -----------------------------------
     // Lane 0 waits for free buffers and arms the barriers; lane c issues box c of a tile (with small pages one
     // thread would spend longer issuing them than they take).  A tile is fetched in boxes of min(page, BN) keys:
     // several pages, or a part of one.
-    if (lane == 0) {
-      mbar_expect_tx(q_full, (uint32_t)(p.tokens_per_tile * p.per) * HS * 2);
-#pragma unroll
-      for (int h = 0; h < H2; ++h)
-        tma_load_3d(q_s + h * (BM * 128), &map_q, h * 64, kvh * p.per, tok0 + t0, q_full);
-    }
+    const int page_shift = 31 - __clz(p.page_size);                 // pages are powers of two
+    const int box_shift = min(page_shift, 6);
+    const int my_box = lane / (HS / 64), my_half = lane - my_box * (HS / 64);
     const int box_rows = 1 << box_shift;
     const int boxes_per_tile = BN >> box_shift;
     const uint32_t box_bytes = (uint32_t)box_rows * HS * 2;         // my_box, my_half: boxes_per_tile * H2 <= 16 lanes have a box
-    // Row of this lane's box of tile j in the pool seen as a matrix (K and V pools are laid out alike), or -1.
-    auto box_row = [&](int j) -> int {
-      const int key = ((tile_base + j) << 6) + (my_box << box_shift);
-      if (j >= n_tiles || my_box >= boxes_per_tile || key > hi_key) return -1;
-      const int pi = key >> page_shift;
-      int page = (j == 0 && early_page != -2) ? early_page : (pi < p.table_width ? bt[pi] : -1);
-      if (page < 0 || page >= p.num_pages) {
-        if (p.error) atomicOr(p.error, YALIS_FLAG_BAD_PAGE);
-        page = 0;
-      }
-      return ((page * p.g + kvh) << page_shift) + (key & (p.page_size - 1));
-    };
+    const bool count_single = !(p.skip_single && slots == 1);
+    uint32_t T = 0;                                         // key tiles handed on so far
+    int n = 0;                                              // items handed on so far
     bool ok = true;
-    auto fetch = [&](int j, int kv, int y) {
-      const int b = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      const int n_boxes = min(boxes_per_tile, ((hi_key - ((tile_base + j) << 6)) >> box_shift) + 1);
-      uint64_t* full = kv == 0 ? &k_full[b] : &v_full[b];
-      uint64_t* empty = kv == 0 ? &k_empty[b] : &v_empty[b];
-      int go = 1;
-      if (lane == 0) {
-        go = mbar_wait(empty, ph ^ 1, abort_flag) ? 1 : 0;
-        if (go) mbar_expect_tx(full, box_bytes * (uint32_t)n_boxes);
+    while (ok) {
+      int item = 0;
+      if (lane == 0) item = atomicAdd(p.work, 1);
+      item = __shfl_sync(0xffffffffu, item, 0);
+      if (item >= p.n_items) break;
+      // Items are numbered share by share, within a share tile by tile with the KV heads of a tile of queries as
+      // neighbours, and later tiles, which see more keys, first, so that the light ones fill the tail.  The
+      // request of the item's tile is found by adding up the requests' tiles, 32 requests at a time (the launch
+      // counts tiles of the whole step, an upper bound that the host can give without the requests' lengths).
+      const int split = item / p.items_per_share, in_share = item - split * p.items_per_share;
+      const int kvh = in_share % p.g;
+      const int flat = p.items_per_share / p.g - 1 - in_share / p.g;
+      int req = -1, tile_in_req = 0;
+      for (int c = 0, seen = 0; c < p.n_requests; c += 32) {
+        int tiles = 0;
+        if (c + lane < p.n_requests) {
+          const int q = p.q_start[c + lane + 1] - p.q_start[c + lane];
+          tiles = (q == 1 && !count_single) ? 0 : (q + p.tokens_per_tile - 1) / p.tokens_per_tile;
+        }
+        int upto = tiles;                                     // tiles of requests c .. c + lane
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int below = __shfl_up_sync(0xffffffffu, upto, o);
+          if (lane >= o) upto += below;
+        }
+        const int total = __shfl_sync(0xffffffffu, upto, 31);
+        if (flat < seen + total) {                            // uniform: flat, seen and total are
+          const int owner = __ffs(__ballot_sync(0xffffffffu, seen + upto > flat)) - 1;
+          req = c + owner;
+          tile_in_req = flat - seen - __shfl_sync(0xffffffffu, upto - tiles, owner);
+          break;
+        }
+        seen += total;
       }
-      go = __shfl_sync(0xffffffffu, go, 0);
-      if (!go) { ok = false; return; }
-      if (lane == 0) STAMP(j, 30 + kv);
-      if (y >= 0)
-        tma_load_2d((kv == 0 ? k_s : v_s) + b * KV_BYTES + my_half * (BN * 128) + my_box * box_rows * 128,
-                    kv == 0 ? &map_k : &map_v, my_half * 64, y, full);
-      __syncwarp();
-      if (kv == 0) k_armed = j + 1; else v_armed = j + 1;
-    };
-    // K runs one tile ahead of V (their buffers come free in that order: QK(j-1), then PV(j-2)); the pages of
-    // a tile are looked up a tile before its K is asked for.
-    int y_v = box_row(0);
-    fetch(0, 0, y_v);                                       // the first keys are on their way before anything else is looked up
-    int y_k = box_row(1), y_ahead = box_row(2);
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      if (j + 1 < n_tiles) fetch(j + 1, 0, y_k);
-      if (ok) fetch(j, 1, y_v);
-      y_v = y_k;
-      y_k = y_ahead;
-      y_ahead = box_row(j + 3);
+      if (req < 0) continue;                                  // past the step's last tile
+      const int32_t* bt = p.block_table + (size_t)req * p.table_width;
+      // The loads below are issued back to back: two round trips to memory (token range and first pages; then
+      // positions) stand between the draw of an item and its first copy, not four.
+      int early_page = -2;                                    // this lane's page of tile 0 (known before the positions are)
+      if (slots == 1) {
+        const int pi = (my_box << box_shift) >> page_shift;
+        early_page = (my_box < boxes_per_tile && pi < p.table_width) ? bt[pi] : -1;
+      }
+      const int tok0 = p.q_start[req], q_len = p.q_start[req + 1] - tok0;
+      const int t0 = tile_in_req * p.tokens_per_tile;         // first token of this item within the request
+      if (p.skip_single && q_len == 1) {
+        // Another kernel writes this request's row; with key splits the second kernel must leave it alone.
+        if (slots > 1 && split == 0)
+          for (int h = lane; h < p.per; h += 32)
+            *reinterpret_cast<float2*>(p.part_ml + (((size_t)tok0 * p.nh + kvh * p.per + h) * slots) * 2) =
+                make_float2(INFINITY, 0.f);
+        continue;
+      }
+      const int n_tok = min(p.tokens_per_tile, q_len - t0);
+      const int n_rows = n_tok * p.per;
+      const int pos_first = p.positions[tok0 + t0];
+      const int hi_key = p.positions[tok0 + t0 + n_tok - 1];
+      // This item's share of the key tiles (all of them without splits).
+      const int all_tiles = hi_key / BN + 1;
+      const int wanted = slots > 1 ? min(slots, (all_tiles + p.tiles_per_split - 1) / p.tiles_per_split) : 1;
+      const int per_split = (all_tiles + wanted - 1) / wanted;
+      const int n_splits = (all_tiles + per_split - 1) / per_split;   // shares that get a tile (7 tiles in 5 shares: 4 of 2)
+      if (split >= n_splits) {
+        if (n_splits > 1)                                     // an unused share of a divided tile: nothing to add
+          for (int r = lane; r < n_rows; r += 32) {
+            const int t_in = r / p.per, head = r - t_in * p.per;
+            const size_t slot = ((size_t)(tok0 + t0 + t_in) * p.nh + kvh * p.per + head) * slots + split;
+            *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(-INFINITY, 0.f);
+          }
+        continue;
+      }
+      const int tile_base = split * per_split;
+      const int n_tiles = min(all_tiles, tile_base + per_split) - tile_base;     // >= 1
+#ifdef YALIS_TRACE_CLOCKS
+      const int trace_row = in_share;
+#endif
+
+      // Hand the item on: the others are through with the item before the one before.
+      const int d = n & 1;
+      if (!warp_wait(&desc_empty[d], ((n >> 1) & 1) ^ 1, abort_flag, lane)) { ok = false; break; }
+      if (lane == 0) {
+        ItemDesc& it = descs[d];
+        it.n_tiles = n_tiles; it.tile_base = tile_base; it.n_splits = n_splits; it.split = split; it.kvh = kvh;
+        it.tok_first = tok0 + t0; it.n_rows = n_rows; it.pos_first = pos_first; it.hi_key = hi_key;
+        it.trace_row = in_share;
+        mbar_arrive(&desc_full[d]);
+        // Q, once the products of the item before, which read it, are done.
+        ok = mbar_wait(q_empty, (n & 1) ^ 1, abort_flag);
+        if (ok) {
+          mbar_expect_tx(q_full, (uint32_t)(p.tokens_per_tile * p.per) * HS * 2);
+#pragma unroll
+          for (int h = 0; h < H2; ++h)
+            tma_load_3d(q_s + h * (BM * 128), &map_q, h * 64, kvh * p.per, tok0 + t0, q_full);
+          q_armed = n + 1;
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      // Row of this lane's box of tile j in the pool seen as a matrix (K and V pools are laid out alike), or -1.
+      auto box_row = [&](int j) -> int {
+        const int key = ((tile_base + j) << 6) + (my_box << box_shift);
+        if (j >= n_tiles || my_box >= boxes_per_tile || key > hi_key) return -1;
+        const int pi = key >> page_shift;
+        int page = (j == 0 && early_page != -2) ? early_page : (pi < p.table_width ? bt[pi] : -1);
+        if (page < 0 || page >= p.num_pages) {
+          if (p.error) atomicOr(p.error, YALIS_FLAG_BAD_PAGE);
+          page = 0;
+        }
+        return ((page * p.g + kvh) << page_shift) + (key & (p.page_size - 1));
+      };
+      auto fetch = [&](int j, int kv, int y) {
+        const int b = (T + j) & 1;
+        const uint32_t ph = ((T + j) >> 1) & 1;
+        const int n_boxes = min(boxes_per_tile, ((hi_key - ((tile_base + j) << 6)) >> box_shift) + 1);
+        uint64_t* full = kv == 0 ? &k_full[b] : &v_full[b];
+        uint64_t* empty = kv == 0 ? &k_empty[b] : &v_empty[b];
+        int go = 1;
+        if (lane == 0) {
+          go = mbar_wait(empty, ph ^ 1, abort_flag) ? 1 : 0;
+          if (go) mbar_expect_tx(full, box_bytes * (uint32_t)n_boxes);
+        }
+        go = __shfl_sync(0xffffffffu, go, 0);
+        if (!go) { ok = false; return; }
+        if (lane == 0) STAMP(j, 30 + kv);
+        if (y >= 0)
+          tma_load_2d((kv == 0 ? k_s : v_s) + b * KV_BYTES + my_half * (BN * 128) + my_box * box_rows * 128,
+                      kv == 0 ? &map_k : &map_v, my_half * 64, y, full);
+        __syncwarp();
+        if (kv == 0) k_armed = (int)T + j + 1; else v_armed = (int)T + j + 1;
+      };
+      // K runs one tile ahead of V (their buffers come free in that order: QK(j-1), then PV(j-2)); the pages of
+      // a tile are looked up a tile before its K is asked for.
+      int y_v = box_row(0);
+      fetch(0, 0, y_v);                                       // the first keys are on their way before anything else is looked up
+      int y_k = box_row(1), y_ahead = box_row(2);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) fetch(j + 1, 0, y_k);
+        if (ok) fetch(j, 1, y_v);
+        y_v = y_k;
+        y_k = y_ahead;
+        y_ahead = box_row(j + 3);
+      }
+      T += (uint32_t)n_tiles;
+      ++n;
+    }
+    // No more items: tell the others (unless something gave up; then they find out from the flag).
+    if (ok) {
+      const int d = n & 1;
+      if (warp_wait(&desc_empty[d], ((n >> 1) & 1) ^ 1, abort_flag, lane) && lane == 0) {
+        descs[d].n_tiles = -1;
+        mbar_arrive(&desc_full[d]);
+      }
     }
     __syncwarp();
   } else if (warp == 5) {
     // ---------------------------------- MMA issuer --------------------------------------------
     // The whole warp runs the loop and every lane waits on the barriers itself; the elected lane issues.  (With
     // one lane polling for the warp, blocks of four and more key tiles ran into their bounded waits.)
-    {
-      const uint32_t elected = elect_one();
-      const uint32_t idesc_qk = idesc_f16(BN, false), idesc_pv = idesc_f16(HS, true);
-      const uint64_t q_desc = desc_kmajor(smem_u32(q_s));
-      const uint64_t k_desc0 = desc_kmajor(smem_u32(k_s));
-      const uint64_t v_desc0 = desc_mnmajor(smem_u32(v_s), BN * 128);
-      bool ok = mbar_wait(q_full, 0, abort_flag);
+    const uint32_t elected = elect_one();
+    const uint32_t idesc_qk = idesc_f16(BN, false), idesc_pv = idesc_f16(HS, true);
+    const uint64_t q_desc = desc_kmajor(smem_u32(q_s));
+    const uint64_t k_desc0 = desc_kmajor(smem_u32(k_s));
+    const uint64_t v_desc0 = desc_mnmajor(smem_u32(v_s), BN * 128);
+    uint32_t T = 0;
+    bool ok = true;
+    for (int n = 0; ok; ++n) {
+      const int d = n & 1;
+      if (!mbar_wait(&desc_full[d], (n >> 1) & 1, abort_flag)) break;
+      const int n_tiles = descs[d].n_tiles;
+      if (n_tiles < 0) break;
+#ifdef YALIS_TRACE_CLOCKS
+      const int trace_row = descs[d].trace_row;
+#endif
+      ok = mbar_wait(q_full, n & 1, abort_flag);
       if (lane == 0) STAMP(63, 3);
       auto issue_qk = [&](int j) -> bool {
-        const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int b = (T + j) & 1;
+        const uint32_t ph = ((T + j) >> 1) & 1;
         // The S buffer is free: the wait for P(j-2), which lay in it, came after every softmax thread had read
         // S(j-2), and the product that read P(j-2) was issued before this one (products run in issue order).
         if (!mbar_wait(&k_full[b], ph, abort_flag)) return false;
@@ -464,20 +532,23 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
         umma_commit(elected, &s_full[b]);
         umma_commit(elected, &k_empty[b]);
+        if (j == n_tiles - 1) umma_commit(elected, q_empty);     // the item's last reader of Q
         return true;
       };
       if (ok) ok = issue_qk(0);
       if (lane == 0) STAMP(63, 4);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int b = (T + j) & 1;
+        const uint32_t ph = ((T + j) >> 1) & 1;
         if (lane == 0) STAMP(j, 6);
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);
         if (!ok) break;
         if (lane == 0) STAMP(j, 7);
         if (!mbar_wait(&v_full[b], ph, abort_flag)) { ok = false; break; }
         if (lane == 0) STAMP(j, 8);
-        if (!mbar_wait(&p_full[b], ph, abort_flag)) { ok = false; break; }      // P(j) written, O rescaled if needed
+        // P(j) written, O rescaled if needed.  For the item's first tile this also says that every softmax warp
+        // has read the O of the item before: a warp arrives here only after its part of that output is written.
+        if (!mbar_wait(&p_full[b], ph, abort_flag)) { ok = false; break; }
         if (lane == 0) STAMP(j, 9);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint64_t v_desc = v_desc0 + (uint64_t)((b * KV_BYTES) >> 4);
@@ -491,164 +562,199 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         umma_commit(elected, &v_empty[b]);
         if (lane == 0) STAMP(j, 10);
       }
-      if (ok) umma_commit(elected, o_done);
+      if (!ok) break;
+      umma_commit(elected, o_done);
+      T += (uint32_t)n_tiles;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&desc_empty[d]);
     }
     __syncwarp();
   } else {
     // ---------------------------------- softmax, one thread per row ----------------------------
     const int r = threadIdx.x;                        // row of the tile = tensor-memory lane
-    const bool valid = r < n_rows;
-    const int t_in = r / p.per, head = r - t_in * p.per;
-    const int pos_row = valid ? p.positions[tok0 + t0 + t_in] : -1;
     const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-    float m_run = -INFINITY, l_run = 0.f;
+    uint32_t T = 0;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int b = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      const int key0 = (tile_base + j) * BN;
-      if (lane == 0) STAMP(j, 0 + (warp ? 6 + warp * 6 : 0));
-      if (!warp_wait(&s_full[b], ph, abort_flag, lane)) { ok = false; break; }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (lane == 0) STAMP(j, 1 + (warp ? 6 + warp * 6 : 0));
-      float sv[BN];
-      {
-        const uint32_t s_addr = lane_base + COL_S + b * BN;
-#pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 32) tmem_ld32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      }
-      // S is in registers now; its buffer is written again only after P(j), which takes its place, has been used.
-      if (lane == 0) STAMP(j, 2 + (warp ? 6 + warp * 6 : 0));
-      if (key0 + BN - 1 > pos_first || !valid) {           // some key of the tile is hidden from this row
-#pragma unroll
-        for (int c = 0; c < BN; ++c)
-          if (!valid || key0 + c > pos_row) sv[c] = -INFINITY;
-      }
-      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < BN; c += 8) {                    // four chains of three-input maxima
-        mx[0] = max3(mx[0], sv[c], sv[c + 1]); mx[1] = max3(mx[1], sv[c + 2], sv[c + 3]);
-        mx[2] = max3(mx[2], sv[c + 4], sv[c + 5]); mx[3] = max3(mx[3], sv[c + 6], sv[c + 7]);
-      }
-      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
-      const float m_new = fmaxf(m_run, m_tile);
-      if (lane == 0) STAMP(j, 3 + (warp ? 6 + warp * 6 : 0));
-      // Keep the older maximum unless the new one is more than 2^8 larger: exp2 of at most 8 is
-      // harmless in float32 and bfloat16, and O then needs no rescaling.
-      const bool grow = (m_new - m_run > 8.0f) || (m_run == -INFINITY && m_new != -INFINITY);
-      const float m_use = grow ? m_new : m_run;
-      const float mb = (m_use == -INFINITY) ? 0.f : m_use;
-      const float corr = grow ? ((m_run == -INFINITY) ? 0.f : ex2(m_run - mb)) : 1.f;
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};
-      const uint32_t p_addr = lane_base + COL_S + b * BN;          // over the first half of S(j)
-#pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int c = 0; c < 32; c += 4) {
-          const float p0 = ex2(fmaf(sv[c0 + c], p.scale_log2, -mb)), p1 = ex2(fmaf(sv[c0 + c + 1], p.scale_log2, -mb));
-          const float p2 = ex2(fmaf(sv[c0 + c + 2], p.scale_log2, -mb)), p3 = ex2(fmaf(sv[c0 + c + 3], p.scale_log2, -mb));
-          ls[0] += p0; ls[1] += p1; ls[2] += p2; ls[3] += p3;
-          pk[c >> 1] = pack_bf16(p0, p1);
-          pk[(c >> 1) + 1] = pack_bf16(p2, p3);
-        }
-        tmem_st16(p_addr + (c0 >> 1), pk);
-      }
-      l_run = l_run * corr + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
-      if (lane == 0) STAMP(j, 4 + (warp ? 6 + warp * 6 : 0));
-      m_run = m_use;
-      // Rescale O in place if some row of this warp moved its maximum (never for the first tile).
-      if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        if (!warp_wait(o_full, (j - 1) & 1, abort_flag, lane)) { ok = false; break; }     // P V of tile j-1 is done
+    for (int n = 0; ok; ++n) {
+      const int d = n & 1;
+      if (!warp_wait(&desc_full[d], (n >> 1) & 1, abort_flag, lane)) break;
+      const int n_tiles = descs[d].n_tiles;
+      if (n_tiles < 0) break;
+      const int tile_base = descs[d].tile_base, n_splits = descs[d].n_splits, split = descs[d].split;
+      const int kvh = descs[d].kvh, tok_first = descs[d].tok_first, n_rows = descs[d].n_rows;
+      const int pos_first = descs[d].pos_first, hi_key = descs[d].hi_key;
+#ifdef YALIS_TRACE_CLOCKS
+      const int trace_row = descs[d].trace_row;
+      if (threadIdx.x == 0) { STAMP(63, 0); GSTAMP(0); }
+#endif
+      const bool valid = r < n_rows;
+      const int t_in = r / p.per, head = r - t_in * p.per;
+      const int pos_row = valid ? p.positions[tok_first + t_in] : -1;
+      float m_run = -INFINITY, l_run = 0.f;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int b = (T + j) & 1;
+        const uint32_t ph = ((T + j) >> 1) & 1;
+        const int key0 = (tile_base + j) * BN;
+        if (lane == 0) STAMP(j, 0 + (warp ? 6 + warp * 6 : 0));
+        if (!warp_wait(&s_full[b], ph, abort_flag, lane)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (lane == 0) STAMP(j, 1 + (warp ? 6 + warp * 6 : 0));
+        float sv[BN];
+        {
+          const uint32_t s_addr = lane_base + COL_S + b * BN;
+#pragma unroll
+          for (int c0 = 0; c0 < BN; c0 += 32) tmem_ld32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(&sv[c0]));
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        }
+        // S is in registers now; its buffer is written again only after P(j), which takes its place, has been used.
+        if (lane == 0) STAMP(j, 2 + (warp ? 6 + warp * 6 : 0));
+        if (key0 + BN - 1 > pos_first || !valid) {           // some key of the tile is hidden from this row
+#pragma unroll
+          for (int c = 0; c < BN; ++c)
+            if (!valid || key0 + c > pos_row) sv[c] = -INFINITY;
+        }
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < BN; c += 8) {                    // four chains of three-input maxima
+          mx[0] = max3(mx[0], sv[c], sv[c + 1]); mx[1] = max3(mx[1], sv[c + 2], sv[c + 3]);
+          mx[2] = max3(mx[2], sv[c + 4], sv[c + 5]); mx[3] = max3(mx[3], sv[c + 6], sv[c + 7]);
+        }
+        const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+        const float m_new = fmaxf(m_run, m_tile);
+        if (lane == 0) STAMP(j, 3 + (warp ? 6 + warp * 6 : 0));
+        // Keep the older maximum unless the new one is more than 2^8 larger: exp2 of at most 8 is
+        // harmless in float32 and bfloat16, and O then needs no rescaling.
+        const bool grow = (m_new - m_run > 8.0f) || (m_run == -INFINITY && m_new != -INFINITY);
+        const float m_use = grow ? m_new : m_run;
+        const float mb = (m_use == -INFINITY) ? 0.f : m_use;
+        const float corr = grow ? ((m_run == -INFINITY) ? 0.f : ex2(m_run - mb)) : 1.f;
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint32_t p_addr = lane_base + COL_S + b * BN;          // over the first half of S(j)
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int c = 0; c < 32; c += 4) {
+            const float p0 = ex2(fmaf(sv[c0 + c], p.scale_log2, -mb)), p1 = ex2(fmaf(sv[c0 + c + 1], p.scale_log2, -mb));
+            const float p2 = ex2(fmaf(sv[c0 + c + 2], p.scale_log2, -mb)), p3 = ex2(fmaf(sv[c0 + c + 3], p.scale_log2, -mb));
+            ls[0] += p0; ls[1] += p1; ls[2] += p2; ls[3] += p3;
+            pk[c >> 1] = pack_bf16(p0, p1);
+            pk[(c >> 1) + 1] = pack_bf16(p2, p3);
+          }
+          tmem_st16(p_addr + (c0 >> 1), pk);
+        }
+        l_run = l_run * corr + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
+        if (lane == 0) STAMP(j, 4 + (warp ? 6 + warp * 6 : 0));
+        m_run = m_use;
+        // Rescale O in place if some row of this warp moved its maximum (never for the first tile).
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          if (!warp_wait(o_full, (T + j - 1) & 1, abort_flag, lane)) { ok = false; break; }     // P V of tile j-1 is done
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+          for (int c0 = 0; c0 < HS; c0 += 16) {
+            uint32_t o[16];
+            tmem_ld16(lane_base + COL_O + c0, o);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
+            tmem_st16(lane_base + COL_O + c0, o);
+          }
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        if (key0 + BN - 1 > hi_key) {
+          // Last tile: rows of V past the last visible key may hold anything (even NaN); zero them
+          // once the tile has landed, and make the writes visible to the tensor core's reads.
+          if (!warp_wait(&v_full[b], ph, abort_flag, lane)) { ok = false; break; }
+          if (r < BN && key0 + r > hi_key) {
+            unsigned char* vt = v_s + b * KV_BYTES;
+#pragma unroll
+            for (int h = 0; h < H2; ++h)
+#pragma unroll
+              for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(vt + h * (BN * 128) + r * 128 + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[b]);
+        if (lane == 0) STAMP(j, 5 + (warp ? 6 + warp * 6 : 0));
+      }
+      // ---- O / l -> global --------------------------------------------------------------------
+      if (ok) ok = warp_wait(o_done, n & 1, abort_flag, lane);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (n_splits > 1) {
+        // a share: unnormalised, with the maximum it is relative to and its sum
+        const size_t slot = ((size_t)(tok_first + (valid ? t_in : 0)) * p.nh + kvh * p.per + (valid ? head : 0)) * slots + split;
+        float* dst = p.part_o + slot * HS;
+        if (valid) *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(m_run, l_run);
 #pragma unroll 1
         for (int c0 = 0; c0 < HS; c0 += 16) {
           uint32_t o[16];
           tmem_ld16(lane_base + COL_O + c0, o);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (valid) {
 #pragma unroll
-          for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
-          tmem_st16(lane_base + COL_O + c0, o);
+            for (int c = 0; c < 16; c += 4)
+              *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+          }
+        }
+      } else {
+        if (slots > 1 && valid) {                             // finished here: the second kernel leaves these rows alone
+          const size_t slot = ((size_t)(tok_first + t_in) * p.nh + kvh * p.per + head) * slots;
+          *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(INFINITY, 0.f);
+        }
+        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        __nv_bfloat16* dst = p.out + (size_t)(tok_first + (valid ? t_in : 0)) * p.out_stride +
+                             (size_t)(kvh * p.per + (valid ? head : 0)) * HS;
+#pragma unroll 1
+        for (int c0 = 0; c0 < HS; c0 += 16) {
+          uint32_t o[16];
+          tmem_ld16(lane_base + COL_O + c0, o);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (valid) {
+            uint4 v0, v1;
+            v0.x = pack_bf16(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
+            v0.y = pack_bf16(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
+            v0.z = pack_bf16(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
+            v0.w = pack_bf16(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
+            v1.x = pack_bf16(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
+            v1.y = pack_bf16(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
+            v1.z = pack_bf16(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
+            v1.w = pack_bf16(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
+            *reinterpret_cast<uint4*>(dst + c0) = v0;
+            *reinterpret_cast<uint4*>(dst + c0 + 8) = v1;
+          }
         }
       }
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      if (key0 + BN - 1 > hi_key) {
-        // Last tile: rows of V past the last visible key may hold anything (even NaN); zero them
-        // once the tile has landed, and make the writes visible to the tensor core's reads.
-        if (!warp_wait(&v_full[b], ph, abort_flag, lane)) { ok = false; break; }
-        if (r < BN && key0 + r > hi_key) {
-          unsigned char* vt = v_s + b * KV_BYTES;
-#pragma unroll
-          for (int h = 0; h < H2; ++h)
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-              *reinterpret_cast<uint4*>(vt + h * (BN * 128) + r * 128 + c * 16) = make_uint4(0u, 0u, 0u, 0u);
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#ifdef YALIS_TRACE_CLOCKS
+      if (threadIdx.x == 0) {
+        GSTAMP(1);
+        unsigned sm_;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_));
+        if (p.trace) p.trace[((size_t)trace_row * 64 + 62) * 32 + 2] = sm_ + 1;
       }
+#endif
+      T += (uint32_t)n_tiles;
+      // The O of this item is in registers or written: the next item's first P V may overwrite it (it waits for
+      // this warp's next arrival at p_full, which comes after this point).
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[b]);
-      if (lane == 0) STAMP(j, 5 + (warp ? 6 + warp * 6 : 0));
-    }
-    // ---- O / l -> global --------------------------------------------------------------------
-    if (ok) ok = warp_wait(o_done, 0, abort_flag, lane);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok && n_splits > 1) {
-      // a share: unnormalised, with the maximum it is relative to and its sum
-      const size_t slot = ((size_t)(tok0 + t0 + (valid ? t_in : 0)) * p.nh + kvh * p.per + (valid ? head : 0)) * slots + split;
-      float* dst = p.part_o + slot * HS;
-      if (valid) *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(m_run, l_run);
-#pragma unroll 1
-      for (int c0 = 0; c0 < HS; c0 += 16) {
-        uint32_t o[16];
-        tmem_ld16(lane_base + COL_O + c0, o);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (valid) {
-#pragma unroll
-          for (int c = 0; c < 16; c += 4)
-            *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(o[c], o[c + 1], o[c + 2], o[c + 3]);
-        }
-      }
-    } else if (ok) {
-      if (slots > 1 && valid) {                             // finished here: the second kernel leaves these rows alone
-        const size_t slot = ((size_t)(tok0 + t0 + t_in) * p.nh + kvh * p.per + head) * slots;
-        *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(INFINITY, 0.f);
-      }
-      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-      __nv_bfloat16* dst = p.out + (size_t)(tok0 + t0 + (valid ? t_in : 0)) * p.out_stride +
-                           (size_t)(kvh * p.per + (valid ? head : 0)) * HS;
-#pragma unroll 1
-      for (int c0 = 0; c0 < HS; c0 += 16) {
-        uint32_t o[16];
-        tmem_ld16(lane_base + COL_O + c0, o);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (valid) {
-          uint4 v0, v1;
-          v0.x = pack_bf16(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
-          v0.y = pack_bf16(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
-          v0.z = pack_bf16(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
-          v0.w = pack_bf16(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
-          v1.x = pack_bf16(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
-          v1.y = pack_bf16(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
-          v1.z = pack_bf16(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
-          v1.w = pack_bf16(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
-          *reinterpret_cast<uint4*>(dst + c0) = v0;
-          *reinterpret_cast<uint4*>(dst + c0 + 8) = v1;
-        }
-      }
+      if (lane == 0) mbar_arrive(&desc_empty[d]);
     }
   }
 
-  // ---- exit: drain on abort, free tensor memory -----------------------------------------------
+  // ---- exit: drain on abort, hand the counter back, free tensor memory -------------------------------------
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (*abort_flag) {
     if (threadIdx.x == 4 * 32) {
       if (p.error) atomicOr(p.error, YALIS_FLAG_WAIT_ATTENTION);
-      for (uint32_t i = 0; i < kSpinLimit; ++i)
-        if (mbar_try_wait(q_full, 0)) break;
+      // copies that were asked for and may not have been waited for
+      if (q_armed > 0)
+        for (uint32_t i = 0; i < kSpinLimit; ++i)
+          if (mbar_try_wait(q_full, (q_armed - 1) & 1)) break;
       for (int j = max(0, k_armed - 2); j < k_armed; ++j)
         for (uint32_t i = 0; i < kSpinLimit; ++i)
           if (mbar_try_wait(&k_full[j & 1], (j >> 1) & 1)) break;
@@ -658,18 +764,19 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     }
     __syncthreads();
   }
+  if (threadIdx.x == 0) {
+    // Every block comes here once, after it has drawn a number past the last item or given up; the last to do
+    // so leaves both counters at zero for the next launch.
+    __threadfence();
+    if (atomicAdd(p.work + 1, 1) == (int)gridDim.x - 1) {
+      p.work[0] = 0;
+      p.work[1] = 0;
+      __threadfence();
+    }
+  }
   if (warp == 5) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
-    if (lane == 0) GSTAMP(8);
   }
-#ifdef YALIS_TRACE_CLOCKS
-  if (threadIdx.x == 0) {
-    GSTAMP(1);
-    unsigned sm_;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_));
-    if (p.trace) p.trace[((size_t)blockIdx.x * 64 + 62) * 32 + 2] = sm_ + 1;
-  }
-#endif
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -749,9 +856,9 @@ __global__ void prefill_merge_splits_kernel(const float* __restrict__ part_o, co
 }
 
 template <int HS>
-int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, int n_requests,
-           int max_q_len, int n_splits, int n_tokens, cudaStream_t stream) {
-  const size_t smem = 1024 + (size_t)BM * HS * 2 + (size_t)4 * BN * HS * 2 + 17 * 8 + 16;
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, int n_splits,
+           int n_tokens, cudaStream_t stream) {
+  const size_t smem = 1024 + (size_t)BM * HS * 2 + (size_t)4 * BN * HS * 2 + kBarriers * 8 + 8 + 2 * sizeof(ItemDesc);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(prefill_attention_tcgen05_kernel<HS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -759,13 +866,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
       return YALIS_ERR_LAUNCH;
     configured = true;
   }
-  // Tiles of queries in the step: sum of ceil(q / tokens_per_tile) over the requests, bounded from their number,
-  // the step's tokens and the longest request.
-  const long long tpt = p.tokens_per_tile;
-  const long long tiles = std::min(((long long)n_tokens + (long long)n_requests * (tpt - 1)) / tpt,
-                                   (long long)n_requests * ((max_q_len + tpt - 1) / tpt));
-  if (tiles * p.g > 0x7fffffffLL) return YALIS_ERR_SHAPE;
-  dim3 grid((unsigned)(tiles * p.g), 1, n_splits);
+  // Two blocks to an SM for the whole launch (fewer if the step has fewer items).
+  dim3 grid((unsigned)std::min<long long>(p.n_items, 2LL * yalis_sm_count()), 1, 1);
   int st = yalis_launch(prefill_attention_tcgen05_kernel<HS>, grid, dim3(kThreads), smem, stream, mq, mk, mv, p);
   if (st != YALIS_OK || n_splits == 1) return st;
   return yalis_launch(prefill_merge_splits_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)p.part_o,
@@ -796,13 +898,14 @@ YALIS_API long long yalis_prefill_attention_tcgen05_scratch_floats(int n_tokens,
 // too few tiles of queries to fill the GPU evenly, or a few of them with far more keys than the rest); it needs
 // scratch: yalis_prefill_attention_tcgen05_scratch_floats floats, and every token row of [0, n_tokens) must then
 // belong to a request.  skip_single = 1 leaves the rows of requests that bring one token unwritten (a decode
-// kernel takes them).
+// kernel takes them).  work: two int32 that are zero and that no other launch uses at the same time (the kernel
+// counts its work items in them and leaves them at zero).
 YALIS_API int yalis_prefill_attention_tcgen05(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
                                               const void* v_pool, const int32_t* positions, const int32_t* q_start,
                                               const int32_t* block_table, int table_width, int page_size,
                                               int num_pages, int n_tokens, int n_requests, int max_q_len, int nh,
                                               int g, int hs, float scale, int n_splits, int tiles_per_split, int skip_single,
-                                              float* scratch, int32_t* error, cudaStream_t stream
+                                              float* scratch, int32_t* work, int32_t* error, cudaStream_t stream
 #ifdef YALIS_TRACE_CLOCKS
                                               , long long* trace
 #endif
@@ -811,6 +914,7 @@ YALIS_API int yalis_prefill_attention_tcgen05(const void* q, int q_stride, void*
   if (g <= 0 || nh % g != 0 || max_q_len < 1 || n_splits < 1 || n_splits > 64) return YALIS_ERR_SHAPE;
   if (n_splits > 1 && (scratch == nullptr || ((uintptr_t)scratch & 15))) return YALIS_ERR_ALIGN;
   if (n_splits > 1 && tiles_per_split < 1) return YALIS_ERR_SHAPE;
+  if (work == nullptr) return YALIS_ERR_ALIGN;
   if (!yalis_prefill_attention_tcgen05_supports(hs, page_size, nh / g)) return YALIS_ERR_SHAPE;
   if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) return YALIS_ERR_ALIGN;
   if ((q_stride % 8) || (out_stride % 8)) return YALIS_ERR_ALIGN;
@@ -821,6 +925,18 @@ YALIS_API int yalis_prefill_attention_tcgen05(const void* q, int q_stride, void*
   p.nh = nh; p.g = g; p.per = nh / g;
   p.n_requests = n_requests;
   p.tokens_per_tile = BM / p.per;
+  {
+    // Tiles of queries in the step: sum of ceil(q / tokens_per_tile) over the requests, bounded from their
+    // number, the step's tokens and the longest request.
+    const long long tpt = p.tokens_per_tile;
+    const long long tiles = std::min(((long long)n_tokens + (long long)n_requests * (tpt - 1)) / tpt,
+                                     (long long)n_requests * ((max_q_len + tpt - 1) / tpt));
+    if (tiles * g * n_splits > 0x7fffffffLL) return YALIS_ERR_SHAPE;
+    p.items_per_share = (int)(tiles * g);
+    p.n_z = n_splits;
+    p.n_items = p.items_per_share * n_splits;
+  }
+  p.work = work;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.tiles_per_split = tiles_per_split > 0 ? tiles_per_split : 1;
   p.skip_single = skip_single ? 1 : 0;
@@ -835,6 +951,6 @@ YALIS_API int yalis_prefill_attention_tcgen05(const void* q, int q_stride, void*
   if (!make_q_map(&mq, q, n_tokens, q_stride, nh, hs, p.per, p.tokens_per_tile) ||
       !make_pool_map(&mk, k_pool, rows, hs, page_size) || !make_pool_map(&mv, v_pool, rows, hs, page_size))
     return YALIS_ERR_LAUNCH;
-  return hs == 64 ? launch<64>(mq, mk, mv, p, n_requests, max_q_len, n_splits, n_tokens, stream)
-                  : launch<128>(mq, mk, mv, p, n_requests, max_q_len, n_splits, n_tokens, stream);
+  return hs == 64 ? launch<64>(mq, mk, mv, p, n_splits, n_tokens, stream)
+                  : launch<128>(mq, mk, mv, p, n_splits, n_tokens, stream);
 }

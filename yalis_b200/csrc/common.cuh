@@ -32,6 +32,19 @@ inline int yalis_launch_status() {
   return cudaGetLastError() == cudaSuccess ? YALIS_OK : YALIS_ERR_LAUNCH;
 }
 
+// Streaming multiprocessors of the current device (asked of the driver once per device).
+inline int yalis_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 // ---- programmatic dependent launch ---------------------------------------------------
 // Every kernel of the library is launched with the "programmatic stream serialization"
 // attribute: the next kernel in the stream may be scheduled while this one still runs, do

@@ -384,19 +384,6 @@ gemm_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
 // ---- host side ------------------------------------------------------------------------------
 
-// Streaming multiprocessors of the current device (asked of the driver once per device).
-int sm_count() {
-  static int cached[64] = {0};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
-}
-
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -497,7 +484,7 @@ YALIS_API int yalis_gemm_wstream_splits(int N, int K) {
   const int kt = (K + TILE_K - 1) / TILE_K;
   int best = 1;
   double best_cost = 1e30;
-  const int sms = sm_count();
+  const int sms = yalis_sm_count();
   for (int s = 1; s <= 16; ++s) {
     if (s > 1 && kt / s < 8) break;
     const int blocks = tiles * s;

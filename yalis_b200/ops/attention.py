@@ -136,6 +136,20 @@ def _tickets(device, n: int) -> torch.Tensor:
     return t
 
 
+_work_counter_cache = {}
+
+
+def _work_counters(device) -> torch.Tensor:
+    """Two zeroed int32 in which the prompt kernel counts its work items.  Every launch leaves them zero, so one
+    pair per device is allocated once (outside any graph capture) and shared by launches that run one after the
+    other; launches of this kernel on two streams at the same time would need a pair each."""
+    key = torch.device(device)
+    t = _work_counter_cache.get(key)
+    if t is None:
+        t = _work_counter_cache[key] = torch.zeros(2, dtype=torch.int32, device=key)
+    return t
+
+
 def paged_attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, positions: torch.Tensor,
                         q_start: torch.Tensor, req_of_token: torch.Tensor, block_table: torch.Tensor, max_q_len: int,
                         num_heads: int, num_kv_heads: int, head_dim: int, scale: Optional[float] = None,
@@ -413,7 +427,7 @@ def prefill_attention_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
         ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(k_pool), ptr(v_pool), ptr(positions), ptr(q_start),
         ptr(block_table), i32(block_table.shape[1]), i32(k_pool.shape[2]), i32(k_pool.shape[0]), i32(n), i32(r),
         i32(max_q_len), i32(num_heads), i32(num_kv_heads), i32(head_dim), f32(scale), i32(kv_splits), i32(tiles_per_split),
-        i32(1 if skip_single else 0), ptr(scratch), ptr(error_flag), stream()), name)
+        i32(1 if skip_single else 0), ptr(scratch), ptr(_work_counters(q.device)), ptr(error_flag), stream()), name)
     return out
 
 
