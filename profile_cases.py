@@ -114,10 +114,21 @@ def attention_prefill(args) -> None:
     if splits == 0:
         splits, limit = prefill_kv_splits(SimpleNamespace(q_start=starts, ctx_before=before), nh // g, g, hs)
 
+    if args.kernel == "library":
+        # The bar: the library attention that the reference's flash backend calls (yalis/attention/backend_impl/
+        # flash.py:52-65), on one request's keys laid out contiguously (its paged form wants pages of 256).
+        assert len(q_lens) == 1 and before == [0], "--kernel library times one whole prompt"
+        from flash_attn import flash_attn_func
+        q4 = q.view(1, n, nh, hs)
+        k4 = torch.randn(1, n, g, hs, device=dev).to(torch.bfloat16)
+        v4 = torch.randn(1, n, g, hs, device=dev).to(torch.bfloat16)
+
     def fn():
         if args.kernel == "tcgen05":
             prefill_attention_tcgen05(q, k_pool, v_pool, pos, q_start, table, max(q_lens), nh, g, hs, kv_splits=splits,
                                       tiles_per_split=limit)
+        elif args.kernel == "library":
+            flash_attn_func(q4, k4, v4, causal=True)
         else:
             paged_attention_mma(q, k_pool, v_pool, pos, q_start, req, table, max(q_lens), nh, g, hs)
 
@@ -251,7 +262,8 @@ def main() -> None:
     ap_.add_argument("--kv-heads", type=int, default=8)
     ap_.add_argument("--head-dim", type=int, default=128)
     ap_.add_argument("--page-size", type=int, default=64)
-    ap_.add_argument("--kernel", default="tcgen05", choices=["tcgen05", "mma"])
+    ap_.add_argument("--kernel", default="tcgen05", choices=["tcgen05", "mma", "library"],
+                     help="library: flash_attn's kernel on contiguous keys, as the bar")
     ap_.add_argument("--launches", type=int, default=4)
     ap_.set_defaults(fn=attention_prefill)
     ew = sub.add_parser("elementwise")

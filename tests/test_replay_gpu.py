@@ -321,6 +321,35 @@ def test_steps_with_portions_are_recorded_when_their_shape_repeats(which, dtype)
             row[e["id"]].append((None, (0 if not row[e["id"]] else row[e["id"]][-1][1]) + len(e["tokens"])))
 
 
+def test_shapes_that_turn_over_faster_than_they_repeat_are_launched(monkeypatch):
+    """Four shapes of step in turn with room for two recordings: the two that are recorded first stay and replay,
+    the others are launched, nothing is recorded over and over; every step gives the logits of the launched
+    path.  A recording that has lain idle long enough makes room in the end."""
+    from yalis_b200.engine import recorded
+    from yalis_b200.engine.engine import Engine, StepEntry
+    d = tiny_model_dir("C", STD["bfloat16"])
+    made = []
+    init = recorded.RecordedStep.__init__
+    monkeypatch.setattr(recorded.RecordedStep, "__init__", lambda self, *a, **k: (made.append(a[1]), init(self, *a, **k))[1])
+    lengths = [16, 20, 24, 28] * 4 + [16, 20] * 2 + [24] * 8          # in turn; then the recorded two; then one of the others
+    outputs = {}
+    for graphs in (False, True):
+        eng = Engine(d, dtype="bfloat16", page_size=16, num_pages=16, max_slots=2)
+        eng.MAX_EXACT_RECORDINGS, eng.IDLE_STEPS_BEFORE_EVICTION = 2, 6
+        outputs[graphs] = []
+        for k, n in enumerate(lengths):
+            eng.add_request(k)
+            out = eng.run([StepEntry(k, [(7 * k + i) % 50 for i in range(n)], [n - 1])], graphs=graphs)
+            outputs[graphs].append((out.captured, out.logits.float().cpu()))
+            eng.finish_request(k)
+        eng.manager.check()
+    assert made == [16, 20, 24]                                       # 24 only once the recording of 16 had lain idle
+    captured = [c for c, _ in outputs[True]]
+    assert captured == [False] * 4 + [True, True, False, False] * 3 + [True] * 4 + [False] * 4 + [True] * 4
+    for (_, a), (_, b) in zip(outputs[False], outputs[True]):
+        torch.testing.assert_close(a, b, rtol=0, atol=0)
+
+
 def test_a_refused_step_reserves_nothing():
     """A step that needs more pages than are free raises before anything runs and keeps no page, whoever calls it."""
     from yalis_b200.engine.engine import Engine, OutOfPages, StepEntry

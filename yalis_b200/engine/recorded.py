@@ -85,6 +85,7 @@ class RecordedStep:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches = 0
         self.replays = 0
+        self.last_used = 0          # the engine's count of steps when this recording was last asked for
         self.copy_done: Optional[torch.cuda.Event] = None
         self.ctx = None
         self.d = None

@@ -22,8 +22,10 @@ never sees the model configuration, the architecture's name or another layer.
 New kinds are added with ``register_part(category, kind, cls)``; nothing else in
 the package has to change.
 
-Steps in which every request brings one token can be recorded once (a CUDA
-graph) and replayed.  A replay runs no Python, so whatever a part decides on the
+A step can be recorded once (a CUDA graph) and replayed: steps in which every
+request brings one token share a recording per bucket of requests, other steps
+get one at their exact counts when their shape comes again.  A replay runs no
+Python, so whatever a part decides on the
 host from the step's facts has to be the same for every step that replays one
 recording: ``capture_key(host)`` returns a hashable that determines all such
 decisions (kernel choice, grid sizes), or ``NOT_CAPTURABLE`` (the default) for a
