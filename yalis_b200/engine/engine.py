@@ -8,8 +8,9 @@ the wanted places and, if asked, chooses a token at each of them.  It does not
 decide what runs next: the scheduler above it does.
 
 There is one step function.  Whether a step is launched kernel by kernel or
-replayed from a recording (a CUDA graph over buffers of fixed size, for steps
-in which every request brings one token) is decided inside it, after the same
+replayed from a recording (a CUDA graph over buffers of fixed size: per bucket
+of requests for steps in which every request brings one token, at the exact
+counts for other steps whose shape comes again) is decided inside it, after the same
 validation and reservation, from the same host arrays, and followed by the same
 commit; trace replay and generation therefore drive the same code.
 
