@@ -350,6 +350,38 @@ def test_shapes_that_turn_over_faster_than_they_repeat_are_launched(monkeypatch)
         torch.testing.assert_close(a, b, rtol=0, atol=0)
 
 
+def test_tensors_stored_in_float32_stay_so_under_bfloat16():
+    """A checkpoint whose embedding, one fused projection part, one down projection and the final norm are stored
+    in float32: the bfloat16 engine keeps them in float32 (their products run on the exact kernels, bfloat16 rows
+    against float32 weights) and its logits still match the plain model, whole and decoded, launched and recorded."""
+    from yalis_b200.weights.safetensors_io import Checkpoint, write_safetensors
+    which, dtype, std = "C", "bfloat16", STD["bfloat16"]
+    src = tiny_model_dir(which, std)
+    with tempfile.TemporaryDirectory() as d:
+        with Checkpoint(src) as ck:
+            tensors = {n: ck.get(n).clone() for n in ck.names()}
+        wide = [n for n in tensors if n.endswith(("embed_tokens.weight", "layers.0.self_attn.k_proj.weight",
+                                                   "layers.1.mlp.down_proj.weight", "model.norm.weight"))]
+        assert len(wide) == 4
+        for n in wide:
+            tensors[n] = tensors[n].float()
+        write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+        with open(os.path.join(src, "config.json")) as f, open(os.path.join(d, "config.json"), "w") as g:
+            g.write(f.read())
+        cfg = plain.read_config(d)
+        requests = make_requests(cfg, [40, 70], seed=21)
+        w = plain.read_weights(d)
+        want = {rid: plain.forward_logits(t, w, cfg).numpy() for rid, t in requests.items()}
+        for graphs in (False, True):
+            steps = traces.number(traces.tail_decoded(requests))
+            out, rep = replay_in_process(d, dtype, page_size_of(which), steps, traces.peak_tokens(steps), graphs=graphs)
+            model = rep.engine.model
+            assert model.embedding.dtype == torch.float32 and model.blocks[0].mixer.w_qkv.dtype == torch.float32
+            assert model.blocks[1].feed_forward.w_down.dtype == torch.float32
+            assert model.blocks[1].mixer.w_qkv.dtype == torch.bfloat16
+            compare(traces.collect(steps, out, cfg["vocab_size"]), want, TOL[dtype], f"float32-stored tensors, graphs={graphs}")
+
+
 def test_a_refused_step_reserves_nothing():
     """A step that needs more pages than are free raises before anything runs and keeps no page, whoever calls it."""
     from yalis_b200.engine.engine import Engine, OutOfPages, StepEntry

@@ -114,3 +114,28 @@ def test_dtype_policy():
     assert target_dtype(ParamSpec((1,)), torch.float32) == torch.float32
     assert target_dtype(ParamSpec((1,), keep_float32=True), torch.bfloat16) == torch.float32
     assert target_dtype(ParamSpec((1,), integer=True), torch.bfloat16) == torch.int32
+    # what the checkpoint stores in 32 (or 64) bits stays float32; 16-bit storage follows the engine
+    assert target_dtype(ParamSpec((1,)), torch.bfloat16, stored=torch.float32) == torch.float32
+    assert target_dtype(ParamSpec((1,)), torch.bfloat16, stored=torch.float64) == torch.float32
+    assert target_dtype(ParamSpec((1,)), torch.bfloat16, stored=torch.float16) == torch.bfloat16
+    assert target_dtype(ParamSpec((1,)), torch.float32, stored=torch.bfloat16) == torch.float32
+    assert target_dtype(ParamSpec((1,), integer=True), torch.bfloat16, stored=torch.int64) == torch.int32
+
+
+def test_a_tensor_stored_in_32_bit_stays_so(tmp_path):
+    """A bfloat16 checkpoint in which one projection and the output matrix are stored in float32: loaded for the
+    bfloat16 engine they stay float32 (and the matrix fused from a float32 and two bfloat16 parts is float32)."""
+    from yalis_b200.weights.loader import load_weights
+    d = write_random_model(preset("tiny-A"), str(tmp_path / "m"), seed=3)
+    with Checkpoint(d) as ck:
+        tensors = {n: ck.get(n).clone() for n in ck.names()}
+    wide = [n for n in tensors if n.endswith("layers.0.self_attn.q_proj.weight") or n.endswith("layers.1.mlp.down_proj.weight")]
+    assert len(wide) == 2
+    for n in wide:
+        tensors[n] = tensors[n].float()
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    model = _model("tiny-A")
+    load_weights(model, d, "cpu", torch.bfloat16)
+    assert model.blocks[0].mixer.w_qkv.dtype == torch.float32 and model.blocks[1].mixer.w_qkv.dtype == torch.bfloat16
+    assert model.blocks[1].feed_forward.w_down.dtype == torch.float32 and model.blocks[0].feed_forward.w_down.dtype == torch.bfloat16
+    assert model.embedding.dtype == torch.bfloat16

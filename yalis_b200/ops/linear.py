@@ -53,9 +53,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     """The projection used by the parts: picks the kernel by dtype and size (see module docstring)."""
     need_cuda("linear", x, w)
     out_dtype = out_dtype or x.dtype
-    if x.dtype == torch.float32:
+    if x.dtype == torch.float32 or w.dtype == torch.float32:
+        # the true 32-bit path, and a weight that its checkpoint stored in float32 (it stays so) under bfloat16 rows
         return gemm_simt(x, w, out_dtype)
-    need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear", "operands must both be bfloat16 or float32")
+    need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear", "operands must be bfloat16 or float32")
     if wstream_preferred(x, w):
         return gemm_wstream(x, w, out_dtype=out_dtype)
     if out_dtype == torch.bfloat16:

@@ -9,7 +9,10 @@ yalis/model_loading.py:201-249.)
 
 dtype policy: floating tensors are held in the engine's dtype (bfloat16, or
 float32 on the 32-bit path); a parameter its part marks ``keep_float32`` (norm
-scales) is held in float32; integer tables are held as int32.
+scales) is held in float32; integer tables are held as int32; and a tensor that
+the checkpoint stores in 32 or 64-bit floating point stays float32 whatever the
+engine's dtype (whoever stored a matrix that wide in a 16-bit checkpoint meant
+it; the products that read it then run on the exact float32 kernels).
 
 Random weights: every matrix and the embedding ~ N(0, 0.02), norm scales 1
 (yalis/external/model.py:113-120), from a generator seeded per tensor by
@@ -54,10 +57,13 @@ class WeightError(RuntimeError):
         super().__init__("\n".join(lines))
 
 
-def target_dtype(ps: ParamSpec, engine_dtype: torch.dtype) -> torch.dtype:
+def target_dtype(ps: ParamSpec, engine_dtype: torch.dtype, stored: Optional[torch.dtype] = None) -> torch.dtype:
+    """The dtype a tensor is held in (see the module docstring); ``stored`` is what the checkpoint holds it in."""
     if ps.integer:
         return torch.int32
-    return torch.float32 if ps.keep_float32 else engine_dtype
+    if ps.keep_float32 or stored in (torch.float32, torch.float64):
+        return torch.float32
+    return engine_dtype
 
 
 def validate(expected: Dict[str, ParamSpec], ckpt: Checkpoint) -> None:
@@ -87,7 +93,7 @@ def load_weights(model, model_dir: str, device, dtype: torch.dtype) -> None:
 
         def fetch(name: str) -> torch.Tensor:
             t = ckpt.get(name)
-            return t.to(device=device, dtype=target_dtype(expected[name], dtype), copy=True)
+            return t.to(device=device, dtype=target_dtype(expected[name], dtype, t.dtype), copy=True)
 
         model.load(fetch, dtype)
 
