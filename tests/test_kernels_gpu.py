@@ -787,6 +787,48 @@ def test_mixed_step_with_its_decoding_requests_in_the_decode_kernel(nh, g, hs, p
     torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("kv_splits, tiles_per_split, skip_single", [(1, 1, False), (1, 1, True), (2, 1, True), (3, 2, False)])
+def test_prefill_attention_tcgen05_many_requests(kv_splits, tiles_per_split, skip_single):
+    """75 requests in one launch (more than the 32 whose tiles a warp adds up at a time), some with one token, one
+    with none: more work items than resident blocks, each block finding the request of its tile from the token
+    ranges; against the exact kernel.  With ``skip_single`` the rows of one-token requests are left as they were."""
+    from yalis_b200.ops.attention import paged_attention_generic, prefill_attention_tcgen05
+    nh, g, hs, page, dtype = 8, 4, 64, 16, torch.bfloat16          # 75 tiles and more x 4 KV heads: over 296 items
+    rng = torch.Generator().manual_seed(77)
+    n_req = 75
+    q_lens = [[1, 2, 17, 40, 33, 1][int(torch.randint(0, 6, (1,), generator=rng))] for _ in range(n_req)]
+    q_lens[40] = 0                                           # a request that brings nothing (as padding does)
+    lens = [ql + int(torch.randint(0, 180, (1,), generator=rng)) for ql in q_lens]
+    lens[40] = 5
+    ks, vs, k_pool, v_pool, table = paged_setup(n_req, lens, g, hs, page, dtype, seed=5)
+    pos, req, q_start = [], [], [0]
+    for r, (l, ql) in enumerate(zip(lens, q_lens)):
+        pos += list(range(l - ql, l))
+        req += [r] * ql
+        q_start.append(q_start[-1] + ql)
+    n = q_start[-1]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    positions, req_of_token, q_start_d = i32(pos), i32(req), i32(q_start)
+    qd = torch.randn(n, nh * hs, generator=rng).to(dtype).to(DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((n, nh * hs), 7.0, dtype=dtype, device=DEV)
+    prefill_attention_tcgen05(qd, k_pool, v_pool, positions, q_start_d, table, max(q_lens), nh, g, hs, error_flag=flag, out=out,
+                              kv_splits=kv_splits, tiles_per_split=tiles_per_split, skip_single=skip_single)
+    torch.cuda.synchronize()
+    assert int(flag) == 0
+    ref = paged_attention_generic(qd, k_pool, v_pool, positions, req_of_token, table, nh, g, hs)
+    single = torch.zeros(n, dtype=torch.bool)
+    for r, ql in enumerate(q_lens):
+        if ql == 1:
+            single[q_start[r]] = True
+    if skip_single:
+        assert torch.all(out[single.to(DEV)] == 7.0)         # untouched
+        keep = (~single).to(DEV)
+        torch.testing.assert_close(out[keep].float(), ref[keep].float(), rtol=2e-2, atol=2e-2)
+    else:
+        torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
 def test_prefill_attention_tcgen05_far_key_and_causal_edge():
     """One key takes nearly all the weight: each query row must return that key's value if it
     can see the key, and must not if the key lies after it (causal edge inside a tile)."""
