@@ -283,8 +283,9 @@ def test_steps_that_take_their_tokens_from_the_device(dtype, graphs):
 @pytest.mark.parametrize("which", ["B", "C"])
 def test_steps_with_portions_are_recorded_when_their_shape_repeats(which, dtype):
     """Three requests fed in lockstep, 16 tokens each per step and then single tokens beside one portion: the second
-    step of a shape is recorded (a CUDA graph at the exact counts of tokens, requests and wanted rows), the later
-    ones replay it, with other tokens, positions and pages each time.  Every logit against the plain model."""
+    step of a shape is recorded (a CUDA graph with room for its tokens, requests and wanted rows rounded up, the
+    rest padding), the later ones replay it, with other tokens, positions and pages each time.  Every logit
+    against the plain model."""
     std = STD[dtype]
     d = tiny_model_dir(which, std)
     cfg = plain.read_config(d)
@@ -306,7 +307,8 @@ def test_steps_with_portions_are_recorded_when_their_shape_repeats(which, dtype)
     out, rep = replay_in_process(d, dtype, page_size_of(which), steps, traces.peak_tokens(steps), graphs=True)
     assert rep.steps_replayed == (5 - 1) + (4 - 1)                 # all but the first of each shape
     exact = [key for key in rep.engine._recordings if not key[4][3]]
-    assert sorted(key[4][:3] for key in exact) == [(12, 3, 3), (48, 3, 6)]
+    # room for (tokens, requests, wanted rows, longest portion): 12 tokens of 3 requests in 16 and 4, and so on
+    assert sorted(key[4][:3] + key[4][4:] for key in exact) == [(16, 4, 4, 16), (64, 4, 8, 16)]
     row = {rid: [] for rid in ids}
     for s in steps:
         arr = out[s["step"]].reshape(-1, cfg["vocab_size"])
@@ -327,14 +329,14 @@ def test_shapes_that_turn_over_faster_than_they_repeat_are_launched(monkeypatch)
     path.  A recording that has lain idle long enough makes room in the end."""
     from yalis_b200.engine import recorded
     from yalis_b200.engine.engine import Engine, StepEntry
-    d = tiny_model_dir("C", STD["bfloat16"])
+    d = tiny_model_dir("C", STD["float32"])          # float32: a padded step gives the same bits
     made = []
     init = recorded.RecordedStep.__init__
     monkeypatch.setattr(recorded.RecordedStep, "__init__", lambda self, *a, **k: (made.append(a[1]), init(self, *a, **k))[1])
-    lengths = [16, 20, 24, 28] * 4 + [16, 20] * 2 + [24] * 8          # in turn; then the recorded two; then one of the others
+    lengths = [16, 40, 70, 130] * 4 + [16, 40] * 2 + [70] * 8         # in turn; then the recorded two; then one of the others
     outputs = {}
     for graphs in (False, True):
-        eng = Engine(d, dtype="bfloat16", page_size=16, num_pages=16, max_slots=2)
+        eng = Engine(d, dtype="float32", page_size=16, num_pages=32, max_slots=2)
         eng.MAX_EXACT_RECORDINGS, eng.IDLE_STEPS_BEFORE_EVICTION = 2, 6
         outputs[graphs] = []
         for k, n in enumerate(lengths):
@@ -343,7 +345,7 @@ def test_shapes_that_turn_over_faster_than_they_repeat_are_launched(monkeypatch)
             outputs[graphs].append((out.captured, out.logits.float().cpu()))
             eng.finish_request(k)
         eng.manager.check()
-    assert made == [16, 20, 24]                                       # 24 only once the recording of 16 had lain idle
+    assert made == [16, 64, 128]                                      # room for 70 only once the recording for 16 had lain idle
     captured = [c for c, _ in outputs[True]]
     assert captured == [False] * 4 + [True, True, False, False] * 3 + [True] * 4 + [False] * 4 + [True] * 4
     for (_, a), (_, b) in zip(outputs[False], outputs[True]):

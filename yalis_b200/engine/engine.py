@@ -447,10 +447,11 @@ class Engine:
         """The recording that replays a step with these facts, or None if the step is to be launched.
 
         Steps of single tokens share a recording per bucket of requests (padded).  Any other step (prompt portions,
-        portions beside decoding requests) is recorded at its exact counts of tokens, requests and wanted rows,
-        and only when the same kind of step has been seen before: serving repeats shapes (a token budget filled
-        by the same number of decoding requests and one portion), one-off shapes are not worth a recording (it
-        costs about three launched steps).  When the exact recordings are full, the least recently used one makes
+        portions beside decoding requests) is recorded with room for its tokens, requests, wanted rows and longest
+        portion rounded up (tokens to a multiple of 64, the others to powers of two; the rest is padding: rows of
+        no request, requests without tokens), and only when the same kind of step has been seen before: serving
+        fills its token budget step after step, one-off shapes are not worth a recording (it costs about three
+        launched steps).  When these recordings are full, the least recently used one makes
         room only if it has lain idle for ``IDLE_STEPS_BEFORE_EVICTION`` steps; otherwise the new shape is
         launched.  (Least-recently-used alone records every step anew when more shapes than there is room for
         come in turn: 130 shapes with room for 48 took 7.1 s instead of 4.2.)"""
@@ -463,7 +464,10 @@ class Engine:
             size = bucket_for(r)
             shape = (size, size, size, True)
         else:
-            shape = (n, r, n_want, False, host.max_q_len)
+            # room for the step: tokens to the next multiple of 64 (a power of two up to 64), requests, wanted
+            # rows and the longest portion to the next power of two; what the step leaves unused is padding
+            shape = (bucket_for(max(n, 16)) if n <= 64 else -(-n // 64) * 64, bucket_for(r),
+                     bucket_for(n_want) if n_want else 0, False, bucket_for(max(host.max_q_len, 16)))
         key = (shape[0], mode, keep_logits, capture_key, shape)
         rec = self._recordings.get(key)
         if rec is not None:
@@ -483,6 +487,7 @@ class Engine:
                 if self._steps_seen - self._recordings[exact[0]].last_used < self.IDLE_STEPS_BEFORE_EVICTION:
                     return None
                 del self._recordings[exact[0]]
-        rec = self._recordings[key] = RecordedStep(self, shape[0], shape[1], shape[2], shape[3], mode, keep_logits, key)
+        rec = self._recordings[key] = RecordedStep(self, shape[0], shape[1], shape[2], shape[3], mode, keep_logits, key,
+                                                   longest_portion=None if shape[3] else shape[4])
         rec.last_used = self._steps_seen
         return rec

@@ -5,17 +5,19 @@ kernels; launched one by one from Python they cost more than they run.  The
 engine records such a step once per (batch bucket, kind of token choice, keys of
 the parts) and every later step of that kind is: fill one pinned buffer with
 the step's arrays, copy it, launch the graph.  Steps that hold prompt portions
-are recorded too, at their exact counts of tokens, requests and wanted rows,
-once the same kind of step has come a second time (a small model's step of a
-few hundred tokens is otherwise bound by the host's launches).  The graph holds the whole step:
+are recorded too, with room for their tokens, requests, wanted rows and longest
+portion rounded up, once the same kind of step has come a second time (a small
+model's step of a few hundred tokens is otherwise bound by the host's
+launches).  The graph holds the whole step:
 embedding, all blocks, final norm, output matrix, token choice and the copy of
 the error word beside the chosen tokens.
 
 This file only runs what the engine has prepared: validation, page
 reservation and commit happen in ``Engine.run_step`` for launched and replayed
 steps alike, and the step's arrays are written by the same ``Engine._fill``.
-What is particular here is the fixed size: a bucket of 1, 2, 4, ... requests,
-padded with rows that every kernel skips, and block tables at their full row
+What is particular here is the fixed size: a bucket of 1, 2, 4, ... requests
+(and, for steps with portions, of tokens in multiples of 64), padded with rows
+that belong to no request and that every kernel skips, and block tables at their full row
 width, of which a step copies only the columns in use.
 
 Shapes inside a graph are fixed, so nothing in a recorded step may depend on a
@@ -34,6 +36,7 @@ The reference gets the same effect from torch.compile's "reduce-overhead" mode
 from __future__ import annotations
 
 import ctypes
+import dataclasses
 import gc
 from typing import Optional
 
@@ -67,8 +70,9 @@ class RecordedStep:
     """Static buffers and the graph for one kind of step (see the module docstring)."""
 
     def __init__(self, engine, n_tokens: int, n_requests: int, n_rows: int, single_tokens: bool, mode: str,
-                 keep_logits: bool, key: tuple):
+                 keep_logits: bool, key: tuple, longest_portion: Optional[int] = None):
         self.engine, self.mode, self.keep_logits, self.key = engine, mode, keep_logits, key
+        self.longest_portion = longest_portion          # the most tokens a request may bring to a replay (None: one)
         self.size, self.n_tokens, self.n_rows, self.single_tokens = n_requests, n_tokens, n_rows, single_tokens
         self.widths = [g.max_pages_per_request for g in engine.groups]
         self.layout = StepLayout(n_tokens, n_requests, n_rows, self.widths, sampling=(mode == "sampled"))
@@ -106,7 +110,10 @@ class RecordedStep:
 
     def _record(self, host: HostStep) -> None:
         eng = self.engine
-        # The facts of this step stand for every step that will replay the recording (they share the parts' keys).
+        # The facts of this step stand for every step that will replay the recording (they share the parts' keys),
+        # but for the longest portion, which is the recording's bound: launches are sized by it.
+        if self.longest_portion is not None:
+            host = dataclasses.replace(host, max_q_len=self.longest_portion, memo=dict(host.memo))
         self.ctx, self.d = eng._context(self.layout, self.dev, host, decode_only=self.single_tokens)
         saved_state = eng.storage.snapshot_state()
         saved_chosen = eng.chosen.clone()
