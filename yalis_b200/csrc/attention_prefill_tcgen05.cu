@@ -215,6 +215,27 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Two float32 operations in one instruction (sm_100): d = a * b + c and d = a + b on pairs held in 64-bit registers
+// (each half rounded as the single operation is).  The softmax warps are bound by their own instruction streams:
+// pairs took 2 % off the kernel, a share of the exponentials as a polynomial on the FMA pipe added 16 to 24 %.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -628,21 +649,29 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const float m_use = grow ? m_new : m_run;
         const float mb = (m_use == -INFINITY) ? 0.f : m_use;
         const float corr = grow ? ((m_run == -INFINITY) ? 0.f : ex2(m_run - mb)) : 1.f;
-        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+        uint64_t ls2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+        const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), nmb2 = pack2(-mb, -mb);
         const uint32_t p_addr = lane_base + COL_S + b * BN;          // over the first half of S(j)
 #pragma unroll
         for (int c0 = 0; c0 < BN; c0 += 32) {
           uint32_t pk[16];
 #pragma unroll
           for (int c = 0; c < 32; c += 4) {
-            const float p0 = ex2(fmaf(sv[c0 + c], p.scale_log2, -mb)), p1 = ex2(fmaf(sv[c0 + c + 1], p.scale_log2, -mb));
-            const float p2 = ex2(fmaf(sv[c0 + c + 2], p.scale_log2, -mb)), p3 = ex2(fmaf(sv[c0 + c + 3], p.scale_log2, -mb));
-            ls[0] += p0; ls[1] += p1; ls[2] += p2; ls[3] += p3;
+            // scale and shift, and the row sums, two values to an instruction
+            float x0, x1, x2, x3;
+            unpack2(fma2(pack2(sv[c0 + c], sv[c0 + c + 1]), scale2, nmb2), x0, x1);
+            unpack2(fma2(pack2(sv[c0 + c + 2], sv[c0 + c + 3]), scale2, nmb2), x2, x3);
+            const float p0 = ex2(x0), p1 = ex2(x1), p2 = ex2(x2), p3 = ex2(x3);
+            ls2[0] = add2(ls2[0], pack2(p0, p1));
+            ls2[1] = add2(ls2[1], pack2(p2, p3));
             pk[c >> 1] = pack_bf16(p0, p1);
             pk[(c >> 1) + 1] = pack_bf16(p2, p3);
           }
           tmem_st16(p_addr + (c0 >> 1), pk);
         }
+        float ls[4];
+        unpack2(ls2[0], ls[0], ls[1]);
+        unpack2(ls2[1], ls[2], ls[3]);
         l_run = l_run * corr + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
         if (lane == 0) STAMP(j, 4 + (warp ? 6 + warp * 6 : 0));
         m_run = m_use;
