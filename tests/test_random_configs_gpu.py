@@ -65,7 +65,7 @@ def test_replay_of_random_configurations(seed, sms, rare, monkeypatch):
                 want = {rid: plain.forward_logits(t, w, pcfg).numpy() for rid, t in reqs.items()}
                 for build in (traces.whole, traces.tail_decoded, traces.portions, traces.mixed):
                     steps = traces.number(build(reqs))
-                    rep = Replayer(d, dtype, traces.peak_tokens(steps), page_size=page)
+                    rep = Replayer(d, dtype, traces.peak_tokens(steps), page_size=page, graphs=trial % 2 == 1)   # every other trial through recorded steps
                     out = {}
                     for s in steps:
                         r = rep.run_step(s)
