@@ -118,6 +118,29 @@ def test_a_refused_step_leaves_every_page_where_it_was():
     m.check()
 
 
+def test_commit_many_is_commit_for_every_request_of_a_step():
+    """One call for all requests of a step: the same lengths, the same pages given back behind a window as
+    request by request, and a wrong entry changes nothing for the others."""
+    m, ref = two_groups(pages=24, page=4, window=10), two_groups(pages=24, page=4, window=10)
+    slots = [m.acquire(), m.acquire(), m.acquire()]
+    assert [ref.acquire() for _ in range(3)] == slots
+    for lens in ([5, 9, 1], [17, 10, 2], [30, 11, 16]):
+        assert m.reserve_many(slots, lens) and ref.reserve_many(slots, lens)
+        given_back = m.commit_many(slots, lens)
+        assert given_back == sum(ref.commit(s, n) for s, n in zip(slots, lens))
+        assert [m.length(s) for s in slots] == lens
+        for g in ("kv_all", "kv_window_10"):
+            assert np.array_equal(m.table(g), ref.table(g)) and m.free_pages(g) == ref.free_pages(g)
+        m.check()
+    assert m.commit_many([], []) == 0
+    with pytest.raises(CacheError):
+        m.commit_many([slots[0], slots[1]], [31, 40])              # the second has no pages for 40 tokens
+    assert m.length(slots[0]) == 30                                 # and the first was not touched
+    with pytest.raises(CacheError):
+        m.commit_many([slots[0]], [29])                             # shorter than what it holds
+    m.check()
+
+
 def test_groups_with_a_window_get_no_more_pages_than_they_can_use():
     from yalis_b200.cache.storage import group_page_bytes, plan_groups, window_group_pages
     from yalis_b200.parts.base import PagedKV, SlotState

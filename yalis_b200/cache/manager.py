@@ -66,6 +66,7 @@ def _bind(lib: ctypes.CDLL) -> None:
         "ycm_reserve": (c_int, [vp, c_int, c_int]),
         "ycm_reserve_many": (c_int, [vp, c_int, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]),
         "ycm_commit": (c_int, [vp, c_int, c_int]),
+        "ycm_commit_many": (c_int, [vp, c_int, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]),
         "ycm_release_slot": (c_int, [vp, c_int]),
         "ycm_table": (ctypes.POINTER(ctypes.c_int32), [vp, c_int]),
         "ycm_ctx_len": (ctypes.POINTER(ctypes.c_int32), [vp]),
@@ -172,6 +173,17 @@ class CacheManager:
 
     def commit(self, slot: int, new_len: int) -> int:
         r = self._lib.ycm_commit(self._h, slot, new_len)
+        if r < 0:
+            raise CacheError(self._err())
+        return r
+
+    def commit_many(self, slots: Sequence[int], new_lens: Sequence[int]) -> int:
+        """``commit`` for all requests of a step in one call; all are checked before anything changes."""
+        n = len(slots)
+        if n != len(new_lens):
+            raise CacheError("commit_many: one length per slot")
+        arr = (ctypes.c_int32 * n)
+        r = self._lib.ycm_commit_many(self._h, n, arr(*slots), arr(*new_lens))
         if r < 0:
             raise CacheError(self._err())
         return r

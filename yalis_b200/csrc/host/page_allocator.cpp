@@ -219,6 +219,23 @@ YCM_API int ycm_commit(void* h, int slot, int new_len) {
   return released;
 }
 
+// ycm_commit for all requests of a step: one call instead of one per request.  All slots and lengths are checked
+// before anything changes.  Returns the number of pages given back, < 0 on misuse.
+YCM_API int ycm_commit_many(void* h, int n, const int32_t* slots, const int32_t* new_lens) {
+  Manager* m = static_cast<Manager*>(h);
+  if (n < 0 || (n > 0 && (slots == nullptr || new_lens == nullptr))) return fail(m, -7, "commit_many: bad arguments");
+  for (int i = 0; i < n; ++i) {
+    if (int e = check_slot(m, slots[i], "commit_many")) return e;
+    if (new_lens[i] < m->ctx_len[slots[i]]) return fail(m, -5, "commit_many: length may not shrink");
+    for (const Group& g : m->groups)
+      if (ceil_div(new_lens[i], g.page_size) > g.end_mapped[slots[i]])
+        return fail(m, -6, "commit_many: tokens beyond the reserved pages");
+  }
+  int released = 0;
+  for (int i = 0; i < n; ++i) released += ycm_commit(h, slots[i], new_lens[i]);
+  return released;
+}
+
 // Give back every page of the slot and the slot itself.  Returns pages given back.
 YCM_API int ycm_release_slot(void* h, int slot) {
   Manager* m = static_cast<Manager*>(h);

@@ -307,7 +307,23 @@ class Engine:
         qs, kv, sl, rows, row_slot = views["qs"], views["kv"], views["slots"], views["rows"], views["row_slot"]
         t = w = 0
         qs[0] = 0
-        for i, e in enumerate(entries):
+        single = max(q_lens, default=0) == 1 and min(q_lens) == 1 and all(len(e.want) <= 1 and (not e.want or e.want[0] == 0) for e in entries)
+        if single:
+            # every request brings one token (a decode step): the same arrays without a loop over numpy scalars
+            r = len(entries)
+            tok[:r] = [0 if e.tokens is None else e.tokens[0] for e in entries]
+            src[:r] = [s if e.tokens is None else -1 for s, e in zip(slots, entries)]
+            pos[:r] = before
+            req[:r] = np.arange(r, dtype=np.int32)
+            qs[:r + 1] = np.arange(r + 1, dtype=np.int32)
+            kv[:r] = np.asarray(before, dtype=np.int32) + 1
+            sl[:r] = slots
+            wanted = [i for i, e in enumerate(entries) if len(e.want)]
+            w = len(wanted)
+            rows[:w] = wanted
+            row_slot[:w] = [slots[i] for i in wanted]
+            t = r
+        for i, e in enumerate(() if single else entries):
             q = q_lens[i]
             if e.tokens is None:
                 tok[t], src[t] = 0, slots[i]
@@ -336,9 +352,9 @@ class Engine:
                 temp[i], topk[i], topp[i] = p.temperature, p.top_k or 0, p.top_p
                 seed[i], draw[i] = as_int64(p.seed), int(d)
             temp[w:], topk[w:], topp[w:], seed[w:], draw[w:] = 0.0, 0, 0.0, 0, 0
+        rows_of = np.asarray(slots, dtype=np.int64)
         for view, u, tbl in zip(views["tables"], used, tables_of):
-            for i, s in enumerate(slots):
-                view[i, :u] = tbl[s, :u]
+            view[:len(slots), :u] = tbl[rows_of, :u]
 
     def _context(self, layout: StepLayout, dev: torch.Tensor, host: HostStep, decode_only: bool) -> Tuple[StepContext, dict]:
         d = layout.views(dev, as_numpy=False)
@@ -405,8 +421,7 @@ class Engine:
             out = recording.run(host, entries, q_lens, sampling, draws, n_want)
         else:
             out = self._run_launched(host, entries, q_lens, sampling, draws, n_want, mode, keep)
-        for s, nl in zip(slots, new_lens):
-            self.manager.commit(s, nl)
+        self.manager.commit_many(slots, new_lens)
         if mode != "none":
             for s, e in zip(slots, entries):
                 if len(e.want):

@@ -270,9 +270,10 @@ class Scheduler:
         done: List[Request] = []
         it = iter(sampled)
         for e in plan.entries:
+            e.request.computed = e.start + e.count
+        self.manager.commit_many([e.request.slot for e in plan.entries], [e.request.computed for e in plan.entries])
+        for e in plan.entries:
             r = e.request
-            r.computed = e.start + e.count
-            self.manager.commit(r.slot, r.computed)
             if not e.samples:
                 continue
             tok = int(next(it))
