@@ -194,7 +194,15 @@ class Scheduler:
         budget = self.max_tokens_per_step - plan.n_tokens
         planned = {id(e.request) for e in plan.entries}
         # 1. decodes, oldest first, so that the youngest is the first to give way
-        for r in sorted(self.running, key=lambda r: r.admitted_at):
+        in_order = sorted(self.running, key=lambda r: r.admitted_at)
+        decoding = [r for r in in_order if id(r) not in planned and r.total - r.computed == 1][:max(budget, 0)]
+        if decoding and self.manager.reserve_many([r.slot for r in decoding], [r.computed + 1 for r in decoding]):
+            # the usual case: every one of them gets its page (or needs none), nobody has to give way
+            plan.entries.extend(PlannedEntry(r, r.computed, 1, True) for r in decoding)
+            planned.update(id(r) for r in decoding)
+            budget -= len(decoding)
+            in_order = ()
+        for r in in_order:
             if id(r) in planned or r not in self.running or r.total - r.computed != 1:
                 continue
             if budget <= 0:
