@@ -829,6 +829,47 @@ def test_prefill_attention_tcgen05_many_requests(kv_splits, tiles_per_split, ski
         torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_prefill_attention_tcgen05_random_steps(seed):
+    """Random steps (head counts, page sizes, 1 to 90 requests of 1 to 700 tokens behind up to 3,000 cached ones,
+    keys divided or not, one-token requests skipped or not), several launches each on the same counters of work
+    items: every launch against the exact kernel, and no bounded wait may run out."""
+    import random
+    from yalis_b200.ops.attention import paged_attention_generic, prefill_attention_tcgen05
+    rng = random.Random(seed)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for trial in range(14):
+        nh, g, hs = rng.choice([(32, 8, 128), (8, 2, 64), (24, 8, 128), (6, 2, 128), (4, 4, 64), (5, 1, 128)])
+        page = rng.choice([8, 16, 32, 64, 128])
+        q_lens = [rng.choice([1, 1, 2, 17, 33, 64, 200, 700]) for _ in range(rng.choice([1, 2, 5, 40, 90]))]
+        if sum(q_lens) > 6000:
+            q_lens = q_lens[:8]
+        lens = [q + rng.choice([0, 0, 3, 100, 900, 3000]) for q in q_lens]
+        ks, vs, k_pool, v_pool, table = paged_setup(len(lens), lens, g, hs, page, torch.bfloat16, seed=seed * 100 + trial)
+        pos, req, q_start = [], [], [0]
+        for r, (l, ql) in enumerate(zip(lens, q_lens)):
+            pos += list(range(l - ql, l))
+            req += [r] * ql
+            q_start.append(q_start[-1] + ql)
+        n = q_start[-1]
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        positions, req_of_token, q_start_d = i32(pos), i32(req), i32(q_start)
+        gen = torch.Generator().manual_seed(trial)
+        qd = torch.randn(n, nh * hs, generator=gen).to(torch.bfloat16).to(DEV)
+        splits, limit = rng.choice([(1, 1), (1, 1), (2, 1), (3, 2), (4, 16), (8, 4)])
+        skip = rng.random() < 0.3
+        ref = paged_attention_generic(qd, k_pool, v_pool, positions, req_of_token, table, nh, g, hs)
+        keep = torch.tensor([not (skip and q_lens[r] == 1) for r in req], dtype=torch.bool, device=DEV)
+        for launch in range(3):
+            out = torch.full((n, nh * hs), 3.0, dtype=torch.bfloat16, device=DEV)
+            prefill_attention_tcgen05(qd, k_pool, v_pool, positions, q_start_d, table, max(q_lens), nh, g, hs, error_flag=flag,
+                                      out=out, kv_splits=splits, tiles_per_split=limit, skip_single=skip)
+            assert int(flag) == 0, (seed, trial, launch)
+            if bool(keep.any()):
+                torch.testing.assert_close(out[keep].float(), ref[keep].float(), rtol=2e-2, atol=2e-2)
+            assert torch.all(out[~keep] == 3.0)
+
+
 def test_prefill_attention_tcgen05_far_key_and_causal_edge():
     """One key takes nearly all the weight: each query row must return that key's value if it
     can see the key, and must not if the key lies after it (causal edge inside a tile)."""
