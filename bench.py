@@ -16,14 +16,16 @@ The line also carries a 2,048-token prefill (``prefill``), the decode step's HBM
 (``roofline``), decode at batch 1 and 64 (``points``), the SM clocks sampled during the
 timed region (``clocks``) and the number of this library's kernels launched in it
 (``gpu_launches``).  Between timed iterations nothing is flushed: a decode step streams
-all weights (15 GB), far more than the 126 MB L2.
+all weights (15 GB), far more than the 126 MB L2.  The device-timed steps start one
+second after the prompt phase, which draws the power limit and leaves the SM clock low for
+a tenth of a second (``config.settle``); ``e2e`` has no such pause.
 
 ``--workload mixed-1b``: Llama-3.2-1B shape, 64 requests decoding beside a 4,096-token
 prompt fed in portions of 512 (steps of 576 tokens); ``value`` is tokens per second over
 those mixed steps.  ``--workload serve-3b``: Llama-3.2-3B shape, 32 requests with prompts
 of 128 to 16,384 tokens, 256 new tokens each at temperature 0.8; ``value`` is generated
 tokens per second of the whole call.  For these, ``--warmup`` and ``--steps`` count whole
-calls (defaults 1 and 3; the median call is reported).
+calls (defaults 2 and 3; the median call is reported).
 """
 
 from __future__ import annotations
@@ -346,6 +348,7 @@ def main() -> int:
             "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
             "seq_len": PROMPT_LEN, "context": cfg["max_position_embeddings"], "page_size": page_size, "parallelism": "none",
             "l2": "inputs larger than L2 (15 GB of weights per step)", "peaks": peak_source,
+            "settle": "1 s idle between the prompt phase and the warm-up steps (the clock recovers from the power cap)",
         },
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4)},
