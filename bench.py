@@ -18,7 +18,8 @@ timed region (``clocks``) and the number of this library's kernels launched in i
 (``gpu_launches``).  Between timed iterations nothing is flushed: a decode step streams
 all weights (15 GB), far more than the 126 MB L2.  The device-timed steps start one
 second after the prompt phase, which draws the power limit and leaves the SM clock low for
-a tenth of a second (``config.settle``); ``e2e`` has no such pause.
+a tenth of a second (``config.settle``); ``right_after_prompts`` is the same measurement
+without the pause, and ``e2e`` has none either.
 
 ``--workload mixed-1b``: Llama-3.2-1B shape, 64 requests decoding beside a 4,096-token
 prompt fed in portions of 512 (steps of 576 tokens); ``value`` is tokens per second over
@@ -333,6 +334,16 @@ def main() -> int:
             ms = bench.run_timed(args.steps)
         results[b] = {"ms_per_step": ms / args.steps, "tok_s": b * args.steps / (ms / 1e3), "kv_tokens": bench.mean_context(args.steps)}
         bench.finish()
+        if b == args.batch and not args.skip_points:
+            # the same steps right after the prompt phase, without the pause: what the low clock after it costs
+            bench = DecodeBench(engine, b, PROMPT_LEN, seed=b + 1000, settle_seconds=0.0)
+            bench.prepare()
+            bench.run(args.warmup)
+            with ClockSampler() as cs:
+                ms = bench.run_timed(args.steps)
+            unsettled = {"value": round(b * args.steps / (ms / 1e3), 2), "ms_per_step": round(ms / args.steps, 4),
+                         "sm_mhz": cs.summary().get("sm_mhz")}
+            bench.finish()
 
     main_r = results[args.batch]
     step_bytes = numbers["weight_bytes_per_step"] + args.batch * main_r["kv_tokens"] * numbers["kv_bytes_per_token"]
@@ -355,6 +366,7 @@ def main() -> int:
         "clocks": clocks, "gpu_launches": int(launches),
     }
     if not args.skip_points:
+        line["right_after_prompts"] = unsettled
         line["points"] = {f"decode_b{b}": round(r["tok_s"], 2) for b, r in results.items() if b != args.batch}
         pf = prefill_bench(engine, PREFILL_TOKENS, warmup=3, iters=7)
         flops = numbers["flops_prefill"](PREFILL_TOKENS)

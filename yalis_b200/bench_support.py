@@ -51,8 +51,10 @@ class DecodeBench:
     """``batch`` requests with ``prompt_len`` cached tokens each, decoded step by step through the engine's
     step function (recorded steps, greedy choice) with the chosen tokens fed back on the device."""
 
-    def __init__(self, engine: Engine, batch: int, prompt_len: int, seed: int = 0, prefill_tokens_per_step: int = 2048):
+    def __init__(self, engine: Engine, batch: int, prompt_len: int, seed: int = 0, prefill_tokens_per_step: int = 2048,
+                 settle_seconds: float = SETTLE_SECONDS):
         self.engine, self.batch, self.prompt_len, self.seed = engine, batch, prompt_len, seed
+        self.settle_seconds = settle_seconds
         self.per_step = prefill_tokens_per_step
         self.ids = [("bench", seed, i) for i in range(batch)]
         self.slots: List[int] = []
@@ -92,7 +94,7 @@ class DecodeBench:
         # that; with this pause 1,965 MHz from the first step).  The steps timed here are to say what the decode
         # kernels do, so they start from a settled clock; the end-to-end figure has no such pause.
         torch.cuda.synchronize()
-        time.sleep(SETTLE_SECONDS)
+        time.sleep(self.settle_seconds)
 
     def run(self, steps: int) -> None:
         eng = self.engine
